@@ -1,0 +1,42 @@
+"""Helpers to load the golden fixtures produced by tests/golden/make_golden.py."""
+
+import glob
+import os
+
+import numpy as np
+
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def golden_names(prefix=""):
+    return sorted(
+        os.path.splitext(os.path.basename(p))[0]
+        for p in glob.glob(os.path.join(GOLDEN_DIR, f"{prefix}*.npz"))
+    )
+
+
+def load_golden(name):
+    z = np.load(os.path.join(GOLDEN_DIR, f"{name}.npz"), allow_pickle=False)
+    g = {k: z[k] for k in z.files}
+    g["cell"] = str(g["cell"])
+    g["K"] = int(g["K"])
+    g["P"] = int(g["P"])
+    g["iters"] = int(g["iters"])
+    g["omega"] = float(g["omega"])
+    g["eps"] = float(g.get("eps", 1e-6))
+    g["n_heads"] = int(g.get("n_heads", 1))
+    g.setdefault("h0", None)
+    return g
+
+
+def linear_grads(g_wx, x, W):
+    """grad_x, grad_W, grad_b of y = x W^T + b given grad_y (reference solvers/vjp.py:109-120)."""
+    gy = g_wx.reshape(-1, g_wx.shape[-1]).astype(np.float64)
+    xx = x.reshape(-1, x.shape[-1]).astype(np.float64)
+    return (gy @ W.astype(np.float64)).reshape(x.shape), gy.T @ xx, gy.sum(0)
+
+
+def clip_mask(raw, cap):
+    if cap < 0:
+        return np.ones_like(raw)
+    return (np.abs(raw) <= cap).astype(raw.dtype)
