@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Benchmark of the Newton+scan training hot path (forward + packed-VJP backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): ParaSLSTM mix='diag', bf16 I/O with fp32 scan state, B=8, T=16384,
+d=1024, picard_iters=5, max_iters=2, one forward + one backward per step, synthetic
+inputs x ~ 0.5*N(0,1), Xavier-uniform W_x, forget-gate bias +3, seed 1.  With N > 1 the
+sequence is sharded along time over N ranks (one process per GPU, NCCL) with T = 16384*N,
+so per-GPU work is fixed (weak scaling) and N = 8 is the T = 131072 case.
+
+`value` is tokens/s at the op boundary (gate pre-activations resident in HBM -> states,
+cotangent -> gradients of the pre-activations and of R), timed with CUDA events.
+`e2e` is the same metric through `newton_apply` + autograd with host-resident inputs,
+including the three W_x GEMMs and the host<->device copies.
+The CPU arm (`--impl reference`, and `cpu_baseline` at N = 1) times the C restatement of
+the reference's eager algorithm (oracle/) on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "pararnn-torch_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+B, T_PER_GPU, D, K_NEWTON, P_PICARD = 8, 16384, 1024, 2, 5
+SEED = 1
+# algorithmic bytes per (token, channel): bf16 I/O (a=2), fp32 work state (w=4), G=S=4
+BYTES_PICARD_MID = 4 * 2 + 4 + 4          # read wx + h, write h
+BYTES_NEWTON_MID = 4 * 2 + 16 + 16        # read wx + state, write state
+BYTES_BWD = 4 * 2 + 4 * 2 + 4 * 2 + 4 * 2  # read states, wx, cotangent; write g_wx
+BYTES_STEP = 224                          # all passes of one forward + backward
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                pass
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names)
+                   if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+
+
+def make_inputs(t_len: int, seed: int):
+    """Synthetic layer inputs and parameters (CPU tensors), fp32 master copies."""
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    x = 0.5 * torch.randn(B, t_len, D, generator=g)
+    bound = (6.0 / (D + 4 * D)) ** 0.5
+    W = (torch.rand(4 * D, D, generator=g) * 2 - 1) * bound
+    bias = torch.zeros(4 * D)
+    bias[D:2 * D] = 3.0
+    R = (torch.randn(4, D, generator=g) * (1.0 / (4 * D)) ** 0.5).clamp(-0.5, 0.5)
+    return x, W, bias, R
+
+
+# ----------------------------------------------------------------------------- CPU arm
+
+def cpu_step(sample, threads):
+    """One forward + backward of the oracle on one batch row; returns seconds."""
+    import numpy as np
+
+    from oracle import oracle
+
+    wx, r, G = sample
+    os.environ["OMP_NUM_THREADS"] = str(threads)
+    t0 = time.perf_counter()
+    res = oracle.newton(oracle.SLSTM_DIAG, wx, r, None, max_iters=K_NEWTON, picard=P_PICARD)
+    oracle.backward(oracle.SLSTM_DIAG, res.states, wx, r, G, None)
+    return time.perf_counter() - t0, res
+
+
+def cpu_sample():
+    import numpy as np
+    import torch
+
+    x, W, bias, R = make_inputs(T_PER_GPU, SEED)
+    xb = x[:1].bfloat16().float()
+    wx = (xb.reshape(-1, D) @ W.bfloat16().float().t() + bias).reshape(1, T_PER_GPU, 4 * D)
+    wx = wx.bfloat16().float().numpy()
+    r = R.bfloat16().float().numpy()
+    G = np.zeros((1, T_PER_GPU, 4, D), dtype=np.float32)
+    G[:, :, 3] = 1.0
+    return wx, r, G
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+
+    oracle.build()
+    threads = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(threads)
+    sample = cpu_sample()
+    for _ in range(args.warmup):
+        cpu_step(sample, threads)
+    times = [cpu_step(sample, threads)[0] for _ in range(args.steps)]
+    sec = sum(times) / len(times)
+    value = T_PER_GPU / sec  # one batch row per step
+    line = {
+        "impl": "reference", "metric": "newton_scan_fwd_bwd_tokens_per_s", "value": value,
+        "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": "1 of 8 batch rows per step (rows are independent), full T=16384, "
+                                   "d=1024, fp32 arithmetic on bf16-rounded inputs"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def workload_config(n):
+    return {"workload": f"ParaSLSTM mix=diag fwd+bwd, B={B}, T={T_PER_GPU * n}, d={D}, bf16 I/O + fp32 "
+                        f"scan state, picard_iters={P_PICARD}, max_iters={K_NEWTON}, seed {SEED}",
+            "global_batch": B, "seq_len": T_PER_GPU * n, "d_model": D,
+            "parallelism": "single GPU" if n == 1 else f"time-sharded x{n} (NCCL carry exchange)",
+            "l2": "inputs (>= 1 GB per pass) are larger than the 126 MB L2; no flush needed"}
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+def time_region(fn, steps, stream_sync, barrier=None):
+    import torch
+
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return e0.elapsed_time(e1) / 1e3
+
+
+def kernel_rooflines(wx, r32, states32, states_io, G_io, peak):
+    """Average launch duration of each scan kernel in isolation, CUDA events on the launch stream."""
+    import torch
+
+    from pararnn_b200 import _lib as L
+    from pararnn_b200 import ops
+
+    lib = L.lib()
+    dev = wx.device
+    ws = torch.empty(lib.prb_pass_workspace_bytes(L.CELL_SLSTM_DIAG, B, T_PER_GPU, D),
+                     dtype=torch.uint8, device=dev)
+    st = ops.DeviceStats(dev, K_NEWTON)
+    stream = ops._stream(dev)
+    hbuf = torch.empty(B, T_PER_GPU, D, dtype=torch.float32, device=dev)
+    hbuf2 = torch.empty_like(hbuf)
+    sout = torch.empty_like(states32)
+    g_wx = torch.empty_like(wx)
+    g_r = torch.empty(4, D, dtype=torch.float32, device=dev)
+    g_h0 = torch.empty(B, 4, D, dtype=torch.float32, device=dev)
+    P = ops._ptr
+    hbuf.copy_(states32[:, :, 3])
+
+    def picard():
+        rc = lib.prb_slstm_picard_pass(P(wx), P(r32), P(hbuf), None, None, P(hbuf2), None, None, None, 0,
+                                       B, T_PER_GPU, D, L.PRB_BF16, 1e-6, P(ws), ws.numel(), P(st.buf), stream)
+        assert rc == 0, rc
+
+    def newton():
+        rc = lib.prb_slstm_newton_pass(P(wx), P(r32), P(states32), None, None, P(sout), None, None, 0, B,
+                                       T_PER_GPU, D, L.PRB_BF16, 1.0, 1e-6, P(ws), ws.numel(), P(st.buf),
+                                       0, stream)
+        assert rc == 0, rc
+
+    def bwd():
+        rc = lib.prb_slstm_bwd_pass(P(states_io), P(wx), P(r32), None, None, P(G_io), P(g_wx), P(g_r),
+                                    P(g_h0), None, 0, B, T_PER_GPU, D, L.PRB_BF16, 1e-6, P(ws), ws.numel(),
+                                    P(st.buf), stream)
+        assert rc == 0, rc
+
+    n_units = B * T_PER_GPU * D
+    out = {}
+    for name, fn, nbytes, per_step in (("slstm_picard_kernel", picard, BYTES_PICARD_MID, P_PICARD + 1),
+                                       ("slstm_newton_kernel", newton, BYTES_NEWTON_MID, K_NEWTON),
+                                       ("slstm_bwd_kernel", bwd, BYTES_BWD, 1)):
+        for _ in range(3):
+            fn()
+        sec = time_region(fn, 10, None) / 10
+        gbs = n_units * nbytes / sec / 1e9
+        out[name] = {"ms_per_launch": sec * 1e3, "achieved": gbs, "frac": gbs / peak,
+                     "launches_per_step": per_step, "algorithmic_bytes_per_launch": n_units * nbytes}
+    return out
+
+
+def run_gpu_single(args):
+    import torch
+
+    from pararnn_b200 import ops
+    import pararnn_b200 as prb
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    peak, peak_kind = measured_peaks()
+    x, W, bias, R = make_inputs(T_PER_GPU, SEED)
+    cell = prb.ParaSLSTM(D, D).to(dev)
+    with torch.no_grad():
+        cell.W_x.weight.copy_(W)
+        cell.W_x.bias.copy_(bias)
+        cell.R.copy_(R)
+    cell = cell.bfloat16()
+    x_host = x.bfloat16().pin_memory()
+    x_dev = x_host.to(dev)
+    with torch.no_grad():
+        wx = cell.W_x(x_dev).contiguous()
+    r_io = cell.clipped_r().detach()
+    G_io = torch.zeros(B, T_PER_GPU, 4, D, dtype=torch.bfloat16, device=dev)
+    G_io[:, :, 3] = 1.0
+    stats = ops.DeviceStats(dev, K_NEWTON)
+    keep = {}
+
+    def step():
+        H = ops.newton_slstm_fused(wx, r_io, None, None, max_iters=K_NEWTON, picard_iters=P_PICARD,
+                                   stats=stats, want_residual=True)
+        keep["out"] = ops.slstm_reverse_vjp(H, wx, r_io, G_io)
+        keep["H"] = H
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(0)
+    sampler.start()
+    sec = time_region(step, args.steps, None)
+    clocks = sampler.stop()
+    hist, res, status = stats.read()
+    assert status == 0, "chain wait timed out"
+    ms = sec / args.steps * 1e3
+    tokens = B * T_PER_GPU
+    value = tokens / (sec / args.steps)
+
+    # end to end through the public API with host-resident inputs
+    cfg = prb.NewtonConfig(max_iters=K_NEWTON, picard_iters=P_PICARD, picard_adapt=False)
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        xd = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        Hs = prb.newton_apply(cell, xd, cfg)
+        loss = Hs[:, :, 3].float().sum()
+        loss.backward()
+        loss_host.copy_(loss.detach(), non_blocking=True)
+        cell.zero_grad(set_to_none=True)
+
+    for _ in range(2):
+        e2e_step()
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_sec = time_region(e2e_step, e2e_steps, None) / e2e_steps
+
+    # per-kernel rooflines
+    states_io = keep["H"]
+    states32 = states_io.float()
+    roofs = kernel_rooflines(wx, r_io.float().contiguous(), states32, states_io, G_io, peak)
+    total = {k: v["ms_per_launch"] * v["launches_per_step"] for k, v in roofs.items()}
+    top = max(total, key=total.get)
+    roofline = {"bound": "hbm", "kernel": top, "achieved": roofs[top]["achieved"], "peak": peak,
+                "unit": "GB/s", "frac": roofs[top]["achieved"] / peak, "peak_kind": peak_kind,
+                "traffic": None, "kernels": roofs,
+                "step": {"algorithmic_bytes": BYTES_STEP * tokens * D,
+                         "achieved": BYTES_STEP * tokens * D / (ms / 1e3) / 1e9,
+                         "frac": BYTES_STEP * tokens * D / (ms / 1e3) / 1e9 / peak,
+                         "frac_of_nominal_8TBs": BYTES_STEP * tokens * D / (ms / 1e3) / 1e9 / NOMINAL_HBM_GBS}}
+
+    # CPU baseline on a bounded sample (rank 0, N = 1 only)
+    threads = os.cpu_count() or 1
+    sample = cpu_sample()
+    cpu_sec, cpu_res = cpu_step(sample, threads)
+    cpu_value = T_PER_GPU / cpu_sec
+
+    line = {
+        "metric": "newton_scan_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 scan arithmetic, bf16 I/O",
+        "data": "synthetic", "config": workload_config(1), "clocks": clocks,
+        "e2e": {"value": tokens / e2e_sec, "unit": "tokens/s",
+                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 4,
+                "ms_per_step": e2e_sec * 1e3,
+                "includes": "H2D of x, 3 W_x GEMMs (cuBLAS), Newton+scan fwd, reverse scan + VJP, D2H of loss"},
+        "gpu_launches": 13 * args.steps,
+        "roofline": roofline,
+        "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": "1 of 8 batch rows (rows are independent), full T=16384, d=1024, "
+                                   "fp32 arithmetic on bf16-rounded inputs, one forward+backward"},
+        "newton": {"iters": K_NEWTON, "residual_history": list(hist), "max_residual": res},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        run_gpu_single(args)
+    else:
+        from bench_sharded import run_gpu_sharded
+
+        run_gpu_sharded(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,195 @@
+/*
+ * pararnn_b200 — C ABI of the B200 (sm_100a) backend for ParaRNN's parallel
+ * training hot path: fused Newton + chained linear scan forward, and the
+ * reverse-time adjoint scan fused with the packed cell VJP.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless stated otherwise;
+ *   - tensors are contiguous, row-major, channel-last:
+ *       wx      (B, T, G*d)   gate pre-activations W_x(x)+b, gate-major inside a row
+ *       states  (B, T, S, d)  S = 1 (GRU, NLRU) or 4 (sLSTM slots c, n, m, h)
+ *   - `dtype` selects the I/O element type of wx / states / h0 / recurrent
+ *     parameters / gradients: PRB_F32 or PRB_BF16.  All arithmetic and every
+ *     intermediate trajectory is fp32;
+ *   - recurrent parameters arrive already clamped (the reference clamps outside
+ *     its kernels) ;
+ *   - calls enqueue work on `stream` and return without synchronising.  The
+ *     return value is 0 or a negative PRB_ERR_* code for argument / launch
+ *     errors.  Device-side conditions (a bounded wait that ran out) are
+ *     reported in prb_stats.status, which the caller reads after it has
+ *     synchronised the stream;
+ *   - scratch memory is provided by the caller: ask prb_*_workspace_bytes()
+ *     and pass a buffer of at least that size (256-byte aligned).
+ *
+ * "Reference" citations are file:line in bugkira/pararnn-torch v0.17.5.
+ */
+#ifndef PARARNN_B200_H
+#define PARARNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* prb_stream_t; /* cudaStream_t */
+
+enum { PRB_F32 = 0, PRB_BF16 = 1 };
+enum { PRB_CELL_GRU_DIAG = 0, PRB_CELL_NLRU = 1, PRB_CELL_SLSTM_DIAG = 2, PRB_CELL_GRU_HEAD = 3 };
+enum {
+    PRB_OK = 0,
+    PRB_ERR_BAD_ARG = -1,     /* null pointer, non-positive size, unknown enum */
+    PRB_ERR_WORKSPACE = -2,   /* workspace missing, misaligned or too small */
+    PRB_ERR_UNSUPPORTED = -3, /* shape outside what the kernels cover */
+    PRB_ERR_LAUNCH = -4,      /* CUDA reported a launch error */
+    PRB_ERR_TOO_LARGE = -5,   /* fixed-capacity entry point: size beyond its limit */
+    PRB_STATUS_CHAIN_TIMEOUT = 1 /* prb_stats.status: a bounded device wait ran out */
+};
+#define PRB_MAX_ITERS 16
+
+/* Device-resident statistics block (64 bytes).  max|F| values are stored as the
+ * IEEE-754 bit pattern of a non-negative float (NaN sorts highest).
+ * Replaces the host-side residual evaluation of the reference,
+ * solvers/newton/__init__.py:582-636 (_fill_stats). */
+typedef struct prb_stats {
+    uint32_t hist_bits[PRB_MAX_ITERS]; /* max|F(H^k)| before Newton pass k */
+    uint32_t final_bits;               /* max|F(H^K)| of the returned trajectory */
+    int32_t status;                    /* 0 or PRB_STATUS_CHAIN_TIMEOUT */
+    int32_t reserved[2];
+} prb_stats;
+
+const char* prb_version(void);
+const char* prb_error_string(int code);
+
+/* Scratch sizes.  `n_heads` is ignored by the diagonal cells. */
+size_t prb_newton_workspace_bytes(int cell, int dtype, int B, int T, int d, int n_heads,
+                                  int max_iters, int picard_iters);
+size_t prb_bwd_workspace_bytes(int cell, int dtype, int B, int T, int d, int n_heads);
+
+/* ---- forward: fused Newton + scan ------------------------------------------------ */
+
+/* ParaGRU mix='diag'.  Replaces pararnn::newton_gru_fused,
+ * kernels/custom_ops.py:146-188 -> kernels/newton_gru.py:332-495.
+ * wx (B,T,3d) gates (z,r,n); a_z,a_r,a_n (d); h0 (B,d) or NULL; out (B,T,d). */
+int prb_newton_gru_fused(const void* wx, const void* a_z, const void* a_r, const void* a_n,
+                         const void* h0, void* out, int B, int T, int d, int dtype, int max_iters,
+                         float omega, int want_residual, void* workspace, size_t workspace_bytes,
+                         prb_stats* stats, prb_stream_t stream);
+
+/* ParaNLRU.  Replaces pararnn::newton_nlru_fused, kernels/custom_ops.py:191-227 ->
+ * kernels/newton_nlru.py:320-475.  wx (B,T,2d) gates (a,c); u (d). */
+int prb_newton_nlru_fused(const void* wx, const void* u, const void* h0, void* out, int B, int T,
+                          int d, int dtype, int max_iters, float omega, int want_residual,
+                          void* workspace, size_t workspace_bytes, prb_stats* stats,
+                          prb_stream_t stream);
+
+/* ParaSLSTM mix='diag', including the frozen-gate Picard warm start.  Replaces
+ * pararnn::newton_slstm_fused, kernels/custom_ops.py:486-540 ->
+ * kernels/newton_slstm.py:2696-2939, and solvers/slstm_picard.py:158-181
+ * (slstm_picard_init).  wx (B,T,4d) gates (i,f,z,o); r (4,d); h0 (B,4,d) or NULL;
+ * states_guess (B,T,4,d) or NULL (when given it replaces the Picard warm start and
+ * is not modified); out (B,T,4,d). */
+int prb_newton_slstm_fused(const void* wx, const void* r, const void* h0, const void* states_guess,
+                           void* out, int B, int T, int d, int dtype, int max_iters,
+                           int picard_iters, float omega, float eps, int want_residual,
+                           void* workspace, size_t workspace_bytes, prb_stats* stats,
+                           prb_stream_t stream);
+
+/* ---- backward: eq. 2.6 reverse scan fused with the packed VJP ------------------- */
+
+/* Replaces reverse_scan_diag + gru_recurrence_vjp / nlru_recurrence_vjp,
+ * solvers/scan.py:126-148, kernels/vjp_gru.py:813-872, kernels/vjp_nlru.py:111-150,
+ * and _t0_state_vjp, solvers/newton/dispatch.py:406-441.
+ * states, grad_states (B,T,d); g_wx (B,T,G*d) in the I/O dtype;
+ * g_params fp32 (NP,d) summed over batch and time (clip mask NOT applied);
+ * g_h0 fp32 (B,d) or NULL. */
+int prb_bwd_gru(const void* states, const void* wx, const void* a_z, const void* a_r,
+                const void* a_n, const void* h0, const void* grad_states, void* g_wx,
+                float* g_params, float* g_h0, int B, int T, int d, int dtype, void* workspace,
+                size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
+int prb_bwd_nlru(const void* states, const void* wx, const void* u, const void* h0,
+                 const void* grad_states, void* g_wx, float* g_params, float* g_h0, int B, int T,
+                 int d, int dtype, void* workspace, size_t workspace_bytes, prb_stats* stats,
+                 prb_stream_t stream);
+
+/* Replaces reverse_scan_block4 + slstm_recurrence_vjp, solvers/scan.py:166-178,
+ * kernels/vjp_slstm.py:234-293.  states, grad_states (B,T,4,d); g_wx (B,T,4d);
+ * g_params fp32 (4,d); g_h0 fp32 (B,4,d) or NULL. */
+int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void* h0,
+                  const void* grad_states, void* g_wx, float* g_params, float* g_h0, int B, int T,
+                  int d, int dtype, float eps, void* workspace, size_t workspace_bytes,
+                  prb_stats* stats, prb_stream_t stream);
+
+/* ---- residual gate ------------------------------------------------------------------- */
+
+/* max|f(H_{t-1},x_t) - H_t| into stats->final_bits.  Replaces the eager
+ * evaluation in solvers/newton/__init__.py:602-606.  params: GRU (3,d) packed
+ * a_z,a_r,a_n; NLRU (1,d); sLSTM (4,d); all in the I/O dtype. */
+int prb_residual(int cell, const void* wx, const void* params, const void* h0, const void* states,
+                 int B, int T, int d, int dtype, float eps, void* workspace, size_t workspace_bytes,
+                 prb_stats* stats, prb_stream_t stream);
+
+/* ---- pass-level entry points ---------------------------------------------------------
+ * One scan pass over a (shard of a) sequence with explicit boundary data, used by the
+ * time-sharded multi-GPU driver and for per-kernel timing.  They replace the per-rank
+ * pieces of the reference's context-parallel scan, solvers/seq_parallel.py:126-342
+ * (local scan, carry, prefix apply), generalised from the scalar monoid to all cells.
+ * Parameters, halos and carries here are fp32; `halo` is the state preceding step 0 of
+ * the shard, `carry_in` the scan carry entering step 0 (NULL = zeros).
+ * mode: 0 = apply, fp32 work trajectory out; 1 = apply, last pass, output in the I/O
+ * dtype; 2 = aggregate only: nothing but the shard's aggregate map is written.
+ * The workspace (prb_pass_workspace_bytes) holds the chain scratch of one pass.
+ * prb_stats is NOT cleared by these calls: hist_bits[hist_slot] / final_bits are
+ * max-accumulated, so the caller zeroes the block once per solve. */
+size_t prb_pass_workspace_bytes(int cell, int B, int T, int d);
+
+int prb_diag_guess(int cell, const void* wx, const float* params, const float* h0, float* out, int B,
+                   int T, int d, int dtype, prb_stream_t stream);
+
+/* scalar-diagonal Newton pass: carry = delta (B,d); aggregate (B,2,d) = (a, b) */
+int prb_diag_newton_pass(int cell, const void* wx, const float* params, const float* hin,
+                         const float* halo, const float* carry_in, void* hout, float* tail_out,
+                         float* agg_out, int mode, int B, int T, int d, int dtype, float omega,
+                         void* workspace, size_t workspace_bytes, prb_stats* stats, int hist_slot,
+                         prb_stream_t stream);
+
+/* reverse pass: carry = nu entering the shard's last step (B,d); head_out = nu leaving
+ * its first step (grad_h0 on the first shard); g_params = this shard's partial sums */
+int prb_diag_bwd_pass(int cell, const void* states, const void* wx, const float* params,
+                      const float* halo, const float* carry_in, const void* grad_states, void* g_wx,
+                      float* g_params, float* head_out, float* agg_out, int mode, int B, int T, int d,
+                      int dtype, void* workspace, size_t workspace_bytes, prb_stats* stats,
+                      prb_stream_t stream);
+
+/* sLSTM frozen-gate pass: h_prev (B,T,d) hidden trajectory of the previous pass or NULL
+ * (zero-hidden pass); h_halo (B,d); carry (B,3,d) = (c,n,m); aggregate (B,4,d) = (a,b,N,C);
+ * writes h_out (B,T,d) or, when state_out is given, the full state (B,T,4,d) */
+int prb_slstm_picard_pass(const void* wx, const float* r, const float* h_prev, const float* h_halo,
+                          const float* carry_in, float* h_out, float* state_out, float* tail_out,
+                          float* agg_out, int mode, int B, int T, int d, int dtype, float eps,
+                          void* workspace, size_t workspace_bytes, prb_stats* stats,
+                          prb_stream_t stream);
+
+/* sLSTM Newton pass: halo, carry (B,4,d); aggregate (B,20,d) = 4x4 row-major M, then v */
+int prb_slstm_newton_pass(const void* wx, const float* r, const float* sin, const float* halo,
+                          const float* carry_in, void* sout, float* tail_out, float* agg_out, int mode,
+                          int B, int T, int d, int dtype, float omega, float eps, void* workspace,
+                          size_t workspace_bytes, prb_stats* stats, int hist_slot,
+                          prb_stream_t stream);
+
+int prb_slstm_bwd_pass(const void* states, const void* wx, const float* r, const float* halo,
+                       const float* carry_in, const void* grad_states, void* g_wx, float* g_params,
+                       float* head_out, float* agg_out, int mode, int B, int T, int d, int dtype,
+                       float eps, void* workspace, size_t workspace_bytes, prb_stats* stats,
+                       prb_stream_t stream);
+
+/* residual of a shard with an fp32 halo; states fp32 (states_f32 != 0) or I/O dtype */
+int prb_residual_pass(int cell, const void* wx, const float* params, const float* halo,
+                      const void* states, int states_f32, int B, int T, int d, int dtype, float eps,
+                      prb_stats* stats, prb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PARARNN_B200_H */

@@ -1,0 +1,748 @@
+// extern "C" entry points declared in include/pararnn_b200.h.  This file owns
+// argument validation, the workspace layout and the sequence of launches that
+// make up one fused forward or backward call; the kernels live in
+// diag_kernels.cu and slstm_kernels.cu.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/pararnn_b200.h"
+#include "kernels.h"
+
+using namespace prb;
+
+static_assert(sizeof(prb_stats) == sizeof(DeviceStats), "stats layout");
+static_assert(PRB_MAX_ITERS == kMaxIters, "history capacity");
+
+namespace {
+
+// Bump allocator over the caller's workspace.  With base == nullptr it only
+// measures, so the size query and the real layout cannot drift apart.
+struct Bump {
+    char* base;
+    size_t off = 0;
+    explicit Bump(void* b) : base(reinterpret_cast<char*>(b)) {}
+    template <typename T>
+    T* take(size_t n) {
+        off = (off + 255) & ~size_t(255);
+        T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+        off += n * sizeof(T);
+        return p;
+    }
+};
+
+constexpr int kTickets = 64;
+
+struct ChainScratch {
+    unsigned* flags;
+    unsigned* tickets;
+    float* agg;
+    float* inc;
+    int n_chains;
+    int max_tt;
+    unsigned next_epoch = 1;
+    int next_ticket = 0;
+};
+
+// nv = floats per lane of the widest map that will travel on this chain
+ChainScratch plan_chain(Bump& b, int B, int T, int d, int min_tile_steps, int nv) {
+    ChainScratch c;
+    c.n_chains = B * ((d + kLanes - 1) / kLanes);
+    c.max_tt = (T + min_tile_steps - 1) / min_tile_steps;
+    const size_t tiles = (size_t)c.n_chains * c.max_tt;
+    c.flags = b.take<unsigned>(tiles + kTickets);
+    c.tickets = c.flags ? c.flags + tiles : nullptr;
+    c.agg = b.take<float>(tiles * nv * kLanes);
+    c.inc = b.take<float>(tiles * nv * kLanes);
+    return c;
+}
+
+Chain next_chain(ChainScratch& c, int T, int tile_steps, int* status) {
+    Chain ch;
+    ch.flags = c.flags;
+    ch.agg = c.agg;
+    ch.inc = c.inc;
+    ch.ticket = c.tickets + (c.next_ticket++ % kTickets);
+    ch.status = status;
+    ch.epoch = c.next_epoch++;
+    ch.n_chains = c.n_chains;
+    ch.n_tt = (T + tile_steps - 1) / tile_steps;
+    return ch;
+}
+
+template <typename T>
+__global__ void cvt_to_f32_kernel(const T* src, float* dst, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = ld_f(src + i);
+}
+template <typename T>
+__global__ void cvt_from_f32_kernel(const float* src, T* dst, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x)
+        st_f(dst + i, src[i]);
+}
+
+void to_f32(const void* src, float* dst, size_t n, int dtype, cudaStream_t s) {
+    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    if (dtype == kF32)
+        cvt_to_f32_kernel<float><<<blocks, 256, 0, s>>>((const float*)src, dst, n);
+    else
+        cvt_to_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)src, dst, n);
+}
+void from_f32(const float* src, void* dst, size_t n, int dtype, cudaStream_t s) {
+    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    if (dtype == kF32)
+        cvt_from_f32_kernel<float><<<blocks, 256, 0, s>>>(src, (float*)dst, n);
+    else
+        cvt_from_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(src, (__nv_bfloat16*)dst, n);
+}
+
+bool bad_dtype(int dtype) { return dtype != kF32 && dtype != kBF16; }
+bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 255u) != 0; }
+
+int check_ws(void* ws, size_t have, size_t need) {
+    if (need == 0) return PRB_OK;
+    if (!ws || misaligned(ws) || have < need) return PRB_ERR_WORKSPACE;
+    return PRB_OK;
+}
+
+// ---------------------------------------------------------------- diag cells
+struct DiagPlan {
+    ChainScratch chain;
+    float* par;
+    float* h0;
+    float* buf[2];
+    size_t total;
+};
+
+DiagPlan plan_diag_fwd(void* ws, int cell, int B, int T, int d, int K, bool has_h0) {
+    Bump b(ws);
+    DiagPlan p;
+    const int np = cell == kCellGruDiag ? 3 : 1;
+    p.chain = plan_chain(b, B, T, d, diag_tile_steps(), 2);
+    p.par = b.take<float>((size_t)np * d);
+    p.h0 = b.take<float>((size_t)B * d);
+    const size_t n = (size_t)B * T * d;
+    p.buf[0] = K >= 2 ? b.take<float>(n) : nullptr;
+    p.buf[1] = K >= 3 ? b.take<float>(n) : nullptr;
+    (void)has_h0;
+    p.total = b.off + 256;
+    return p;
+}
+
+int run_diag_fwd(int cell, const void* wx, const void* const* pars, const void* h0, void* out, int B,
+                 int T, int d, int dtype, int K, float omega, int want_residual, void* ws,
+                 size_t ws_bytes, prb_stats* stats, cudaStream_t s) {
+    if (!wx || !out || !stats || B < 1 || T < 1 || d < 1 || K < 0 || K > kMaxIters || bad_dtype(dtype))
+        return PRB_ERR_BAD_ARG;
+    const int np = cell == kCellGruDiag ? 3 : 1;
+    for (int i = 0; i < np; ++i)
+        if (!pars[i]) return PRB_ERR_BAD_ARG;
+    DiagPlan p = plan_diag_fwd(nullptr, cell, B, T, d, K, h0 != nullptr);
+    if (int e = check_ws(ws, ws_bytes, p.total)) return e;
+    p = plan_diag_fwd(ws, cell, B, T, d, K, h0 != nullptr);
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    cudaMemsetAsync(st, 0, sizeof(DeviceStats), s);
+    cudaMemsetAsync(p.chain.flags, 0, ((size_t)p.chain.n_chains * p.chain.max_tt + kTickets) * 4, s);
+    for (int i = 0; i < np; ++i) to_f32(pars[i], p.par + (size_t)i * d, d, dtype, s);
+    const float* h0f = nullptr;
+    if (h0) {
+        to_f32(h0, p.h0, (size_t)B * d, dtype, s);
+        h0f = p.h0;
+    }
+    if (K == 0) {
+        launch_diag_guess(cell, dtype, false, wx, p.par, h0f, out, B, T, d, s);
+    }
+    for (int k = 0; k < K; ++k) {
+        DiagFwdArgs a{};
+        a.wx = wx;
+        a.par = p.par;
+        a.halo = h0f;
+        a.carry_in = nullptr;
+        a.hin = k > 0 ? p.buf[(k - 1) & 1] : nullptr;
+        a.hout = (k == K - 1) ? out : (void*)p.buf[k & 1];
+        a.resid_bits = &st->hist_bits[k];
+        a.B = B;
+        a.T = T;
+        a.d = d;
+        a.omega = omega;
+        a.chain = next_chain(p.chain, T, diag_tile_steps(), &st->status);
+        if (launch_diag_newton(cell, dtype, a, k == 0, k == K - 1, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+    }
+    if (want_residual)
+        if (launch_diag_residual(cell, dtype, false, wx, p.par, h0f, out, B, T, d, &st->final_bits, s) !=
+            cudaSuccess)
+            return PRB_ERR_LAUNCH;
+    return cudaGetLastError() == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+}
+
+struct DiagBwdPlan {
+    ChainScratch chain;
+    float* par;
+    float* h0;
+    float* partial;
+    size_t total;
+};
+
+DiagBwdPlan plan_diag_bwd(void* ws, int cell, int B, int T, int d) {
+    Bump b(ws);
+    DiagBwdPlan p;
+    const int np = cell == kCellGruDiag ? 3 : 1;
+    p.chain = plan_chain(b, B, T, d, diag_tile_steps(), 2);
+    p.par = b.take<float>((size_t)np * d);
+    p.h0 = b.take<float>((size_t)B * d);
+    p.partial = b.take<float>((size_t)B * p.chain.max_tt * np * d);
+    p.total = b.off + 256;
+    return p;
+}
+
+int run_diag_bwd(int cell, const void* states, const void* wx, const void* const* pars,
+                 const void* h0, const void* grad_states, void* g_wx, float* g_params, float* g_h0,
+                 int B, int T, int d, int dtype, void* ws, size_t ws_bytes, prb_stats* stats,
+                 cudaStream_t s) {
+    if (!states || !wx || !grad_states || !g_wx || !g_params || !stats || B < 1 || T < 1 || d < 1 ||
+        bad_dtype(dtype))
+        return PRB_ERR_BAD_ARG;
+    const int np = cell == kCellGruDiag ? 3 : 1;
+    for (int i = 0; i < np; ++i)
+        if (!pars[i]) return PRB_ERR_BAD_ARG;
+    DiagBwdPlan p = plan_diag_bwd(nullptr, cell, B, T, d);
+    if (int e = check_ws(ws, ws_bytes, p.total)) return e;
+    p = plan_diag_bwd(ws, cell, B, T, d);
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    cudaMemsetAsync(st, 0, sizeof(DeviceStats), s);
+    cudaMemsetAsync(p.chain.flags, 0, ((size_t)p.chain.n_chains * p.chain.max_tt + kTickets) * 4, s);
+    for (int i = 0; i < np; ++i) to_f32(pars[i], p.par + (size_t)i * d, d, dtype, s);
+    const float* h0f = nullptr;
+    if (h0) {
+        to_f32(h0, p.h0, (size_t)B * d, dtype, s);
+        h0f = p.h0;
+    }
+    DiagBwdArgs a{};
+    a.wx = wx;
+    a.states = states;
+    a.grad_states = grad_states;
+    a.par = p.par;
+    a.halo = h0f;
+    a.g_wx = g_wx;
+    a.gp_partial = p.partial;
+    a.g_h0 = g_h0;
+    a.B = B;
+    a.T = T;
+    a.d = d;
+    a.chain = next_chain(p.chain, T, diag_tile_steps(), &st->status);
+    if (launch_diag_bwd(cell, dtype, a, false, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+    if (launch_reduce_partials(p.partial, B * a.chain.n_tt, np * d, g_params, s) != cudaSuccess)
+        return PRB_ERR_LAUNCH;
+    return PRB_OK;
+}
+
+// ---------------------------------------------------------------- sLSTM
+struct SlstmPlan {
+    ChainScratch chain;
+    float* r;
+    float* h0;
+    float* hb[2];
+    float* sb[2];
+    size_t total;
+};
+
+SlstmPlan plan_slstm_fwd(void* ws, int B, int T, int d, int K, int P, bool has_guess) {
+    Bump b(ws);
+    SlstmPlan p;
+    const int min_tile = slstm_tile_steps() < slstm_picard_tile_steps() ? slstm_tile_steps()
+                                                                         : slstm_picard_tile_steps();
+    p.chain = plan_chain(b, B, T, d, min_tile, 20);
+    p.r = b.take<float>((size_t)4 * d);
+    p.h0 = b.take<float>((size_t)B * 4 * d);
+    const size_t nh = (size_t)B * T * d;
+    const bool picard = !has_guess;
+    p.hb[0] = (picard && P >= 1) ? b.take<float>(nh) : nullptr;
+    p.hb[1] = (picard && P >= 2) ? b.take<float>(nh) : nullptr;
+    p.sb[0] = b.take<float>(nh * 4);
+    p.sb[1] = K >= 2 ? b.take<float>(nh * 4) : nullptr;
+    p.total = b.off + 256;
+    return p;
+}
+
+int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* guess, void* out, int B,
+                  int T, int d, int dtype, int K, int P, float omega, float eps, int want_residual,
+                  void* ws, size_t ws_bytes, prb_stats* stats, cudaStream_t s) {
+    if (!wx || !r || !out || !stats || B < 1 || T < 1 || d < 1 || K < 0 || K > kMaxIters || P < 0 ||
+        bad_dtype(dtype))
+        return PRB_ERR_BAD_ARG;
+    SlstmPlan p = plan_slstm_fwd(nullptr, B, T, d, K, P, guess != nullptr);
+    if (int e = check_ws(ws, ws_bytes, p.total)) return e;
+    p = plan_slstm_fwd(ws, B, T, d, K, P, guess != nullptr);
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    cudaMemsetAsync(st, 0, sizeof(DeviceStats), s);
+    cudaMemsetAsync(p.chain.flags, 0, ((size_t)p.chain.n_chains * p.chain.max_tt + kTickets) * 4, s);
+    to_f32(r, p.r, (size_t)4 * d, dtype, s);
+    const float* h0f = nullptr;
+    if (h0) {
+        to_f32(h0, p.h0, (size_t)B * 4 * d, dtype, s);
+        h0f = p.h0;
+    }
+    const size_t nst = (size_t)B * T * 4 * d;
+    if (guess) {
+        to_f32(guess, p.sb[0], nst, dtype, s);
+    } else {
+        for (int pass = 0; pass <= P; ++pass) {
+            SlstmPicardArgs a{};
+            a.wx = wx;
+            a.r = p.r;
+            a.h_prev = pass > 0 ? p.hb[(pass - 1) & 1] : nullptr;
+            a.h_halo = h0f ? h0f + 3 * (size_t)d : nullptr;
+            a.halo_stride = 4 * d;
+            a.carry_in = h0f;  // slots (c, n, m) of h0
+            a.carry_stride = 4 * d;
+            if (pass == P)
+                a.state_out = p.sb[0];
+            else
+                a.h_out = p.hb[pass & 1];
+            a.B = B;
+            a.T = T;
+            a.d = d;
+            a.eps = eps;
+            a.chain = next_chain(p.chain, T, slstm_picard_tile_steps(), &st->status);
+            if (launch_slstm_picard(dtype, a, false, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+        }
+    }
+    if (K == 0) from_f32(p.sb[0], out, nst, dtype, s);
+    for (int k = 0; k < K; ++k) {
+        SlstmNewtonArgs a{};
+        a.wx = wx;
+        a.r = p.r;
+        a.sin = p.sb[k & 1];
+        a.halo = h0f;
+        a.halo_stride = 4 * d;
+        a.sout = (k == K - 1) ? out : (void*)p.sb[(k + 1) & 1];
+        a.resid_bits = &st->hist_bits[k];
+        a.B = B;
+        a.T = T;
+        a.d = d;
+        a.omega = omega;
+        a.eps = eps;
+        a.chain = next_chain(p.chain, T, slstm_tile_steps(), &st->status);
+        if (launch_slstm_newton(dtype, a, k == K - 1, false, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+    }
+    if (want_residual)
+        if (launch_slstm_residual(dtype, false, wx, p.r, h0f, 4 * d, out, B, T, d, eps, &st->final_bits,
+                                  s) != cudaSuccess)
+            return PRB_ERR_LAUNCH;
+    return cudaGetLastError() == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+}
+
+struct SlstmBwdPlan {
+    ChainScratch chain;
+    float* r;
+    float* h0;
+    float* partial;
+    size_t total;
+};
+
+SlstmBwdPlan plan_slstm_bwd(void* ws, int B, int T, int d) {
+    Bump b(ws);
+    SlstmBwdPlan p;
+    p.chain = plan_chain(b, B, T, d, slstm_tile_steps(), 20);
+    p.r = b.take<float>((size_t)4 * d);
+    p.h0 = b.take<float>((size_t)B * 4 * d);
+    p.partial = b.take<float>((size_t)B * p.chain.max_tt * 4 * d);
+    p.total = b.off + 256;
+    return p;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* prb_version(void) { return "pararnn_b200 0.1 (sm_100a)"; }
+
+const char* prb_error_string(int code) {
+    switch (code) {
+        case PRB_OK: return "ok";
+        case PRB_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size or unknown enum)";
+        case PRB_ERR_WORKSPACE: return "workspace missing, not 256-byte aligned, or too small";
+        case PRB_ERR_UNSUPPORTED: return "shape not supported by this kernel";
+        case PRB_ERR_LAUNCH: return "CUDA launch error";
+        case PRB_ERR_TOO_LARGE: return "size exceeds the fixed capacity of this entry point";
+        case PRB_STATUS_CHAIN_TIMEOUT: return "a bounded device-side wait ran out";
+        default: return "unknown code";
+    }
+}
+
+size_t prb_newton_workspace_bytes(int cell, int dtype, int B, int T, int d, int n_heads,
+                                  int max_iters, int picard_iters) {
+    (void)dtype;
+    (void)n_heads;
+    if (B < 1 || T < 1 || d < 1) return 0;
+    if (cell == kCellGruDiag || cell == kCellNlru)
+        return plan_diag_fwd(nullptr, cell, B, T, d, max_iters, true).total;
+    if (cell == kCellSlstmDiag) return plan_slstm_fwd(nullptr, B, T, d, max_iters, picard_iters, false).total;
+    return 0;
+}
+
+size_t prb_bwd_workspace_bytes(int cell, int dtype, int B, int T, int d, int n_heads) {
+    (void)dtype;
+    (void)n_heads;
+    if (B < 1 || T < 1 || d < 1) return 0;
+    if (cell == kCellGruDiag || cell == kCellNlru) return plan_diag_bwd(nullptr, cell, B, T, d).total;
+    if (cell == kCellSlstmDiag) return plan_slstm_bwd(nullptr, B, T, d).total;
+    return 0;
+}
+
+int prb_newton_gru_fused(const void* wx, const void* a_z, const void* a_r, const void* a_n,
+                         const void* h0, void* out, int B, int T, int d, int dtype, int max_iters,
+                         float omega, int want_residual, void* workspace, size_t workspace_bytes,
+                         prb_stats* stats, prb_stream_t stream) {
+    const void* pars[3] = {a_z, a_r, a_n};
+    return run_diag_fwd(kCellGruDiag, wx, pars, h0, out, B, T, d, dtype, max_iters, omega,
+                        want_residual, workspace, workspace_bytes, stats, (cudaStream_t)stream);
+}
+
+int prb_newton_nlru_fused(const void* wx, const void* u, const void* h0, void* out, int B, int T,
+                          int d, int dtype, int max_iters, float omega, int want_residual,
+                          void* workspace, size_t workspace_bytes, prb_stats* stats,
+                          prb_stream_t stream) {
+    const void* pars[3] = {u, nullptr, nullptr};
+    return run_diag_fwd(kCellNlru, wx, pars, h0, out, B, T, d, dtype, max_iters, omega, want_residual,
+                        workspace, workspace_bytes, stats, (cudaStream_t)stream);
+}
+
+int prb_newton_slstm_fused(const void* wx, const void* r, const void* h0, const void* states_guess,
+                           void* out, int B, int T, int d, int dtype, int max_iters,
+                           int picard_iters, float omega, float eps, int want_residual,
+                           void* workspace, size_t workspace_bytes, prb_stats* stats,
+                           prb_stream_t stream) {
+    return run_slstm_fwd(wx, r, h0, states_guess, out, B, T, d, dtype, max_iters, picard_iters, omega,
+                         eps, want_residual, workspace, workspace_bytes, stats, (cudaStream_t)stream);
+}
+
+int prb_bwd_gru(const void* states, const void* wx, const void* a_z, const void* a_r,
+                const void* a_n, const void* h0, const void* grad_states, void* g_wx,
+                float* g_params, float* g_h0, int B, int T, int d, int dtype, void* workspace,
+                size_t workspace_bytes, prb_stats* stats, prb_stream_t stream) {
+    const void* pars[3] = {a_z, a_r, a_n};
+    return run_diag_bwd(kCellGruDiag, states, wx, pars, h0, grad_states, g_wx, g_params, g_h0, B, T, d,
+                        dtype, workspace, workspace_bytes, stats, (cudaStream_t)stream);
+}
+
+int prb_bwd_nlru(const void* states, const void* wx, const void* u, const void* h0,
+                 const void* grad_states, void* g_wx, float* g_params, float* g_h0, int B, int T,
+                 int d, int dtype, void* workspace, size_t workspace_bytes, prb_stats* stats,
+                 prb_stream_t stream) {
+    const void* pars[3] = {u, nullptr, nullptr};
+    return run_diag_bwd(kCellNlru, states, wx, pars, h0, grad_states, g_wx, g_params, g_h0, B, T, d,
+                        dtype, workspace, workspace_bytes, stats, (cudaStream_t)stream);
+}
+
+int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void* h0,
+                  const void* grad_states, void* g_wx, float* g_params, float* g_h0, int B, int T,
+                  int d, int dtype, float eps, void* workspace, size_t workspace_bytes,
+                  prb_stats* stats, prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!states || !wx || !r || !grad_states || !g_wx || !g_params || !stats || B < 1 || T < 1 ||
+        d < 1 || bad_dtype(dtype))
+        return PRB_ERR_BAD_ARG;
+    SlstmBwdPlan p = plan_slstm_bwd(nullptr, B, T, d);
+    if (int e = check_ws(workspace, workspace_bytes, p.total)) return e;
+    p = plan_slstm_bwd(workspace, B, T, d);
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    cudaMemsetAsync(st, 0, sizeof(DeviceStats), s);
+    cudaMemsetAsync(p.chain.flags, 0, ((size_t)p.chain.n_chains * p.chain.max_tt + kTickets) * 4, s);
+    to_f32(r, p.r, (size_t)4 * d, dtype, s);
+    const float* h0f = nullptr;
+    if (h0) {
+        to_f32(h0, p.h0, (size_t)B * 4 * d, dtype, s);
+        h0f = p.h0;
+    }
+    SlstmBwdArgs a{};
+    a.wx = wx;
+    a.states = states;
+    a.grad_states = grad_states;
+    a.r = p.r;
+    a.halo = h0f;
+    a.halo_stride = 4 * d;
+    a.g_wx = g_wx;
+    a.gp_partial = p.partial;
+    a.g_h0 = g_h0;
+    a.B = B;
+    a.T = T;
+    a.d = d;
+    a.eps = eps;
+    a.chain = next_chain(p.chain, T, slstm_tile_steps(), &st->status);
+    if (launch_slstm_bwd(dtype, a, false, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+    if (launch_reduce_partials(p.partial, B * a.chain.n_tt, 4 * d, g_params, s) != cudaSuccess)
+        return PRB_ERR_LAUNCH;
+    return PRB_OK;
+}
+
+/* ---- pass-level entry points (time-sharded driver, profiling) ------------------- */
+
+size_t prb_pass_workspace_bytes(int cell, int B, int T, int d) {
+    if (B < 1 || T < 1 || d < 1) return 0;
+    Bump b(nullptr);
+    const bool sl = cell == kCellSlstmDiag;
+    const int tile = sl ? (slstm_tile_steps() < slstm_picard_tile_steps() ? slstm_tile_steps()
+                                                                           : slstm_picard_tile_steps())
+                        : diag_tile_steps();
+    plan_chain(b, B, T, d, tile, sl ? 20 : 2);
+    b.take<float>((size_t)B * ((T + tile - 1) / tile) * 4 * d);
+    return b.off + 256;
+}
+
+namespace {
+struct PassWs {
+    ChainScratch chain;
+    float* partial;
+};
+int pass_ws(int cell, int B, int T, int d, void* ws, size_t ws_bytes, cudaStream_t s, PassWs& out) {
+    if (int e = check_ws(ws, ws_bytes, prb_pass_workspace_bytes(cell, B, T, d))) return e;
+    Bump b(ws);
+    const bool sl = cell == kCellSlstmDiag;
+    const int tile = sl ? (slstm_tile_steps() < slstm_picard_tile_steps() ? slstm_tile_steps()
+                                                                           : slstm_picard_tile_steps())
+                        : diag_tile_steps();
+    out.chain = plan_chain(b, B, T, d, tile, sl ? 20 : 2);
+    out.partial = b.take<float>((size_t)B * ((T + tile - 1) / tile) * 4 * d);
+    cudaMemsetAsync(out.chain.flags, 0, ((size_t)out.chain.n_chains * out.chain.max_tt + kTickets) * 4, s);
+    return PRB_OK;
+}
+}  // namespace
+
+int prb_diag_guess(int cell, const void* wx, const float* params, const float* h0, float* out, int B,
+                   int T, int d, int dtype, prb_stream_t stream) {
+    if (!wx || !params || !out || B < 1 || T < 1 || d < 1 || bad_dtype(dtype)) return PRB_ERR_BAD_ARG;
+    if (cell != kCellGruDiag && cell != kCellNlru) return PRB_ERR_UNSUPPORTED;
+    return launch_diag_guess(cell, dtype, true, wx, params, h0, out, B, T, d, (cudaStream_t)stream) ==
+                   cudaSuccess
+               ? PRB_OK
+               : PRB_ERR_LAUNCH;
+}
+
+int prb_diag_newton_pass(int cell, const void* wx, const float* params, const float* hin,
+                         const float* halo, const float* carry_in, void* hout, float* tail_out,
+                         float* agg_out, int mode, int B, int T, int d, int dtype, float omega,
+                         void* workspace, size_t workspace_bytes, prb_stats* stats, int hist_slot,
+                         prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!wx || !params || !hin || !stats || B < 1 || T < 1 || d < 1 || bad_dtype(dtype) || mode < 0 ||
+        mode > 2 || hist_slot < 0 || hist_slot >= kMaxIters)
+        return PRB_ERR_BAD_ARG;
+    if (cell != kCellGruDiag && cell != kCellNlru) return PRB_ERR_UNSUPPORTED;
+    if ((mode == 2 && !agg_out) || (mode != 2 && !hout)) return PRB_ERR_BAD_ARG;
+    PassWs w;
+    if (int e = pass_ws(cell, B, T, d, workspace, workspace_bytes, s, w)) return e;
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    DiagFwdArgs a{};
+    a.wx = wx;
+    a.par = params;
+    a.halo = halo;
+    a.carry_in = carry_in;
+    a.hin = hin;
+    a.hout = hout;
+    a.tail_out = tail_out;
+    a.agg_out = agg_out;
+    a.resid_bits = &st->hist_bits[hist_slot];
+    a.B = B;
+    a.T = T;
+    a.d = d;
+    a.omega = omega;
+    a.chain = next_chain(w.chain, T, diag_tile_steps(), &st->status);
+    cudaError_t e = mode == 2 ? launch_diag_newton_agg(cell, dtype, a, s)
+                              : launch_diag_newton(cell, dtype, a, false, mode == 1, s);
+    return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+}
+
+int prb_diag_bwd_pass(int cell, const void* states, const void* wx, const float* params,
+                      const float* halo, const float* carry_in, const void* grad_states, void* g_wx,
+                      float* g_params, float* head_out, float* agg_out, int mode, int B, int T, int d,
+                      int dtype, void* workspace, size_t workspace_bytes, prb_stats* stats,
+                      prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!states || !wx || !params || !grad_states || !stats || B < 1 || T < 1 || d < 1 ||
+        bad_dtype(dtype) || (mode != 0 && mode != 2))
+        return PRB_ERR_BAD_ARG;
+    if (cell != kCellGruDiag && cell != kCellNlru) return PRB_ERR_UNSUPPORTED;
+    if ((mode == 2 && !agg_out) || (mode == 0 && (!g_wx || !g_params))) return PRB_ERR_BAD_ARG;
+    PassWs w;
+    if (int e = pass_ws(cell, B, T, d, workspace, workspace_bytes, s, w)) return e;
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    const int np = cell == kCellGruDiag ? 3 : 1;
+    DiagBwdArgs a{};
+    a.wx = wx;
+    a.states = states;
+    a.grad_states = grad_states;
+    a.par = params;
+    a.halo = halo;
+    a.carry_in = carry_in;
+    a.g_wx = g_wx;
+    a.gp_partial = w.partial;
+    a.g_h0 = head_out;
+    a.agg_out = agg_out;
+    a.B = B;
+    a.T = T;
+    a.d = d;
+    a.chain = next_chain(w.chain, T, diag_tile_steps(), &st->status);
+    if (launch_diag_bwd(cell, dtype, a, mode == 2, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+    if (mode == 0 &&
+        launch_reduce_partials(w.partial, B * a.chain.n_tt, np * d, g_params, s) != cudaSuccess)
+        return PRB_ERR_LAUNCH;
+    return PRB_OK;
+}
+
+int prb_slstm_picard_pass(const void* wx, const float* r, const float* h_prev, const float* h_halo,
+                          const float* carry_in, float* h_out, float* state_out, float* tail_out,
+                          float* agg_out, int mode, int B, int T, int d, int dtype, float eps,
+                          void* workspace, size_t workspace_bytes, prb_stats* stats,
+                          prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!wx || !r || !stats || B < 1 || T < 1 || d < 1 || bad_dtype(dtype) || (mode != 0 && mode != 2))
+        return PRB_ERR_BAD_ARG;
+    if ((mode == 2 && !agg_out) || (mode == 0 && !h_out && !state_out)) return PRB_ERR_BAD_ARG;
+    PassWs w;
+    if (int e = pass_ws(kCellSlstmDiag, B, T, d, workspace, workspace_bytes, s, w)) return e;
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    SlstmPicardArgs a{};
+    a.wx = wx;
+    a.r = r;
+    a.h_prev = h_prev;
+    a.h_halo = h_halo;
+    a.halo_stride = d;
+    a.carry_in = carry_in;
+    a.carry_stride = 3 * d;
+    a.h_out = h_out;
+    a.state_out = state_out;
+    a.tail_out = tail_out;
+    a.agg_out = agg_out;
+    a.B = B;
+    a.T = T;
+    a.d = d;
+    a.eps = eps;
+    a.chain = next_chain(w.chain, T, slstm_picard_tile_steps(), &st->status);
+    return launch_slstm_picard(dtype, a, mode == 2, s) == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+}
+
+int prb_slstm_newton_pass(const void* wx, const float* r, const float* sin, const float* halo,
+                          const float* carry_in, void* sout, float* tail_out, float* agg_out, int mode,
+                          int B, int T, int d, int dtype, float omega, float eps, void* workspace,
+                          size_t workspace_bytes, prb_stats* stats, int hist_slot,
+                          prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!wx || !r || !sin || !stats || B < 1 || T < 1 || d < 1 || bad_dtype(dtype) || mode < 0 ||
+        mode > 2 || hist_slot < 0 || hist_slot >= kMaxIters)
+        return PRB_ERR_BAD_ARG;
+    if ((mode == 2 && !agg_out) || (mode != 2 && !sout)) return PRB_ERR_BAD_ARG;
+    PassWs w;
+    if (int e = pass_ws(kCellSlstmDiag, B, T, d, workspace, workspace_bytes, s, w)) return e;
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    SlstmNewtonArgs a{};
+    a.wx = wx;
+    a.r = r;
+    a.sin = sin;
+    a.halo = halo;
+    a.halo_stride = 4 * d;
+    a.carry_in = carry_in;
+    a.sout = sout;
+    a.tail_out = tail_out;
+    a.agg_out = agg_out;
+    a.resid_bits = &st->hist_bits[hist_slot];
+    a.B = B;
+    a.T = T;
+    a.d = d;
+    a.omega = omega;
+    a.eps = eps;
+    a.chain = next_chain(w.chain, T, slstm_tile_steps(), &st->status);
+    return launch_slstm_newton(dtype, a, mode == 1, mode == 2, s) == cudaSuccess ? PRB_OK
+                                                                                   : PRB_ERR_LAUNCH;
+}
+
+int prb_slstm_bwd_pass(const void* states, const void* wx, const float* r, const float* halo,
+                       const float* carry_in, const void* grad_states, void* g_wx, float* g_params,
+                       float* head_out, float* agg_out, int mode, int B, int T, int d, int dtype,
+                       float eps, void* workspace, size_t workspace_bytes, prb_stats* stats,
+                       prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!states || !wx || !r || !grad_states || !stats || B < 1 || T < 1 || d < 1 || bad_dtype(dtype) ||
+        (mode != 0 && mode != 2))
+        return PRB_ERR_BAD_ARG;
+    if ((mode == 2 && !agg_out) || (mode == 0 && (!g_wx || !g_params))) return PRB_ERR_BAD_ARG;
+    PassWs w;
+    if (int e = pass_ws(kCellSlstmDiag, B, T, d, workspace, workspace_bytes, s, w)) return e;
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    SlstmBwdArgs a{};
+    a.wx = wx;
+    a.states = states;
+    a.grad_states = grad_states;
+    a.r = r;
+    a.halo = halo;
+    a.halo_stride = 4 * d;
+    a.carry_in = carry_in;
+    a.g_wx = g_wx;
+    a.gp_partial = w.partial;
+    a.g_h0 = head_out;
+    a.agg_out = agg_out;
+    a.B = B;
+    a.T = T;
+    a.d = d;
+    a.eps = eps;
+    a.chain = next_chain(w.chain, T, slstm_tile_steps(), &st->status);
+    if (launch_slstm_bwd(dtype, a, mode == 2, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+    if (mode == 0 && launch_reduce_partials(w.partial, B * a.chain.n_tt, 4 * d, g_params, s) != cudaSuccess)
+        return PRB_ERR_LAUNCH;
+    return PRB_OK;
+}
+
+int prb_residual_pass(int cell, const void* wx, const float* params, const float* halo,
+                      const void* states, int states_f32, int B, int T, int d, int dtype, float eps,
+                      prb_stats* stats, prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!wx || !params || !states || !stats || B < 1 || T < 1 || d < 1 || bad_dtype(dtype))
+        return PRB_ERR_BAD_ARG;
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    cudaError_t e;
+    if (cell == kCellSlstmDiag)
+        e = launch_slstm_residual(dtype, states_f32 != 0, wx, params, halo, 4 * d, states, B, T, d, eps,
+                                  &st->final_bits, s);
+    else if (cell == kCellGruDiag || cell == kCellNlru)
+        e = launch_diag_residual(cell, dtype, states_f32 != 0, wx, params, halo, states, B, T, d,
+                                 &st->final_bits, s);
+    else
+        return PRB_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+}
+
+int prb_residual(int cell, const void* wx, const void* params, const void* h0, const void* states,
+                 int B, int T, int d, int dtype, float eps, void* workspace, size_t workspace_bytes,
+                 prb_stats* stats, prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!wx || !params || !states || !stats || B < 1 || T < 1 || d < 1 || bad_dtype(dtype))
+        return PRB_ERR_BAD_ARG;
+    const int np = cell == kCellGruDiag ? 3 : (cell == kCellNlru ? 1 : 4);
+    const int S = cell == kCellSlstmDiag ? 4 : 1;
+    if (cell != kCellGruDiag && cell != kCellNlru && cell != kCellSlstmDiag) return PRB_ERR_UNSUPPORTED;
+    Bump b(nullptr);
+    b.take<float>((size_t)np * d);
+    b.take<float>((size_t)B * S * d);
+    const size_t need = b.off + 256;
+    if (int e = check_ws(workspace, workspace_bytes, need)) return e;
+    Bump bb(workspace);
+    float* par = bb.take<float>((size_t)np * d);
+    float* h0buf = bb.take<float>((size_t)B * S * d);
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    cudaMemsetAsync(&st->final_bits, 0, sizeof(unsigned), s);
+    to_f32(params, par, (size_t)np * d, dtype, s);
+    const float* h0f = nullptr;
+    if (h0) {
+        to_f32(h0, h0buf, (size_t)B * S * d, dtype, s);
+        h0f = h0buf;
+    }
+    cudaError_t e;
+    if (cell == kCellSlstmDiag)
+        e = launch_slstm_residual(dtype, false, wx, par, h0f, 4 * d, states, B, T, d, eps, &st->final_bits, s);
+    else
+        e = launch_diag_residual(cell, dtype, false, wx, par, h0f, states, B, T, d, &st->final_bits, s);
+    return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+}
+
+}  // extern "C"

@@ -1,0 +1,118 @@
+// Internal launcher interface between the C ABI (capi.cu) and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+#include "common.cuh"
+
+namespace prb {
+
+enum Cell : int { kCellGruDiag = 0, kCellNlru = 1, kCellSlstmDiag = 2, kCellGruHead = 3 };
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+// ---- scalar-diagonal cells ------------------------------------------------
+struct DiagFwdArgs {
+    const void* wx;         // (B,T,G*d) I/O dtype
+    const float* par;       // clamped recurrent vectors, fp32 [NP][d]
+    const float* halo;      // (B,d) fp32 state preceding step 0 (h0), may be null = zeros
+    const float* carry_in;  // (B,d) fp32 delta entering step 0, may be null = zeros
+    const float* hin;       // (B,T,d) fp32 input trajectory (unused by the first pass)
+    void* hout;             // (B,T,d) fp32 work trajectory, or I/O dtype on the last pass
+    float* tail_out;        // (B,d) delta leaving the last step, may be null
+    float* agg_out;         // (B,2,d) shard aggregate (aggregate-only sweep)
+    unsigned* resid_bits;   // max|F| of the input trajectory (atomicMax target)
+    int B, T, d;
+    float omega;
+    Chain chain;
+};
+
+struct DiagBwdArgs {
+    const void* wx;           // (B,T,G*d)
+    const void* states;       // (B,T,d) converged trajectory, I/O dtype
+    const void* grad_states;  // (B,T,d) I/O dtype
+    const float* par;
+    const float* halo;      // (B,d) state preceding step 0
+    const float* carry_in;  // (B,d) nu entering the last step (from the next shard), may be null
+    void* g_wx;             // (B,T,G*d) I/O dtype
+    float* gp_partial;      // (B*n_tt, NP, d) per-tile parameter partial sums
+    float* g_h0;            // (B,d) nu leaving step 0 (= grad_h0 on the first shard), may be null
+    float* agg_out;         // (B,2,d)
+    float* mu_out;          // optional (B,T,d) fp32
+    int B, T, d;
+    Chain chain;
+};
+
+int diag_tile_steps();
+cudaError_t launch_diag_newton(int cell, int dtype, const DiagFwdArgs& a, bool first, bool last,
+                               cudaStream_t s);
+cudaError_t launch_diag_newton_agg(int cell, int dtype, const DiagFwdArgs& a, cudaStream_t s);
+cudaError_t launch_diag_guess(int cell, int dtype, bool out_f32, const void* wx, const float* par,
+                              const float* h0, void* out, int B, int T, int d, cudaStream_t s);
+cudaError_t launch_diag_residual(int cell, int dtype, bool st_f32, const void* wx, const float* par,
+                                 const float* halo, const void* st, int B, int T, int d,
+                                 unsigned* dst, cudaStream_t s);
+cudaError_t launch_diag_bwd(int cell, int dtype, const DiagBwdArgs& a, bool agg_only, cudaStream_t s);
+cudaError_t launch_reduce_partials(const float* part, int rows, int np_d, float* out, cudaStream_t s);
+
+// ---- ParaSLSTM mix='diag' ----------------------------------------------------
+struct SlstmPicardArgs {
+    const void* wx;        // (B,T,4d) I/O dtype, gate order (i,f,z,o)
+    const float* r;        // (4,d) fp32 clamped
+    const float* h_prev;   // (B,T,d) fp32 hidden trajectory of the previous pass; null = zero-hidden pass
+    const float* h_halo;   // (B,d) hidden state preceding step 0 for h_prev; null = zeros
+    const float* carry_in; // (c,n,m) entering step 0, slot stride d; null = zeros
+    float* h_out;          // (B,T,d) fp32 hidden only (not the last Picard pass)
+    float* state_out;      // (B,T,4,d) fp32 full state (last Picard pass), slots (c,n,m,h)
+    float* tail_out;       // (B,3,d) (c,n,m) leaving the last step, may be null
+    float* agg_out;        // (B,4,d) shard aggregate (a,b,N,C)
+    int halo_stride;       // batch stride (floats) of h_halo
+    int carry_stride;      // batch stride (floats) of carry_in, slots (c,n,m) d apart
+    int B, T, d;
+    float eps;
+    Chain chain;
+};
+
+struct SlstmNewtonArgs {
+    const void* wx;
+    const float* r;
+    const float* sin;       // (B,T,4,d) fp32 input trajectory
+    const float* halo;      // (B,4,d) state preceding step 0; null = zeros
+    const float* carry_in;  // (B,4,d) delta entering step 0; null = zeros
+    void* sout;             // (B,T,4,d) fp32, or I/O dtype on the last pass
+    float* tail_out;        // (B,4,d)
+    float* agg_out;         // (B,20,d)
+    unsigned* resid_bits;
+    int halo_stride;        // batch stride (floats) of halo
+    int B, T, d;
+    float omega, eps;
+    Chain chain;
+};
+
+struct SlstmBwdArgs {
+    const void* wx;
+    const void* states;       // (B,T,4,d) I/O dtype
+    const void* grad_states;  // (B,T,4,d) I/O dtype
+    const float* r;
+    const float* halo;      // (B,4,d)
+    const float* carry_in;  // (B,4,d) nu entering the last step
+    void* g_wx;             // (B,T,4d)
+    float* gp_partial;      // (B*n_tt,4,d)
+    float* g_h0;            // (B,4,d)
+    float* agg_out;         // (B,20,d)
+    int halo_stride;
+    int B, T, d;
+    float eps;
+    Chain chain;
+};
+
+int slstm_tile_steps();
+int slstm_picard_tile_steps();
+cudaError_t launch_slstm_picard(int dtype, const SlstmPicardArgs& a, bool agg_only, cudaStream_t s);
+cudaError_t launch_slstm_newton(int dtype, const SlstmNewtonArgs& a, bool last, bool agg_only,
+                                cudaStream_t s);
+cudaError_t launch_slstm_residual(int dtype, bool st_f32, const void* wx, const float* r,
+                                  const float* halo, int halo_stride, const void* st, int B, int T,
+                                  int d, float eps, unsigned* dst, cudaStream_t s);
+cudaError_t launch_slstm_bwd(int dtype, const SlstmBwdArgs& a, bool agg_only, cudaStream_t s);
+
+}  // namespace prb

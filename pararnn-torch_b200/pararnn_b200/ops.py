@@ -1,0 +1,334 @@
+"""Operators of the CUDA backend, one per fused op of the reference.
+
+Names, argument order and error behaviour follow the reference's custom ops
+(``pararnn::newton_gru_fused`` etc., reference ``kernels/custom_ops.py:146-540``)
+and its packed VJP functions (reference ``kernels/vjp_*.py``).  Each function
+validates its tensors, allocates outputs and scratch through PyTorch's caching
+allocator, and calls the C ABI on the current CUDA stream.  Nothing here computes
+on the host, and there is no fallback: without a CUDA device or without the built
+library the functions raise.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import struct
+
+import torch
+from torch import Tensor
+
+from . import _lib as L
+
+_DTYPES = {torch.float32: L.PRB_F32, torch.bfloat16: L.PRB_BF16}
+
+
+def _dtype_code(t: Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(
+            f"pararnn_b200 kernels take float32 or bfloat16 tensors, got {t.dtype}"
+        ) from None
+
+
+def _check_cuda(*tensors: Tensor | None) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(
+                "pararnn_b200 operators need CUDA tensors (this backend has no CPU path); "
+                f"got a tensor on {t.device}"
+            )
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"tensors on different devices: {dev} and {t.device}")
+    assert dev is not None
+    return dev
+
+
+def _ptr(t: Tensor | None):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _same(t: Tensor | None, ref: Tensor) -> Tensor | None:
+    """Contiguous copy in the I/O dtype of ``ref`` (the reference copies non-contiguous inputs)."""
+    if t is None:
+        return None
+    return t.detach().to(dtype=ref.dtype).contiguous()
+
+
+def _workspace(nbytes: int, device) -> Tensor:
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def _stream(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _raise(code: int, what: str) -> None:
+    if code == 0:
+        return
+    msg = f"{what}: {L.error_string(code)} (code {code})"
+    if code in (-1, -3, -5):
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+class DeviceStats:
+    """Handle on the device-side statistics block of one forward call."""
+
+    def __init__(self, device, max_iters: int):
+        self.buf = torch.zeros(L.STATS_BYTES, dtype=torch.uint8, device=device)
+        self.max_iters = int(max_iters)
+
+    def read(self) -> tuple[tuple[float, ...], float, int]:
+        """One small device-to-host copy: (residual_history, final max|F|, status)."""
+        raw = bytes(self.buf.cpu().numpy().tobytes())
+        hist = struct.unpack(f"<{L.MAX_ITERS}f", raw[: 4 * L.MAX_ITERS])
+        final = struct.unpack("<f", raw[4 * L.MAX_ITERS: 4 * L.MAX_ITERS + 4])[0]
+        status = struct.unpack("<i", raw[4 * L.MAX_ITERS + 4: 4 * L.MAX_ITERS + 8])[0]
+        return tuple(hist[: self.max_iters]), final, status
+
+
+def _reject_packed(cu_seqlens, block_table) -> None:
+    if cu_seqlens is not None:
+        raise NotImplementedError("packed cu_seqlens batches are not covered by the CUDA backend yet")
+    if block_table is not None:
+        raise NotImplementedError("block_table (paged h0) is not covered by the CUDA backend yet")
+
+
+def _check_iters(max_iters: int) -> None:
+    if not 0 <= int(max_iters) <= L.MAX_ITERS:
+        raise ValueError(f"max_iters must be in [0, {L.MAX_ITERS}], got {max_iters}")
+
+
+# ---------------------------------------------------------------------------- forward
+
+def newton_gru_fused(wx: Tensor, a_z: Tensor, a_r: Tensor, a_n: Tensor, h0: Tensor | None = None,
+                     cu_seqlens: Tensor | None = None, block_table: Tensor | None = None, *,
+                     max_iters: int, omega: float = 1.0, stats: DeviceStats | None = None,
+                     want_residual: bool = True) -> Tensor:
+    """Fused Newton for ``ParaGRU(mix='diag')``: ``wx (B,T,3d)`` -> ``H (B,T,d)`` in ``wx.dtype``."""
+    _reject_packed(cu_seqlens, block_table)
+    dev = _check_cuda(wx, a_z, a_r, a_n, h0)
+    _check_iters(max_iters)
+    if wx.dim() != 3 or wx.shape[-1] % 3:
+        raise ValueError(f"wx must be (B, T, 3*d), got {tuple(wx.shape)}")
+    B, T, d3 = wx.shape
+    d = d3 // 3
+    for name, p in (("a_z", a_z), ("a_r", a_r), ("a_n", a_n)):
+        if p.numel() != d:
+            raise ValueError(f"{name} must have {d} elements, got {tuple(p.shape)}")
+    if h0 is not None and tuple(h0.shape) != (B, d):
+        raise ValueError(f"h0 must be ({B}, {d}), got {tuple(h0.shape)}")
+    if T < 1:
+        raise ValueError("time must be >= 1")
+    code = _dtype_code(wx)
+    wx_c = wx.detach().contiguous()
+    az, ar, an, h0c = _same(a_z, wx), _same(a_r, wx), _same(a_n, wx), _same(h0, wx)
+    out = torch.empty(B, T, d, dtype=wx.dtype, device=dev)
+    st = stats or DeviceStats(dev, max_iters)
+    lib = L.lib()
+    with torch.cuda.device(dev):
+        nbytes = lib.prb_newton_workspace_bytes(L.CELL_GRU_DIAG, code, B, T, d, 1, max_iters, 0)
+        ws = _workspace(nbytes, dev)
+        rc = lib.prb_newton_gru_fused(_ptr(wx_c), _ptr(az), _ptr(ar), _ptr(an), _ptr(h0c), _ptr(out),
+                                      B, T, d, code, int(max_iters), float(omega),
+                                      int(want_residual), _ptr(ws), ws.numel(), _ptr(st.buf),
+                                      _stream(dev))
+    _raise(rc, "newton_gru_fused")
+    return out
+
+
+def newton_nlru_fused(wx: Tensor, u: Tensor, h0: Tensor | None = None,
+                      cu_seqlens: Tensor | None = None, block_table: Tensor | None = None, *,
+                      max_iters: int, omega: float = 1.0, stats: DeviceStats | None = None,
+                      want_residual: bool = True) -> Tensor:
+    """Fused Newton for ``ParaNLRU``: ``wx (B,T,2d)`` -> ``H (B,T,d)``."""
+    _reject_packed(cu_seqlens, block_table)
+    dev = _check_cuda(wx, u, h0)
+    _check_iters(max_iters)
+    if wx.dim() != 3 or wx.shape[-1] % 2:
+        raise ValueError(f"wx must be (B, T, 2*d), got {tuple(wx.shape)}")
+    B, T, d2 = wx.shape
+    d = d2 // 2
+    if u.numel() != d:
+        raise ValueError(f"u must have {d} elements, got {tuple(u.shape)}")
+    if h0 is not None and tuple(h0.shape) != (B, d):
+        raise ValueError(f"h0 must be ({B}, {d}), got {tuple(h0.shape)}")
+    if T < 1:
+        raise ValueError("time must be >= 1")
+    code = _dtype_code(wx)
+    wx_c = wx.detach().contiguous()
+    uc, h0c = _same(u, wx), _same(h0, wx)
+    out = torch.empty(B, T, d, dtype=wx.dtype, device=dev)
+    st = stats or DeviceStats(dev, max_iters)
+    lib = L.lib()
+    with torch.cuda.device(dev):
+        nbytes = lib.prb_newton_workspace_bytes(L.CELL_NLRU, code, B, T, d, 1, max_iters, 0)
+        ws = _workspace(nbytes, dev)
+        rc = lib.prb_newton_nlru_fused(_ptr(wx_c), _ptr(uc), _ptr(h0c), _ptr(out), B, T, d, code,
+                                       int(max_iters), float(omega), int(want_residual), _ptr(ws),
+                                       ws.numel(), _ptr(st.buf), _stream(dev))
+    _raise(rc, "newton_nlru_fused")
+    return out
+
+
+def newton_slstm_fused(wx: Tensor, r: Tensor, h0: Tensor | None = None,
+                       states: Tensor | None = None, block_table: Tensor | None = None, *,
+                       max_iters: int, omega: float = 1.0, eps: float = 1e-6,
+                       log_coords: bool = False, scan_tile: str = "assoc", time_loop: bool = False,
+                       window_len: int = 0, picard_iters: int = 0,
+                       stats: DeviceStats | None = None, want_residual: bool = True) -> Tensor:
+    """Fused Newton for ``ParaSLSTM(mix='diag')``: ``wx (B,T,4d)`` -> ``H (B,T,4,d)``.
+
+    ``states`` is an optional initial guess (cloned, never modified).  Without it the
+    kernel runs the zero-hidden frozen-gate scan followed by ``picard_iters`` Picard
+    passes itself (the reference does this in ``slstm_picard_init`` before calling its op).
+    """
+    _reject_packed(None, block_table)
+    if log_coords:
+        raise TypeError("coords='log' is not covered by the CUDA backend")
+    if scan_tile != "assoc" or time_loop or window_len:
+        raise TypeError("scan_tile / fused_time_loop / fused_window_len ablations are not available")
+    dev = _check_cuda(wx, r, h0, states)
+    _check_iters(max_iters)
+    if wx.dim() != 3 or wx.shape[-1] % 4:
+        raise ValueError(f"wx must be (B, T, 4*d), got {tuple(wx.shape)}")
+    B, T, d4 = wx.shape
+    d = d4 // 4
+    if tuple(r.shape) != (4, d):
+        raise ValueError(f"r must be (4, {d}), got {tuple(r.shape)}")
+    if h0 is not None and tuple(h0.shape) != (B, 4, d):
+        raise ValueError(f"h0 must be ({B}, 4, {d}), got {tuple(h0.shape)}")
+    if states is not None and tuple(states.shape) != (B, T, 4, d):
+        raise ValueError(f"states must be ({B}, {T}, 4, {d}), got {tuple(states.shape)}")
+    if T < 1:
+        raise ValueError("time must be >= 1")
+    if picard_iters < 0 or picard_iters + max_iters > 40:
+        raise ValueError("picard_iters out of range")
+    code = _dtype_code(wx)
+    wx_c = wx.detach().contiguous()
+    rc_, h0c, gc = _same(r, wx), _same(h0, wx), _same(states, wx)
+    out = torch.empty(B, T, 4, d, dtype=wx.dtype, device=dev)
+    st = stats or DeviceStats(dev, max_iters)
+    lib = L.lib()
+    with torch.cuda.device(dev):
+        nbytes = lib.prb_newton_workspace_bytes(L.CELL_SLSTM_DIAG, code, B, T, d, 1, max_iters,
+                                                int(picard_iters))
+        ws = _workspace(nbytes, dev)
+        rc = lib.prb_newton_slstm_fused(_ptr(wx_c), _ptr(rc_), _ptr(h0c), _ptr(gc), _ptr(out), B, T,
+                                        d, code, int(max_iters), int(picard_iters), float(omega),
+                                        float(eps), int(want_residual), _ptr(ws), ws.numel(),
+                                        _ptr(st.buf), _stream(dev))
+    _raise(rc, "newton_slstm_fused")
+    return out
+
+
+# ---------------------------------------------------------------------------- backward
+
+def _bwd_common(states, wx, grad_states, h0):
+    dev = _check_cuda(states, wx, grad_states, h0)
+    code = _dtype_code(wx)
+    st = states.detach().to(wx.dtype).contiguous()
+    gs = grad_states.detach().to(wx.dtype).contiguous()
+    return dev, code, st, wx.detach().contiguous(), gs, _same(h0, wx)
+
+
+def gru_reverse_vjp(states: Tensor, wx: Tensor, a_z: Tensor, a_r: Tensor, a_n: Tensor,
+                    grad_states: Tensor, h0: Tensor | None = None):
+    """Eq. 2.6 reverse scan fused with the packed GRU VJP.
+
+    Returns ``(g_wx, g_az, g_ar, g_an, g_h0)``; parameter grads are fp32 sums over batch and
+    time with no clip mask (the caller applies it, reference ``solvers/vjp.py:141-144``)."""
+    dev, code, st, wxc, gs, h0c = _bwd_common(states, wx, grad_states, h0)
+    B, T, d3 = wx.shape
+    d = d3 // 3
+    if tuple(states.shape) != (B, T, d) or tuple(grad_states.shape) != (B, T, d):
+        raise ValueError("states / grad_states must be (B, T, d)")
+    g_wx = torch.empty_like(wxc)
+    g_par = torch.empty(3, d, dtype=torch.float32, device=dev)
+    g_h0 = torch.empty(B, d, dtype=torch.float32, device=dev)
+    sb = DeviceStats(dev, 0)
+    az, ar, an = _same(a_z, wx), _same(a_r, wx), _same(a_n, wx)  # keep alive across the call
+    lib = L.lib()
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.prb_bwd_workspace_bytes(L.CELL_GRU_DIAG, code, B, T, d, 1), dev)
+        rc = lib.prb_bwd_gru(_ptr(st), _ptr(wxc), _ptr(az), _ptr(ar),
+                             _ptr(an), _ptr(h0c), _ptr(gs), _ptr(g_wx), _ptr(g_par),
+                             _ptr(g_h0), B, T, d, code, _ptr(ws), ws.numel(), _ptr(sb.buf),
+                             _stream(dev))
+    _raise(rc, "gru_reverse_vjp")
+    return g_wx, g_par[0], g_par[1], g_par[2], g_h0
+
+
+def nlru_reverse_vjp(states: Tensor, wx: Tensor, u: Tensor, grad_states: Tensor,
+                     h0: Tensor | None = None):
+    """Eq. 2.6 reverse scan fused with the packed NLRU VJP: ``(g_wx, g_u, g_h0)``."""
+    dev, code, st, wxc, gs, h0c = _bwd_common(states, wx, grad_states, h0)
+    B, T, d2 = wx.shape
+    d = d2 // 2
+    if tuple(states.shape) != (B, T, d) or tuple(grad_states.shape) != (B, T, d):
+        raise ValueError("states / grad_states must be (B, T, d)")
+    g_wx = torch.empty_like(wxc)
+    g_par = torch.empty(1, d, dtype=torch.float32, device=dev)
+    g_h0 = torch.empty(B, d, dtype=torch.float32, device=dev)
+    sb = DeviceStats(dev, 0)
+    uc = _same(u, wx)
+    lib = L.lib()
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.prb_bwd_workspace_bytes(L.CELL_NLRU, code, B, T, d, 1), dev)
+        rc = lib.prb_bwd_nlru(_ptr(st), _ptr(wxc), _ptr(uc), _ptr(h0c), _ptr(gs),
+                              _ptr(g_wx), _ptr(g_par), _ptr(g_h0), B, T, d, code, _ptr(ws),
+                              ws.numel(), _ptr(sb.buf), _stream(dev))
+    _raise(rc, "nlru_reverse_vjp")
+    return g_wx, g_par[0], g_h0
+
+
+def slstm_reverse_vjp(states: Tensor, wx: Tensor, r: Tensor, grad_states: Tensor,
+                      h0: Tensor | None = None, eps: float = 1e-6):
+    """Eq. 2.6 reverse scan (4x4 blocks, J^T) fused with the packed sLSTM VJP:
+    ``(g_wx (B,T,4d), g_r (4,d) fp32, g_h0 (B,4,d) fp32)``."""
+    dev, code, st, wxc, gs, h0c = _bwd_common(states, wx, grad_states, h0)
+    B, T, d4 = wx.shape
+    d = d4 // 4
+    if tuple(states.shape) != (B, T, 4, d) or tuple(grad_states.shape) != (B, T, 4, d):
+        raise ValueError("states / grad_states must be (B, T, 4, d)")
+    g_wx = torch.empty_like(wxc)
+    g_par = torch.empty(4, d, dtype=torch.float32, device=dev)
+    g_h0 = torch.empty(B, 4, d, dtype=torch.float32, device=dev)
+    sb = DeviceStats(dev, 0)
+    rc_ = _same(r, wx)
+    lib = L.lib()
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.prb_bwd_workspace_bytes(L.CELL_SLSTM_DIAG, code, B, T, d, 1), dev)
+        rc = lib.prb_bwd_slstm(_ptr(st), _ptr(wxc), _ptr(rc_), _ptr(h0c), _ptr(gs),
+                               _ptr(g_wx), _ptr(g_par), _ptr(g_h0), B, T, d, code, float(eps),
+                               _ptr(ws), ws.numel(), _ptr(sb.buf), _stream(dev))
+    _raise(rc, "slstm_reverse_vjp")
+    return g_wx, g_par, g_h0
+
+
+def residual_max(cell_code: int, wx: Tensor, params: Tensor, states: Tensor,
+                 h0: Tensor | None = None, eps: float = 1e-6) -> float:
+    """``max|f(H_{t-1}, x_t) - H_t|`` evaluated on the device (one host sync)."""
+    dev = _check_cuda(wx, params, states, h0)
+    code = _dtype_code(wx)
+    B, T = wx.shape[:2]
+    d = states.shape[-1]
+    sb = DeviceStats(dev, 0)
+    lib = L.lib()
+    with torch.cuda.device(dev):
+        ws = _workspace(1 << 20, dev)
+        need = (params.numel() + (0 if h0 is None else h0.numel())) * 4 + 4096
+        if need > ws.numel():
+            ws = _workspace(need, dev)
+        wxc, pc, h0c, stc = wx.detach().contiguous(), _same(params, wx), _same(h0, wx), _same(states, wx)
+        rc = lib.prb_residual(int(cell_code), _ptr(wxc), _ptr(pc),
+                              _ptr(h0c), _ptr(stc), B, T, d, code, float(eps),
+                              _ptr(ws), ws.numel(), _ptr(sb.buf), _stream(dev))
+    _raise(rc, "residual_max")
+    return sb.read()[1]

@@ -1,0 +1,97 @@
+"""Host-side mirror of the reference interface: configuration, cells, sequential unroll."""
+
+import numpy as np
+import pytest
+import torch
+
+import pararnn_b200 as prb
+from golden_util import golden_names, load_golden
+from oracle import oracle
+from pararnn_b200.config import resolve_max_iters, validate_config
+
+
+def _cell_from_golden(g):
+    d = g["params"].shape[-1] if g["cell"] != "gru_head" else g["W"].shape[0] // 3
+    d_in = g["W"].shape[1]
+    if g["cell"] == "gru_diag":
+        cell = prb.ParaGRU(d_in, d)
+        names = ("a_z", "a_r", "a_n")
+    elif g["cell"] == "gru_head":
+        cell = prb.ParaGRU(d_in, d, mix="head", n_heads=g["n_heads"])
+        names = ("A_z", "A_r", "A_n")
+    elif g["cell"] == "nlru":
+        cell = prb.ParaNLRU(d_in, d)
+        names = ("u",)
+    else:
+        cell = prb.ParaSLSTM(d_in, d, eps=g["eps"])
+        names = ("R",)
+    with torch.no_grad():
+        cell.W_x.weight.copy_(torch.from_numpy(g["W"]))
+        cell.W_x.bias.copy_(torch.from_numpy(g["b"]))
+        if names == ("R",):
+            cell.R.copy_(torch.from_numpy(g["raw_params"]))
+        else:
+            for n, v in zip(names, g["raw_params"]):
+                getattr(cell, n).copy_(torch.from_numpy(v))
+    return cell
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_sequential_apply_matches_reference(name):
+    g = load_golden(name)
+    cell = _cell_from_golden(g)
+    h0 = None if g["h0"] is None else torch.from_numpy(g["h0"])
+    with torch.no_grad():
+        H = prb.sequential_apply(cell, torch.from_numpy(g["x"]), h0).numpy()
+    scale = max(1.0, float(np.abs(g["H_seq"]).max()))
+    assert np.abs(H - g["H_seq"]).max() <= 2e-6 * scale
+
+
+def test_parameter_order_is_the_autograd_contract():
+    assert [n for n, _ in prb.ParaGRU(4, 8).named_parameters()] == ["a_z", "a_r", "a_n", "W_x.weight", "W_x.bias"]
+    assert [n for n, _ in prb.ParaGRU(4, 8, mix="head", n_heads=2).named_parameters()] == [
+        "A_z", "A_r", "A_n", "W_x.weight", "W_x.bias"]
+    assert [n for n, _ in prb.ParaNLRU(4, 8).named_parameters()] == ["u", "W_x.weight", "W_x.bias"]
+    assert [n for n, _ in prb.ParaSLSTM(4, 8).named_parameters()] == ["R", "W_x.weight", "W_x.bias"]
+
+
+def test_config_validation_errors():
+    for bad in (dict(scan_backend="nope"), dict(jacobian="x"), dict(coords="polar"), dict(chunk_len=0),
+                dict(max_iters=-1), dict(picard_iters=-2), dict(residual_fail=-1.0),
+                dict(newton_iters_by_t={64: 2}), dict(scan_tile="zig"),
+                dict(fused_window_len=64), dict(fused_early_exit=True, residual_atol=None)):
+        with pytest.raises(ValueError):
+            validate_config(prb.NewtonConfig(**bad))
+    validate_config(prb.NewtonConfig())
+    validate_config(prb.compile_safe_config())
+
+
+def test_resolve_max_iters_and_picard_ladder():
+    assert resolve_max_iters(prb.NewtonConfig(max_iters=None), 4096) == 3
+    cfg = prb.NewtonConfig(max_iters=None, newton_iters_by_t={64: 2, 1024: 3, 4096: 4})
+    assert [resolve_max_iters(cfg, t) for t in (64, 1000, 1024, 5000)] == [2, 2, 3, 4]
+    assert [prb.slstm_auto_picard(t) for t in (1, 64, 65, 2048, 2049)] == [1, 1, 3, 3, 5]
+    assert [prb.slstm_picard_next(p) for p in (0, 1, 3, 5)] == [1, 3, 5, None]
+
+
+def test_newton_apply_has_no_cpu_path():
+    cell = prb.ParaGRU(4, 8)
+    with pytest.raises(RuntimeError, match="no CPU solver"):
+        prb.newton_apply(cell, torch.randn(2, 5, 4))
+    with pytest.raises(TypeError, match="single CUDA"):
+        prb.newton_apply(cell, torch.randn(2, 5, 4), prb.NewtonConfig(scan_backend="eager"))
+    with pytest.raises(TypeError):
+        prb.newton_apply(cell, torch.randn(2, 5, 4), prb.NewtonConfig(picard_iters=2))
+
+
+def test_ops_reject_cpu_tensors():
+    from pararnn_b200 import ops
+
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.newton_nlru_fused(torch.randn(1, 4, 8), torch.randn(4), max_iters=1)
+
+
+def test_oracle_early_stop_counts_residual_evaluations():
+    g = load_golden("gru_diag_k3")
+    r = oracle.newton(oracle.GRU_DIAG, g["wx"], g["params"], max_iters=8, early_atol=1e-5)
+    assert r.iters < 8 and r.history[-1] < 1e-5 and all(h >= 1e-5 for h in r.history[:-1])
