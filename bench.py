@@ -336,7 +336,7 @@ def run_gpu_single(args):
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 4,
                 "ms_per_step": e2e_sec * 1e3,
                 "includes": "H2D of x, 3 W_x GEMMs (cuBLAS), Newton+scan fwd, reverse scan + VJP, D2H of loss"},
-        "gpu_launches": 13 * args.steps,
+        "gpu_launches": 12 * args.steps,
         "roofline": roofline,
         "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": "1 of 8 batch rows (rows are independent), full T=16384, d=1024, "

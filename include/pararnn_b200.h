@@ -48,7 +48,7 @@ enum {
 };
 #define PRB_MAX_ITERS 16
 
-/* Device-resident statistics block (64 bytes).  max|F| values are stored as the
+/* Device-resident statistics block (80 bytes).  max|F| values are stored as the
  * IEEE-754 bit pattern of a non-negative float (NaN sorts highest).
  * Replaces the host-side residual evaluation of the reference,
  * solvers/newton/__init__.py:582-636 (_fill_stats). */
@@ -183,6 +183,14 @@ int prb_slstm_bwd_pass(const void* states, const void* wx, const float* r, const
                        float* head_out, float* agg_out, int mode, int B, int T, int d, int dtype,
                        float eps, void* workspace, size_t workspace_bytes, prb_stats* stats,
                        prb_stream_t stream);
+
+/* Carry entering `rank` from the all-gathered per-rank slots (world, B, NV, d): the first
+ * rank in scan order (rank 0, or world-1 when reverse != 0) stores the exact carry leaving it
+ * in its first NS rows, every other rank its aggregate map.  monoid: 0 scalar affine
+ * (NV 2, NS 1), 1 4x4 affine (NV 20, NS 4), 2 sLSTM frozen-gate (NV 4, NS 3).  Replaces the
+ * serial fold of solvers/seq_parallel.py:185-191. */
+int prb_fold_carries(int monoid, const float* gathered, int rank, int world, int reverse,
+                     float* carry_out, int B, int d, prb_stream_t stream);
 
 /* residual of a shard with an fp32 halo; states fp32 (states_f32 != 0) or I/O dtype */
 int prb_residual_pass(int cell, const void* wx, const float* params, const float* halo,

@@ -162,6 +162,7 @@ int run_diag_fwd(int cell, const void* wx, const void* const* pars, const void* 
         a.hin = k > 0 ? p.buf[(k - 1) & 1] : nullptr;
         a.hout = (k == K - 1) ? out : (void*)p.buf[k & 1];
         a.resid_bits = &st->hist_bits[k];
+        a.final_bits = (want_residual && k == K - 1) ? &st->final_bits : nullptr;
         a.B = B;
         a.T = T;
         a.d = d;
@@ -169,7 +170,7 @@ int run_diag_fwd(int cell, const void* wx, const void* const* pars, const void* 
         a.chain = next_chain(p.chain, T, diag_tile_steps(), &st->status);
         if (launch_diag_newton(cell, dtype, a, k == 0, k == K - 1, s) != cudaSuccess) return PRB_ERR_LAUNCH;
     }
-    if (want_residual)
+    if (want_residual && K == 0)
         if (launch_diag_residual(cell, dtype, false, wx, p.par, h0f, out, B, T, d, &st->final_bits, s) !=
             cudaSuccess)
             return PRB_ERR_LAUNCH;
@@ -318,6 +319,7 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
         a.halo_stride = 4 * d;
         a.sout = (k == K - 1) ? out : (void*)p.sb[(k + 1) & 1];
         a.resid_bits = &st->hist_bits[k];
+        a.final_bits = (want_residual && k == K - 1) ? &st->final_bits : nullptr;
         a.B = B;
         a.T = T;
         a.d = d;
@@ -326,7 +328,7 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
         a.chain = next_chain(p.chain, T, slstm_tile_steps(), &st->status);
         if (launch_slstm_newton(dtype, a, k == K - 1, false, s) != cudaSuccess) return PRB_ERR_LAUNCH;
     }
-    if (want_residual)
+    if (want_residual && K == 0)
         if (launch_slstm_residual(dtype, false, wx, p.r, h0f, 4 * d, out, B, T, d, eps, &st->final_bits,
                                   s) != cudaSuccess)
             return PRB_ERR_LAUNCH;
@@ -350,6 +352,35 @@ SlstmBwdPlan plan_slstm_bwd(void* ws, int B, int T, int d) {
     p.partial = b.take<float>((size_t)B * p.chain.max_tt * 4 * d);
     p.total = b.off + 256;
     return p;
+}
+
+
+// Carry entering a rank of a time-sharded pass.  `gathered` holds one slot per rank
+// (slot stride nv*B*d floats): the first rank in scan order stores the exact carry leaving it
+// (ns floats per channel), every other rank its shard aggregate map (nv floats per channel).
+// carry(rank) = map(rank-1) o ... o map(first+1) applied to tail(first).
+template <class M>
+__global__ void fold_carries_kernel(const float* gathered, int rank, int world, int reverse, float* out,
+                                    int B, int d, int nv_slot) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= B * d) return;
+    const int b = idx / d, ch = idx % d;
+    const size_t slot = (size_t)nv_slot * B * d;
+    const int first = reverse ? world - 1 : 0;
+    const int step = reverse ? -1 : 1;
+    float vec[M::NS];
+    const float* p0 = gathered + (size_t)first * slot + (size_t)b * nv_slot * d + ch;
+#pragma unroll
+    for (int i = 0; i < M::NS; ++i) vec[i] = p0[(size_t)i * d];
+    for (int q = first + step; q != rank; q += step) {
+        float m[M::NV];
+        const float* p = gathered + (size_t)q * slot + (size_t)b * nv_slot * d + ch;
+#pragma unroll
+        for (int i = 0; i < M::NV; ++i) m[i] = p[(size_t)i * d];
+        M::apply(m, vec);
+    }
+#pragma unroll
+    for (int i = 0; i < M::NS; ++i) out[((size_t)b * M::NS + i) * d + ch] = vec[i];
 }
 
 }  // namespace
@@ -544,6 +575,7 @@ int prb_diag_newton_pass(int cell, const void* wx, const float* params, const fl
     a.tail_out = tail_out;
     a.agg_out = agg_out;
     a.resid_bits = &st->hist_bits[hist_slot];
+    a.final_bits = mode == 1 ? &st->final_bits : nullptr;
     a.B = B;
     a.T = T;
     a.d = d;
@@ -647,6 +679,7 @@ int prb_slstm_newton_pass(const void* wx, const float* r, const float* sin, cons
     a.tail_out = tail_out;
     a.agg_out = agg_out;
     a.resid_bits = &st->hist_bits[hist_slot];
+    a.final_bits = mode == 1 ? &st->final_bits : nullptr;
     a.B = B;
     a.T = T;
     a.d = d;
@@ -710,6 +743,24 @@ int prb_residual_pass(int cell, const void* wx, const float* params, const float
     else
         return PRB_ERR_UNSUPPORTED;
     return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+}
+
+int prb_fold_carries(int monoid, const float* gathered, int rank, int world, int reverse,
+                     float* carry_out, int B, int d, prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!gathered || !carry_out || B < 1 || d < 1 || world < 2 || rank < 0 || rank >= world)
+        return PRB_ERR_BAD_ARG;
+    if ((!reverse && rank == 0) || (reverse && rank == world - 1)) return PRB_ERR_BAD_ARG;
+    const int n = B * d, blk = 128, grid = (n + blk - 1) / blk;
+    if (monoid == 0)
+        fold_carries_kernel<Affine1><<<grid, blk, 0, s>>>(gathered, rank, world, reverse, carry_out, B, d, 2);
+    else if (monoid == 1)
+        fold_carries_kernel<Affine4><<<grid, blk, 0, s>>>(gathered, rank, world, reverse, carry_out, B, d, 20);
+    else if (monoid == 2)
+        fold_carries_kernel<PicardMonoid><<<grid, blk, 0, s>>>(gathered, rank, world, reverse, carry_out, B, d, 4);
+    else
+        return PRB_ERR_BAD_ARG;
+    return cudaGetLastError() == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
 
 int prb_residual(int cell, const void* wx, const void* params, const void* h0, const void* states,

@@ -4,6 +4,7 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <math_constants.h>
 #include <stdint.h>
 
 namespace prb {
@@ -289,6 +290,36 @@ struct Affine4 {
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = r[i];
+    }
+};
+
+// Summary monoid of the sLSTM frozen-gate (Picard) recurrence.
+// Frozen-gate recurrence on (c, n, m):  m' = max(zf + m, zi),
+// n' = exp(zf + m - m') n + exp(zi - m'),  c' likewise with tanh(zz).
+// A run of steps is summarised by (a, b, N, C):
+//   m_out = max(a + m_in, b)
+//   n_out = exp(a + m_in - m_out) n_in + exp(b - m_out) N      (c likewise with C)
+// with a = sum zf, b = max_s (zi_s + sum_{r>s} zf_r) and N, C normalised to b.
+struct PicardMonoid {
+    static constexpr int NV = 4, NS = 3;  // map (a,b,N,C); vec (c,n,m)
+    __device__ static __forceinline__ void compose(float (&acc)[4], const float (&nx)[4]) {
+        const float b1a = acc[1] + nx[0];
+        const float b = fmaxf(b1a, nx[1]);
+        const float s1 = (b1a > -CUDART_INF_F) ? expf(b1a - b) : 0.f;
+        const float s2 = (nx[1] > -CUDART_INF_F) ? expf(nx[1] - b) : 0.f;
+        acc[0] += nx[0];
+        acc[1] = b;
+        acc[2] = acc[2] * s1 + nx[2] * s2;
+        acc[3] = acc[3] * s1 + nx[3] * s2;
+    }
+    __device__ static __forceinline__ void apply(const float (&m)[4], float (&v)[3]) {
+        const float am = m[0] + v[2];
+        const float mo = fmaxf(am, m[1]);
+        const float s1 = expf(am - mo);
+        const float s2 = (m[1] > -CUDART_INF_F) ? expf(m[1] - mo) : 0.f;
+        v[0] = v[0] * s1 + m[3] * s2;
+        v[1] = v[1] * s1 + m[2] * s2;
+        v[2] = mo;
     }
 };
 

@@ -165,14 +165,24 @@ __global__ void __launch_bounds__(W * 32) diag_newton_kernel(DiagFwdArgs a) {
     float carry[1], tile_end[1];
     tile_exchange<Affine1, W>(a.chain, chain, tt, my_map, boundary, carry, smem, tile_end);
 
+    unsigned fmax = 0u;
+    const bool want_final = LAST && a.final_bits != nullptr;
     if (ch_ok) {
         if (LAST) {
+            // the residual of the returned trajectory is evaluated on the fp32 values before
+            // rounding; the new state preceding this sub-tile is old state + omega * carry
             TIO* out = reinterpret_cast<TIO*>(a.hout) + (size_t)b * a.T * a.d + ch;
+            float prev_new = fmaf(a.omega, carry[0], hold[0]);
 #pragma unroll
             for (int i = 0; i < L; ++i)
-                if (t0 + i < a.T)
-                    st_f(out + (size_t)(t0 + i) * a.d,
-                         fmaf(a.omega, fmaf(P[i], carry[0], D[i]), hold[i + 1]));
+                if (t0 + i < a.T) {
+                    const float nv = fmaf(a.omega, fmaf(P[i], carry[0], D[i]), hold[i + 1]);
+                    if (want_final) {
+                        fmax = max(fmax, absbits(C::step(prev_new, g[i], par) - nv));
+                        prev_new = nv;
+                    }
+                    st_f(out + (size_t)(t0 + i) * a.d, nv);
+                }
         } else {
             float* out = reinterpret_cast<float*>(a.hout) + (size_t)b * a.T * a.d + ch;
 #pragma unroll
@@ -184,6 +194,10 @@ __global__ void __launch_bounds__(W * 32) diag_newton_kernel(DiagFwdArgs a) {
             a.tail_out[(size_t)b * a.d + ch] = tile_end[0];
     }
     block_residual_max(rmax, a.resid_bits, s_red);
+    if (want_final) {
+        __syncthreads();
+        block_residual_max(fmax, a.final_bits, s_red);
+    }
 }
 
 // Aggregate-only sweep over a time shard: same linearisation, but the chain

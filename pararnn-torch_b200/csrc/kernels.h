@@ -21,6 +21,7 @@ struct DiagFwdArgs {
     float* tail_out;        // (B,d) delta leaving the last step, may be null
     float* agg_out;         // (B,2,d) shard aggregate (aggregate-only sweep)
     unsigned* resid_bits;   // max|F| of the input trajectory (atomicMax target)
+    unsigned* final_bits;   // last pass only: max|F| of the output trajectory, may be null
     int B, T, d;
     float omega;
     Chain chain;
@@ -82,6 +83,7 @@ struct SlstmNewtonArgs {
     float* tail_out;        // (B,4,d)
     float* agg_out;         // (B,20,d)
     unsigned* resid_bits;
+    unsigned* final_bits;   // last pass only: max|F| of the output trajectory, may be null
     int halo_stride;        // batch stride (floats) of halo
     int B, T, d;
     float omega, eps;

@@ -16,36 +16,6 @@
 namespace prb {
 
 // ------------------------------------------------------------------ Picard
-//
-// Frozen-gate recurrence on (c, n, m):  m' = max(zf + m, zi),
-// n' = exp(zf + m - m') n + exp(zi - m'),  c' likewise with tanh(zz).
-// A run of steps is summarised by (a, b, N, C):
-//   m_out = max(a + m_in, b)
-//   n_out = exp(a + m_in - m_out) n_in + exp(b - m_out) N      (c likewise with C)
-// with a = sum zf, b = max_s (zi_s + sum_{r>s} zf_r) and N, C normalised to b.
-struct PicardMonoid {
-    static constexpr int NV = 4, NS = 3;  // map (a,b,N,C); vec (c,n,m)
-    __device__ static __forceinline__ void compose(float (&acc)[4], const float (&nx)[4]) {
-        const float b1a = acc[1] + nx[0];
-        const float b = fmaxf(b1a, nx[1]);
-        const float s1 = (b1a > -CUDART_INF_F) ? expf(b1a - b) : 0.f;
-        const float s2 = (nx[1] > -CUDART_INF_F) ? expf(nx[1] - b) : 0.f;
-        acc[0] += nx[0];
-        acc[1] = b;
-        acc[2] = acc[2] * s1 + nx[2] * s2;
-        acc[3] = acc[3] * s1 + nx[3] * s2;
-    }
-    __device__ static __forceinline__ void apply(const float (&m)[4], float (&v)[3]) {
-        const float am = m[0] + v[2];
-        const float mo = fmaxf(am, m[1]);
-        const float s1 = expf(am - mo);
-        const float s2 = (m[1] > -CUDART_INF_F) ? expf(m[1] - mo) : 0.f;
-        v[0] = v[0] * s1 + m[3] * s2;
-        v[1] = v[1] * s1 + m[2] * s2;
-        v[2] = mo;
-    }
-};
-
 template <typename TIO, int L, int W, bool AGG>
 __global__ void __launch_bounds__(W * 32) slstm_picard_kernel(SlstmPicardArgs a) {
     using M = PicardMonoid;
@@ -340,6 +310,13 @@ __global__ void __launch_bounds__(W * 32) slstm_newton_kernel(SlstmNewtonArgs a)
     tile_exchange<Affine4, W>(a.chain, chain, tt, mp, boundary, carry, smem, tile_end);
 
     float xc = carry[0], xn = carry[1], xm = carry[2], xh = carry[3];
+    // On the last pass the residual of the RETURNED trajectory is evaluated here, on the fp32
+    // values before they are rounded to the I/O dtype: F(H^K)_t = f(H^K_{t-1}, x_t) - H^K_t,
+    // where H^K at the step before this sub-tile is the old state plus omega times the carry.
+    float pn4[4] = {fmaf(a.omega, xc, st[0][0]), fmaf(a.omega, xn, st[0][1]),
+                    fmaf(a.omega, xm, st[0][2]), fmaf(a.omega, xh, st[0][3])};
+    unsigned fmax = 0u;
+    const bool want_final = LAST && a.final_bits != nullptr;
 #pragma unroll
     for (int i = 0; i < L; ++i) {
         const int t = t0 + i;
@@ -347,6 +324,13 @@ __global__ void __launch_bounds__(W * 32) slstm_newton_kernel(SlstmNewtonArgs a)
         if (t < a.T && ch_ok) {
             const float o0 = fmaf(a.omega, xc, st[i + 1][0]), o1 = fmaf(a.omega, xn, st[i + 1][1]);
             const float o2 = fmaf(a.omega, xm, st[i + 1][2]), o3 = fmaf(a.omega, xh, st[i + 1][3]);
+            if (want_final) {
+                float pred[4];
+                slstm_predict(pn4, w[i], r4, a.eps, pred);
+                fmax = max(fmax, max(max(absbits(pred[0] - o0), absbits(pred[1] - o1)),
+                                     max(absbits(pred[2] - o2), absbits(pred[3] - o3))));
+                pn4[0] = o0; pn4[1] = o1; pn4[2] = o2; pn4[3] = o3;
+            }
             if (LAST) {
                 TIO* o = reinterpret_cast<TIO*>(a.sout) + ((size_t)b * a.T + t) * 4 * d + ch;
                 st_f(o, o0);
@@ -367,6 +351,10 @@ __global__ void __launch_bounds__(W * 32) slstm_newton_kernel(SlstmNewtonArgs a)
         for (int q = 0; q < 4; ++q) a.tail_out[((size_t)b * 4 + q) * d + ch] = tile_end[q];
     }
     block_residual_max(rmax, a.resid_bits, s_red);
+    if (want_final) {
+        __syncthreads();
+        block_residual_max(fmax, a.final_bits, s_red);
+    }
 }
 
 // ------------------------------------------------------------------ residual

@@ -73,7 +73,11 @@ def test_picard_guess_matches_oracle(P):
     wx, r, h0 = make_problem("slstm_diag", 2, 300, 40, seed=P, h0=True, rec_scale=2.0)
     want = oracle.guess(oracle.SLSTM_DIAG, wx, r, h0, picard=P)
     H, _, _ = _fwd(wx, r, h0, 0, P)
-    _check_states(H, want, 1.0)
+    # the warm start is a guess, not a fixed point: the chained (a, b, N, C) summaries and the
+    # reference's cumsum / cummax formulation round differently over hundreds of steps
+    for slot in range(4):
+        scale = max(1.0, np.abs(want[:, :, slot]).max())
+        assert np.abs(H[:, :, slot] - want[:, :, slot]).max() <= 3e-5 * scale
 
 
 SHAPES = [(1, 1, 1), (2, 2, 5), (1, 31, 33), (2, 32, 32), (3, 33, 31), (2, 127, 70), (2, 129, 64),
@@ -82,10 +86,15 @@ SHAPES = [(1, 1, 1), (2, 2, 5), (1, 31, 33), (2, 32, 32), (3, 33, 31), (2, 127, 
 
 @pytest.mark.parametrize("B,T,d", SHAPES)
 def test_forward_seeded_vs_oracle_fp32(B, T, d):
+    # short sequences: a stress setting where Newton does the work; long sequences: a milder
+    # one (the stress setting leaves the Newton basin beyond a few hundred steps)
+    stress = T <= 129
     wx, r, h0 = make_problem("slstm_diag", B, T, d, seed=B * 1000 + T + d, h0=(T % 2 == 1),
-                             x_scale=0.7, rec_scale=1.5)
-    want = oracle.newton(oracle.SLSTM_DIAG, wx, r, h0, max_iters=3, picard=2)
-    H, hist, res = _fwd(wx, r, h0, 3, 2)
+                             x_scale=0.7 if stress else 0.6, rec_scale=1.5 if stress else 1.2,
+                             bias_f=0.0 if stress else 1.0)
+    P = 2 if stress else 3
+    want = oracle.newton(oracle.SLSTM_DIAG, wx, r, h0, max_iters=3, picard=P)
+    H, hist, res = _fwd(wx, r, h0, 3, P)
     amp = max(1.0, max(want.history))
     _check_states(H, want.states, amp)
     scale = max(1.0, float(np.abs(want.states).max()))
@@ -109,11 +118,13 @@ def test_forget_bias_config_shape_family():
 
 
 def test_states_guess_argument_replaces_picard():
-    wx, r, h0 = make_problem("slstm_diag", 2, 200, 24, seed=4, x_scale=0.7)
+    wx, r, h0 = make_problem("slstm_diag", 2, 200, 24, seed=4, x_scale=0.5, bias_f=1.0)
     guess = oracle.guess(oracle.SLSTM_DIAG, wx, r, None, picard=1)
-    a, _, _ = _fwd(wx, r, None, 2, 1)
-    b, _, _ = _fwd(wx, r, None, 2, 0, guess=guess)
-    assert np.abs(a - b).max() <= 1e-5
+    a, ha, _ = _fwd(wx, r, None, 3, 1)
+    b, hb, _ = _fwd(wx, r, None, 3, 0, guess=guess)
+    assert ha[-1] < 1e-3 and hb[-1] < 1e-3
+    assert np.abs(a[:, :, 3] - b[:, :, 3]).max() <= 1e-5
+    assert np.abs(a - b).max() <= 4e-6 * np.abs(a).max()
 
 
 @pytest.mark.parametrize("B,T,d", [(1, 1, 3), (2, 33, 31), (2, 513, 70), (1, 3000, 64)])
