@@ -197,6 +197,35 @@ int prb_residual_pass(int cell, const void* wx, const float* params, const float
                       const void* states, int states_f32, int B, int T, int d, int dtype, float eps,
                       prb_stats* stats, prb_stream_t stream);
 
+/* ---- entry point that allocates nothing ------------------------------------------------
+ * No counterpart in the reference (its ops allocate scratch through PyTorch on every call).
+ *
+ * prb_bwd_nlru_static is prb_bwd_nlru without the workspace argument: its scratch (chain
+ * flags, tile aggregates, fp32 copies of u and h0, per-tile parameter partials) lives in a
+ * fixed array of PRB_STATIC_SCRATCH_BYTES inside the library.  It is meant for callers that
+ * must not, or cannot, obtain device memory at the point of the call: code running inside a
+ * region where the allocator is off limits (a real-time or interrupt-like service loop, a
+ * host callback, a plugin whose host owns all device memory and hands out none), or a
+ * process whose memory budget was fixed at start-up.  The function and everything it calls
+ * use no cudaMalloc / cudaFree and no allocating library routine; the caller still passes
+ * every input and output buffer, including the prb_stats block.
+ *
+ * Limits and rules
+ *   - the problem must satisfy prb_bwd_workspace_bytes(PRB_CELL_NLRU, ...) <=
+ *     PRB_STATIC_SCRATCH_BYTES (8 MiB); larger shapes return PRB_ERR_TOO_LARGE and launch
+ *     nothing;
+ *   - every GPU that loads the library holds the 8 MiB until the process exits;
+ *   - the first call on each device looks up the array's device address (with that device
+ *     current) and remembers it; make that first call outside any stream capture;
+ *   - all calls on a device share the one array and it keeps whatever the last call left in
+ *     it: the call re-clears what has to start at zero, but two calls whose GPU work can
+ *     overlap (different streams, or two host threads) race on it.  Serialise them. */
+#define PRB_STATIC_SCRATCH_BYTES (8u << 20)
+size_t prb_static_scratch_bytes(void);
+int prb_bwd_nlru_static(const void* states, const void* wx, const void* u, const void* h0,
+                        const void* grad_states, void* g_wx, float* g_params, float* g_h0, int B,
+                        int T, int d, int dtype, prb_stats* stats, prb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -796,4 +796,49 @@ int prb_residual(int cell, const void* wx, const void* params, const void* h0, c
     return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
 
+
+/* ---- entry point that allocates nothing ---------------------------------------------- */
+
+// Scratch for prb_bwd_nlru_static.  It is part of the library image: every GPU whose
+// context loads this library carries these bytes until the process exits.  In host code the
+// name `g_static_scratch` is only a handle for cudaGetSymbolAddress; the address that
+// kernels may dereference is the one that call returns for the current device.
+static __device__ __align__(256) unsigned char g_static_scratch[PRB_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};
+
+// Device address of the static scratch on the current device, resolved once per device.
+int static_scratch_address(void** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return PRB_ERR_LAUNCH;
+    if (!g_static_scratch_addr[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) return PRB_ERR_LAUNCH;
+        g_static_scratch_addr[dev] = p;
+    }
+    *out = g_static_scratch_addr[dev];
+    return PRB_OK;
+}
+}  // namespace
+
+size_t prb_static_scratch_bytes(void) { return PRB_STATIC_SCRATCH_BYTES; }
+
+int prb_bwd_nlru_static(const void* states, const void* wx, const void* u, const void* h0,
+                        const void* grad_states, void* g_wx, float* g_params, float* g_h0, int B,
+                        int T, int d, int dtype, prb_stats* stats, prb_stream_t stream) {
+    if (B < 1 || T < 1 || d < 1) return PRB_ERR_BAD_ARG;
+    // the same layout the workspace-taking entry point uses; refuse what does not fit
+    if (plan_diag_bwd(nullptr, kCellNlru, B, T, d).total > PRB_STATIC_SCRATCH_BYTES)
+        return PRB_ERR_TOO_LARGE;
+    void* scratch = nullptr;
+    if (int e = static_scratch_address(&scratch)) return e;
+    // run_diag_bwd clears the chain flags, the ticket counters and the statistics block before
+    // the kernels start; everything else in the scratch is written before it is read.
+    const void* pars[3] = {u, nullptr, nullptr};
+    return run_diag_bwd(kCellNlru, states, wx, pars, h0, grad_states, g_wx, g_params, g_h0, B, T, d,
+                        dtype, scratch, PRB_STATIC_SCRATCH_BYTES, stats, (cudaStream_t)stream);
+}
+
 }  // extern "C"

@@ -46,6 +46,8 @@ _SIGNATURES = {
     "prb_slstm_newton_pass": (_INT, [_VOIDP] * 8 + [_INT] * 5 + [_FLOAT, _FLOAT, _VOIDP, _SIZE, _VOIDP, _INT, _VOIDP]),
     "prb_slstm_bwd_pass": (_INT, [_VOIDP] * 10 + [_INT] * 5 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_fold_carries": (_INT, [_INT, _VOIDP, _INT, _INT, _INT, _VOIDP, _INT, _INT, _VOIDP]),
+    "prb_static_scratch_bytes": (_SIZE, []),
+    "prb_bwd_nlru_static": (_INT, [_VOIDP] * 8 + [_INT] * 4 + [_VOIDP, _VOIDP]),
     "prb_residual_pass": (_INT, [_INT] + [_VOIDP] * 4 + [_INT] * 5 + [_FLOAT, _VOIDP, _VOIDP]),
 }
 
