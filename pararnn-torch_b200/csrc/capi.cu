@@ -4,6 +4,7 @@
 // diag_kernels.cu and slstm_kernels.cu.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <stdlib.h>
 
 #include "../../include/pararnn_b200.h"
 #include "kernels.h"
@@ -95,6 +96,17 @@ void from_f32(const float* src, void* dst, size_t n, int dtype, cudaStream_t s) 
         cvt_from_f32_kernel<float><<<blocks, 256, 0, s>>>(src, (float*)dst, n);
     else
         cvt_from_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(src, (__nv_bfloat16*)dst, n);
+}
+
+// Kernel family for a sLSTM pass: the persistent-chain kernels need enough independent chains
+// to fill the GPU (one CTA per chain) and TMA-compatible strides.  PRB_KERNEL_PATH=persist or
+// =lookback overrides the choice (used by the tests to cover both families on small shapes).
+bool use_persist(int dtype, int B, int T, int d) {
+    const char* env = getenv("PRB_KERNEL_PATH");
+    if (env && env[0] == 'l') return false;
+    if (!slstm_persist_ok(dtype, B, T, d)) return false;
+    if (env && env[0] == 'p') return true;
+    return B * ((d + kLanes - 1) / kLanes) >= 96;
 }
 
 bool bad_dtype(int dtype) { return dtype != kF32 && dtype != kBF16; }
@@ -285,6 +297,7 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
         h0f = p.h0;
     }
     const size_t nst = (size_t)B * T * 4 * d;
+    const bool persist = use_persist(dtype, B, T, d);
     if (guess) {
         to_f32(guess, p.sb[0], nst, dtype, s);
     } else {
@@ -306,7 +319,9 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
             a.d = d;
             a.eps = eps;
             a.chain = next_chain(p.chain, T, slstm_picard_tile_steps(), &st->status);
-            if (launch_slstm_picard(dtype, a, false, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+            cudaError_t e = persist ? launch_slstm_picard_persist(dtype, a, s) : cudaErrorNotSupported;
+            if (e == cudaErrorNotSupported) e = launch_slstm_picard(dtype, a, false, s);
+            if (e != cudaSuccess) return PRB_ERR_LAUNCH;
         }
     }
     if (K == 0) from_f32(p.sb[0], out, nst, dtype, s);
@@ -326,7 +341,9 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
         a.omega = omega;
         a.eps = eps;
         a.chain = next_chain(p.chain, T, slstm_tile_steps(), &st->status);
-        if (launch_slstm_newton(dtype, a, k == K - 1, false, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+        cudaError_t e = persist ? launch_slstm_newton_persist(dtype, a, k == K - 1, s) : cudaErrorNotSupported;
+        if (e == cudaErrorNotSupported) e = launch_slstm_newton(dtype, a, k == K - 1, false, s);
+        if (e != cudaSuccess) return PRB_ERR_LAUNCH;
     }
     if (want_residual && K == 0)
         if (launch_slstm_residual(dtype, false, wx, p.r, h0f, 4 * d, out, B, T, d, eps, &st->final_bits,
@@ -502,8 +519,12 @@ int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void*
     a.d = d;
     a.eps = eps;
     a.chain = next_chain(p.chain, T, slstm_tile_steps(), &st->status);
-    if (launch_slstm_bwd(dtype, a, false, s) != cudaSuccess) return PRB_ERR_LAUNCH;
-    if (launch_reduce_partials(p.partial, B * a.chain.n_tt, 4 * d, g_params, s) != cudaSuccess)
+    int rows = B * a.chain.n_tt;
+    cudaError_t e = use_persist(dtype, B, T, d) ? launch_slstm_bwd_persist(dtype, a, s) : cudaErrorNotSupported;
+    if (e == cudaSuccess) rows = B;  // the persistent kernel writes one partial per batch row
+    if (e == cudaErrorNotSupported) e = launch_slstm_bwd(dtype, a, false, s);
+    if (e != cudaSuccess) return PRB_ERR_LAUNCH;
+    if (launch_reduce_partials(p.partial, rows, 4 * d, g_params, s) != cudaSuccess)
         return PRB_ERR_LAUNCH;
     return PRB_OK;
 }
@@ -652,7 +673,10 @@ int prb_slstm_picard_pass(const void* wx, const float* r, const float* h_prev, c
     a.d = d;
     a.eps = eps;
     a.chain = next_chain(w.chain, T, slstm_picard_tile_steps(), &st->status);
-    return launch_slstm_picard(dtype, a, mode == 2, s) == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+    cudaError_t e = (mode == 0 && use_persist(dtype, B, T, d)) ? launch_slstm_picard_persist(dtype, a, s)
+                                                                : cudaErrorNotSupported;
+    if (e == cudaErrorNotSupported) e = launch_slstm_picard(dtype, a, mode == 2, s);
+    return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
 
 int prb_slstm_newton_pass(const void* wx, const float* r, const float* sin, const float* halo,
@@ -686,8 +710,11 @@ int prb_slstm_newton_pass(const void* wx, const float* r, const float* sin, cons
     a.omega = omega;
     a.eps = eps;
     a.chain = next_chain(w.chain, T, slstm_tile_steps(), &st->status);
-    return launch_slstm_newton(dtype, a, mode == 1, mode == 2, s) == cudaSuccess ? PRB_OK
-                                                                                   : PRB_ERR_LAUNCH;
+    cudaError_t e = (mode != 2 && use_persist(dtype, B, T, d))
+                        ? launch_slstm_newton_persist(dtype, a, mode == 1, s)
+                        : cudaErrorNotSupported;
+    if (e == cudaErrorNotSupported) e = launch_slstm_newton(dtype, a, mode == 1, mode == 2, s);
+    return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
 
 int prb_slstm_bwd_pass(const void* states, const void* wx, const float* r, const float* halo,
@@ -720,8 +747,13 @@ int prb_slstm_bwd_pass(const void* states, const void* wx, const float* r, const
     a.d = d;
     a.eps = eps;
     a.chain = next_chain(w.chain, T, slstm_tile_steps(), &st->status);
-    if (launch_slstm_bwd(dtype, a, mode == 2, s) != cudaSuccess) return PRB_ERR_LAUNCH;
-    if (mode == 0 && launch_reduce_partials(w.partial, B * a.chain.n_tt, 4 * d, g_params, s) != cudaSuccess)
+    int rows = B * a.chain.n_tt;
+    cudaError_t e = (mode == 0 && use_persist(dtype, B, T, d)) ? launch_slstm_bwd_persist(dtype, a, s)
+                                                                : cudaErrorNotSupported;
+    if (e == cudaSuccess) rows = B;
+    if (e == cudaErrorNotSupported) e = launch_slstm_bwd(dtype, a, mode == 2, s);
+    if (e != cudaSuccess) return PRB_ERR_LAUNCH;
+    if (mode == 0 && launch_reduce_partials(w.partial, rows, 4 * d, g_params, s) != cudaSuccess)
         return PRB_ERR_LAUNCH;
     return PRB_OK;
 }

@@ -117,4 +117,10 @@ cudaError_t launch_slstm_residual(int dtype, bool st_f32, const void* wx, const 
                                   int d, float eps, unsigned* dst, cudaStream_t s);
 cudaError_t launch_slstm_bwd(int dtype, const SlstmBwdArgs& a, bool agg_only, cudaStream_t s);
 
+// persistent-chain variants (slstm_persist.cu); cudaErrorNotSupported when TMA rules are not met
+bool slstm_persist_ok(int dtype, int B, int T, int d);
+cudaError_t launch_slstm_picard_persist(int dtype, const SlstmPicardArgs& a, cudaStream_t s);
+cudaError_t launch_slstm_newton_persist(int dtype, const SlstmNewtonArgs& a, bool last, cudaStream_t s);
+cudaError_t launch_slstm_bwd_persist(int dtype, const SlstmBwdArgs& a, cudaStream_t s);
+
 }  // namespace prb
