@@ -302,10 +302,13 @@ def run_gpu_single(args):
         loss_host.copy_(loss.detach(), non_blocking=True)
         cell.zero_grad(set_to_none=True)
 
-    for _ in range(2):
-        e2e_step()
-    e2e_steps = max(2, min(args.steps, 5))
-    e2e_sec = time_region(e2e_step, e2e_steps, None) / e2e_steps
+    if args.no_e2e:
+        e2e_sec = float("nan")
+    else:
+        for _ in range(2):
+            e2e_step()
+        e2e_steps = max(2, min(args.steps, 5))
+        e2e_sec = time_region(e2e_step, e2e_steps, None) / e2e_steps
 
     # per-kernel rooflines
     states_io = keep["H"]
@@ -323,9 +326,12 @@ def run_gpu_single(args):
 
     # CPU baseline on a bounded sample (rank 0, N = 1 only)
     threads = os.cpu_count() or 1
-    sample = cpu_sample()
-    cpu_sec, cpu_res = cpu_step(sample, threads)
-    cpu_value = T_PER_GPU / cpu_sec
+    if args.no_cpu:
+        cpu_value = float("nan")
+    else:
+        sample = cpu_sample()
+        cpu_sec, cpu_res = cpu_step(sample, threads)
+        cpu_value = T_PER_GPU / cpu_sec
 
     line = {
         "metric": "newton_scan_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": 1,
@@ -347,12 +353,18 @@ def run_gpu_single(args):
 
 
 def main():
+    global T_PER_GPU
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--seq-len", type=int, default=T_PER_GPU,
+                    help="time steps per GPU (profiling captures use a smaller case)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg")
     args = ap.parse_args()
+    T_PER_GPU = args.seq_len
     if args.impl == "reference":
         run_reference_arm(args)
         return

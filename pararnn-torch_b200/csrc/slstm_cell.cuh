@@ -10,6 +10,7 @@ struct SlstmLin {
     // structured Jacobian pieces of one step
     float f, jcm, jch, jnm, jnh, alpha, dm, ia, ib, ie;
     float pc, pn, pm, ph;  // prediction f(H_{t-1}, x_t)
+    float it, z, og, invD;  // gate activations (used by the reverse kernels)
 };
 
 __device__ __forceinline__ void slstm_linearize(const float (&prev)[4], const float (&w)[4],
@@ -21,14 +22,20 @@ __device__ __forceinline__ void slstm_linearize(const float (&prev)[4], const fl
     const float mn = fmaxf(left, zi);
     const float alpha = left > zi ? 1.f : (left == zi ? 0.5f : 0.f);
     const float beta = 1.f - alpha;
-    const float it = expf(zi - mn);
-    const float ft = expf(left - mn);
+    // one of the two exponentials is exp(0) = 1 exactly
+    const float e_ = exp_f(-fabsf(left - zi));
+    const float it = left >= zi ? e_ : 1.f;
+    const float ft = left >= zi ? 1.f : e_;
     const float z = tanh_f(zz);
     const float og = sigmoid_f(zo);
     const float nn = fmaf(ft, n, it);
     const float cn = fmaf(ft, c, it * z);
-    const float invD = __frcp_rn(nn + eps);
+    const float invD = rcp_f(nn + eps);
     const float u = cn * invD;  // c_new / D
+    o.it = it;
+    o.z = z;
+    o.og = og;
+    o.invD = invD;
     o.pc = cn;
     o.pn = nn;
     o.pm = mn;
@@ -56,15 +63,17 @@ __device__ __forceinline__ void slstm_predict(const float (&prev)[4], const floa
     const float zz = fmaf(r[2], h, w[2]), zo = fmaf(r[3], h, w[3]);
     const float left = zf + m;
     const float mn = fmaxf(left, zi);
-    const float it = expf(zi - mn);
-    const float ft = expf(left - mn);
+    // one of the two exponentials is exp(0) = 1 exactly
+    const float e_ = exp_f(-fabsf(left - zi));
+    const float it = left >= zi ? e_ : 1.f;
+    const float ft = left >= zi ? 1.f : e_;
     const float z = tanh_f(zz);
     const float nn = fmaf(ft, n, it);
     const float cn = fmaf(ft, c, it * z);
     pred[0] = cn;
     pred[1] = nn;
     pred[2] = mn;
-    pred[3] = sigmoid_f(zo) * (cn * __frcp_rn(nn + eps));
+    pred[3] = sigmoid_f(zo) * (cn * rcp_f(nn + eps));
 }
 
 // x <- J x + F  for the state ordering (c, n, m, h); fh2 = Fh - ia*Fc - ib*Fn

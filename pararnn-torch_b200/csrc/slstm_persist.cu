@@ -372,7 +372,7 @@ slstm_picard_persist_kernel(const __grid_constant__ CUtensorMap tm_wx,
         for (int i = 0; i < L; ++i) {
             if (t0 + i < a.T) {
                 const float b1a = mp[1] + zf[i];
-                const float e = expf(-fabsf(b1a - zi[i]));
+                const float e = exp_f(-fabsf(b1a - zi[i]));
                 const bool left = b1a >= zi[i];
                 const float s1 = left ? 1.f : e, s2 = left ? e : 1.f;
                 mp[0] += zf[i];
@@ -412,13 +412,13 @@ slstm_picard_persist_kernel(const __grid_constant__ CUtensorMap tm_wx,
             const int t = t0 + i;
             if (t < a.T) {
                 const float left = zf[i] + m;
-                const float e = expf(-fabsf(left - zi[i]));
+                const float e = exp_f(-fabsf(left - zi[i]));
                 const bool lw = left >= zi[i];
                 const float ft = lw ? 1.f : e, it = lw ? e : 1.f;
                 m = lw ? left : zi[i];
                 n = fmaf(ft, n, it);
                 c = fmaf(ft, c, it * zz[i]);
-                const float h = sigmoid_f(zo[i]) * (c / (n + a.eps));
+                const float h = sigmoid_f(zo[i]) * (c * rcp_f(n + a.eps));
                 if (ch_ok) {
                     if (a.state_out) {
                         float* o = a.state_out + ((size_t)b * a.T + t) * 4 * d + ch;
@@ -553,16 +553,13 @@ slstm_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid
             SlstmLin lin;
             slstm_linearize(prev, w, r4, a.eps, lin);
             {
-                const float zi = fmaf(r4[0], prev[3], w[0]), zf = fmaf(r4[1], prev[3], w[1]);
-                const float left = zf + prev[2];
-                const float mn = fmaxf(left, zi);
-                act[i].i = expf(zi - mn);
+                act[i].i = lin.it;
                 act[i].f = lin.f;
-                act[i].z = tanh_f(fmaf(r4[2], prev[3], w[2]));
-                act[i].o = sigmoid_f(fmaf(r4[3], prev[3], w[3]));
+                act[i].z = lin.z;
+                act[i].o = lin.og;
                 act[i].c = prev[0];
                 act[i].n = prev[1];
-                act[i].invD = __frcp_rn(lin.pn + a.eps);
+                act[i].invD = lin.invD;
                 act[i].alpha = lin.alpha;
                 act[i].hp = prev[3];
             }

@@ -1,0 +1,372 @@
+"""Time-sharded (sequence-parallel) Newton solve: each rank owns a contiguous time shard of
+``x`` / ``wx`` / ``H`` and only per-shard scan carries cross ranks.
+
+Counterpart of the reference's context-parallel scan (reference
+``solvers/seq_parallel.py:126-342``), which exists for the scalar monoid only, keeps ``H``
+replicated and all-gathers the full update every iteration.  Here every cell and every pass type
+is sharded, trajectories stay sharded, and one pass costs one small all-gather:
+
+* the first rank in scan direction knows the carry entering its shard and sweeps once;
+* every other rank first runs an aggregate-only sweep (mode 2 of the pass-level C ABI) that
+  yields the affine map of its whole shard, the maps are all-gathered, ``prb_fold_carries`` turns
+  them into the carry entering the rank, and a second sweep applies it.
+
+The per-rank algorithm is written as a generator that yields its collectives.  ``DistComm``
+fulfils them with ``torch.distributed`` (one process per GPU); ``run_lockstep`` fulfils them for
+several ranks inside one process, which is how the multi-rank path is tested on a single GPU and,
+with a CPU stand-in for the local kernels, on CPU.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+from torch import Tensor
+
+
+def time_shard_bounds(time: int, rank: int, world_size: int) -> tuple[int, int]:
+    """Contiguous ``[start, end)``; the last rank takes the remainder (reference convention,
+    ``solvers/seq_parallel.py:126-138``)."""
+    if world_size < 1:
+        raise ValueError(f"world_size must be >= 1, got {world_size}")
+    if not 0 <= rank < world_size:
+        raise ValueError(f"rank={rank} outside [0, {world_size})")
+    if time < 0:
+        raise ValueError(f"time must be >= 0, got {time}")
+    base = time // world_size
+    if rank < world_size - 1:
+        return rank * base, (rank + 1) * base
+    return (world_size - 1) * base, time
+
+
+# ------------------------------------------------------------------------------- comms
+
+class DistComm:
+    """Collectives over a ``torch.distributed`` process group."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+
+        self.dist, self.group = dist, group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+
+    def gather(self, t: Tensor) -> Tensor:
+        out = torch.empty((self.world, *t.shape), dtype=t.dtype, device=t.device)
+        self.dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
+        return out
+
+    def reduce_max(self, t: Tensor) -> Tensor:
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX, group=self.group)
+        return t
+
+    def reduce_sum(self, t: Tensor) -> Tensor:
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM, group=self.group)
+        return t
+
+
+def drive(program, comm: DistComm):
+    """Run one rank's program, fulfilling its collectives with ``comm``."""
+    try:
+        req = next(program)
+        while True:
+            op, t = req
+            res = getattr(comm, op)(t)
+            req = program.send(res)
+    except StopIteration as stop:
+        return stop.value
+
+
+def run_lockstep(programs):
+    """Run the programs of all ranks in one process, in lockstep (single-device emulation)."""
+    n = len(programs)
+    results, reqs, alive = [None] * n, [None] * n, [True] * n
+    for i, p in enumerate(programs):
+        try:
+            reqs[i] = next(p)
+        except StopIteration as stop:
+            results[i], alive[i] = stop.value, False
+    while any(alive):
+        assert all(alive), "ranks disagree on the number of collectives"
+        ops = {r[0] for r in reqs}
+        assert len(ops) == 1, f"ranks disagree on the collective: {ops}"
+        op = ops.pop()
+        tensors = [r[1] for r in reqs]
+        if op == "gather":
+            stacked = torch.stack([t.contiguous() for t in tensors])
+            answers = [stacked.clone() for _ in range(n)]
+        elif op == "reduce_max":
+            m = torch.stack(tensors).amax(0)
+            answers = [m.clone() for _ in range(n)]
+        elif op == "reduce_sum":
+            m = torch.stack(tensors).sum(0)
+            answers = [m.clone() for _ in range(n)]
+        else:
+            raise ValueError(op)
+        for i, p in enumerate(programs):
+            try:
+                reqs[i] = p.send(answers[i])
+            except StopIteration as stop:
+                results[i], alive[i] = stop.value, False
+    return results
+
+
+# ------------------------------------------------------------------------------- local ops
+
+MONOID = {"affine1": 0, "affine4": 1, "picard": 2}
+NV = {"affine1": 2, "affine4": 20, "picard": 4}
+NS = {"affine1": 1, "affine4": 4, "picard": 3}
+
+
+@dataclass
+class ShardResult:
+    states: Tensor               # local shard of H in the I/O dtype
+    halo: Tensor | None          # fp32 state preceding the shard (None on rank 0 without h0)
+    stats_bits: Tensor           # int32 view of the statistics block, max-reduced over ranks
+
+
+class CudaShardOps:
+    """Local scan passes of one rank on its GPU, through the pass-level C ABI."""
+
+    def __init__(self, kind: str, wx: Tensor, rec: tuple[Tensor, ...], eps: float, omega: float):
+        from . import _lib as L
+        from . import ops
+
+        self.L, self.ops, self.lib = L, ops, L.lib()
+        self.kind, self.wx, self.eps, self.omega = kind, wx.contiguous(), float(eps), float(omega)
+        self.dev = wx.device
+        self.code = ops._dtype_code(wx)
+        self.B, self.T = wx.shape[:2]
+        gates = {"gru_diag": 3, "nlru": 2, "slstm_diag": 4}[kind]
+        self.d = wx.shape[2] // gates
+        self.cell = {"gru_diag": L.CELL_GRU_DIAG, "nlru": L.CELL_NLRU, "slstm_diag": L.CELL_SLSTM_DIAG}[kind]
+        self.slots = 4 if kind == "slstm_diag" else 1
+        self.par = torch.stack([p.detach().float().reshape(-1) for p in rec]).contiguous() \
+            if kind != "slstm_diag" else rec[0].detach().float().contiguous()
+        with torch.cuda.device(self.dev):
+            n = self.lib.prb_pass_workspace_bytes(self.cell, self.B, self.T, self.d)
+        self.ws = torch.empty(max(n, 256), dtype=torch.uint8, device=self.dev)
+        self.stats = ops.DeviceStats(self.dev, L.MAX_ITERS)
+        self.monoid = "affine4" if kind == "slstm_diag" else "affine1"
+
+    # helpers
+    def _p(self, t):
+        return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+    def _stream(self):
+        return self.ops._stream(self.dev)
+
+    def _check(self, rc, what):
+        self.ops._raise(rc, what)
+
+    def new_traj(self):
+        shape = (self.B, self.T, 4, self.d) if self.slots == 4 else (self.B, self.T, self.d)
+        return torch.empty(shape, dtype=torch.float32, device=self.dev)
+
+    def new_out(self):
+        shape = (self.B, self.T, 4, self.d) if self.slots == 4 else (self.B, self.T, self.d)
+        return torch.empty(shape, dtype=self.wx.dtype, device=self.dev)
+
+    def fold(self, monoid: str, gathered: Tensor, rank: int, world: int, reverse: bool) -> Tensor:
+        out = torch.empty(self.B, NS[monoid], self.d, dtype=torch.float32, device=self.dev)
+        with torch.cuda.device(self.dev):
+            rc = self.lib.prb_fold_carries(MONOID[monoid], self._p(gathered), rank, world, int(reverse),
+                                           self._p(out), self.B, self.d, self._stream())
+        self._check(rc, "fold_carries")
+        return out
+
+    def diag_guess(self, h0):
+        out = self.new_traj()
+        with torch.cuda.device(self.dev):
+            rc = self.lib.prb_diag_guess(self.cell, self._p(self.wx), self._p(self.par), self._p(h0),
+                                         self._p(out), self.B, self.T, self.d, self.code, self._stream())
+        self._check(rc, "diag_guess")
+        return out
+
+    def newton_pass(self, traj, halo, carry, mode, out, hist_slot):
+        """mode 0/1: returns the carry leaving the shard; mode 2: returns the shard aggregate."""
+        nv, ns = NV[self.monoid], NS[self.monoid]
+        res = torch.empty(self.B, nv if mode == 2 else ns, self.d, dtype=torch.float32, device=self.dev)
+        tail = None if mode == 2 else res
+        agg = res if mode == 2 else None
+        with torch.cuda.device(self.dev):
+            if self.kind == "slstm_diag":
+                rc = self.lib.prb_slstm_newton_pass(
+                    self._p(self.wx), self._p(self.par), self._p(traj), self._p(halo), self._p(carry),
+                    self._p(out), self._p(tail), self._p(agg), mode, self.B, self.T, self.d, self.code,
+                    self.omega, self.eps, self._p(self.ws), self.ws.numel(), self._p(self.stats.buf),
+                    hist_slot, self._stream())
+            else:
+                rc = self.lib.prb_diag_newton_pass(
+                    self.cell, self._p(self.wx), self._p(self.par), self._p(traj), self._p(halo),
+                    self._p(carry), self._p(out), self._p(tail), self._p(agg), mode, self.B, self.T, self.d,
+                    self.code, self.omega, self._p(self.ws), self.ws.numel(), self._p(self.stats.buf),
+                    hist_slot, self._stream())
+        self._check(rc, "newton_pass")
+        return res
+
+    def picard_pass(self, h_prev, h_halo, carry, mode, h_out, state_out):
+        res = torch.empty(self.B, 4 if mode == 2 else 3, self.d, dtype=torch.float32, device=self.dev)
+        with torch.cuda.device(self.dev):
+            rc = self.lib.prb_slstm_picard_pass(
+                self._p(self.wx), self._p(self.par), self._p(h_prev), self._p(h_halo), self._p(carry),
+                self._p(h_out), self._p(state_out), self._p(None if mode == 2 else res),
+                self._p(res if mode == 2 else None), mode, self.B, self.T, self.d, self.code, self.eps,
+                self._p(self.ws), self.ws.numel(), self._p(self.stats.buf), self._stream())
+        self._check(rc, "picard_pass")
+        return res
+
+    def bwd_pass(self, states, grad_states, halo, carry, mode):
+        """mode 0: returns (g_wx, g_params, head); mode 2: returns the aggregate."""
+        nv, ns = NV[self.monoid], NS[self.monoid]
+        npar = self.par.shape[0]
+        st = states.to(self.wx.dtype).contiguous()
+        gs = grad_states.to(self.wx.dtype).contiguous()
+        if mode == 2:
+            agg = torch.empty(self.B, nv, self.d, dtype=torch.float32, device=self.dev)
+            g_wx = g_par = head = None
+        else:
+            agg = None
+            g_wx = torch.empty_like(self.wx)
+            g_par = torch.empty(npar, self.d, dtype=torch.float32, device=self.dev)
+            head = torch.empty(self.B, ns, self.d, dtype=torch.float32, device=self.dev)
+        with torch.cuda.device(self.dev):
+            if self.kind == "slstm_diag":
+                rc = self.lib.prb_slstm_bwd_pass(
+                    self._p(st), self._p(self.wx), self._p(self.par), self._p(halo), self._p(carry),
+                    self._p(gs), self._p(g_wx), self._p(g_par), self._p(head), self._p(agg), mode, self.B,
+                    self.T, self.d, self.code, self.eps, self._p(self.ws), self.ws.numel(),
+                    self._p(self.stats.buf), self._stream())
+            else:
+                rc = self.lib.prb_diag_bwd_pass(
+                    self.cell, self._p(st), self._p(self.wx), self._p(self.par), self._p(halo),
+                    self._p(carry), self._p(gs), self._p(g_wx), self._p(g_par), self._p(head), self._p(agg),
+                    mode, self.B, self.T, self.d, self.code, self._p(self.ws), self.ws.numel(),
+                    self._p(self.stats.buf), self._stream())
+        self._check(rc, "bwd_pass")
+        return agg if mode == 2 else (g_wx, g_par, head)
+
+    def stats_bits(self) -> Tensor:
+        return self.stats.buf.view(torch.int32)
+
+
+# ------------------------------------------------------------------------------- programs
+
+def _pad(t: Tensor, nv: int) -> Tensor:
+    """Place a (B, ns, d) carry in the first rows of a (B, nv, d) gather slot."""
+    if t.shape[1] == nv:
+        return t
+    out = t.new_zeros(t.shape[0], nv, t.shape[2])
+    out[:, : t.shape[1]] = t
+    return out
+
+
+def _sharded_scan(ops, rank, world, reverse, monoid, boundary, sweep):
+    """One sharded scan pass.  ``sweep(mode, carry)`` runs the local kernel: mode 2 returns the
+    shard aggregate, otherwise it applies ``carry`` and returns the carry leaving the shard.
+    Yields one gather; returns ``(carry entering this rank, carry leaving it)``."""
+    first = world - 1 if reverse else 0
+    if world == 1:
+        return boundary, sweep(False, boundary)
+    if rank == first:
+        leaving = sweep(False, boundary)
+        gathered = yield ("gather", _pad(leaving, NV[monoid]))
+        return boundary, leaving
+    agg = sweep(True, None)
+    gathered = yield ("gather", agg)
+    carry = ops.fold(monoid, gathered, rank, world, reverse)
+    leaving = sweep(False, carry)
+    return carry, leaving
+
+
+def forward_program(ops, rank: int, world: int, K: int, P: int, h0: Tensor | None):
+    """Forward solve of one rank.  ``h0`` (fp32, state layout) is used on rank 0 only.
+    Returns a ``ShardResult``."""
+    kind = ops.kind
+    B, d = ops.B, ops.d
+    dev = ops.dev
+
+    def prev_rank_last(t_last: Tensor):
+        """Exchange the last state of every rank's shard; returns the previous rank's."""
+        gathered = yield ("gather", t_last.contiguous())
+        return gathered[rank - 1] if rank > 0 else None
+
+    if kind == "slstm_diag":
+        h_prev, h_halo = None, None
+        carry0 = None if h0 is None or rank > 0 else h0[:, :3].contiguous()
+        traj = None
+        for p in range(P + 1):
+            last = p == P
+            h_out = None if last else torch.empty(B, ops.T, d, dtype=torch.float32, device=dev)
+            state_out = ops.new_traj() if last else None
+            if p > 0:
+                if world > 1:
+                    h_halo = yield from prev_rank_last(h_prev[:, -1])
+                if rank == 0:
+                    h_halo = None if h0 is None else h0[:, 3].contiguous()
+
+            def sweep(agg_only, carry, h_prev=h_prev, h_halo=h_halo, h_out=h_out, state_out=state_out):
+                return ops.picard_pass(h_prev, h_halo, carry, 2 if agg_only else 0, h_out, state_out)
+
+            yield from _sharded_scan(ops, rank, world, False, "picard", carry0, sweep)
+            h_prev = h_out
+            traj = state_out
+        halo = None
+        if world > 1:
+            halo = yield from prev_rank_last(traj[:, -1])
+        if rank == 0:
+            halo = None if h0 is None else h0.contiguous()
+    else:
+        traj = ops.diag_guess(h0 if rank == 0 else None)
+        halo = None
+        if world > 1:
+            halo = yield from prev_rank_last(traj[:, -1])
+        if rank == 0:
+            halo = h0
+
+    out = ops.new_out()
+    if K == 0:
+        out.copy_(traj)
+    for k in range(K):
+        last = k == K - 1
+        dst = out if last else ops.new_traj()
+
+        def sweep(agg_only, carry, traj=traj, halo=halo, dst=dst, last=last, k=k):
+            return ops.newton_pass(traj, halo, carry, 2 if agg_only else (1 if last else 0), dst, k)
+
+        carry, _ = yield from _sharded_scan(ops, rank, world, False, ops.monoid, None, sweep)
+        if rank > 0 and carry is not None and not last:
+            # the carry entering the shard is the update of the previous rank's last step
+            c = carry if ops.slots == 4 else carry[:, 0]
+            halo = halo + ops.omega * c
+        traj = dst
+    # halo of the returned trajectory (I/O dtype values), used by the backward pass
+    halo_out = None
+    if world > 1:
+        halo_out = yield from prev_rank_last(out[:, -1].float())
+    if rank == 0:
+        halo_out = h0
+    bits = ops.stats_bits().clone()
+    if world > 1:
+        bits = yield ("reduce_max", bits)
+    return ShardResult(out, halo_out, bits)
+
+
+def backward_program(ops, rank: int, world: int, states: Tensor, grad_states: Tensor,
+                     halo: Tensor | None):
+    """Reverse scan + packed VJP of one rank.  Returns ``(g_wx, g_params, g_h0)`` with the
+    parameter gradients already summed over ranks; ``g_h0`` is meaningful on rank 0."""
+
+    def sweep(agg_only, carry):
+        if agg_only:
+            return ops.bwd_pass(states, grad_states, halo, None, 2)
+        sweep.out = ops.bwd_pass(states, grad_states, halo, carry, 0)
+        return sweep.out[2]
+
+    yield from _sharded_scan(ops, rank, world, True, ops.monoid, None, sweep)
+    g_wx, g_par, head = sweep.out
+    if world > 1:
+        g_par = yield ("reduce_sum", g_par)
+    return g_wx, g_par, head
