@@ -370,3 +370,147 @@ def backward_program(ops, rank: int, world: int, states: Tensor, grad_states: Te
     if world > 1:
         g_par = yield ("reduce_sum", g_par)
     return g_wx, g_par, head
+
+
+# ------------------------------------------------------------------------------- public entry
+
+def _bits_to_stats(bits: Tensor, K: int):
+    import struct
+
+    raw = bits.cpu().numpy().tobytes()
+    vals = struct.unpack("<20i", raw[:80])
+    as_f = struct.unpack("<17f", raw[:68])
+    return tuple(as_f[:K]), as_f[16], vals[17]
+
+
+def _h0_f32(h0: Tensor | None):
+    return None if h0 is None else h0.detach().float().contiguous()
+
+
+class _ShardedFixedPoint(torch.autograd.Function):
+    """Autograd contract of the time-sharded solve: every rank returns the gradient of its own
+    shard of ``x``; parameter gradients are summed over ranks (each rank holds the full sum);
+    ``grad_h0`` is non-zero on rank 0."""
+
+    @staticmethod
+    def forward(ctx, cell, kind, cfg, stats, comm, has_h0, x_in, h0_in, *params):
+        from .newton import _gate, _recurrent_params
+
+        del params
+        with torch.no_grad():
+            wx = cell.W_x(x_in)
+            ops = CudaShardOps(kind, wx, _recurrent_params(cell, kind), getattr(cell, "eps", 1e-6),
+                               cfg.omega)
+            h0 = _h0_f32(h0_in) if has_h0 else None
+            res = drive(forward_program(ops, comm.rank, comm.world, int(cfg.max_iters),
+                                        int(cfg.picard_iters or 0), h0), comm)
+        if stats is not None or cfg.residual_fail is not None:
+            hist, final, status = _bits_to_stats(res.stats_bits, int(cfg.max_iters))
+            _gate(cell, x_in, cfg, final, int(cfg.max_iters), hist, stats, status)
+        ctx.cell, ctx.kind, ctx.cfg, ctx.comm, ctx.has_h0, ctx.ops = cell, kind, cfg, comm, has_h0, ops
+        ctx.halo = res.halo
+        ctx.save_for_backward(x_in, h0_in, res.states)
+        return res.states
+
+    @staticmethod
+    def backward(ctx, grad_states):
+        from .newton import _clip_mask
+
+        x_in, h0_in, states = ctx.saved_tensors
+        cell, comm, ops = ctx.cell, ctx.comm, ctx.ops
+        with torch.no_grad():
+            g_wx, g_par, head = drive(backward_program(ops, comm.rank, comm.world, states,
+                                                       grad_states, ctx.halo), comm)
+            names = {"gru_diag": ("a_z", "a_r", "a_n"), "nlru": ("u",), "slstm_diag": ("R",)}[ctx.kind]
+            named = dict(cell.named_parameters())
+            cap = getattr(cell, "max_recurrent_norm", None)
+            grads = {}
+            if ctx.kind == "slstm_diag":
+                pieces = {"R": g_par}
+            else:
+                pieces = {n: g_par[i] for i, n in enumerate(names)}
+            for n, g in pieces.items():
+                raw = named[n]
+                g = g.reshape(raw.shape)
+                mask = _clip_mask(raw.detach(), cap)
+                grads[n] = (g * mask if mask is not None else g).to(raw.dtype)
+            lin = cell.W_x
+            gy = g_wx.reshape(-1, g_wx.shape[-1])
+            xx = x_in.detach().reshape(-1, x_in.shape[-1])
+            grad_x = (gy @ lin.weight.detach().to(gy.dtype)).reshape(x_in.shape)
+            gw = (gy.t() @ xx.to(gy.dtype)).float()
+            gb = gy.float().sum(0)
+            if comm.world > 1:
+                gw = comm.reduce_sum(gw)
+                gb = comm.reduce_sum(gb)
+            grads["W_x.weight"] = gw.to(lin.weight.dtype)
+            if lin.bias is not None:
+                grads["W_x.bias"] = gb.to(lin.bias.dtype)
+        out_params = []
+        for name, p in cell.named_parameters():
+            g = grads.get(name)
+            out_params.append(g if (g is not None and p.requires_grad) else None)
+        grad_h0 = None
+        if ctx.has_h0 and h0_in.requires_grad:
+            g0 = head if ops.slots == 4 else head[:, 0]
+            grad_h0 = (g0 if comm.rank == 0 else torch.zeros_like(g0)).to(h0_in.dtype)
+        if not x_in.requires_grad:
+            grad_x = None
+        return (None, None, None, None, None, None, grad_x, grad_h0, *out_params)
+
+
+def newton_apply_sharded(cell, kind: str, x: Tensor, cfg, *, h0: Tensor | None = None, stats=None,
+                         group=None) -> Tensor:
+    """``newton_apply`` for ``scan_backend="context_parallel"``: ``x`` is THIS rank's time shard
+    ``(B, T_local, d_in)`` (shards follow ``time_shard_bounds``), the result is the matching
+    shard of ``H``.  ``h0`` is read on rank 0.  Needs an initialised process group."""
+    import torch.distributed as dist
+
+    if kind == "gru_head":
+        raise TypeError("time sharding of ParaGRU(mix='head') is not available")
+    if cfg.chunk_len is not None or cfg.recompute:
+        raise ValueError("chunk_len / recompute cannot be combined with scan_backend='context_parallel'")
+    if not dist.is_available() or not dist.is_initialized():
+        raise RuntimeError("scan_backend='context_parallel' needs torch.distributed.init_process_group")
+    comm = DistComm(group)
+    params = tuple(cell.parameters())
+    has_h0 = h0 is not None
+    h0_leaf = h0 if has_h0 else x.new_zeros(())
+    cfg2 = cfg
+    if cfg.picard_adapt:
+        from dataclasses import replace
+
+        cfg2 = replace(cfg, picard_adapt=False)  # the retry ladder is a host loop; pin P when sharding
+    if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in params)
+                                    or (has_h0 and h0.requires_grad)):
+        return _ShardedFixedPoint.apply(cell, kind, cfg2, stats, comm, has_h0, x, h0_leaf, *params)
+    with torch.no_grad():
+        return _ShardedFixedPoint.forward(_Ctx(), cell, kind, cfg2, stats, comm, has_h0, x, h0_leaf)
+
+
+class _Ctx:
+    """Stand-in for the autograd context when no gradient is needed."""
+
+    def save_for_backward(self, *a):
+        pass
+
+
+def emulate_sharded(kind: str, wx: Tensor, rec, *, world: int, K: int, P: int = 0, h0=None,
+                    eps: float = 1e-6, omega: float = 1.0, grad_states: Tensor | None = None,
+                    ops_factory=None):
+    """Run the time-sharded programs of ``world`` virtual ranks in one process on one device
+    (shards of ``wx`` along time per ``time_shard_bounds``).  Returns the concatenated states,
+    the statistics bits and, when ``grad_states`` is given, ``(g_wx, g_params, g_h0)``."""
+    factory = ops_factory or CudaShardOps
+    T = wx.shape[1]
+    bounds = [time_shard_bounds(T, r, world) for r in range(world)]
+    ops = [factory(kind, wx[:, s:e].contiguous(), rec, eps, omega) for s, e in bounds]
+    res = run_lockstep([forward_program(ops[r], r, world, K, P, _h0_f32(h0)) for r in range(world)])
+    states = torch.cat([r.states for r in res], dim=1)
+    out = [states, res[0].stats_bits]
+    if grad_states is not None:
+        back = run_lockstep([
+            backward_program(ops[r], r, world, res[r].states, grad_states[:, s:e].contiguous(), res[r].halo)
+            for r, (s, e) in enumerate(bounds)])
+        out.append((torch.cat([b[0] for b in back], dim=1), back[0][1], back[0][2]))
+    return tuple(out)

@@ -1,0 +1,57 @@
+"""Time-sharded solve on ONE GPU: the programs of 2-4 virtual ranks run in lockstep in one
+process (no kernel waits on another rank), and the result must match the unsharded kernels."""
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import dev, make_problem, rel_err
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _rec(kind, params):
+    if kind == "slstm_diag":
+        return (dev(params),)
+    return tuple(dev(p) for p in params)
+
+
+@pytest.mark.parametrize("kind,K,P", [("gru_diag", 3, 0), ("nlru", 2, 0), ("slstm_diag", 2, 3)])
+@pytest.mark.parametrize("world,T", [(2, 257), (3, 100), (4, 1024)])
+@pytest.mark.parametrize("path", ["lookback", "persist"])
+def test_sharded_matches_oracle(kind, K, P, world, T, path, monkeypatch):
+    from pararnn_b200.seq_shard import _bits_to_stats, emulate_sharded
+
+    monkeypatch.setenv("PRB_KERNEL_PATH", path)
+    B, d = 2, 40
+    wx, params, h0 = make_problem(kind, B, T, d, seed=T + world, h0=True, x_scale=0.6, bias_f=1.0)
+    want = oracle.newton(oracle.KIND[kind], wx, params, h0, max_iters=K, picard=P)
+    G = np.random.default_rng(1).standard_normal(want.states.shape).astype(np.float32)
+    states, bits, grads = emulate_sharded(kind, dev(wx), _rec(kind, params), world=world, K=K, P=P,
+                                          h0=dev(h0), grad_states=dev(G))
+    H = states.cpu().numpy()
+    amp = max(1.0, max(want.history))
+    scale = max(1.0, float(np.abs(want.states).max()))
+    assert np.abs(H - want.states).max() <= 1e-5 * amp * scale
+    hist, final, status = _bits_to_stats(bits, K)
+    assert status == 0
+    np.testing.assert_allclose(np.asarray(hist), np.asarray(want.history), rtol=2e-2, atol=4e-6 * scale)
+    assert abs(final - want.max_residual) <= 2e-2 * want.max_residual + 4e-6 * scale * amp
+    # backward at the sharded trajectory
+    w_wx, w_p, w_h0 = oracle.backward(oracle.KIND[kind], H, wx, params, G, h0)
+    g_wx, g_p, g_h0 = grads
+    assert rel_err(g_wx.cpu().numpy(), w_wx) <= 5e-5
+    assert rel_err(g_p.cpu().numpy().reshape(-1), w_p.reshape(-1)) <= 1e-4
+    assert rel_err(g_h0.cpu().numpy().reshape(w_h0.shape), w_h0) <= 5e-5
+
+
+def test_sharded_equals_unsharded_bf16():
+    from pararnn_b200 import ops
+    from pararnn_b200.seq_shard import emulate_sharded
+
+    wx, r, _ = make_problem("slstm_diag", 2, 2048, 64, seed=5, x_scale=0.5, bias_f=3.0)
+    wxd, rd = dev(wx, torch.bfloat16), dev(r, torch.bfloat16)
+    one = ops.newton_slstm_fused(wxd, rd, None, None, max_iters=2, picard_iters=5)
+    many, _ = emulate_sharded("slstm_diag", wxd, (rd,), world=4, K=2, P=5)
+    assert rel_err(many[:, :, 3].float().cpu().numpy(), one[:, :, 3].float().cpu().numpy()) <= 2e-2
