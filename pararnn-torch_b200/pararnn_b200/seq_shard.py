@@ -54,9 +54,10 @@ class DistComm:
         self.world = dist.get_world_size(group)
 
     def gather(self, t: Tensor) -> Tensor:
-        out = torch.empty((self.world, *t.shape), dtype=t.dtype, device=t.device)
-        self.dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
-        return out
+        flat = t.contiguous().view(-1)
+        out = torch.empty(self.world * flat.numel(), dtype=t.dtype, device=t.device)
+        self.dist.all_gather_into_tensor(out, flat, group=self.group)
+        return out.view(self.world, *t.shape)
 
     def reduce_max(self, t: Tensor) -> Tensor:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX, group=self.group)
