@@ -97,8 +97,9 @@ def make_inputs(t_len: int, seed: int):
     """Synthetic layer inputs and parameters (CPU tensors), fp32 master copies."""
     import torch
 
-    g = torch.Generator().manual_seed(seed)
-    x = 0.5 * torch.randn(B, t_len, D, generator=g)
+    g = torch.Generator().manual_seed(SEED)
+    gx = torch.Generator().manual_seed(seed)
+    x = 0.5 * torch.randn(B, t_len, D, generator=gx)
     bound = (6.0 / (D + 4 * D)) ** 0.5
     W = (torch.rand(4 * D, D, generator=g) * 2 - 1) * bound
     bias = torch.zeros(4 * D)
@@ -352,6 +353,115 @@ def run_gpu_single(args):
     print(json.dumps(line))
 
 
+def run_gpu_sharded(args):
+    """N ranks, one per GPU: the sequence (T = T_PER_GPU * N) is sharded along time; every scan
+    pass exchanges per-shard carries with one NCCL all-gather.  Max over ranks of the
+    event-timed region; rank 0 prints the line."""
+    import torch
+    import torch.distributed as dist
+
+    import pararnn_b200 as prb
+    from pararnn_b200.seq_shard import (CudaShardOps, DistComm, _bits_to_stats, backward_program, drive,
+                                        forward_program)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    comm = DistComm()
+    peak, peak_kind = measured_peaks()
+    x, W, bias, R = make_inputs(T_PER_GPU, SEED + 1000 * rank)
+    cell = prb.ParaSLSTM(D, D).to(dev)
+    with torch.no_grad():
+        cell.W_x.weight.copy_(W)
+        cell.W_x.bias.copy_(bias)
+        cell.R.copy_(R)
+    cell = cell.bfloat16()
+    x_host = x.bfloat16().pin_memory()
+    x_dev = x_host.to(dev)
+    with torch.no_grad():
+        wx = cell.W_x(x_dev).contiguous()
+    G_io = torch.zeros(B, T_PER_GPU, 4, D, dtype=torch.bfloat16, device=dev)
+    G_io[:, :, 3] = 1.0
+    rec = (cell.clipped_r().detach(),)
+    keep = {}
+
+    def step():
+        ops = CudaShardOps("slstm_diag", wx, rec, 1e-6, 1.0)
+        res = drive(forward_program(ops, rank, world, K_NEWTON, P_PICARD, None), comm)
+        keep["bwd"] = drive(backward_program(ops, rank, world, res.states, G_io, res.halo), comm)
+        keep["res"] = res
+
+    def barrier():
+        dist.barrier(device_ids=[local])
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    sec = time_region(step, args.steps, None, barrier)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([sec], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    sec = float(t.item())
+    hist, res_final, status = _bits_to_stats(keep["res"].stats_bits, K_NEWTON)
+
+    # end to end through the public API (host-resident shard of x per rank)
+    cfg = prb.NewtonConfig(max_iters=K_NEWTON, picard_iters=P_PICARD, picard_adapt=False,
+                           scan_backend="context_parallel")
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        xd = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        Hs = prb.newton_apply(cell, xd, cfg)
+        loss = Hs[:, :, 3].float().sum()
+        loss.backward()
+        loss_host.copy_(loss.detach(), non_blocking=True)
+        cell.zero_grad(set_to_none=True)
+
+    e2e_sec = float("nan")
+    if not args.no_e2e:
+        for _ in range(2):
+            e2e_step()
+        n_e2e = max(2, min(args.steps, 5))
+        e2e_sec = time_region(e2e_step, n_e2e, None, barrier) / n_e2e
+        t = torch.tensor([e2e_sec], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_sec = float(t.item())
+    if rank == 0:
+        assert status == 0, "chain wait timed out"
+        ms = sec / args.steps * 1e3
+        tokens = B * T_PER_GPU * world
+        step_bytes = BYTES_STEP * tokens * D
+        line = {
+            "metric": "newton_scan_fwd_bwd_tokens_per_s", "value": tokens / (sec / args.steps),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 scan arithmetic, bf16 I/O", "data": "synthetic",
+            "config": workload_config(world), "clocks": clocks,
+            "e2e": {"value": tokens / e2e_sec, "unit": "tokens/s",
+                    "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": 4 * world,
+                    "ms_per_step": e2e_sec * 1e3,
+                    "includes": "per rank: H2D of its x shard, 3 W_x GEMMs, sharded Newton+scan fwd and "
+                                "reverse scan + VJP with NCCL carry exchange and gradient all-reduce, "
+                                "D2H of loss"},
+            "gpu_launches": (2 * (P_PICARD + 1 + K_NEWTON + 1) + 12) * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "peak": peak * world,
+                         "unit": "GB/s", "achieved": step_bytes / (ms / 1e3) / 1e9,
+                         "frac": step_bytes / (ms / 1e3) / 1e9 / (peak * world), "peak_kind": peak_kind,
+                         "traffic": None,
+                         "note": "ranks other than the first sweep each pass twice (aggregate, then apply)"},
+            "newton": {"iters": K_NEWTON, "residual_history": list(hist), "max_residual": res_final},
+        }
+        print(json.dumps(line))
+    dist.barrier(device_ids=[local])
+    dist.destroy_process_group()
+
+
 def main():
     global T_PER_GPU
     ap = argparse.ArgumentParser()
@@ -371,8 +481,6 @@ def main():
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         run_gpu_single(args)
     else:
-        from bench_sharded import run_gpu_sharded
-
         run_gpu_sharded(args)
 
 

@@ -96,6 +96,28 @@ int prb_newton_slstm_fused(const void* wx, const void* r, const void* h0, const 
                            void* workspace, size_t workspace_bytes, prb_stats* stats,
                            prb_stream_t stream);
 
+/* ParaGRU mix='head' (per-head dense recurrence, d_head in {8,16,32,64}).  Replaces
+ * pararnn::newton_gru_head_fused, kernels/custom_ops.py:311-386 ->
+ * kernels/newton_gru_head.py:96-195,460-567.  wx (B,T,3d) gate-major then head;
+ * a_z,a_r,a_n (H,dh,dh) with y = h A; h0 (B,d) or NULL; out (B,T,d). */
+size_t prb_gru_head_workspace_bytes(int B, int T, int d, int n_heads, int max_iters);
+int prb_newton_gru_head_fused(const void* wx, const void* a_z, const void* a_r, const void* a_n,
+                              const void* h0, void* out, int B, int T, int d, int n_heads, int dtype,
+                              int max_iters, float omega, int want_residual, void* workspace,
+                              size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
+
+/* Reverse walk with the factorised J^T and the gate part of the packed VJP.  Replaces
+ * pararnn::reverse_gru_head_factor (kernels/custom_ops.py:389-434,
+ * kernels/newton_gru_head.py:198-258,570-652), gru_head_t0_vjp (:261-297) and the g_wx part of
+ * gru_head_recurrence_vjp (kernels/vjp_gru.py:656-810).  g_wx (B,T,3d) I/O dtype;
+ * u_out (B,T,d) fp32 = h_prev * r; g_h0 (B,d) fp32 or NULL.  The parameter gradients are
+ * batched outer-product sums the caller forms with a library GEMM:
+ * grad A_z = sum h_prev^T g_z, grad A_r = sum h_prev^T g_r, grad A_n = sum u^T g_n. */
+int prb_bwd_gru_head(const void* states, const void* wx, const void* a_z, const void* a_r,
+                     const void* a_n, const void* h0, const void* grad_states, void* g_wx, float* u_out,
+                     float* g_h0, int B, int T, int d, int n_heads, int dtype, void* workspace,
+                     size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
+
 /* ---- backward: eq. 2.6 reverse scan fused with the packed VJP ------------------- */
 
 /* Replaces reverse_scan_diag + gru_recurrence_vjp / nlru_recurrence_vjp,

@@ -529,6 +529,115 @@ int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void*
     return PRB_OK;
 }
 
+/* ---- ParaGRU mix='head' -------------------------------------------------------------- */
+
+namespace {
+struct HeadPlan {
+    float* A;
+    float* h0;
+    float* buf[2];
+    size_t total;
+};
+HeadPlan plan_head(void* ws, int B, int T, int d, int H, int K) {
+    Bump b(ws);
+    HeadPlan p;
+    const int dh = d / H;
+    p.A = b.take<float>((size_t)3 * H * dh * dh);
+    p.h0 = b.take<float>((size_t)B * d);
+    const size_t n = (size_t)B * T * d;
+    p.buf[0] = K > 3 ? b.take<float>(n) : nullptr;
+    p.buf[1] = K > 6 ? b.take<float>(n) : nullptr;
+    p.total = b.off + 256;
+    return p;
+}
+bool head_dim_ok(int d, int H) {
+    if (H < 1 || d % H) return false;
+    const int dh = d / H;
+    return dh == 8 || dh == 16 || dh == 32 || dh == 64;
+}
+}  // namespace
+
+size_t prb_gru_head_workspace_bytes(int B, int T, int d, int n_heads, int max_iters) {
+    if (B < 1 || T < 1 || d < 1 || !head_dim_ok(d, n_heads)) return 0;
+    return plan_head(nullptr, B, T, d, n_heads, max_iters).total;
+}
+
+int prb_newton_gru_head_fused(const void* wx, const void* a_z, const void* a_r, const void* a_n,
+                              const void* h0, void* out, int B, int T, int d, int n_heads, int dtype,
+                              int max_iters, float omega, int want_residual, void* workspace,
+                              size_t workspace_bytes, prb_stats* stats, prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!wx || !a_z || !a_r || !a_n || !out || !stats || B < 1 || T < 1 || d < 1 || max_iters < 0 ||
+        max_iters > kMaxIters || bad_dtype(dtype))
+        return PRB_ERR_BAD_ARG;
+    if (!head_dim_ok(d, n_heads)) return PRB_ERR_UNSUPPORTED;
+    const int K = max_iters, H = n_heads, dh = d / H;
+    HeadPlan p = plan_head(nullptr, B, T, d, H, K);
+    if (int e = check_ws(workspace, workspace_bytes, p.total)) return e;
+    p = plan_head(workspace, B, T, d, H, K);
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    cudaMemsetAsync(st, 0, sizeof(DeviceStats), s);
+    const size_t asz = (size_t)H * dh * dh;
+    to_f32(a_z, p.A, asz, dtype, s);
+    to_f32(a_r, p.A + asz, asz, dtype, s);
+    to_f32(a_n, p.A + 2 * asz, asz, dtype, s);
+    const float* h0f = nullptr;
+    if (h0) {
+        to_f32(h0, p.h0, (size_t)B * d, dtype, s);
+        h0f = p.h0;
+    }
+    if (K == 0) {
+        // the guess itself: one stage with omega = 0 returns H^0 and its residual
+        return launch_gru_head_fwd(dtype, wx, p.A, h0f, nullptr, out, true, 1, false, &st->final_bits,
+                                   &st->final_bits, B, T, d, H, 0.f, s) == cudaSuccess
+                   ? PRB_OK
+                   : PRB_ERR_LAUNCH;
+    }
+    int done = 0, flip = 0;
+    const float* hin = nullptr;
+    while (done < K) {
+        const int n = K - done < 3 ? K - done : 3;
+        const bool last = done + n == K;
+        void* dst = last ? out : (void*)p.buf[flip];
+        if (launch_gru_head_fwd(dtype, wx, p.A, h0f, hin, dst, last, n, last && want_residual,
+                                &st->hist_bits[done], &st->final_bits, B, T, d, H, omega, s) != cudaSuccess)
+            return PRB_ERR_LAUNCH;
+        hin = p.buf[flip];
+        flip ^= 1;
+        done += n;
+    }
+    return PRB_OK;
+}
+
+int prb_bwd_gru_head(const void* states, const void* wx, const void* a_z, const void* a_r,
+                     const void* a_n, const void* h0, const void* grad_states, void* g_wx, float* u_out,
+                     float* g_h0, int B, int T, int d, int n_heads, int dtype, void* workspace,
+                     size_t workspace_bytes, prb_stats* stats, prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!states || !wx || !a_z || !a_r || !a_n || !grad_states || !g_wx || !u_out || !stats || B < 1 ||
+        T < 1 || d < 1 || bad_dtype(dtype))
+        return PRB_ERR_BAD_ARG;
+    if (!head_dim_ok(d, n_heads)) return PRB_ERR_UNSUPPORTED;
+    const int H = n_heads, dh = d / H;
+    HeadPlan p = plan_head(nullptr, B, T, d, H, 0);
+    if (int e = check_ws(workspace, workspace_bytes, p.total)) return e;
+    p = plan_head(workspace, B, T, d, H, 0);
+    cudaMemsetAsync(stats, 0, sizeof(DeviceStats), s);
+    const size_t asz = (size_t)H * dh * dh;
+    to_f32(a_z, p.A, asz, dtype, s);
+    to_f32(a_r, p.A + asz, asz, dtype, s);
+    to_f32(a_n, p.A + 2 * asz, asz, dtype, s);
+    const float* h0f = nullptr;
+    if (h0) {
+        to_f32(h0, p.h0, (size_t)B * d, dtype, s);
+        h0f = p.h0;
+    }
+    return launch_gru_head_bwd(dtype, wx, states, grad_states, p.A, h0f, g_wx, u_out, g_h0, B, T, d, H, s) ==
+                   cudaSuccess
+               ? PRB_OK
+               : PRB_ERR_LAUNCH;
+}
+
 /* ---- pass-level entry points (time-sharded driver, profiling) ------------------- */
 
 size_t prb_pass_workspace_bytes(int cell, int B, int T, int d) {

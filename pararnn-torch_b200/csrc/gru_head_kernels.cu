@@ -1,0 +1,354 @@
+// ParaGRU mix='head': per-head dense recurrence (row-vector convention y = h A, A (d_in, d_out)).
+//
+//   z = sigmoid(h A_z + z_x),  r = sigmoid(h A_r + r_x),  n = tanh((h*r) A_n + n_x),
+//   f = h + z (n - h)
+//   J d   = (1-z) d + (n-h) z' (d A_z) + z n' ((r d + h r' (d A_r)) A_n)
+//   J^T m = (1-z) m + A_z (z'(n-h) m) + r g + A_r (r' h g),   g = A_n (n' z m)
+//
+// Reference restated: cells/para_gru.py:385-412 and :468-479 (step, dense J),
+// kernels/gru_head_factor.py:31-112 (factorised J d and J^T m),
+// kernels/vjp_gru.py:141-221 (packed VJP), kernels/newton_gru_head.py:460-652 (the
+// reference's sequential-in-time Newton and reverse walks).
+//
+// Forward kernel: one CTA per (batch row, head).  The K Newton iterations run as a skewed
+// software pipeline over ONE sweep of the time axis: stage s handles time step tick - s, so at
+// every tick all stages work in parallel (stage s+1 linearises around the trajectory stage s
+// produced one tick earlier).  A stage is a group of 64 threads; thread o keeps column o of
+// A_z, A_r, A_n in registers, the vectors being multiplied are broadcast from shared memory.
+// An optional last stage evaluates the residual of the final trajectory.  No intermediate
+// trajectory touches HBM.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace prb {
+
+constexpr int kHG = 64;  // threads per stage group
+
+__device__ __forceinline__ void stage_bar(int id) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(kHG) : "memory");
+}
+
+// dot products of two broadcast vectors with two register-resident columns
+template <int DH>
+__device__ __forceinline__ void dot2x2(const float* va, const float* vb, const float (&c0)[DH],
+                                       const float (&c1)[DH], float& a0, float& a1, float& b0, float& b1) {
+    a0 = a1 = b0 = b1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < DH; i += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(va + i);
+        const float4 y = *reinterpret_cast<const float4*>(vb + i);
+        a0 = fmaf(x.x, c0[i], a0); a0 = fmaf(x.y, c0[i + 1], a0); a0 = fmaf(x.z, c0[i + 2], a0); a0 = fmaf(x.w, c0[i + 3], a0);
+        a1 = fmaf(x.x, c1[i], a1); a1 = fmaf(x.y, c1[i + 1], a1); a1 = fmaf(x.z, c1[i + 2], a1); a1 = fmaf(x.w, c1[i + 3], a1);
+        b0 = fmaf(y.x, c0[i], b0); b0 = fmaf(y.y, c0[i + 1], b0); b0 = fmaf(y.z, c0[i + 2], b0); b0 = fmaf(y.w, c0[i + 3], b0);
+        b1 = fmaf(y.x, c1[i], b1); b1 = fmaf(y.y, c1[i + 1], b1); b1 = fmaf(y.z, c1[i + 2], b1); b1 = fmaf(y.w, c1[i + 3], b1);
+    }
+}
+template <int DH>
+__device__ __forceinline__ void dot2x1(const float* va, const float* vb, const float (&c)[DH], float& a,
+                                       float& b) {
+    a = b = 0.f;
+#pragma unroll
+    for (int i = 0; i < DH; i += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(va + i);
+        const float4 y = *reinterpret_cast<const float4*>(vb + i);
+        a = fmaf(x.x, c[i], a); a = fmaf(x.y, c[i + 1], a); a = fmaf(x.z, c[i + 2], a); a = fmaf(x.w, c[i + 3], a);
+        b = fmaf(y.x, c[i], b); b = fmaf(y.y, c[i + 1], b); b = fmaf(y.z, c[i + 2], b); b = fmaf(y.w, c[i + 3], b);
+    }
+}
+
+struct HeadFwdArgs {
+    const void* wx;      // (B,T,3d) I/O dtype
+    const float* A;      // (3,H,dh,dh) fp32, order A_z, A_r, A_n
+    const float* h0;     // (B,d) fp32 or null
+    const float* hin;    // (B,T,d) fp32 input trajectory, null = App. A guess computed in place
+    void* hout;          // (B,T,d): fp32 work trajectory or I/O dtype (out_io)
+    unsigned* hist_bits; // n_newton slots
+    unsigned* final_bits;
+    int out_io, n_newton, resid;
+    int B, T, d, H;
+    float omega;
+};
+
+template <typename TIO, int DH>
+__global__ void __launch_bounds__(256, 1) gru_head_newton_kernel(HeadFwdArgs a) {
+    constexpr int MAXS = 4;
+    __shared__ __align__(16) float s_vec[MAXS][2][kHG];    // hp, delta of each stage
+    __shared__ __align__(16) float s_vec2[MAXS][2][kHG];   // u, du of each stage
+    __shared__ float s_traj[MAXS + 1][2][kHG];             // trajectory entering each stage
+    __shared__ unsigned s_red[8];
+    const int stage = threadIdx.x / kHG, o = threadIdx.x % kHG;
+    const int nstg = a.n_newton + (a.resid ? 1 : 0);
+    const int b = blockIdx.x / a.H, head = blockIdx.x % a.H;
+    const bool act = o < DH;
+    const bool is_resid = a.resid && stage == a.n_newton;
+    const int oc = act ? o : 0;
+
+    float az[DH], ar[DH], an[DH];
+    {
+        const size_t hs = (size_t)DH * DH;
+        const float* Az = a.A + ((size_t)0 * a.H + head) * hs;
+        const float* Ar = a.A + ((size_t)1 * a.H + head) * hs;
+        const float* An = a.A + ((size_t)2 * a.H + head) * hs;
+#pragma unroll
+        for (int i = 0; i < DH; ++i) {
+            az[i] = __ldg(Az + (size_t)i * DH + oc);
+            ar[i] = __ldg(Ar + (size_t)i * DH + oc);
+            an[i] = __ldg(An + (size_t)i * DH + oc);
+        }
+    }
+    const TIO* wx = reinterpret_cast<const TIO*>(a.wx) + (size_t)b * a.T * 3 * a.d + head * DH + oc;
+    const float* hin = a.hin ? a.hin + (size_t)b * a.T * a.d + head * DH + oc : nullptr;
+    const float h_init = a.h0 ? __ldg(a.h0 + (size_t)b * a.d + head * DH + oc) : 0.f;
+
+    float hp = h_init, dl = 0.f;
+    unsigned rmax = 0u;
+    s_vec[stage][0][o] = act ? hp : 0.f;
+    s_vec[stage][1][o] = 0.f;
+    s_vec2[stage][0][o] = 0.f;
+    s_vec2[stage][1][o] = 0.f;
+
+    // With no input trajectory, stage 0 linearises around the App. A guess f(0, x_t) (h0 only
+    // at t = 0), which needs no matrix product except at t = 0 with a non-zero h0.
+    float guess0 = 0.f;
+    if (!a.hin && a.h0 && stage == 0) {
+        __syncthreads();
+        float pz, pr, d0, d1;
+        dot2x2<DH>(s_vec[0][0], s_vec[0][1], az, ar, pz, pr, d0, d1);
+        const float z = sigmoid_f(pz + ld_f(wx)), r = sigmoid_f(pr + ld_f(wx + a.d));
+        s_vec2[0][0][o] = act ? hp * r : 0.f;
+        stage_bar(1);
+        float pn, d2;
+        dot2x1<DH>(s_vec2[0][0], s_vec2[0][1], an, pn, d2);
+        const float n = tanh_f(pn + ld_f(wx + 2 * (size_t)a.d));
+        guess0 = hp + z * (n - hp);
+    } else if (!a.hin && a.h0) {
+        __syncthreads();
+    }
+
+    const int n_ticks = a.T + nstg - 1;
+    for (int tick = 0; tick < n_ticks; ++tick) {
+        __syncthreads();
+        const int t = tick - stage;
+        const bool on = stage < nstg && t >= 0 && t < a.T;
+        float zx = 0.f, rx = 0.f, nx = 0.f, cur = 0.f;
+        if (on) {
+            zx = ld_f(wx + (size_t)t * 3 * a.d);
+            rx = ld_f(wx + (size_t)t * 3 * a.d + a.d);
+            nx = ld_f(wx + (size_t)t * 3 * a.d + 2 * (size_t)a.d);
+            if (stage == 0) {
+                if (hin) {
+                    cur = __ldg(hin + (size_t)t * a.d);
+                } else if (t == 0 && a.h0) {
+                    cur = guess0;
+                } else {
+                    cur = sigmoid_f(zx) * tanh_f(nx);  // f(0, x): z * n
+                }
+            } else {
+                cur = s_traj[stage][(tick + 1) & 1][o];
+            }
+        }
+        if (stage < nstg) {
+            float pz, pr, dz, dr;
+            dot2x2<DH>(s_vec[stage][0], s_vec[stage][1], az, ar, pz, pr, dz, dr);
+            const float z = sigmoid_f(pz + zx), r = sigmoid_f(pr + rx);
+            const float rp = r * (1.f - r);
+            s_vec2[stage][0][o] = act ? hp * r : 0.f;
+            s_vec2[stage][1][o] = act ? fmaf(r, dl, hp * rp * dr) : 0.f;
+            stage_bar(1 + stage);
+            float pn, dn;
+            dot2x1<DH>(s_vec2[stage][0], s_vec2[stage][1], an, pn, dn);
+            if (on) {
+                const float n = tanh_f(pn + nx);
+                const float f = fmaf(z, n - hp, hp);
+                const float F = f - cur;
+                if (act) rmax = max(rmax, absbits(F));
+                if (!is_resid) {
+                    const float jd = (1.f - z) * dl + (n - hp) * z * (1.f - z) * dz + z * (1.f - n * n) * dn;
+                    dl = jd + F;
+                    const float nv = fmaf(a.omega, dl, cur);
+                    s_traj[stage + 1][tick & 1][o] = nv;
+                    if (stage == a.n_newton - 1 && act) {
+                        const size_t idx = ((size_t)b * a.T + t) * a.d + head * DH + o;
+                        if (a.out_io)
+                            st_f(reinterpret_cast<TIO*>(a.hout) + idx, nv);
+                        else
+                            reinterpret_cast<float*>(a.hout)[idx] = nv;
+                    }
+                }
+                hp = cur;
+            }
+            // vectors of the next tick (all reads of this tick's vectors are behind the stage barrier)
+            s_vec[stage][0][o] = act ? hp : 0.f;
+            s_vec[stage][1][o] = act ? dl : 0.f;
+        }
+    }
+    // per-stage maxima: stage s < n_newton -> hist_bits[s]; residual stage -> final_bits
+    for (int s = 0; s < nstg; ++s) {
+        __syncthreads();
+        unsigned v = (stage == s) ? rmax : 0u;
+        unsigned* dst = (a.resid && s == a.n_newton) ? a.final_bits : a.hist_bits + s;
+        block_residual_max(v, dst, s_red);
+    }
+}
+
+// ------------------------------------------------------------------ backward
+struct HeadBwdArgs {
+    const void* wx;           // (B,T,3d)
+    const void* states;       // (B,T,d) I/O dtype
+    const void* grad_states;  // (B,T,d) I/O dtype
+    const float* A;           // (3,H,dh,dh)
+    const float* h0;          // (B,d) fp32 or null
+    void* g_wx;               // (B,T,3d) I/O dtype
+    float* u_out;             // (B,T,d) fp32: h_prev * r (operand of the A_n gradient)
+    float* g_h0;              // (B,d) fp32 or null
+    int B, T, d, H;
+};
+
+// Two groups of 64 threads per (batch row, head): group 0 recomputes the gates of step t one
+// tick ahead (columns of A in registers), group 1 walks the adjoint backwards (rows of A in
+// registers):  nu_{t-1} = J_t^T (nu_t + g_t).
+template <typename TIO, int DH>
+__global__ void __launch_bounds__(128, 1) gru_head_bwd_kernel(HeadBwdArgs a) {
+    __shared__ __align__(16) float s_h[2][kHG];       // h_prev broadcast for the gate group
+    __shared__ __align__(16) float s_u[2][kHG];       // h_prev * r
+    __shared__ float s_gate[2][4][kHG];               // z, r, n, h_prev handed to the adjoint group
+    __shared__ __align__(16) float s_w[2][kHG];       // w_z, w_n
+    __shared__ __align__(16) float s_v3[2][kHG];      // r' h g (second slot unused, kept zero)
+    const int grp = threadIdx.x / kHG, o = threadIdx.x % kHG;
+    const int b = blockIdx.x / a.H, head = blockIdx.x % a.H;
+    const bool act = o < DH;
+    const int oc = act ? o : 0;
+    const size_t hs = (size_t)DH * DH;
+    const float* Az = a.A + ((size_t)0 * a.H + head) * hs;
+    const float* Ar = a.A + ((size_t)1 * a.H + head) * hs;
+    const float* An = a.A + ((size_t)2 * a.H + head) * hs;
+    float m0[DH], m1[DH], m2[DH];
+#pragma unroll
+    for (int i = 0; i < DH; ++i) {
+        if (grp == 0) {  // columns: m[i] = A[i][o]
+            m0[i] = __ldg(Az + (size_t)i * DH + oc);
+            m1[i] = __ldg(Ar + (size_t)i * DH + oc);
+            m2[i] = __ldg(An + (size_t)i * DH + oc);
+        } else {         // rows: m[k] = A[o][k]
+            m0[i] = __ldg(Az + (size_t)oc * DH + i);
+            m1[i] = __ldg(Ar + (size_t)oc * DH + i);
+            m2[i] = __ldg(An + (size_t)oc * DH + i);
+        }
+    }
+    const size_t base = (size_t)b * a.T * a.d + head * DH + oc;
+    const TIO* wx = reinterpret_cast<const TIO*>(a.wx) + (size_t)b * a.T * 3 * a.d + head * DH + oc;
+    const TIO* st = reinterpret_cast<const TIO*>(a.states) + base;
+    const TIO* gs = reinterpret_cast<const TIO*>(a.grad_states) + base;
+    TIO* gwx = reinterpret_cast<TIO*>(a.g_wx) + (size_t)b * a.T * 3 * a.d + head * DH + oc;
+    const float h_init = a.h0 ? __ldg(a.h0 + (size_t)b * a.d + head * DH + oc) : 0.f;
+    s_h[0][o] = 0.f; s_h[1][o] = 0.f; s_u[0][o] = 0.f; s_u[1][o] = 0.f;
+    s_w[0][o] = 0.f; s_w[1][o] = 0.f; s_v3[0][o] = 0.f; s_v3[1][o] = 0.f;
+    float nu = 0.f;
+    __syncthreads();
+    // tick k: gate group handles step T-1-k, adjoint group handles step T-k (one tick later)
+    for (int k = 0; k <= a.T; ++k) {
+        if (grp == 0) {
+            const int t = a.T - 1 - k;
+            if (t >= 0) {
+                const float hpv = (t == 0) ? h_init : ld_f(st + (size_t)(t - 1) * a.d);
+                s_h[0][o] = act ? hpv : 0.f;
+                stage_bar(1);
+                float pz, pr, d0, d1;
+                dot2x2<DH>(s_h[0], s_h[1], m0, m1, pz, pr, d0, d1);
+                const float z = sigmoid_f(pz + ld_f(wx + (size_t)t * 3 * a.d));
+                const float r = sigmoid_f(pr + ld_f(wx + (size_t)t * 3 * a.d + a.d));
+                s_u[0][o] = act ? hpv * r : 0.f;
+                stage_bar(1);
+                float pn, d2;
+                dot2x1<DH>(s_u[0], s_u[1], m2, pn, d2);
+                const float n = tanh_f(pn + ld_f(wx + (size_t)t * 3 * a.d + 2 * (size_t)a.d));
+                s_gate[k & 1][0][o] = z;
+                s_gate[k & 1][1][o] = r;
+                s_gate[k & 1][2][o] = n;
+                s_gate[k & 1][3][o] = hpv;
+                if (act) a.u_out[base + (size_t)t * a.d] = hpv * r;
+            }
+        } else {
+            const int t = a.T - k;
+            if (t < a.T) {
+                const float z = s_gate[(k + 1) & 1][0][o], r = s_gate[(k + 1) & 1][1][o];
+                const float n = s_gate[(k + 1) & 1][2][o], hpv = s_gate[(k + 1) & 1][3][o];
+                const float mu = nu + ld_f(gs + (size_t)t * a.d);
+                const float w_z = z * (1.f - z) * (n - hpv) * mu;
+                const float w_n = (1.f - n * n) * z * mu;
+                s_w[0][o] = act ? w_z : 0.f;
+                s_w[1][o] = act ? w_n : 0.f;
+                stage_bar(2);
+                // t2 = A_z w_z (rows of A_z), g = A_n w_n (rows of A_n)
+                float t2 = 0.f, g = 0.f;
+#pragma unroll
+                for (int i = 0; i < DH; i += 4) {
+                    const float4 x = *reinterpret_cast<const float4*>(s_w[0] + i);
+                    const float4 y = *reinterpret_cast<const float4*>(s_w[1] + i);
+                    t2 = fmaf(x.x, m0[i], t2); t2 = fmaf(x.y, m0[i + 1], t2); t2 = fmaf(x.z, m0[i + 2], t2); t2 = fmaf(x.w, m0[i + 3], t2);
+                    g = fmaf(y.x, m2[i], g); g = fmaf(y.y, m2[i + 1], g); g = fmaf(y.z, m2[i + 2], g); g = fmaf(y.w, m2[i + 3], g);
+                }
+                const float v3 = r * (1.f - r) * hpv * g;
+                s_v3[0][o] = act ? v3 : 0.f;
+                stage_bar(2);
+                float t4, d3;
+                dot2x1<DH>(s_v3[0], s_v3[1], m1, t4, d3);
+                if (act) {
+                    st_f(gwx + (size_t)t * 3 * a.d, w_z);
+                    st_f(gwx + (size_t)t * 3 * a.d + a.d, v3);
+                    st_f(gwx + (size_t)t * 3 * a.d + 2 * (size_t)a.d, w_n);
+                }
+                nu = (1.f - z) * mu + t2 + r * g + t4;
+            }
+        }
+        __syncthreads();
+    }
+    if (grp == 1 && act && a.g_h0) a.g_h0[(size_t)b * a.d + head * DH + o] = nu;
+}
+
+// ------------------------------------------------------------------ launchers
+template <typename TIO>
+static cudaError_t launch_head_fwd_t(const HeadFwdArgs& a, int dh, cudaStream_t s) {
+    const int grid = a.B * a.H;
+    const int threads = kHG * (a.n_newton + (a.resid ? 1 : 0));
+    switch (dh) {
+        case 8: gru_head_newton_kernel<TIO, 8><<<grid, threads, 0, s>>>(a); break;
+        case 16: gru_head_newton_kernel<TIO, 16><<<grid, threads, 0, s>>>(a); break;
+        case 32: gru_head_newton_kernel<TIO, 32><<<grid, threads, 0, s>>>(a); break;
+        case 64: gru_head_newton_kernel<TIO, 64><<<grid, threads, 0, s>>>(a); break;
+        default: return cudaErrorNotSupported;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gru_head_fwd(int dtype, const void* wx, const float* A, const float* h0,
+                                const float* hin, void* hout, bool out_io, int n_newton, bool resid,
+                                unsigned* hist_bits, unsigned* final_bits, int B, int T, int d, int H,
+                                float omega, cudaStream_t s) {
+    HeadFwdArgs a{wx, A, h0, hin, hout, hist_bits, final_bits, out_io ? 1 : 0, n_newton, resid ? 1 : 0,
+                  B, T, d, H, omega};
+    if (n_newton + (resid ? 1 : 0) < 1 || n_newton + (resid ? 1 : 0) > 4) return cudaErrorInvalidValue;
+    return dtype == kF32 ? launch_head_fwd_t<float>(a, d / H, s) : launch_head_fwd_t<__nv_bfloat16>(a, d / H, s);
+}
+
+template <typename TIO>
+static cudaError_t launch_head_bwd_t(const HeadBwdArgs& a, int dh, cudaStream_t s) {
+    const int grid = a.B * a.H;
+    switch (dh) {
+        case 8: gru_head_bwd_kernel<TIO, 8><<<grid, 128, 0, s>>>(a); break;
+        case 16: gru_head_bwd_kernel<TIO, 16><<<grid, 128, 0, s>>>(a); break;
+        case 32: gru_head_bwd_kernel<TIO, 32><<<grid, 128, 0, s>>>(a); break;
+        case 64: gru_head_bwd_kernel<TIO, 64><<<grid, 128, 0, s>>>(a); break;
+        default: return cudaErrorNotSupported;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gru_head_bwd(int dtype, const void* wx, const void* states, const void* grad_states,
+                                const float* A, const float* h0, void* g_wx, float* u_out, float* g_h0,
+                                int B, int T, int d, int H, cudaStream_t s) {
+    HeadBwdArgs a{wx, states, grad_states, A, h0, g_wx, u_out, g_h0, B, T, d, H};
+    return dtype == kF32 ? launch_head_bwd_t<float>(a, d / H, s) : launch_head_bwd_t<__nv_bfloat16>(a, d / H, s);
+}
+
+}  // namespace prb

@@ -123,4 +123,14 @@ cudaError_t launch_slstm_picard_persist(int dtype, const SlstmPicardArgs& a, cud
 cudaError_t launch_slstm_newton_persist(int dtype, const SlstmNewtonArgs& a, bool last, cudaStream_t s);
 cudaError_t launch_slstm_bwd_persist(int dtype, const SlstmBwdArgs& a, cudaStream_t s);
 
+
+// ---- ParaGRU mix='head' (gru_head_kernels.cu) --------------------------------------------
+cudaError_t launch_gru_head_fwd(int dtype, const void* wx, const float* A, const float* h0,
+                                const float* hin, void* hout, bool out_io, int n_newton, bool resid,
+                                unsigned* hist_bits, unsigned* final_bits, int B, int T, int d, int H,
+                                float omega, cudaStream_t s);
+cudaError_t launch_gru_head_bwd(int dtype, const void* wx, const void* states, const void* grad_states,
+                                const float* A, const float* h0, void* g_wx, float* u_out, float* g_h0,
+                                int B, int T, int d, int H, cudaStream_t s);
+
 }  // namespace prb

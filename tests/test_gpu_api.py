@@ -11,7 +11,7 @@ from test_host_api import _cell_from_golden
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("name", [n for n in golden_names() if not n.startswith("gru_head")])
+@pytest.mark.parametrize("name", golden_names())
 def test_newton_apply_and_grads_match_reference(name):
     g = load_golden(name)
     cell = _cell_from_golden(g).cuda()
@@ -30,7 +30,8 @@ def test_newton_apply_and_grads_match_reference(name):
     if g["history"][-1] > 1e-2:
         return  # far from converged: gradients of two different iterates are not comparable
     tol = 5e-4 * amp
-    names = {"gru_diag": ("a_z", "a_r", "a_n"), "nlru": ("u",), "slstm_diag": ("R",)}[g["cell"]]
+    names = {"gru_diag": ("a_z", "a_r", "a_n"), "nlru": ("u",), "slstm_diag": ("R",),
+             "gru_head": ("A_z", "A_r", "A_n")}[g["cell"]]
     got = (cell.R.grad.cpu().numpy() if names == ("R",)
            else np.stack([getattr(cell, n).grad.cpu().numpy() for n in names]))
     for a, b in ((x.grad.cpu().numpy(), g["g_x"]), (cell.W_x.weight.grad.cpu().numpy(), g["g_W"]),
