@@ -98,16 +98,20 @@ void from_f32(const float* src, void* dst, size_t n, int dtype, cudaStream_t s) 
         cvt_from_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(src, (__nv_bfloat16*)dst, n);
 }
 
-// Kernel family for a sLSTM pass: the persistent-chain kernels need enough independent chains
-// to fill the GPU (one CTA per chain) and TMA-compatible strides.  PRB_KERNEL_PATH=persist or
-// =lookback overrides the choice (used by the tests to cover both families on small shapes).
-bool use_persist(int dtype, int B, int T, int d) {
+// Kernel family for a sLSTM pass: 0 = look-back kernels (any shape), 1 = persistent-chain
+// kernels with per-thread map composition, 2 = warp-pipelined persistent kernels.  The
+// persistent families need enough independent chains to fill the GPU (one CTA per chain) and
+// TMA-compatible strides.  PRB_KERNEL_PATH=lookback|persist|pipe overrides the choice (used by
+// the tests to cover every family on small shapes).
+int kernel_path(int dtype, int B, int T, int d) {
     const char* env = getenv("PRB_KERNEL_PATH");
-    if (env && env[0] == 'l') return false;
-    if (!slstm_persist_ok(dtype, B, T, d)) return false;
-    if (env && env[0] == 'p') return true;
-    return B * ((d + kLanes - 1) / kLanes) >= 96;
+    if (env && env[0] == 'l') return 0;
+    if (!slstm_persist_ok(dtype, B, T, d)) return 0;
+    if (env && env[0] == 'p' && env[1] == 'e') return 1;
+    if (env && env[0] == 'p') return 2;
+    return B * ((d + kLanes - 1) / kLanes) >= 96 ? 2 : 0;
 }
+bool use_persist(int dtype, int B, int T, int d) { return kernel_path(dtype, B, T, d) != 0; }
 
 bool bad_dtype(int dtype) { return dtype != kF32 && dtype != kBF16; }
 bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 255u) != 0; }
@@ -297,7 +301,8 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
         h0f = p.h0;
     }
     const size_t nst = (size_t)B * T * 4 * d;
-    const bool persist = use_persist(dtype, B, T, d);
+    const int path = kernel_path(dtype, B, T, d);
+    const bool persist = path != 0;
     if (guess) {
         to_f32(guess, p.sb[0], nst, dtype, s);
     } else {
@@ -319,7 +324,9 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
             a.d = d;
             a.eps = eps;
             a.chain = next_chain(p.chain, T, slstm_picard_tile_steps(), &st->status);
-            cudaError_t e = persist ? launch_slstm_picard_persist(dtype, a, s) : cudaErrorNotSupported;
+            cudaError_t e = cudaErrorNotSupported;
+            if (path == 2) e = launch_slstm_picard_pipe(dtype, a, s);
+            if (path == 1) e = launch_slstm_picard_persist(dtype, a, s);
             if (e == cudaErrorNotSupported) e = launch_slstm_picard(dtype, a, false, s);
             if (e != cudaSuccess) return PRB_ERR_LAUNCH;
         }
@@ -341,7 +348,9 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
         a.omega = omega;
         a.eps = eps;
         a.chain = next_chain(p.chain, T, slstm_tile_steps(), &st->status);
-        cudaError_t e = persist ? launch_slstm_newton_persist(dtype, a, k == K - 1, s) : cudaErrorNotSupported;
+        cudaError_t e = cudaErrorNotSupported;
+        if (path == 2) e = launch_slstm_newton_pipe(dtype, a, k == K - 1, s);
+        if (path == 1) e = launch_slstm_newton_persist(dtype, a, k == K - 1, s);
         if (e == cudaErrorNotSupported) e = launch_slstm_newton(dtype, a, k == K - 1, false, s);
         if (e != cudaSuccess) return PRB_ERR_LAUNCH;
     }
@@ -520,7 +529,10 @@ int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void*
     a.eps = eps;
     a.chain = next_chain(p.chain, T, slstm_tile_steps(), &st->status);
     int rows = B * a.chain.n_tt;
-    cudaError_t e = use_persist(dtype, B, T, d) ? launch_slstm_bwd_persist(dtype, a, s) : cudaErrorNotSupported;
+    const int path = kernel_path(dtype, B, T, d);
+    cudaError_t e = cudaErrorNotSupported;
+    if (path == 2) e = launch_slstm_bwd_pipe(dtype, a, s);
+    if (path == 1) e = launch_slstm_bwd_persist(dtype, a, s);
     if (e == cudaSuccess) rows = B;  // the persistent kernel writes one partial per batch row
     if (e == cudaErrorNotSupported) e = launch_slstm_bwd(dtype, a, false, s);
     if (e != cudaSuccess) return PRB_ERR_LAUNCH;
@@ -782,8 +794,10 @@ int prb_slstm_picard_pass(const void* wx, const float* r, const float* h_prev, c
     a.d = d;
     a.eps = eps;
     a.chain = next_chain(w.chain, T, slstm_picard_tile_steps(), &st->status);
-    cudaError_t e = (mode == 0 && use_persist(dtype, B, T, d)) ? launch_slstm_picard_persist(dtype, a, s)
-                                                                : cudaErrorNotSupported;
+    const int path = mode == 0 ? kernel_path(dtype, B, T, d) : 0;
+    cudaError_t e = cudaErrorNotSupported;
+    if (path == 2) e = launch_slstm_picard_pipe(dtype, a, s);
+    if (path == 1) e = launch_slstm_picard_persist(dtype, a, s);
     if (e == cudaErrorNotSupported) e = launch_slstm_picard(dtype, a, mode == 2, s);
     return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
@@ -819,9 +833,10 @@ int prb_slstm_newton_pass(const void* wx, const float* r, const float* sin, cons
     a.omega = omega;
     a.eps = eps;
     a.chain = next_chain(w.chain, T, slstm_tile_steps(), &st->status);
-    cudaError_t e = (mode != 2 && use_persist(dtype, B, T, d))
-                        ? launch_slstm_newton_persist(dtype, a, mode == 1, s)
-                        : cudaErrorNotSupported;
+    const int path = mode != 2 ? kernel_path(dtype, B, T, d) : 0;
+    cudaError_t e = cudaErrorNotSupported;
+    if (path == 2) e = launch_slstm_newton_pipe(dtype, a, mode == 1, s);
+    if (path == 1) e = launch_slstm_newton_persist(dtype, a, mode == 1, s);
     if (e == cudaErrorNotSupported) e = launch_slstm_newton(dtype, a, mode == 1, mode == 2, s);
     return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
@@ -857,8 +872,10 @@ int prb_slstm_bwd_pass(const void* states, const void* wx, const float* r, const
     a.eps = eps;
     a.chain = next_chain(w.chain, T, slstm_tile_steps(), &st->status);
     int rows = B * a.chain.n_tt;
-    cudaError_t e = (mode == 0 && use_persist(dtype, B, T, d)) ? launch_slstm_bwd_persist(dtype, a, s)
-                                                                : cudaErrorNotSupported;
+    const int path = mode == 0 ? kernel_path(dtype, B, T, d) : 0;
+    cudaError_t e = cudaErrorNotSupported;
+    if (path == 2) e = launch_slstm_bwd_pipe(dtype, a, s);
+    if (path == 1) e = launch_slstm_bwd_persist(dtype, a, s);
     if (e == cudaSuccess) rows = B;
     if (e == cudaErrorNotSupported) e = launch_slstm_bwd(dtype, a, mode == 2, s);
     if (e != cudaSuccess) return PRB_ERR_LAUNCH;

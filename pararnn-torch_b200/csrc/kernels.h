@@ -123,6 +123,11 @@ cudaError_t launch_slstm_picard_persist(int dtype, const SlstmPicardArgs& a, cud
 cudaError_t launch_slstm_newton_persist(int dtype, const SlstmNewtonArgs& a, bool last, cudaStream_t s);
 cudaError_t launch_slstm_bwd_persist(int dtype, const SlstmBwdArgs& a, cudaStream_t s);
 
+// warp-pipelined variants (slstm_pipe.cu)
+cudaError_t launch_slstm_newton_pipe(int dtype, const SlstmNewtonArgs& a, bool last, cudaStream_t s);
+cudaError_t launch_slstm_picard_pipe(int dtype, const SlstmPicardArgs& a, cudaStream_t s);
+cudaError_t launch_slstm_bwd_pipe(int dtype, const SlstmBwdArgs& a, cudaStream_t s);
+
 
 // ---- ParaGRU mix='head' (gru_head_kernels.cu) --------------------------------------------
 cudaError_t launch_gru_head_fwd(int dtype, const void* wx, const float* A, const float* h0,

@@ -94,6 +94,25 @@ struct SlstmAct {
     float i, f, z, o, c, n, invD, alpha, hp;
 };
 
+// Gate activations of one step (no Jacobian entries): what the packed VJP consumes.
+__device__ __forceinline__ void slstm_acts(const float (&prev)[4], const float (&w)[4],
+                                           const float (&r)[4], float eps, SlstmAct& o) {
+    const float c = prev[0], n = prev[1], m = prev[2], h = prev[3];
+    const float zi = fmaf(r[0], h, w[0]), zf = fmaf(r[1], h, w[1]);
+    const float zz = fmaf(r[2], h, w[2]), zo = fmaf(r[3], h, w[3]);
+    const float left = zf + m;
+    const float e_ = exp_f(-fabsf(left - zi));
+    o.i = left >= zi ? e_ : 1.f;
+    o.f = left >= zi ? 1.f : e_;
+    o.alpha = left > zi ? 1.f : (left == zi ? 0.5f : 0.f);
+    o.z = tanh_f(zz);
+    o.o = sigmoid_f(zo);
+    o.c = c;
+    o.n = n;
+    o.invD = rcp_f(fmaf(o.f, n, o.i) + eps);
+    o.hp = h;
+}
+
 // y = J^T x with the structured J (11 FMA)
 __device__ __forceinline__ void slstm_apply_t(const SlstmLin& l, float& xc, float& xn, float& xm,
                                               float& xh) {
