@@ -430,9 +430,12 @@ struct PipePicardSmem {
     static constexpr int SLOT_OFF = NSTAGE * STAGE;
     static constexpr int SLOT_BYTES = W * 3 * kLanes * 4;
     static constexpr int BAR_OFF = (SLOT_OFF + SLOT_BYTES + 7) / 8 * 8;
-    static constexpr int TOTAL = BAR_OFF + 2 * NSTAGE * 8 + 64;
+    static constexpr int TOTAL = BAR_OFF + (2 * NSTAGE + W) * 8 + 64;
 };
 
+// The baton is the true state, passed in two parts: m as soon as the max-plus recurrence of the
+// warp's steps is done (named barrier), (c, n) after the multiply-add recurrences (mbarrier), so
+// that the next warp's m recurrence overlaps this warp's exponentials.
 // The baton is the true state (c, n, m).  Inside a warp's L steps the max-plus recurrence of m
 // runs first (two dependent ops per step), then the L exponentials are independent of each
 // other, then the two multiply-add recurrences of n and c run.
@@ -446,6 +449,7 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
     float* s_slot = reinterpret_cast<float*>(smem + S::SLOT_OFF);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::BAR_OFF);
     uint64_t* empty = full + NSTAGE;
+    uint64_t* cnbar = empty + NSTAGE;  // [W]: (c, n) entering warp w is ready
 
     const int d = a.d;
     const int ncb = (d + kLanes - 1) / kLanes;
@@ -465,6 +469,7 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], W);
         }
+        for (int w2 = 0; w2 < W; ++w2) mbar_init(&cnbar[w2], 1);
         mbar_fence_init();
     }
     if (warp == 0) {
@@ -528,7 +533,7 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
             }
 
             if (!(r == 0 && warp == 0)) named_sync(1 + warp, 64);
-            float c = slot_in[0], n = slot_in[kLanes], m = slot_in[2 * kLanes];
+            float m = slot_in[2 * kLanes];
             float dlt[L], ms[L];
 #pragma unroll
             for (int i = 0; i < L; ++i) {
@@ -541,9 +546,18 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
                 }
                 ms[i] = m;
             }
+            slot_out[2 * kLanes] = m;
+            if (!(r == n_rounds - 1 && warp == W - 1)) named_arrive(1 + next, 64);
             float e[L];
 #pragma unroll
             for (int i = 0; i < L; ++i) e[i] = exp_f(-fabsf(dlt[i]));
+            // (c, n) from the previous warp: its r-th hand-over for warps > 0, the last warp's
+            // (r-1)-th for warp 0
+            if (!(r == 0 && warp == 0)) {
+                const uint32_t par = (warp == 0 ? r - 1 : r) & 1;
+                if (!mbar_wait_bounded(&cnbar[warp], par, kPipeWaitLimit)) timed_out = true;
+            }
+            float c = slot_in[0], n = slot_in[kLanes];
             float cs[L], ns[L];
 #pragma unroll
             for (int i = 0; i < L; ++i) {
@@ -558,8 +572,8 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
             }
             slot_out[0] = c;
             slot_out[kLanes] = n;
-            slot_out[2 * kLanes] = m;
-            if (!(r == n_rounds - 1 && warp == W - 1)) named_arrive(1 + next, 64);
+            __syncwarp();
+            if (lane == 0 && !(r == n_rounds - 1 && warp == W - 1)) mbar_arrive(&cnbar[next]);
 
 #pragma unroll
             for (int i = 0; i < L; ++i) {
