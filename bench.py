@@ -462,6 +462,87 @@ def run_gpu_sharded(args):
     dist.destroy_process_group()
 
 
+def run_secondary(args):
+    """Other BASELINE configurations (one JSON line each): `--workload c1|c3|c5`.
+    c1: ParaGRU diag fp32 B=2 T=1024 d=64 K=3; c3: ParaGRU head 8x64 B=16 T=4096 K=3 (fp32 and
+    bf16); c5: 12 x ParaNLRU d=768 bf16 B=4 T=8192 K=2 residual stack.  Forward + backward through
+    newton_apply (layer boundary: includes the W_x GEMMs), CUDA events, inputs resident in HBM."""
+    import torch
+
+    import pararnn_b200 as prb
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        return time_region(fn, args.steps, None) / args.steps
+
+    lines = []
+    if args.workload == "c1":
+        torch.manual_seed(0)
+        cell = prb.ParaGRU(64, 64).to(dev)
+        torch.nn.init.xavier_uniform_(cell.W_x.weight)
+        x = torch.randn(2, 1024, 64, device=dev, requires_grad=True)
+        cfg = prb.NewtonConfig(max_iters=3)
+
+        def step():
+            prb.newton_apply(cell, x, cfg).sum().backward()
+
+        sec = timed(step)
+        rep = prb.verify_agreement(cell, x.detach(), config=cfg)
+        lines.append({"workload": "c1 ParaGRU diag fp32 B=2 T=1024 d=64 K=3", "ms_per_step": sec * 1e3,
+                      "tokens_per_s": 2 * 1024 / sec, "agreement_max_abs": rep.max_abs,
+                      "newton_iters": rep.newton_iters})
+    elif args.workload == "c3":
+        for dtype in (torch.float32, torch.bfloat16):
+            torch.manual_seed(2)
+            cell = prb.ParaGRU(512, 512, mix="head", n_heads=8)
+            with torch.no_grad():
+                torch.nn.init.xavier_uniform_(cell.W_x.weight)
+                for A in (cell.A_z, cell.A_r, cell.A_n):
+                    for hd in range(8):
+                        torch.nn.init.orthogonal_(A[hd], gain=0.9)
+            cell = cell.to(dev, dtype)
+            x = torch.randn(16, 4096, 512, device=dev, dtype=dtype, requires_grad=True)
+            cfg = prb.NewtonConfig(max_iters=3)
+            st = prb.NewtonStats()
+
+            def step():
+                prb.newton_apply(cell, x, cfg, stats=st).float().sum().backward()
+
+            sec = timed(step)
+            lines.append({"workload": f"c3 ParaGRU head 8x64 B=16 T=4096 K=3 {str(dtype)[6:]}",
+                          "ms_per_step": sec * 1e3, "tokens_per_s": 16 * 4096 / sec,
+                          "residual_history": list(st.residual_history), "max_residual": st.max_residual})
+    else:
+        torch.manual_seed(4)
+        cells = []
+        for _ in range(12):
+            c = prb.ParaNLRU(768, 768)
+            with torch.no_grad():
+                a0 = torch.empty(768).uniform_(0.9, 0.999)
+                c.W_x.bias[:768] = torch.log(a0 / (1 - a0))
+            cells.append(c.to(dev, torch.bfloat16))
+        emb = (torch.randn(50304, 768) * 0.02).to(dev, torch.bfloat16)
+        ids = torch.randint(0, 50304, (4, 8192), device=dev)
+        cfg = prb.NewtonConfig(max_iters=2)
+        norm = torch.nn.RMSNorm(768).to(dev, torch.bfloat16)
+
+        def step():
+            h = emb[ids].requires_grad_(True)
+            for c in cells:
+                h = h + prb.newton_apply(c, norm(h), cfg)
+            h.float().sum().backward()
+
+        sec = timed(step)
+        lines.append({"workload": "c5 12 x ParaNLRU d=768 bf16 B=4 T=8192 K=2 residual stack",
+                      "ms_per_step": sec * 1e3, "tokens_per_s": 4 * 8192 / sec})
+    for ln in lines:
+        print(json.dumps(ln))
+
+
 def main():
     global T_PER_GPU
     ap = argparse.ArgumentParser()
@@ -471,12 +552,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--seq-len", type=int, default=T_PER_GPU,
                     help="time steps per GPU (profiling captures use a smaller case)")
+    ap.add_argument("--workload", default="c2", choices=("c2", "c1", "c3", "c5"),
+                    help="c2 (default) is the headline line; the others print secondary lines")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg")
     args = ap.parse_args()
     T_PER_GPU = args.seq_len
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.workload != "c2":
+        run_secondary(args)
         return
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         run_gpu_single(args)

@@ -112,6 +112,14 @@ int kernel_path(int dtype, int B, int T, int d) {
     return B * ((d + kLanes - 1) / kLanes) >= 96 ? 2 : 0;
 }
 bool use_persist(int dtype, int B, int T, int d) { return kernel_path(dtype, B, T, d) != 0; }
+// aggregate-only sweeps: one CTA per chain when there are enough chains (or when a persistent
+// family is forced), else the look-back kernels with map carries
+bool agg_seg(int B, int d) {
+    const char* env = getenv("PRB_KERNEL_PATH");
+    if (env && env[0] == 'l') return false;
+    if (env && env[0] == 'p') return true;
+    return B * ((d + kLanes - 1) / kLanes) >= 96;
+}
 
 bool bad_dtype(int dtype) { return dtype != kF32 && dtype != kBF16; }
 bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 255u) != 0; }
@@ -794,10 +802,11 @@ int prb_slstm_picard_pass(const void* wx, const float* r, const float* h_prev, c
     a.d = d;
     a.eps = eps;
     a.chain = next_chain(w.chain, T, slstm_picard_tile_steps(), &st->status);
-    const int path = mode == 0 ? kernel_path(dtype, B, T, d) : 0;
+    const int path = kernel_path(dtype, B, T, d);
     cudaError_t e = cudaErrorNotSupported;
-    if (path == 2) e = launch_slstm_picard_pipe(dtype, a, s);
-    if (path == 1) e = launch_slstm_picard_persist(dtype, a, s);
+    if (mode == 2 && agg_seg(B, d)) e = launch_slstm_picard_agg_seg(dtype, a, s);
+    if (mode == 0 && path == 2) e = launch_slstm_picard_pipe(dtype, a, s);
+    if (mode == 0 && path == 1) e = launch_slstm_picard_persist(dtype, a, s);
     if (e == cudaErrorNotSupported) e = launch_slstm_picard(dtype, a, mode == 2, s);
     return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
@@ -833,10 +842,11 @@ int prb_slstm_newton_pass(const void* wx, const float* r, const float* sin, cons
     a.omega = omega;
     a.eps = eps;
     a.chain = next_chain(w.chain, T, slstm_tile_steps(), &st->status);
-    const int path = mode != 2 ? kernel_path(dtype, B, T, d) : 0;
+    const int path = kernel_path(dtype, B, T, d);
     cudaError_t e = cudaErrorNotSupported;
-    if (path == 2) e = launch_slstm_newton_pipe(dtype, a, mode == 1, s);
-    if (path == 1) e = launch_slstm_newton_persist(dtype, a, mode == 1, s);
+    if (mode == 2 && agg_seg(B, d)) e = launch_slstm_newton_agg_seg(dtype, a, s);
+    if (mode != 2 && path == 2) e = launch_slstm_newton_pipe(dtype, a, mode == 1, s);
+    if (mode != 2 && path == 1) e = launch_slstm_newton_persist(dtype, a, mode == 1, s);
     if (e == cudaErrorNotSupported) e = launch_slstm_newton(dtype, a, mode == 1, mode == 2, s);
     return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
@@ -872,10 +882,11 @@ int prb_slstm_bwd_pass(const void* states, const void* wx, const float* r, const
     a.eps = eps;
     a.chain = next_chain(w.chain, T, slstm_tile_steps(), &st->status);
     int rows = B * a.chain.n_tt;
-    const int path = mode == 0 ? kernel_path(dtype, B, T, d) : 0;
+    const int path = kernel_path(dtype, B, T, d);
     cudaError_t e = cudaErrorNotSupported;
-    if (path == 2) e = launch_slstm_bwd_pipe(dtype, a, s);
-    if (path == 1) e = launch_slstm_bwd_persist(dtype, a, s);
+    if (mode == 2 && agg_seg(B, d)) e = launch_slstm_bwd_agg_seg(dtype, a, s);
+    if (mode == 0 && path == 2) e = launch_slstm_bwd_pipe(dtype, a, s);
+    if (mode == 0 && path == 1) e = launch_slstm_bwd_persist(dtype, a, s);
     if (e == cudaSuccess) rows = B;
     if (e == cudaErrorNotSupported) e = launch_slstm_bwd(dtype, a, mode == 2, s);
     if (e != cudaSuccess) return PRB_ERR_LAUNCH;

@@ -128,6 +128,11 @@ cudaError_t launch_slstm_newton_pipe(int dtype, const SlstmNewtonArgs& a, bool l
 cudaError_t launch_slstm_picard_pipe(int dtype, const SlstmPicardArgs& a, cudaStream_t s);
 cudaError_t launch_slstm_bwd_pipe(int dtype, const SlstmBwdArgs& a, cudaStream_t s);
 
+// aggregate-only sweeps with one CTA per chain (slstm_agg.cu); any shape
+cudaError_t launch_slstm_newton_agg_seg(int dtype, const SlstmNewtonArgs& a, cudaStream_t s);
+cudaError_t launch_slstm_picard_agg_seg(int dtype, const SlstmPicardArgs& a, cudaStream_t s);
+cudaError_t launch_slstm_bwd_agg_seg(int dtype, const SlstmBwdArgs& a, cudaStream_t s);
+
 
 // ---- ParaGRU mix='head' (gru_head_kernels.cu) --------------------------------------------
 cudaError_t launch_gru_head_fwd(int dtype, const void* wx, const float* A, const float* h0,
