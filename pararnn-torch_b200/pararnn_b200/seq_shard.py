@@ -295,28 +295,49 @@ def forward_program(ops, rank: int, world: int, K: int, P: int, h0: Tensor | Non
         return gathered[rank - 1] if rank > 0 else None
 
     if kind == "slstm_diag":
-        h_prev, h_halo = None, None
+        # No halo exchange is needed between the frozen-gate passes: the carry entering a rank is
+        # the state (c, n, m) at the previous rank's last step, and with that step's output-gate
+        # pre-activation (which the previous rank knows BEFORE the pass and ships in its gather
+        # slot) the hidden value at that step follows as sigmoid(zo) c / (n + eps).
+        h_prev = None
+        h_halo = None if (h0 is None or rank > 0) else h0[:, 3].contiguous()
         carry0 = None if h0 is None or rank > 0 else h0[:, :3].contiguous()
         traj = None
+        r_o = ops.par[3]
+        wx_o_last = ops.wx[:, -1, 3 * d:].float()
+        wx_o = ops.wx[:, :, 3 * d:]
+        halo = None
         for p in range(P + 1):
             last = p == P
             h_out = None if last else torch.empty(B, ops.T, d, dtype=torch.float32, device=dev)
             state_out = ops.new_traj() if last else None
-            if p > 0:
-                if world > 1:
-                    h_halo = yield from prev_rank_last(h_prev[:, -1])
+            if h_prev is None:
+                zo_last = wx_o_last
+            elif ops.T >= 2:
+                zo_last = wx_o_last + r_o * h_prev[:, -2]
+            else:
+                zo_last = wx_o_last + r_o * (h_halo if h_halo is not None else 0.0)
+            carry = carry0
+            if world > 1:
                 if rank == 0:
-                    h_halo = None if h0 is None else h0[:, 3].contiguous()
-
-            def sweep(agg_only, carry, h_prev=h_prev, h_halo=h_halo, h_out=h_out, state_out=state_out):
-                return ops.picard_pass(h_prev, h_halo, carry, 2 if agg_only else 0, h_out, state_out)
-
-            yield from _sharded_scan(ops, rank, world, False, "picard", carry0, sweep)
+                    leaving = ops.picard_pass(h_prev, h_halo, carry0, 0, h_out, state_out)
+                    slot = torch.cat([leaving, leaving.new_zeros(B, 1, d), zo_last[:, None]], dim=1)
+                    gathered = yield ("gather", slot)
+                else:
+                    agg = ops.picard_pass(h_prev, h_halo, None, 2, None, None)
+                    gathered = yield ("gather", torch.cat([agg, zo_last[:, None]], dim=1))
+                    carry = ops.fold("picard", gathered[:, :, :4].contiguous(), rank, world, False)
+                    ops.picard_pass(h_prev, h_halo, carry, 0, h_out, state_out)
+                    # hidden state at the previous rank's last step under the new trajectory
+                    zo_prev = gathered[rank - 1][:, 4]
+                    h_end = torch.sigmoid(zo_prev) * carry[:, 0] / (carry[:, 1] + ops.eps)
+                    h_halo = h_end
+                    if last:
+                        halo = torch.cat([carry, h_end[:, None]], dim=1)
+            else:
+                ops.picard_pass(h_prev, h_halo, carry0, 0, h_out, state_out)
             h_prev = h_out
             traj = state_out
-        halo = None
-        if world > 1:
-            halo = yield from prev_rank_last(traj[:, -1])
         if rank == 0:
             halo = None if h0 is None else h0.contiguous()
     else:
@@ -338,15 +359,16 @@ def forward_program(ops, rank: int, world: int, K: int, P: int, h0: Tensor | Non
             return ops.newton_pass(traj, halo, carry, 2 if agg_only else (1 if last else 0), dst, k)
 
         carry, _ = yield from _sharded_scan(ops, rank, world, False, ops.monoid, None, sweep)
-        if rank > 0 and carry is not None and not last:
+        if rank > 0 and carry is not None:
             # the carry entering the shard is the update of the previous rank's last step
             c = carry if ops.slots == 4 else carry[:, 0]
             halo = halo + ops.omega * c
         traj = dst
-    # halo of the returned trajectory (I/O dtype values), used by the backward pass
-    halo_out = None
-    if world > 1:
-        halo_out = yield from prev_rank_last(out[:, -1].float())
+    # state preceding the shard in the RETURNED trajectory (used by the backward pass): the old
+    # halo plus the last update, rounded like the stored output
+    halo_out = halo
+    if rank > 0 and K > 0 and halo is not None:
+        halo_out = halo.to(out.dtype).float()
     if rank == 0:
         halo_out = h0
     bits = ops.stats_bits().clone()
