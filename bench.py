@@ -41,6 +41,9 @@ BYTES_PICARD_MID = 4 * 2 + 4 + 4          # read wx + h, write h
 BYTES_NEWTON_MID = 4 * 2 + 16 + 16        # read wx + state, write state
 BYTES_BWD = 4 * 2 + 4 * 2 + 4 * 2 + 4 * 2  # read states, wx, cotangent; write g_wx
 BYTES_STEP = 224                          # all passes of one forward + backward
+# DRAM bytes per (token, channel) of each kernel from the committed ncu capture
+# (profiles/slstm_pipe_kernels_B8_T4096_d1024_bf16.md); traffic grows in proportion to the units
+NCU_TRAFFIC_PER_UNIT = {"slstm_picard_kernel": 15.44, "slstm_newton_kernel": 39.02, "slstm_bwd_kernel": 31.37}
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
@@ -319,7 +322,7 @@ def run_gpu_single(args):
     top = max(total, key=total.get)
     roofline = {"bound": "hbm", "kernel": top, "achieved": roofs[top]["achieved"], "peak": peak,
                 "unit": "GB/s", "frac": roofs[top]["achieved"] / peak, "peak_kind": peak_kind,
-                "traffic": None, "kernels": roofs,
+                "traffic": NCU_TRAFFIC_PER_UNIT[top] * B * T_PER_GPU * D, "kernels": roofs,
                 "step": {"algorithmic_bytes": BYTES_STEP * tokens * D,
                          "achieved": BYTES_STEP * tokens * D / (ms / 1e3) / 1e9,
                          "frac": BYTES_STEP * tokens * D / (ms / 1e3) / 1e9 / peak,

@@ -28,32 +28,68 @@ __device__ __forceinline__ void stage_bar(int id) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(kHG) : "memory");
 }
 
-// dot products of two broadcast vectors with two register-resident columns
+// dot products of two broadcast vectors with two register-resident columns.  Every product is
+// split over four partial accumulators: with one warp per scheduler the latency of the dependent
+// FMA chain, not the issue rate, sets the pace.
 template <int DH>
 __device__ __forceinline__ void dot2x2(const float* va, const float* vb, const float (&c0)[DH],
                                        const float (&c1)[DH], float& a0, float& a1, float& b0, float& b1) {
-    a0 = a1 = b0 = b1 = 0.f;
+    float pa0[4] = {0.f, 0.f, 0.f, 0.f}, pa1[4] = {0.f, 0.f, 0.f, 0.f};
+    float pb0[4] = {0.f, 0.f, 0.f, 0.f}, pb1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < DH; i += 4) {
         const float4 x = *reinterpret_cast<const float4*>(va + i);
         const float4 y = *reinterpret_cast<const float4*>(vb + i);
-        a0 = fmaf(x.x, c0[i], a0); a0 = fmaf(x.y, c0[i + 1], a0); a0 = fmaf(x.z, c0[i + 2], a0); a0 = fmaf(x.w, c0[i + 3], a0);
-        a1 = fmaf(x.x, c1[i], a1); a1 = fmaf(x.y, c1[i + 1], a1); a1 = fmaf(x.z, c1[i + 2], a1); a1 = fmaf(x.w, c1[i + 3], a1);
-        b0 = fmaf(y.x, c0[i], b0); b0 = fmaf(y.y, c0[i + 1], b0); b0 = fmaf(y.z, c0[i + 2], b0); b0 = fmaf(y.w, c0[i + 3], b0);
-        b1 = fmaf(y.x, c1[i], b1); b1 = fmaf(y.y, c1[i + 1], b1); b1 = fmaf(y.z, c1[i + 2], b1); b1 = fmaf(y.w, c1[i + 3], b1);
+        const float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            pa0[k] = fmaf(xs[k], c0[i + k], pa0[k]);
+            pa1[k] = fmaf(xs[k], c1[i + k], pa1[k]);
+            pb0[k] = fmaf(ys[k], c0[i + k], pb0[k]);
+            pb1[k] = fmaf(ys[k], c1[i + k], pb1[k]);
+        }
     }
+    a0 = (pa0[0] + pa0[1]) + (pa0[2] + pa0[3]);
+    a1 = (pa1[0] + pa1[1]) + (pa1[2] + pa1[3]);
+    b0 = (pb0[0] + pb0[1]) + (pb0[2] + pb0[3]);
+    b1 = (pb1[0] + pb1[1]) + (pb1[2] + pb1[3]);
 }
 template <int DH>
 __device__ __forceinline__ void dot2x1(const float* va, const float* vb, const float (&c)[DH], float& a,
                                        float& b) {
-    a = b = 0.f;
+    float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < DH; i += 4) {
         const float4 x = *reinterpret_cast<const float4*>(va + i);
         const float4 y = *reinterpret_cast<const float4*>(vb + i);
-        a = fmaf(x.x, c[i], a); a = fmaf(x.y, c[i + 1], a); a = fmaf(x.z, c[i + 2], a); a = fmaf(x.w, c[i + 3], a);
-        b = fmaf(y.x, c[i], b); b = fmaf(y.y, c[i + 1], b); b = fmaf(y.z, c[i + 2], b); b = fmaf(y.w, c[i + 3], b);
+        const float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            pa[k] = fmaf(xs[k], c[i + k], pa[k]);
+            pb[k] = fmaf(ys[k], c[i + k], pb[k]);
+        }
     }
+    a = (pa[0] + pa[1]) + (pa[2] + pa[3]);
+    b = (pb[0] + pb[1]) + (pb[2] + pb[3]);
+}
+// two products with two different row sets (reverse kernel)
+template <int DH>
+__device__ __forceinline__ void dot1x1x2(const float* va, const float* vb, const float (&c0)[DH],
+                                         const float (&c1)[DH], float& a, float& b) {
+    float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < DH; i += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(va + i);
+        const float4 y = *reinterpret_cast<const float4*>(vb + i);
+        const float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            pa[k] = fmaf(xs[k], c0[i + k], pa[k]);
+            pb[k] = fmaf(ys[k], c1[i + k], pb[k]);
+        }
+    }
+    a = (pa[0] + pa[1]) + (pa[2] + pa[3]);
+    b = (pb[0] + pb[1]) + (pb[2] + pb[3]);
 }
 
 struct HeadFwdArgs {
@@ -126,60 +162,79 @@ __global__ void __launch_bounds__(256, 1) gru_head_newton_kernel(HeadFwdArgs a) 
     }
 
     const int n_ticks = a.T + nstg - 1;
-    for (int tick = 0; tick < n_ticks; ++tick) {
-        __syncthreads();
+    // inputs are fetched PF ticks ahead into a small register ring, so that no global-memory
+    // latency sits on the tick-to-tick critical path
+    constexpr int PF = 4;
+    float b_zx[PF], b_rx[PF], b_nx[PF], b_hin[PF];
+    auto fetch = [&](int tick, int slot) {
         const int t = tick - stage;
-        const bool on = stage < nstg && t >= 0 && t < a.T;
-        float zx = 0.f, rx = 0.f, nx = 0.f, cur = 0.f;
-        if (on) {
-            zx = ld_f(wx + (size_t)t * 3 * a.d);
-            rx = ld_f(wx + (size_t)t * 3 * a.d + a.d);
-            nx = ld_f(wx + (size_t)t * 3 * a.d + 2 * (size_t)a.d);
-            if (stage == 0) {
-                if (hin) {
-                    cur = __ldg(hin + (size_t)t * a.d);
-                } else if (t == 0 && a.h0) {
-                    cur = guess0;
-                } else {
-                    cur = sigmoid_f(zx) * tanh_f(nx);  // f(0, x): z * n
-                }
-            } else {
-                cur = s_traj[stage][(tick + 1) & 1][o];
-            }
+        b_zx[slot] = b_rx[slot] = b_nx[slot] = b_hin[slot] = 0.f;
+        if (stage < nstg && t >= 0 && t < a.T) {
+            b_zx[slot] = ld_f(wx + (size_t)t * 3 * a.d);
+            b_rx[slot] = ld_f(wx + (size_t)t * 3 * a.d + a.d);
+            b_nx[slot] = ld_f(wx + (size_t)t * 3 * a.d + 2 * (size_t)a.d);
+            if (stage == 0 && hin) b_hin[slot] = __ldg(hin + (size_t)t * a.d);
         }
-        if (stage < nstg) {
-            float pz, pr, dz, dr;
-            dot2x2<DH>(s_vec[stage][0], s_vec[stage][1], az, ar, pz, pr, dz, dr);
-            const float z = sigmoid_f(pz + zx), r = sigmoid_f(pr + rx);
-            const float rp = r * (1.f - r);
-            s_vec2[stage][0][o] = act ? hp * r : 0.f;
-            s_vec2[stage][1][o] = act ? fmaf(r, dl, hp * rp * dr) : 0.f;
-            stage_bar(1 + stage);
-            float pn, dn;
-            dot2x1<DH>(s_vec2[stage][0], s_vec2[stage][1], an, pn, dn);
+    };
+#pragma unroll
+    for (int j = 0; j < PF; ++j) fetch(j, j);
+    for (int tick0 = 0; tick0 < n_ticks; tick0 += PF) {
+#pragma unroll
+        for (int j = 0; j < PF; ++j) {
+            const int tick = tick0 + j;
+            if (tick >= n_ticks) break;
+            __syncthreads();
+            const int t = tick - stage;
+            const bool on = stage < nstg && t >= 0 && t < a.T;
+            const float zx = b_zx[j], rx = b_rx[j], nx = b_nx[j];
+            float cur = 0.f;
             if (on) {
-                const float n = tanh_f(pn + nx);
-                const float f = fmaf(z, n - hp, hp);
-                const float F = f - cur;
-                if (act) rmax = max(rmax, absbits(F));
-                if (!is_resid) {
-                    const float jd = (1.f - z) * dl + (n - hp) * z * (1.f - z) * dz + z * (1.f - n * n) * dn;
-                    dl = jd + F;
-                    const float nv = fmaf(a.omega, dl, cur);
-                    s_traj[stage + 1][tick & 1][o] = nv;
-                    if (stage == a.n_newton - 1 && act) {
-                        const size_t idx = ((size_t)b * a.T + t) * a.d + head * DH + o;
-                        if (a.out_io)
-                            st_f(reinterpret_cast<TIO*>(a.hout) + idx, nv);
-                        else
-                            reinterpret_cast<float*>(a.hout)[idx] = nv;
+                if (stage == 0) {
+                    if (hin) {
+                        cur = b_hin[j];
+                    } else if (t == 0 && a.h0) {
+                        cur = guess0;
+                    } else {
+                        cur = sigmoid_f(zx) * tanh_f(nx);  // f(0, x): z * n
                     }
+                } else {
+                    cur = s_traj[stage][(tick + 1) & 1][o];
                 }
-                hp = cur;
             }
-            // vectors of the next tick (all reads of this tick's vectors are behind the stage barrier)
-            s_vec[stage][0][o] = act ? hp : 0.f;
-            s_vec[stage][1][o] = act ? dl : 0.f;
+            fetch(tick + PF, j);
+            if (stage < nstg) {
+                float pz, pr, dz, dr;
+                dot2x2<DH>(s_vec[stage][0], s_vec[stage][1], az, ar, pz, pr, dz, dr);
+                const float z = sigmoid_f(pz + zx), r = sigmoid_f(pr + rx);
+                const float rp = r * (1.f - r);
+                s_vec2[stage][0][o] = act ? hp * r : 0.f;
+                s_vec2[stage][1][o] = act ? fmaf(r, dl, hp * rp * dr) : 0.f;
+                stage_bar(1 + stage);
+                float pn, dn;
+                dot2x1<DH>(s_vec2[stage][0], s_vec2[stage][1], an, pn, dn);
+                if (on) {
+                    const float n = tanh_f(pn + nx);
+                    const float f = fmaf(z, n - hp, hp);
+                    const float F = f - cur;
+                    if (act) rmax = max(rmax, absbits(F));
+                    if (!is_resid) {
+                        const float jd = (1.f - z) * dl + (n - hp) * z * (1.f - z) * dz + z * (1.f - n * n) * dn;
+                        dl = jd + F;
+                        const float nv = fmaf(a.omega, dl, cur);
+                        s_traj[stage + 1][tick & 1][o] = nv;
+                        if (stage == a.n_newton - 1 && act) {
+                            const size_t idx = ((size_t)b * a.T + t) * a.d + head * DH + o;
+                            if (a.out_io)
+                                st_f(reinterpret_cast<TIO*>(a.hout) + idx, nv);
+                            else
+                                reinterpret_cast<float*>(a.hout)[idx] = nv;
+                        }
+                    }
+                    hp = cur;
+                }
+                s_vec[stage][0][o] = act ? hp : 0.f;
+                s_vec[stage][1][o] = act ? dl : 0.f;
+            }
         }
     }
     // per-stage maxima: stage s < n_newton -> hist_bits[s]; residual stage -> final_bits
@@ -245,63 +300,84 @@ __global__ void __launch_bounds__(128, 1) gru_head_bwd_kernel(HeadBwdArgs a) {
     s_w[0][o] = 0.f; s_w[1][o] = 0.f; s_v3[0][o] = 0.f; s_v3[1][o] = 0.f;
     float nu = 0.f;
     __syncthreads();
-    // tick k: gate group handles step T-1-k, adjoint group handles step T-k (one tick later)
-    for (int k = 0; k <= a.T; ++k) {
+    // tick k: gate group handles step T-1-k, adjoint group handles step T-k (one tick later).
+    // Global inputs are fetched PF ticks ahead into a register ring.
+    constexpr int PF = 4;
+    float b0[PF], b1[PF], b2[PF], b3[PF];
+    auto fetch = [&](int k, int slot) {
+        b0[slot] = b1[slot] = b2[slot] = b3[slot] = 0.f;
         if (grp == 0) {
             const int t = a.T - 1 - k;
-            if (t >= 0) {
-                const float hpv = (t == 0) ? h_init : ld_f(st + (size_t)(t - 1) * a.d);
-                s_h[0][o] = act ? hpv : 0.f;
-                stage_bar(1);
-                float pz, pr, d0, d1;
-                dot2x2<DH>(s_h[0], s_h[1], m0, m1, pz, pr, d0, d1);
-                const float z = sigmoid_f(pz + ld_f(wx + (size_t)t * 3 * a.d));
-                const float r = sigmoid_f(pr + ld_f(wx + (size_t)t * 3 * a.d + a.d));
-                s_u[0][o] = act ? hpv * r : 0.f;
-                stage_bar(1);
-                float pn, d2;
-                dot2x1<DH>(s_u[0], s_u[1], m2, pn, d2);
-                const float n = tanh_f(pn + ld_f(wx + (size_t)t * 3 * a.d + 2 * (size_t)a.d));
-                s_gate[k & 1][0][o] = z;
-                s_gate[k & 1][1][o] = r;
-                s_gate[k & 1][2][o] = n;
-                s_gate[k & 1][3][o] = hpv;
-                if (act) a.u_out[base + (size_t)t * a.d] = hpv * r;
+            if (t >= 0 && k >= 0) {
+                b0[slot] = (t == 0) ? h_init : ld_f(st + (size_t)(t - 1) * a.d);
+                b1[slot] = ld_f(wx + (size_t)t * 3 * a.d);
+                b2[slot] = ld_f(wx + (size_t)t * 3 * a.d + a.d);
+                b3[slot] = ld_f(wx + (size_t)t * 3 * a.d + 2 * (size_t)a.d);
             }
         } else {
             const int t = a.T - k;
-            if (t < a.T) {
-                const float z = s_gate[(k + 1) & 1][0][o], r = s_gate[(k + 1) & 1][1][o];
-                const float n = s_gate[(k + 1) & 1][2][o], hpv = s_gate[(k + 1) & 1][3][o];
-                const float mu = nu + ld_f(gs + (size_t)t * a.d);
-                const float w_z = z * (1.f - z) * (n - hpv) * mu;
-                const float w_n = (1.f - n * n) * z * mu;
-                s_w[0][o] = act ? w_z : 0.f;
-                s_w[1][o] = act ? w_n : 0.f;
-                stage_bar(2);
-                // t2 = A_z w_z (rows of A_z), g = A_n w_n (rows of A_n)
-                float t2 = 0.f, g = 0.f;
-#pragma unroll
-                for (int i = 0; i < DH; i += 4) {
-                    const float4 x = *reinterpret_cast<const float4*>(s_w[0] + i);
-                    const float4 y = *reinterpret_cast<const float4*>(s_w[1] + i);
-                    t2 = fmaf(x.x, m0[i], t2); t2 = fmaf(x.y, m0[i + 1], t2); t2 = fmaf(x.z, m0[i + 2], t2); t2 = fmaf(x.w, m0[i + 3], t2);
-                    g = fmaf(y.x, m2[i], g); g = fmaf(y.y, m2[i + 1], g); g = fmaf(y.z, m2[i + 2], g); g = fmaf(y.w, m2[i + 3], g);
-                }
-                const float v3 = r * (1.f - r) * hpv * g;
-                s_v3[0][o] = act ? v3 : 0.f;
-                stage_bar(2);
-                float t4, d3;
-                dot2x1<DH>(s_v3[0], s_v3[1], m1, t4, d3);
-                if (act) {
-                    st_f(gwx + (size_t)t * 3 * a.d, w_z);
-                    st_f(gwx + (size_t)t * 3 * a.d + a.d, v3);
-                    st_f(gwx + (size_t)t * 3 * a.d + 2 * (size_t)a.d, w_n);
-                }
-                nu = (1.f - z) * mu + t2 + r * g + t4;
-            }
+            if (t >= 0 && t < a.T) b0[slot] = ld_f(gs + (size_t)t * a.d);
         }
-        __syncthreads();
+    };
+#pragma unroll
+    for (int j = 0; j < PF; ++j) fetch(j, j);
+    for (int k0 = 0; k0 <= a.T; k0 += PF) {
+#pragma unroll
+        for (int j = 0; j < PF; ++j) {
+            const int k = k0 + j;
+            if (k > a.T) break;
+            if (grp == 0) {
+                const int t = a.T - 1 - k;
+                const float hpv = b0[j], zx = b1[j], rx = b2[j], nx = b3[j];
+                fetch(k + PF, j);
+                if (t >= 0) {
+                    s_h[0][o] = act ? hpv : 0.f;
+                    stage_bar(1);
+                    float pz, pr, d0, d1;
+                    dot2x2<DH>(s_h[0], s_h[1], m0, m1, pz, pr, d0, d1);
+                    const float z = sigmoid_f(pz + zx);
+                    const float r = sigmoid_f(pr + rx);
+                    s_u[0][o] = act ? hpv * r : 0.f;
+                    stage_bar(1);
+                    float pn, d2;
+                    dot2x1<DH>(s_u[0], s_u[1], m2, pn, d2);
+                    const float n = tanh_f(pn + nx);
+                    s_gate[k & 1][0][o] = z;
+                    s_gate[k & 1][1][o] = r;
+                    s_gate[k & 1][2][o] = n;
+                    s_gate[k & 1][3][o] = hpv;
+                    if (act) a.u_out[base + (size_t)t * a.d] = hpv * r;
+                }
+            } else {
+                const int t = a.T - k;
+                const float gv = b0[j];
+                fetch(k + PF, j);
+                if (t < a.T) {
+                    const float z = s_gate[(k + 1) & 1][0][o], r = s_gate[(k + 1) & 1][1][o];
+                    const float n = s_gate[(k + 1) & 1][2][o], hpv = s_gate[(k + 1) & 1][3][o];
+                    const float mu = nu + gv;
+                    const float w_z = z * (1.f - z) * (n - hpv) * mu;
+                    const float w_n = (1.f - n * n) * z * mu;
+                    s_w[0][o] = act ? w_z : 0.f;
+                    s_w[1][o] = act ? w_n : 0.f;
+                    stage_bar(2);
+                    float t2, g;
+                    dot1x1x2<DH>(s_w[0], s_w[1], m0, m2, t2, g);
+                    const float v3 = r * (1.f - r) * hpv * g;
+                    s_v3[0][o] = act ? v3 : 0.f;
+                    stage_bar(2);
+                    float t4, d3;
+                    dot2x1<DH>(s_v3[0], s_v3[1], m1, t4, d3);
+                    if (act) {
+                        st_f(gwx + (size_t)t * 3 * a.d, w_z);
+                        st_f(gwx + (size_t)t * 3 * a.d + a.d, v3);
+                        st_f(gwx + (size_t)t * 3 * a.d + 2 * (size_t)a.d, w_n);
+                    }
+                    nu = (1.f - z) * mu + t2 + r * g + t4;
+                }
+            }
+            __syncthreads();
+        }
     }
     if (grp == 1 && act && a.g_h0) a.g_h0[(size_t)b * a.d + head * DH + o] = nu;
 }
