@@ -110,11 +110,11 @@ int prb_newton_gru_head_fused(const void* wx, const void* a_z, const void* a_r, 
  * pararnn::reverse_gru_head_factor (kernels/custom_ops.py:389-434,
  * kernels/newton_gru_head.py:198-258,570-652), gru_head_t0_vjp (:261-297) and the g_wx part of
  * gru_head_recurrence_vjp (kernels/vjp_gru.py:656-810).  g_wx (B,T,3d) I/O dtype;
- * u_out (B,T,d) fp32 = h_prev * r; g_h0 (B,d) fp32 or NULL.  The parameter gradients are
- * batched outer-product sums the caller forms with a library GEMM:
- * grad A_z = sum h_prev^T g_z, grad A_r = sum h_prev^T g_r, grad A_n = sum u^T g_n. */
+ * g_a (3,H,dh,dh) fp32 = grad of (A_z, A_r, A_n), the outer-product sums
+ * sum h_prev^T g_z, sum h_prev^T g_r, sum (h_prev r)^T g_n accumulated in the same sweep
+ * (no clip mask applied); g_h0 (B,d) fp32 or NULL. */
 int prb_bwd_gru_head(const void* states, const void* wx, const void* a_z, const void* a_r,
-                     const void* a_n, const void* h0, const void* grad_states, void* g_wx, float* u_out,
+                     const void* a_n, const void* h0, const void* grad_states, void* g_wx, float* g_a,
                      float* g_h0, int B, int T, int d, int n_heads, int dtype, void* workspace,
                      size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
 

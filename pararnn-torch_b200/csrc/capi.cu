@@ -556,6 +556,7 @@ struct HeadPlan {
     float* A;
     float* h0;
     float* buf[2];
+    float* gA_part;
     size_t total;
 };
 HeadPlan plan_head(void* ws, int B, int T, int d, int H, int K) {
@@ -567,6 +568,7 @@ HeadPlan plan_head(void* ws, int B, int T, int d, int H, int K) {
     const size_t n = (size_t)B * T * d;
     p.buf[0] = K > 3 ? b.take<float>(n) : nullptr;
     p.buf[1] = K > 6 ? b.take<float>(n) : nullptr;
+    p.gA_part = b.take<float>((size_t)B * 3 * H * dh * dh);
     p.total = b.off + 256;
     return p;
 }
@@ -630,11 +632,11 @@ int prb_newton_gru_head_fused(const void* wx, const void* a_z, const void* a_r, 
 }
 
 int prb_bwd_gru_head(const void* states, const void* wx, const void* a_z, const void* a_r,
-                     const void* a_n, const void* h0, const void* grad_states, void* g_wx, float* u_out,
+                     const void* a_n, const void* h0, const void* grad_states, void* g_wx, float* g_a,
                      float* g_h0, int B, int T, int d, int n_heads, int dtype, void* workspace,
                      size_t workspace_bytes, prb_stats* stats, prb_stream_t stream) {
     cudaStream_t s = (cudaStream_t)stream;
-    if (!states || !wx || !a_z || !a_r || !a_n || !grad_states || !g_wx || !u_out || !stats || B < 1 ||
+    if (!states || !wx || !a_z || !a_r || !a_n || !grad_states || !g_wx || !g_a || !stats || B < 1 ||
         T < 1 || d < 1 || bad_dtype(dtype))
         return PRB_ERR_BAD_ARG;
     if (!head_dim_ok(d, n_heads)) return PRB_ERR_UNSUPPORTED;
@@ -652,10 +654,11 @@ int prb_bwd_gru_head(const void* states, const void* wx, const void* a_z, const 
         to_f32(h0, p.h0, (size_t)B * d, dtype, s);
         h0f = p.h0;
     }
-    return launch_gru_head_bwd(dtype, wx, states, grad_states, p.A, h0f, g_wx, u_out, g_h0, B, T, d, H, s) ==
-                   cudaSuccess
-               ? PRB_OK
-               : PRB_ERR_LAUNCH;
+    if (launch_gru_head_bwd(dtype, wx, states, grad_states, p.A, h0f, g_wx, p.gA_part, g_h0, B, T, d, H, s) !=
+        cudaSuccess)
+        return PRB_ERR_LAUNCH;
+    return launch_reduce_partials(p.gA_part, B, 3 * H * dh * dh, g_a, s) == cudaSuccess ? PRB_OK
+                                                                                         : PRB_ERR_LAUNCH;
 }
 
 /* ---- pass-level entry points (time-sharded driver, profiling) ------------------- */

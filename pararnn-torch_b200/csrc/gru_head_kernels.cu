@@ -24,6 +24,17 @@ namespace prb {
 
 constexpr int kHG = 64;  // threads per stage group
 
+// Raw loads for the prefetch rings: the conversion to float happens where the value is used, so
+// that nothing waits on the load at the point where it is issued.
+__device__ __forceinline__ float raw_f(float v) { return v; }
+__device__ __forceinline__ float raw_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T raw_zero();
+template <>
+__device__ __forceinline__ float raw_zero<float>() { return 0.f; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 raw_zero<__nv_bfloat16>() { return __ushort_as_bfloat16(0); }
+
 __device__ __forceinline__ void stage_bar(int id) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(kHG) : "memory");
 }
@@ -90,6 +101,38 @@ __device__ __forceinline__ void dot1x1x2(const float* va, const float* vb, const
     }
     a = (pa[0] + pa[1]) + (pa[2] + pa[3]);
     b = (pb[0] + pb[1]) + (pb[2] + pb[3]);
+}
+
+// one broadcast vector against two / one register-resident columns
+template <int DH>
+__device__ __forceinline__ void dot1x2(const float* va, const float (&c0)[DH], const float (&c1)[DH],
+                                       float& a0, float& a1) {
+    float p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < DH; i += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(va + i);
+        const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            p0[k] = fmaf(xs[k], c0[i + k], p0[k]);
+            p1[k] = fmaf(xs[k], c1[i + k], p1[k]);
+        }
+    }
+    a0 = (p0[0] + p0[1]) + (p0[2] + p0[3]);
+    a1 = (p1[0] + p1[1]) + (p1[2] + p1[3]);
+}
+template <int DH>
+__device__ __forceinline__ float dot1x1(const float* va, const float (&c)[DH]) {
+    float p[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < DH; i += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(va + i);
+        p[0] = fmaf(x.x, c[i], p[0]);
+        p[1] = fmaf(x.y, c[i + 1], p[1]);
+        p[2] = fmaf(x.z, c[i + 2], p[2]);
+        p[3] = fmaf(x.w, c[i + 3], p[3]);
+    }
+    return (p[0] + p[1]) + (p[2] + p[3]);
 }
 
 struct HeadFwdArgs {
@@ -165,14 +208,16 @@ __global__ void __launch_bounds__(256, 1) gru_head_newton_kernel(HeadFwdArgs a) 
     // inputs are fetched PF ticks ahead into a small register ring, so that no global-memory
     // latency sits on the tick-to-tick critical path
     constexpr int PF = 4;
-    float b_zx[PF], b_rx[PF], b_nx[PF], b_hin[PF];
+    TIO b_zx[PF], b_rx[PF], b_nx[PF];
+    float b_hin[PF];
     auto fetch = [&](int tick, int slot) {
         const int t = tick - stage;
-        b_zx[slot] = b_rx[slot] = b_nx[slot] = b_hin[slot] = 0.f;
+        b_zx[slot] = b_rx[slot] = b_nx[slot] = raw_zero<TIO>();
+        b_hin[slot] = 0.f;
         if (stage < nstg && t >= 0 && t < a.T) {
-            b_zx[slot] = ld_f(wx + (size_t)t * 3 * a.d);
-            b_rx[slot] = ld_f(wx + (size_t)t * 3 * a.d + a.d);
-            b_nx[slot] = ld_f(wx + (size_t)t * 3 * a.d + 2 * (size_t)a.d);
+            b_zx[slot] = __ldg(wx + (size_t)t * 3 * a.d);
+            b_rx[slot] = __ldg(wx + (size_t)t * 3 * a.d + a.d);
+            b_nx[slot] = __ldg(wx + (size_t)t * 3 * a.d + 2 * (size_t)a.d);
             if (stage == 0 && hin) b_hin[slot] = __ldg(hin + (size_t)t * a.d);
         }
     };
@@ -186,7 +231,7 @@ __global__ void __launch_bounds__(256, 1) gru_head_newton_kernel(HeadFwdArgs a) 
             __syncthreads();
             const int t = tick - stage;
             const bool on = stage < nstg && t >= 0 && t < a.T;
-            const float zx = b_zx[j], rx = b_rx[j], nx = b_nx[j];
+            const float zx = raw_f(b_zx[j]), rx = raw_f(b_rx[j]), nx = raw_f(b_nx[j]);
             float cur = 0.f;
             if (on) {
                 if (stage == 0) {
@@ -254,21 +299,25 @@ struct HeadBwdArgs {
     const float* A;           // (3,H,dh,dh)
     const float* h0;          // (B,d) fp32 or null
     void* g_wx;               // (B,T,3d) I/O dtype
-    float* u_out;             // (B,T,d) fp32: h_prev * r (operand of the A_n gradient)
+    float* gA_part;           // (B,3,H,dh,dh) fp32: this batch row's share of grad A
     float* g_h0;              // (B,d) fp32 or null
     int B, T, d, H;
 };
 
-// Two groups of 64 threads per (batch row, head): group 0 recomputes the gates of step t one
-// tick ahead (columns of A in registers), group 1 walks the adjoint backwards (rows of A in
-// registers):  nu_{t-1} = J_t^T (nu_t + g_t).
+// Three groups of 64 threads per (batch row, head), skewed by one tick each:
+//   group 0 recomputes the gates of step t (columns of A in registers),
+//   group 1 walks the adjoint backwards, nu_{t-1} = J_t^T (nu_t + g_t) (rows of A in registers),
+//   group 2 accumulates the outer products of the packed VJP,
+//           grad A_z += h_prev^T d_z, grad A_r += h_prev^T d_r, grad A_n += (h_prev r)^T d_n,
+//           thread o keeping column o of all three in registers for the whole sweep.
 template <typename TIO, int DH>
-__global__ void __launch_bounds__(128, 1) gru_head_bwd_kernel(HeadBwdArgs a) {
-    __shared__ __align__(16) float s_h[2][kHG];       // h_prev broadcast for the gate group
-    __shared__ __align__(16) float s_u[2][kHG];       // h_prev * r
+__global__ void __launch_bounds__(192, 1) gru_head_bwd_kernel(HeadBwdArgs a) {
+    __shared__ __align__(16) float s_h[3][kHG];       // h_prev of the last three steps (ring)
+    __shared__ __align__(16) float s_u[3][kHG];       // h_prev * r, same ring
     __shared__ float s_gate[2][4][kHG];               // z, r, n, h_prev handed to the adjoint group
     __shared__ __align__(16) float s_w[2][kHG];       // w_z, w_n
-    __shared__ __align__(16) float s_v3[2][kHG];      // r' h g (second slot unused, kept zero)
+    __shared__ __align__(16) float s_v3[kHG];         // r' h g
+    __shared__ float s_d[2][3][kHG];                  // d_z, d_r, d_n handed to the outer-product group
     const int grp = threadIdx.x / kHG, o = threadIdx.x % kHG;
     const int b = blockIdx.x / a.H, head = blockIdx.x % a.H;
     const bool act = o < DH;
@@ -280,14 +329,16 @@ __global__ void __launch_bounds__(128, 1) gru_head_bwd_kernel(HeadBwdArgs a) {
     float m0[DH], m1[DH], m2[DH];
 #pragma unroll
     for (int i = 0; i < DH; ++i) {
-        if (grp == 0) {  // columns: m[i] = A[i][o]
+        if (grp == 0) {         // columns: m[i] = A[i][o]
             m0[i] = __ldg(Az + (size_t)i * DH + oc);
             m1[i] = __ldg(Ar + (size_t)i * DH + oc);
             m2[i] = __ldg(An + (size_t)i * DH + oc);
-        } else {         // rows: m[k] = A[o][k]
+        } else if (grp == 1) {  // rows: m[k] = A[o][k]
             m0[i] = __ldg(Az + (size_t)oc * DH + i);
             m1[i] = __ldg(Ar + (size_t)oc * DH + i);
             m2[i] = __ldg(An + (size_t)oc * DH + i);
+        } else {                // accumulators of grad A[i][o]
+            m0[i] = 0.f; m1[i] = 0.f; m2[i] = 0.f;
         }
     }
     const size_t base = (size_t)b * a.T * a.d + head * DH + oc;
@@ -296,63 +347,65 @@ __global__ void __launch_bounds__(128, 1) gru_head_bwd_kernel(HeadBwdArgs a) {
     const TIO* gs = reinterpret_cast<const TIO*>(a.grad_states) + base;
     TIO* gwx = reinterpret_cast<TIO*>(a.g_wx) + (size_t)b * a.T * 3 * a.d + head * DH + oc;
     const float h_init = a.h0 ? __ldg(a.h0 + (size_t)b * a.d + head * DH + oc) : 0.f;
-    s_h[0][o] = 0.f; s_h[1][o] = 0.f; s_u[0][o] = 0.f; s_u[1][o] = 0.f;
-    s_w[0][o] = 0.f; s_w[1][o] = 0.f; s_v3[0][o] = 0.f; s_v3[1][o] = 0.f;
+    if (grp == 0) {
+#pragma unroll
+        for (int j = 0; j < 3; ++j) { s_h[j][o] = 0.f; s_u[j][o] = 0.f; }
+        s_w[0][o] = 0.f; s_w[1][o] = 0.f; s_v3[o] = 0.f;
+    }
     float nu = 0.f;
     __syncthreads();
-    // tick k: gate group handles step T-1-k, adjoint group handles step T-k (one tick later).
+    // tick k: group 0 handles step T-1-k, group 1 step T-k, group 2 step T+1-k.
     // Global inputs are fetched PF ticks ahead into a register ring.
     constexpr int PF = 4;
-    float b0[PF], b1[PF], b2[PF], b3[PF];
+    TIO b0[PF], b1[PF], b2[PF], b3[PF];
     auto fetch = [&](int k, int slot) {
-        b0[slot] = b1[slot] = b2[slot] = b3[slot] = 0.f;
+        b0[slot] = b1[slot] = b2[slot] = b3[slot] = raw_zero<TIO>();
         if (grp == 0) {
             const int t = a.T - 1 - k;
             if (t >= 0 && k >= 0) {
-                b0[slot] = (t == 0) ? h_init : ld_f(st + (size_t)(t - 1) * a.d);
-                b1[slot] = ld_f(wx + (size_t)t * 3 * a.d);
-                b2[slot] = ld_f(wx + (size_t)t * 3 * a.d + a.d);
-                b3[slot] = ld_f(wx + (size_t)t * 3 * a.d + 2 * (size_t)a.d);
+                if (t > 0) b0[slot] = __ldg(st + (size_t)(t - 1) * a.d);
+                b1[slot] = __ldg(wx + (size_t)t * 3 * a.d);
+                b2[slot] = __ldg(wx + (size_t)t * 3 * a.d + a.d);
+                b3[slot] = __ldg(wx + (size_t)t * 3 * a.d + 2 * (size_t)a.d);
             }
-        } else {
+        } else if (grp == 1) {
             const int t = a.T - k;
-            if (t >= 0 && t < a.T) b0[slot] = ld_f(gs + (size_t)t * a.d);
+            if (t >= 0 && t < a.T) b0[slot] = __ldg(gs + (size_t)t * a.d);
         }
     };
 #pragma unroll
     for (int j = 0; j < PF; ++j) fetch(j, j);
-    for (int k0 = 0; k0 <= a.T; k0 += PF) {
+    int ring = 0;  // k % 3
+    for (int k0 = 0; k0 <= a.T + 1; k0 += PF) {
 #pragma unroll
         for (int j = 0; j < PF; ++j) {
             const int k = k0 + j;
-            if (k > a.T) break;
+            if (k > a.T + 1) break;
             if (grp == 0) {
                 const int t = a.T - 1 - k;
-                const float hpv = b0[j], zx = b1[j], rx = b2[j], nx = b3[j];
+                const float hpv = (t == 0) ? h_init : raw_f(b0[j]);
+                const float zx = raw_f(b1[j]), rx = raw_f(b2[j]), nx = raw_f(b3[j]);
                 fetch(k + PF, j);
                 if (t >= 0) {
-                    s_h[0][o] = act ? hpv : 0.f;
+                    s_h[ring][o] = act ? hpv : 0.f;
                     stage_bar(1);
-                    float pz, pr, d0, d1;
-                    dot2x2<DH>(s_h[0], s_h[1], m0, m1, pz, pr, d0, d1);
+                    float pz, pr;
+                    dot1x2<DH>(s_h[ring], m0, m1, pz, pr);
                     const float z = sigmoid_f(pz + zx);
                     const float r = sigmoid_f(pr + rx);
-                    s_u[0][o] = act ? hpv * r : 0.f;
+                    s_u[ring][o] = act ? hpv * r : 0.f;
                     stage_bar(1);
-                    float pn, d2;
-                    dot2x1<DH>(s_u[0], s_u[1], m2, pn, d2);
-                    const float n = tanh_f(pn + nx);
+                    const float n = tanh_f(dot1x1<DH>(s_u[ring], m2) + nx);
                     s_gate[k & 1][0][o] = z;
                     s_gate[k & 1][1][o] = r;
                     s_gate[k & 1][2][o] = n;
                     s_gate[k & 1][3][o] = hpv;
-                    if (act) a.u_out[base + (size_t)t * a.d] = hpv * r;
                 }
-            } else {
+            } else if (grp == 1) {
                 const int t = a.T - k;
-                const float gv = b0[j];
+                const float gv = raw_f(b0[j]);
                 fetch(k + PF, j);
-                if (t < a.T) {
+                if (t >= 0 && t < a.T) {
                     const float z = s_gate[(k + 1) & 1][0][o], r = s_gate[(k + 1) & 1][1][o];
                     const float n = s_gate[(k + 1) & 1][2][o], hpv = s_gate[(k + 1) & 1][3][o];
                     const float mu = nu + gv;
@@ -364,22 +417,54 @@ __global__ void __launch_bounds__(128, 1) gru_head_bwd_kernel(HeadBwdArgs a) {
                     float t2, g;
                     dot1x1x2<DH>(s_w[0], s_w[1], m0, m2, t2, g);
                     const float v3 = r * (1.f - r) * hpv * g;
-                    s_v3[0][o] = act ? v3 : 0.f;
+                    s_v3[o] = act ? v3 : 0.f;
                     stage_bar(2);
-                    float t4, d3;
-                    dot2x1<DH>(s_v3[0], s_v3[1], m1, t4, d3);
+                    const float t4 = dot1x1<DH>(s_v3, m1);
                     if (act) {
                         st_f(gwx + (size_t)t * 3 * a.d, w_z);
                         st_f(gwx + (size_t)t * 3 * a.d + a.d, v3);
                         st_f(gwx + (size_t)t * 3 * a.d + 2 * (size_t)a.d, w_n);
                     }
+                    s_d[k & 1][0][o] = w_z;
+                    s_d[k & 1][1][o] = v3;
+                    s_d[k & 1][2][o] = w_n;
                     nu = (1.f - z) * mu + t2 + r * g + t4;
                 }
+            } else {
+                const int t = a.T + 1 - k;
+                if (t >= 0 && t < a.T) {
+                    const float dz = s_d[(k + 1) & 1][0][o], dr = s_d[(k + 1) & 1][1][o];
+                    const float dn = s_d[(k + 1) & 1][2][o];
+                    const int slot = ring == 2 ? 0 : ring + 1;  // (k - 2) % 3
+#pragma unroll
+                    for (int i = 0; i < DH; i += 4) {
+                        const float4 x = *reinterpret_cast<const float4*>(&s_h[slot][i]);
+                        const float4 y = *reinterpret_cast<const float4*>(&s_u[slot][i]);
+                        const float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            m0[i + q] = fmaf(xs[q], dz, m0[i + q]);
+                            m1[i + q] = fmaf(xs[q], dr, m1[i + q]);
+                            m2[i + q] = fmaf(ys[q], dn, m2[i + q]);
+                        }
+                    }
+                }
             }
+            ring = ring == 2 ? 0 : ring + 1;
             __syncthreads();
         }
     }
     if (grp == 1 && act && a.g_h0) a.g_h0[(size_t)b * a.d + head * DH + o] = nu;
+    if (grp == 2 && act) {
+        float* dst = a.gA_part + (((size_t)b * 3) * a.H + head) * hs + o;
+        const size_t gs3 = (size_t)a.H * hs;
+#pragma unroll
+        for (int i = 0; i < DH; ++i) {
+            dst[(size_t)i * DH] = m0[i];
+            dst[gs3 + (size_t)i * DH] = m1[i];
+            dst[2 * gs3 + (size_t)i * DH] = m2[i];
+        }
+    }
 }
 
 // ------------------------------------------------------------------ launchers
@@ -411,19 +496,19 @@ template <typename TIO>
 static cudaError_t launch_head_bwd_t(const HeadBwdArgs& a, int dh, cudaStream_t s) {
     const int grid = a.B * a.H;
     switch (dh) {
-        case 8: gru_head_bwd_kernel<TIO, 8><<<grid, 128, 0, s>>>(a); break;
-        case 16: gru_head_bwd_kernel<TIO, 16><<<grid, 128, 0, s>>>(a); break;
-        case 32: gru_head_bwd_kernel<TIO, 32><<<grid, 128, 0, s>>>(a); break;
-        case 64: gru_head_bwd_kernel<TIO, 64><<<grid, 128, 0, s>>>(a); break;
+        case 8: gru_head_bwd_kernel<TIO, 8><<<grid, 192, 0, s>>>(a); break;
+        case 16: gru_head_bwd_kernel<TIO, 16><<<grid, 192, 0, s>>>(a); break;
+        case 32: gru_head_bwd_kernel<TIO, 32><<<grid, 192, 0, s>>>(a); break;
+        case 64: gru_head_bwd_kernel<TIO, 64><<<grid, 192, 0, s>>>(a); break;
         default: return cudaErrorNotSupported;
     }
     return cudaGetLastError();
 }
 
 cudaError_t launch_gru_head_bwd(int dtype, const void* wx, const void* states, const void* grad_states,
-                                const float* A, const float* h0, void* g_wx, float* u_out, float* g_h0,
+                                const float* A, const float* h0, void* g_wx, float* gA_part, float* g_h0,
                                 int B, int T, int d, int H, cudaStream_t s) {
-    HeadBwdArgs a{wx, states, grad_states, A, h0, g_wx, u_out, g_h0, B, T, d, H};
+    HeadBwdArgs a{wx, states, grad_states, A, h0, g_wx, gA_part, g_h0, B, T, d, H};
     return dtype == kF32 ? launch_head_bwd_t<float>(a, d / H, s) : launch_head_bwd_t<__nv_bfloat16>(a, d / H, s);
 }
 

@@ -140,7 +140,7 @@ cudaError_t launch_gru_head_fwd(int dtype, const void* wx, const float* A, const
                                 unsigned* hist_bits, unsigned* final_bits, int B, int T, int d, int H,
                                 float omega, cudaStream_t s);
 cudaError_t launch_gru_head_bwd(int dtype, const void* wx, const void* states, const void* grad_states,
-                                const float* A, const float* h0, void* g_wx, float* u_out, float* g_h0,
+                                const float* A, const float* h0, void* g_wx, float* gA_part, float* g_h0,
                                 int B, int T, int d, int H, cudaStream_t s);
 
 }  // namespace prb

@@ -60,7 +60,7 @@ def gru_head_reverse_vjp(states: Tensor, wx: Tensor, a_z: Tensor, a_r: Tensor, a
                          grad_states: Tensor, h0: Tensor | None = None):
     """Reverse walk with the factorised ``J^T`` fused with the gate part of the packed VJP.
     Returns ``(g_wx, g_Az, g_Ar, g_An, g_h0)``; the ``A`` gradients are fp32 ``(H, dh, dh)``
-    outer-product sums formed with one batched GEMM each (no clip mask applied)."""
+    outer-product sums accumulated by the same kernel (no clip mask applied)."""
     dev = _check_cuda(states, wx, a_z, a_r, a_n, grad_states, h0)
     B, T, d, H = _head_shape(wx, a_z)
     dh = d // H
@@ -72,24 +72,15 @@ def gru_head_reverse_vjp(states: Tensor, wx: Tensor, a_z: Tensor, a_r: Tensor, a
     gs = grad_states.detach().to(wx.dtype).contiguous()
     az, ar, an, h0c = _same(a_z, wx), _same(a_r, wx), _same(a_n, wx), _same(h0, wx)
     g_wx = torch.empty_like(wx_c)
-    u = torch.empty(B, T, d, dtype=torch.float32, device=dev)
+    g_a = torch.empty(3, H, dh, dh, dtype=torch.float32, device=dev)
     g_h0 = torch.empty(B, d, dtype=torch.float32, device=dev)
     sb = DeviceStats(dev, 0)
     lib = L.lib()
     with torch.cuda.device(dev):
         ws = _workspace(lib.prb_gru_head_workspace_bytes(B, T, d, H, 0), dev)
         rc = lib.prb_bwd_gru_head(_ptr(st), _ptr(wx_c), _ptr(az), _ptr(ar), _ptr(an), _ptr(h0c), _ptr(gs),
-                                  _ptr(g_wx), _ptr(u), _ptr(g_h0), B, T, d, H, code, _ptr(ws), ws.numel(),
+                                  _ptr(g_wx), _ptr(g_a), _ptr(g_h0), B, T, d, H, code, _ptr(ws), ws.numel(),
                                   _ptr(sb.buf), _stream(dev))
     _raise(rc, "gru_head_reverse_vjp")
-    # parameter gradients: (H, dh, B*T) @ (H, B*T, dh) batched GEMMs in fp32
-    h_prev = torch.empty(B, T, d, dtype=torch.float32, device=dev)
-    h_prev[:, 1:] = st[:, :-1].float()
-    h_prev[:, 0] = 0.0 if h0c is None else h0c.float()
-    gz, gr, gn = g_wx.float().view(B * T, 3, H, dh).unbind(1)
-    hp = h_prev.view(B * T, H, dh).permute(1, 2, 0)
-    uu = u.view(B * T, H, dh).permute(1, 2, 0)
-    g_az = torch.bmm(hp, gz.permute(1, 0, 2))
-    g_ar = torch.bmm(hp, gr.permute(1, 0, 2))
-    g_an = torch.bmm(uu, gn.permute(1, 0, 2))
+    g_az, g_ar, g_an = g_a.unbind(0)
     return g_wx, g_az, g_ar, g_an, g_h0
