@@ -121,6 +121,16 @@ bool agg_seg(int B, int d) {
     return B * ((d + kLanes - 1) / kLanes) >= 96;
 }
 
+// scalar-diagonal cells: pipelined persistent kernels when TMA can address the arrays and there
+// are enough chains to occupy a good part of the GPU (one CTA per chain); else look-back kernels
+bool diag_pipe(int dtype, int B, int T, int d) {
+    const char* env = getenv("PRB_KERNEL_PATH");
+    if (env && env[0] == 'l') return false;
+    if (!slstm_persist_ok(dtype, B, T, d)) return false;
+    if (env && env[0] == 'p') return true;
+    return B * ((d + kLanes - 1) / kLanes) >= 48;
+}
+
 bool bad_dtype(int dtype) { return dtype != kF32 && dtype != kBF16; }
 bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 255u) != 0; }
 
@@ -192,7 +202,10 @@ int run_diag_fwd(int cell, const void* wx, const void* const* pars, const void* 
         a.d = d;
         a.omega = omega;
         a.chain = next_chain(p.chain, T, diag_tile_steps(), &st->status);
-        if (launch_diag_newton(cell, dtype, a, k == 0, k == K - 1, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+        const cudaError_t e = diag_pipe(dtype, B, T, d)
+                                  ? launch_diag_newton_pipe(cell, dtype, a, k == 0, k == K - 1, s)
+                                  : launch_diag_newton(cell, dtype, a, k == 0, k == K - 1, s);
+        if (e != cudaSuccess) return PRB_ERR_LAUNCH;
     }
     if (want_residual && K == 0)
         if (launch_diag_residual(cell, dtype, false, wx, p.par, h0f, out, B, T, d, &st->final_bits, s) !=
@@ -256,8 +269,12 @@ int run_diag_bwd(int cell, const void* states, const void* wx, const void* const
     a.T = T;
     a.d = d;
     a.chain = next_chain(p.chain, T, diag_tile_steps(), &st->status);
-    if (launch_diag_bwd(cell, dtype, a, false, s) != cudaSuccess) return PRB_ERR_LAUNCH;
-    if (launch_reduce_partials(p.partial, B * a.chain.n_tt, np * d, g_params, s) != cudaSuccess)
+    const bool pipe = diag_pipe(dtype, B, T, d);
+    if ((pipe ? launch_diag_bwd_pipe(cell, dtype, a, s) : launch_diag_bwd(cell, dtype, a, false, s)) !=
+        cudaSuccess)
+        return PRB_ERR_LAUNCH;
+    // one partial row per tile (look-back) or per batch row (one CTA per chain)
+    if (launch_reduce_partials(p.partial, pipe ? B : B * a.chain.n_tt, np * d, g_params, s) != cudaSuccess)
         return PRB_ERR_LAUNCH;
     return PRB_OK;
 }
@@ -735,7 +752,8 @@ int prb_diag_newton_pass(int cell, const void* wx, const float* params, const fl
     a.omega = omega;
     a.chain = next_chain(w.chain, T, diag_tile_steps(), &st->status);
     cudaError_t e = mode == 2 ? launch_diag_newton_agg(cell, dtype, a, s)
-                              : launch_diag_newton(cell, dtype, a, false, mode == 1, s);
+                    : diag_pipe(dtype, B, T, d) ? launch_diag_newton_pipe(cell, dtype, a, false, mode == 1, s)
+                                                : launch_diag_newton(cell, dtype, a, false, mode == 1, s);
     return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
 
@@ -769,9 +787,12 @@ int prb_diag_bwd_pass(int cell, const void* states, const void* wx, const float*
     a.T = T;
     a.d = d;
     a.chain = next_chain(w.chain, T, diag_tile_steps(), &st->status);
-    if (launch_diag_bwd(cell, dtype, a, mode == 2, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+    const bool pipe = mode == 0 && diag_pipe(dtype, B, T, d);
+    if ((pipe ? launch_diag_bwd_pipe(cell, dtype, a, s) : launch_diag_bwd(cell, dtype, a, mode == 2, s)) !=
+        cudaSuccess)
+        return PRB_ERR_LAUNCH;
     if (mode == 0 &&
-        launch_reduce_partials(w.partial, B * a.chain.n_tt, np * d, g_params, s) != cudaSuccess)
+        launch_reduce_partials(w.partial, pipe ? B : B * a.chain.n_tt, np * d, g_params, s) != cudaSuccess)
         return PRB_ERR_LAUNCH;
     return PRB_OK;
 }

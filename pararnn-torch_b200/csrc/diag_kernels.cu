@@ -9,77 +9,10 @@
 //   solvers/scan.py:126-148, solvers/newton/dispatch.py:406-441 eq. 2.6 reverse scan
 //   kernels/vjp_gru.py:107-138, kernels/vjp_nlru.py:88-108      packed VJP
 #include "common.cuh"
+#include "diag_cell.cuh"
 #include "kernels.h"
 
 namespace prb {
-
-template <int CELL>
-struct DiagCell;
-
-template <>
-struct DiagCell<kCellGruDiag> {
-    static constexpr int G = 3, NP = 3;
-    struct Acts {
-        float z, r, n;
-    };
-    __device__ static __forceinline__ void eval(float h, const float (&g)[3], const float (&p)[3],
-                                                float& f, float& j, Acts& a) {
-        a.z = sigmoid_f(fmaf(p[0], h, g[0]));
-        a.r = sigmoid_f(fmaf(p[1], h, g[1]));
-        a.n = tanh_f(fmaf(p[2], h * a.r, g[2]));
-        f = fmaf(a.z, a.n - h, h);
-        const float zp = a.z * (1.f - a.z), rp = a.r * (1.f - a.r), np_ = 1.f - a.n * a.n;
-        j = (1.f - a.z) + (a.n - h) * zp * p[0] + a.z * np_ * p[2] * (a.r + h * rp * p[1]);
-    }
-    __device__ static __forceinline__ float step(float h, const float (&g)[3], const float (&p)[3]) {
-        const float z = sigmoid_f(fmaf(p[0], h, g[0]));
-        const float r = sigmoid_f(fmaf(p[1], h, g[1]));
-        const float n = tanh_f(fmaf(p[2], h * r, g[2]));
-        return fmaf(z, n - h, h);
-    }
-    // packed VJP: gate pre-activation grads and the per-step parameter terms
-    __device__ static __forceinline__ void vjp(float h, const Acts& a, const float (&p)[3], float mu,
-                                               float (&gw)[3], float (&gp)[3]) {
-        const float d_z = mu * (a.n - h);
-        const float d_n = mu * a.z * (1.f - a.n * a.n);
-        const float d_zp = d_z * a.z * (1.f - a.z);
-        const float d_rp = (d_n * p[2] * h) * a.r * (1.f - a.r);
-        gw[0] = d_zp;
-        gw[1] = d_rp;
-        gw[2] = d_n;
-        gp[0] = d_zp * h;
-        gp[1] = d_rp * h;
-        gp[2] = d_n * (h * a.r);
-    }
-};
-
-template <>
-struct DiagCell<kCellNlru> {
-    static constexpr int G = 2, NP = 1;
-    struct Acts {
-        float a, n;
-    };
-    __device__ static __forceinline__ void eval(float h, const float (&g)[2], const float (&p)[1],
-                                                float& f, float& j, Acts& a) {
-        a.a = sigmoid_f(g[0]);
-        a.n = tanh_f(fmaf(p[0], h, g[1]));
-        f = fmaf(a.a, h, (1.f - a.a) * a.n);
-        j = fmaf((1.f - a.a) * (1.f - a.n * a.n), p[0], a.a);
-    }
-    __device__ static __forceinline__ float step(float h, const float (&g)[2], const float (&p)[1]) {
-        const float a = sigmoid_f(g[0]);
-        const float n = tanh_f(fmaf(p[0], h, g[1]));
-        return fmaf(a, h, (1.f - a) * n);
-    }
-    __device__ static __forceinline__ void vjp(float h, const Acts& a, const float (&p)[1], float mu,
-                                               float (&gw)[2], float (&gp)[1]) {
-        const float d_a = mu * (h - a.n) * a.a * (1.f - a.a);
-        const float d_c = mu * (1.f - a.a) * (1.f - a.n * a.n);
-        gw[0] = d_a;
-        gw[1] = d_c;
-        gp[0] = d_c * h;
-    }
-};
 
 // ------------------------------------------------------------------ forward
 //

@@ -1,0 +1,59 @@
+"""The GRU-diag / NLRU parity tests once more, forced onto the pipelined persistent kernels
+(PRB_KERNEL_PATH=pipe), plus shapes chosen for that family: channel counts TMA can address
+(d a multiple of 4 in fp32, of 8 in bf16), sequence lengths around the 64-step round, a ragged
+last channel block.  Shapes TMA cannot address fall back to the look-back kernels."""
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import bf16_round, dev, make_problem, rel_err
+from oracle import oracle
+from test_gpu_diag import *  # noqa: F401,F403
+from test_gpu_diag import _bwd, _fwd, pytestmark  # noqa: F401
+
+
+@pytest.fixture(autouse=True)
+def _force_pipelined_kernels(monkeypatch):
+    monkeypatch.setenv("PRB_KERNEL_PATH", "pipe")
+
+
+PIPE_SHAPES = [(1, 1, 32), (2, 63, 64), (1, 64, 40), (3, 65, 96), (2, 128, 36), (1, 1000, 64), (4, 4097, 72)]
+
+
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru"])
+@pytest.mark.parametrize("B,T,d", PIPE_SHAPES)
+@pytest.mark.parametrize("K", [1, 2, 4])
+def test_pipe_forward_vs_oracle_fp32(kind, B, T, d, K):
+    wx, params, h0 = make_problem(kind, B, T, d, seed=B * 77 + T + d, h0=(T % 2 == 1))
+    want = oracle.newton(oracle.KIND[kind], wx, params, h0, max_iters=K)
+    H, hist, res = _fwd(kind, wx, params, h0, K)
+    amp = max(1.0, max(want.history))
+    assert np.abs(H - want.states).max() <= 1e-5 * amp
+    np.testing.assert_allclose(np.asarray(hist), np.asarray(want.history), rtol=5e-3, atol=2e-6)
+    assert abs(res - want.max_residual) <= 5e-3 * want.max_residual + 2e-6
+
+
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru"])
+@pytest.mark.parametrize("B,T,d", PIPE_SHAPES)
+def test_pipe_backward_vs_oracle_fp32(kind, B, T, d):
+    wx, params, h0 = make_problem(kind, B, T, d, seed=B + T + d, h0=(T % 2 == 0))
+    H = oracle.newton(oracle.KIND[kind], wx, params, h0, max_iters=6).states
+    G = np.random.default_rng(3).standard_normal(H.shape).astype(np.float32)
+    want = oracle.backward(oracle.KIND[kind], H, wx, params, G, h0)
+    got = _bwd(kind, H, wx, params, G, h0)
+    assert rel_err(got[0], want[0]) <= 2e-5
+    assert rel_err(got[1], np.asarray(want[1]).reshape(got[1].shape)) <= 2e-5
+    if h0 is not None:
+        assert rel_err(got[2], want[2]) <= 2e-5
+
+
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru"])
+def test_pipe_bf16_matches_lookback_family(kind, monkeypatch):
+    """Two independent implementations on the same bf16 problem."""
+    wx, params, h0 = make_problem(kind, 2, 777, 64, seed=9, h0=True)
+    wx, params, h0 = bf16_round(wx), bf16_round(params), bf16_round(h0)
+    a, _, _ = _fwd(kind, wx, params, h0, 2, dtype=torch.bfloat16)
+    monkeypatch.setenv("PRB_KERNEL_PATH", "lookback")
+    b, _, _ = _fwd(kind, wx, params, h0, 2, dtype=torch.bfloat16)
+    assert rel_err(a, b) <= 1e-2
