@@ -58,16 +58,48 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML polled every
+    5 ms from a thread (read-only queries), or `nvidia-smi -lms 100` when NVML is not importable."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
+        self.sm, self.mx, self.seen, self._stop, self._thread = [], [], set(), False, None
+
+    def _poll_nvml(self, nv, handle):
+        bits = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                "sw_power_cap": 0x4}
+        while not self._stop:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                self.mx.append(float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                self.seen.update(n for n, b in bits.items() if mask & b)
+            except Exception:
+                pass
+            time.sleep(0.005)
 
     def start(self):
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = self.index
+            if visible:
+                ids = [v for v in visible.split(",") if v.strip()]
+                if self.index < len(ids) and ids[self.index].strip().isdigit():
+                    phys = int(ids[self.index])
+            handle = nv.nvmlDeviceGetHandleByIndex(phys)
+            self._thread = threading.Thread(target=self._poll_nvml, args=(nv, handle), daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self._thread = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -81,6 +113,13 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        if self._thread is not None:
+            self._stop = True
+            self._thread.join(timeout=1)
+            reasons = [n for n in self.NAMES if n in self.seen]
+            return {"sm_mhz": statistics.median(self.sm) if self.sm else None,
+                    "sm_max_mhz": max(self.mx) if self.mx else None, "reasons": reasons,
+                    "samples": len(self.sm), "source": "nvml"}
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -89,11 +128,11 @@ class ClockSampler:
                 pass
         sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
         mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names)
+        reasons = [n for i, n in enumerate(self.NAMES)
                    if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm),
+                "source": "nvidia-smi"}
 
 
 def make_inputs(t_len: int, seed: int):
@@ -298,13 +337,37 @@ def run_gpu_single(args):
     cfg = prb.NewtonConfig(max_iters=K_NEWTON, picard_iters=P_PICARD, picard_adapt=False)
     loss_host = torch.empty((), dtype=torch.float32).pin_memory()
 
+    # Input pipeline of the end-to-end step: the pinned host batch of step i+1 is copied on a second
+    # stream into the other of two device buffers while step i computes; every step still issues
+    # one full host->device copy of its input and one device->host read of its loss.
+    copy_stream = torch.cuda.Stream()
+    x_bufs = [torch.empty_like(x_dev) for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    for ev in consumed:
+        ev.record()
+    e2e_state = {"i": 0}
+
+    def prefetch(i):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[i % 2])
+            x_bufs[i % 2].copy_(x_host, non_blocking=True)
+            ready[i % 2].record(copy_stream)
+
+    prefetch(0)
+
     def e2e_step():
-        xd = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        i = e2e_state["i"]
+        torch.cuda.current_stream().wait_event(ready[i % 2])
+        prefetch(i + 1)
+        xd = x_bufs[i % 2].detach().requires_grad_(True)
         Hs = prb.newton_apply(cell, xd, cfg)
         loss = Hs[:, :, 3].float().sum()
         loss.backward()
+        consumed[i % 2].record()
         loss_host.copy_(loss.detach(), non_blocking=True)
         cell.zero_grad(set_to_none=True)
+        e2e_state["i"] = i + 1
 
     if args.no_e2e:
         e2e_sec = float("nan")
@@ -345,7 +408,8 @@ def run_gpu_single(args):
         "e2e": {"value": tokens / e2e_sec, "unit": "tokens/s",
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 4,
                 "ms_per_step": e2e_sec * 1e3,
-                "includes": "H2D of x, 3 W_x GEMMs (cuBLAS), Newton+scan fwd, reverse scan + VJP, D2H of loss"},
+                "includes": "H2D of x (double-buffered on a copy stream, one copy per step), 3 W_x GEMMs "
+                            "(cuBLAS), Newton+scan fwd, reverse scan + VJP, D2H of loss"},
         "gpu_launches": 12 * args.steps,
         "roofline": roofline,
         "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": threads, "kind": "port",
@@ -418,13 +482,37 @@ def run_gpu_sharded(args):
                            scan_backend="context_parallel")
     loss_host = torch.empty((), dtype=torch.float32).pin_memory()
 
+    # Input pipeline of the end-to-end step: the pinned host batch of step i+1 is copied on a second
+    # stream into the other of two device buffers while step i computes; every step still issues
+    # one full host->device copy of its input and one device->host read of its loss.
+    copy_stream = torch.cuda.Stream()
+    x_bufs = [torch.empty_like(x_dev) for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    for ev in consumed:
+        ev.record()
+    e2e_state = {"i": 0}
+
+    def prefetch(i):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[i % 2])
+            x_bufs[i % 2].copy_(x_host, non_blocking=True)
+            ready[i % 2].record(copy_stream)
+
+    prefetch(0)
+
     def e2e_step():
-        xd = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        i = e2e_state["i"]
+        torch.cuda.current_stream().wait_event(ready[i % 2])
+        prefetch(i + 1)
+        xd = x_bufs[i % 2].detach().requires_grad_(True)
         Hs = prb.newton_apply(cell, xd, cfg)
         loss = Hs[:, :, 3].float().sum()
         loss.backward()
+        consumed[i % 2].record()
         loss_host.copy_(loss.detach(), non_blocking=True)
         cell.zero_grad(set_to_none=True)
+        e2e_state["i"] = i + 1
 
     e2e_sec = float("nan")
     if not args.no_e2e:
@@ -469,13 +557,16 @@ def run_secondary(args):
     """Other BASELINE configurations (one JSON line each): `--workload c1|c3|c5`.
     c1: ParaGRU diag fp32 B=2 T=1024 d=64 K=3; c3: ParaGRU head 8x64 B=16 T=4096 K=3 (fp32 and
     bf16); c5: 12 x ParaNLRU d=768 bf16 B=4 T=8192 K=2 residual stack.  Forward + backward through
-    newton_apply (layer boundary: includes the W_x GEMMs), CUDA events, inputs resident in HBM."""
+    newton_apply (layer boundary: includes the W_x GEMMs), CUDA events, inputs resident in HBM.
+    `--seq-len` shortens c3 / c5 for profiling captures."""
     import torch
 
     import pararnn_b200 as prb
 
     dev = torch.device("cuda:0")
     torch.cuda.set_device(0)
+    t_c3 = args.seq_len if args.seq_len != T_PER_GPU else 4096
+    t_c5 = args.seq_len if args.seq_len != T_PER_GPU else 8192
 
     def timed(fn):
         for _ in range(max(args.warmup, 3)):
@@ -508,7 +599,7 @@ def run_secondary(args):
                     for hd in range(8):
                         torch.nn.init.orthogonal_(A[hd], gain=0.9)
             cell = cell.to(dev, dtype)
-            x = torch.randn(16, 4096, 512, device=dev, dtype=dtype, requires_grad=True)
+            x = torch.randn(16, t_c3, 512, device=dev, dtype=dtype, requires_grad=True)
             cfg = prb.NewtonConfig(max_iters=3)
             st = prb.NewtonStats()
 
@@ -516,8 +607,8 @@ def run_secondary(args):
                 prb.newton_apply(cell, x, cfg, stats=st).float().sum().backward()
 
             sec = timed(step)
-            lines.append({"workload": f"c3 ParaGRU head 8x64 B=16 T=4096 K=3 {str(dtype)[6:]}",
-                          "ms_per_step": sec * 1e3, "tokens_per_s": 16 * 4096 / sec,
+            lines.append({"workload": f"c3 ParaGRU head 8x64 B=16 T={t_c3} K=3 {str(dtype)[6:]}",
+                          "ms_per_step": sec * 1e3, "tokens_per_s": 16 * t_c3 / sec,
                           "residual_history": list(st.residual_history), "max_residual": st.max_residual})
     else:
         torch.manual_seed(4)
@@ -529,7 +620,7 @@ def run_secondary(args):
                 c.W_x.bias[:768] = torch.log(a0 / (1 - a0))
             cells.append(c.to(dev, torch.bfloat16))
         emb = (torch.randn(50304, 768) * 0.02).to(dev, torch.bfloat16)
-        ids = torch.randint(0, 50304, (4, 8192), device=dev)
+        ids = torch.randint(0, 50304, (4, t_c5), device=dev)
         cfg = prb.NewtonConfig(max_iters=2)
         norm = torch.nn.RMSNorm(768).to(dev, torch.bfloat16)
 
@@ -540,8 +631,8 @@ def run_secondary(args):
             h.float().sum().backward()
 
         sec = timed(step)
-        lines.append({"workload": "c5 12 x ParaNLRU d=768 bf16 B=4 T=8192 K=2 residual stack",
-                      "ms_per_step": sec * 1e3, "tokens_per_s": 4 * 8192 / sec})
+        lines.append({"workload": f"c5 12 x ParaNLRU d=768 bf16 B=4 T={t_c5} K=2 residual stack",
+                      "ms_per_step": sec * 1e3, "tokens_per_s": 4 * t_c5 / sec})
     for ln in lines:
         print(json.dumps(ln))
 
