@@ -35,6 +35,7 @@ for p in (ROOT, os.path.join(ROOT, "pararnn-torch_b200")):
         sys.path.insert(0, p)
 
 B, T_PER_GPU, D, K_NEWTON, P_PICARD = 8, 16384, 1024, 2, 5
+DEFAULT_T = T_PER_GPU
 SEED = 1
 # algorithmic bytes per (token, channel): bf16 I/O (a=2), fp32 work state (w=4), G=S=4
 BYTES_PICARD_MID = 4 * 2 + 4 + 4          # read wx + h, write h
@@ -565,8 +566,8 @@ def run_secondary(args):
 
     dev = torch.device("cuda:0")
     torch.cuda.set_device(0)
-    t_c3 = args.seq_len if args.seq_len != T_PER_GPU else 4096
-    t_c5 = args.seq_len if args.seq_len != T_PER_GPU else 8192
+    t_c3 = args.seq_len if args.seq_len != DEFAULT_T else 4096
+    t_c5 = args.seq_len if args.seq_len != DEFAULT_T else 8192
 
     def timed(fn):
         for _ in range(max(args.warmup, 3)):

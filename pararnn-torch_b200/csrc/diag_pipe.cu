@@ -25,7 +25,6 @@ namespace prb {
 namespace {
 
 constexpr uint32_t kDiagPipeWaitLimit = 1u << 26;
-constexpr int kDPL = 8;
 
 __device__ __forceinline__ void dp_mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -65,7 +64,7 @@ struct DiagPipeFwdSmem {
 };
 
 template <int CELL, typename TIO, int L, int W, int NSTAGE, bool FIRST, bool LAST>
-__global__ void __launch_bounds__((W + 1) * 32, W > 8 ? 1 : 2)
+__global__ void __launch_bounds__((W + 1) * 32, W * L > 64 ? 1 : 2)
 diag_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_h,
                         DiagFwdArgs a) {
     using C = DiagCell<CELL>;
@@ -257,7 +256,7 @@ struct DiagPipeBwdSmem {
 // moves towards lower steps.  Parameter gradients are accumulated per thread over the whole
 // sweep and summed over the warps in a fixed order: one partial row per chain.
 template <int CELL, typename TIO, int L, int W, int NSTAGE>
-__global__ void __launch_bounds__((W + 1) * 32, W > 8 ? 1 : 2)
+__global__ void __launch_bounds__((W + 1) * 32, W * L > 64 ? 1 : 2)
 diag_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_st,
                      const __grid_constant__ CUtensorMap tm_g, DiagBwdArgs a) {
     using C = DiagCell<CELL>;
@@ -410,10 +409,10 @@ diag_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
 }
 
 // ------------------------------------------------------------------ launchers
-template <int CELL, typename TIO, int NSTAGE, int W>
+template <int CELL, typename TIO, int NSTAGE, int L, int W>
 cudaError_t launch_fwd_w(const DiagFwdArgs& a, bool first, bool last, cudaStream_t s) {
     constexpr int G = DiagCell<CELL>::G;
-    constexpr int kDPW = W;
+    constexpr int kDPW = W, kDPL = L;
     using S = DiagPipeFwdSmem<G, TIO, kDPL, kDPW, NSTAGE>;
     CUtensorMap tm_wx, tm_h;
     const uint64_t rows = (uint64_t)a.B * a.T;
@@ -444,14 +443,14 @@ inline bool wide_cta(int B, int d) { return B * ((d + kLanes - 1) / kLanes) <= 2
 
 template <int CELL, typename TIO, int NSTAGE>
 cudaError_t launch_fwd_t(const DiagFwdArgs& a, bool first, bool last, cudaStream_t s) {
-    return wide_cta(a.B, a.d) ? launch_fwd_w<CELL, TIO, NSTAGE, 16>(a, first, last, s)
-                              : launch_fwd_w<CELL, TIO, NSTAGE, 8>(a, first, last, s);
+    if (!wide_cta(a.B, a.d)) return launch_fwd_w<CELL, TIO, NSTAGE, 8, 8>(a, first, last, s);
+    return launch_fwd_w<CELL, TIO, NSTAGE, 8, 16>(a, first, last, s);
 }
 
-template <int CELL, typename TIO, int NSTAGE, int W>
+template <int CELL, typename TIO, int NSTAGE, int L, int W>
 cudaError_t launch_bwd_w(const DiagBwdArgs& a, cudaStream_t s) {
     constexpr int G = DiagCell<CELL>::G;
-    constexpr int kDPW = W;
+    constexpr int kDPW = W, kDPL = L;
     using S = DiagPipeBwdSmem<G, TIO, kDPL, kDPW, NSTAGE>;
     CUtensorMap tm_wx, tm_st, tm_g;
     const uint64_t rows = (uint64_t)a.B * a.T;
@@ -468,8 +467,8 @@ cudaError_t launch_bwd_w(const DiagBwdArgs& a, cudaStream_t s) {
 
 template <int CELL, typename TIO, int NSTAGE>
 cudaError_t launch_bwd_t(const DiagBwdArgs& a, cudaStream_t s) {
-    return wide_cta(a.B, a.d) ? launch_bwd_w<CELL, TIO, NSTAGE, 16>(a, s)
-                              : launch_bwd_w<CELL, TIO, NSTAGE, 8>(a, s);
+    if (!wide_cta(a.B, a.d)) return launch_bwd_w<CELL, TIO, NSTAGE, 8, 8>(a, s);
+    return launch_bwd_w<CELL, TIO, NSTAGE, 8, 16>(a, s);
 }
 
 }  // namespace
