@@ -17,6 +17,8 @@
 #include "slstm_cell.cuh"
 #include "tma.cuh"
 
+#include <type_traits>
+
 namespace prb {
 
 constexpr uint32_t kPipeWaitLimit = 1u << 26;
@@ -118,104 +120,113 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
             const float* t_st = reinterpret_cast<const float*>(smem + s * S::STAGE + S::WX_BYTES);
             const int t0 = r * LT + warp * L;
 
-            float w[L][4], st[L + 1][4];
-#pragma unroll
-            for (int i = 0; i < L; ++i) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    w[i][q] = (float)t_wx[((warp * L + i) * 4 + q) * kLanes + lane];
-                    st[i + 1][q] = t_st[((warp * L + i + 1) * 4 + q) * kLanes + lane];
-                }
-            }
-            if (t0 == 0) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    st[0][q] = a.halo ? __ldg(a.halo + (size_t)b * a.halo_stride + (size_t)q * d + chl) : 0.f;
-            } else {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) st[0][q] = t_st[((warp * L) * 4 + q) * kLanes + lane];
-            }
-            // this warp is done with the stage: let the producer refill it
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-
-            // ---- carry-independent part
-            SlstmLin lin[L];
-            float F[L][4];
-#pragma unroll
-            for (int i = 0; i < L; ++i) {
-                slstm_linearize(st[i], w[i], r4, a.eps, lin[i]);
-                const bool ok = t0 + i < a.T;
-                float fc = lin[i].pc - st[i + 1][0], fn = lin[i].pn - st[i + 1][1];
-                float fm = lin[i].pm - st[i + 1][2], fh = lin[i].ph - st[i + 1][3];
-                if (!ok) {
-                    lin[i].f = 1.f; lin[i].jcm = 0.f; lin[i].jch = 0.f; lin[i].jnm = 0.f; lin[i].jnh = 0.f;
-                    lin[i].alpha = 1.f; lin[i].dm = 0.f; lin[i].ia = 0.f; lin[i].ib = 0.f; lin[i].ie = 1.f;
-                    fc = fn = fm = fh = 0.f;
-                } else if (ch_ok) {
-                    rmax = max(rmax, max(max(absbits(fc), absbits(fn)), max(absbits(fm), absbits(fh))));
-                }
-                F[i][0] = fc;
-                F[i][1] = fn;
-                F[i][2] = fm;
-                F[i][3] = fh - lin[i].ia * fc - lin[i].ib * fn;
-            }
-
-            // ---- the baton: carry from the previous warp (previous round's last warp for warp 0)
-            if (!(r == 0 && warp == 0)) named_sync(1 + warp, 64);
-            float xc = slot_in[0], xn = slot_in[kLanes], xm = slot_in[2 * kLanes], xh = slot_in[3 * kLanes];
-            const float c0 = xc, c1 = xn, c2 = xm, c3 = xh;
-            float dl[L][4];
-#pragma unroll
-            for (int i = 0; i < L; ++i) {
-                slstm_apply(lin[i], F[i][0], F[i][1], F[i][2], F[i][3], xc, xn, xm, xh);
-                dl[i][0] = xc; dl[i][1] = xn; dl[i][2] = xm; dl[i][3] = xh;
-            }
-            slot_out[0] = xc;
-            slot_out[kLanes] = xn;
-            slot_out[2 * kLanes] = xm;
-            slot_out[3 * kLanes] = xh;
-            if (!(r == n_rounds - 1 && warp == W - 1)) named_arrive(1 + next, 64);
-
-            // ---- results
-            float pn4[4] = {fmaf(a.omega, c0, st[0][0]), fmaf(a.omega, c1, st[0][1]),
-                            fmaf(a.omega, c2, st[0][2]), fmaf(a.omega, c3, st[0][3])};
-#pragma unroll
-            for (int i = 0; i < L; ++i) {
-                const int t = t0 + i;
-                if (t < a.T && ch_ok) {
-                    const float o0 = fmaf(a.omega, dl[i][0], st[i + 1][0]);
-                    const float o1 = fmaf(a.omega, dl[i][1], st[i + 1][1]);
-                    const float o2 = fmaf(a.omega, dl[i][2], st[i + 1][2]);
-                    const float o3 = fmaf(a.omega, dl[i][3], st[i + 1][3]);
-                    if (want_final) {
-                        float pred[4];
-                        slstm_predict(pn4, w[i], r4, a.eps, pred);
-                        fmax = max(fmax, max(max(absbits(pred[0] - o0), absbits(pred[1] - o1)),
-                                             max(absbits(pred[2] - o2), absbits(pred[3] - o3))));
-                        pn4[0] = o0; pn4[1] = o1; pn4[2] = o2; pn4[3] = o3;
-                    }
-                    if (LAST) {
-                        TIO* o = reinterpret_cast<TIO*>(a.sout) + ((size_t)b * a.T + t) * 4 * d + ch;
-                        st_f(o, o0);
-                        st_f(o + d, o1);
-                        st_f(o + 2 * (size_t)d, o2);
-                        st_f(o + 3 * (size_t)d, o3);
-                    } else {
-                        float* o = reinterpret_cast<float*>(a.sout) + ((size_t)b * a.T + t) * 4 * d + ch;
-                        o[0] = o0;
-                        o[d] = o1;
-                        o[2 * (size_t)d] = o2;
-                        o[3 * (size_t)d] = o3;
+            // Rounds that lie fully inside the sequence take a variant without range checks.
+            auto round_body = [&](auto full_c) {
+                constexpr bool FULL = decltype(full_c)::value;
+                float w[L][4], st[L + 1][4];
+    #pragma unroll
+                for (int i = 0; i < L; ++i) {
+    #pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        w[i][q] = (float)t_wx[((warp * L + i) * 4 + q) * kLanes + lane];
+                        st[i + 1][q] = t_st[((warp * L + i + 1) * 4 + q) * kLanes + lane];
                     }
                 }
-            }
-            if (r == n_rounds - 1 && warp == W - 1 && a.tail_out && ch_ok) {
-                a.tail_out[((size_t)b * 4 + 0) * d + ch] = xc;
-                a.tail_out[((size_t)b * 4 + 1) * d + ch] = xn;
-                a.tail_out[((size_t)b * 4 + 2) * d + ch] = xm;
-                a.tail_out[((size_t)b * 4 + 3) * d + ch] = xh;
-            }
+                if (t0 == 0) {
+    #pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        st[0][q] = a.halo ? __ldg(a.halo + (size_t)b * a.halo_stride + (size_t)q * d + chl) : 0.f;
+                } else {
+    #pragma unroll
+                    for (int q = 0; q < 4; ++q) st[0][q] = t_st[((warp * L) * 4 + q) * kLanes + lane];
+                }
+                // this warp is done with the stage: let the producer refill it
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+
+                // ---- carry-independent part
+                SlstmLin lin[L];
+                float F[L][4];
+    #pragma unroll
+                for (int i = 0; i < L; ++i) {
+                    slstm_linearize(st[i], w[i], r4, a.eps, lin[i]);
+                    const bool ok = FULL || t0 + i < a.T;
+                    float fc = lin[i].pc - st[i + 1][0], fn = lin[i].pn - st[i + 1][1];
+                    float fm = lin[i].pm - st[i + 1][2], fh = lin[i].ph - st[i + 1][3];
+                    if (!ok) {
+                        lin[i].f = 1.f; lin[i].jcm = 0.f; lin[i].jch = 0.f; lin[i].jnm = 0.f; lin[i].jnh = 0.f;
+                        lin[i].alpha = 1.f; lin[i].dm = 0.f; lin[i].ia = 0.f; lin[i].ib = 0.f; lin[i].ie = 1.f;
+                        fc = fn = fm = fh = 0.f;
+                    } else if (ch_ok) {
+                        rmax = max(rmax, max(max(absbits(fc), absbits(fn)), max(absbits(fm), absbits(fh))));
+                    }
+                    F[i][0] = fc;
+                    F[i][1] = fn;
+                    F[i][2] = fm;
+                    F[i][3] = fh - lin[i].ia * fc - lin[i].ib * fn;
+                }
+
+                // ---- the baton: carry from the previous warp (previous round's last warp for warp 0)
+                if (!(r == 0 && warp == 0)) named_sync(1 + warp, 64);
+                float xc = slot_in[0], xn = slot_in[kLanes], xm = slot_in[2 * kLanes], xh = slot_in[3 * kLanes];
+                const float c0 = xc, c1 = xn, c2 = xm, c3 = xh;
+                float dl[L][4];
+    #pragma unroll
+                for (int i = 0; i < L; ++i) {
+                    slstm_apply(lin[i], F[i][0], F[i][1], F[i][2], F[i][3], xc, xn, xm, xh);
+                    dl[i][0] = xc; dl[i][1] = xn; dl[i][2] = xm; dl[i][3] = xh;
+                }
+                slot_out[0] = xc;
+                slot_out[kLanes] = xn;
+                slot_out[2 * kLanes] = xm;
+                slot_out[3 * kLanes] = xh;
+                if (!(r == n_rounds - 1 && warp == W - 1)) named_arrive(1 + next, 64);
+
+                // ---- results
+                const size_t o_base = ((size_t)b * a.T + t0) * 4 * d + ch;
+                float pn4[4] = {fmaf(a.omega, c0, st[0][0]), fmaf(a.omega, c1, st[0][1]),
+                                fmaf(a.omega, c2, st[0][2]), fmaf(a.omega, c3, st[0][3])};
+    #pragma unroll
+                for (int i = 0; i < L; ++i) {
+                    const int t = t0 + i;
+                    if ((FULL || t < a.T) && ch_ok) {
+                        const float o0 = fmaf(a.omega, dl[i][0], st[i + 1][0]);
+                        const float o1 = fmaf(a.omega, dl[i][1], st[i + 1][1]);
+                        const float o2 = fmaf(a.omega, dl[i][2], st[i + 1][2]);
+                        const float o3 = fmaf(a.omega, dl[i][3], st[i + 1][3]);
+                        if (want_final) {
+                            float pred[4];
+                            slstm_predict(pn4, w[i], r4, a.eps, pred);
+                            fmax = max(fmax, max(max(absbits(pred[0] - o0), absbits(pred[1] - o1)),
+                                                 max(absbits(pred[2] - o2), absbits(pred[3] - o3))));
+                            pn4[0] = o0; pn4[1] = o1; pn4[2] = o2; pn4[3] = o3;
+                        }
+                        if (LAST) {
+                            TIO* o = reinterpret_cast<TIO*>(a.sout) + o_base + (size_t)i * 4 * d;
+                            st_f(o, o0);
+                            st_f(o + d, o1);
+                            st_f(o + 2 * (size_t)d, o2);
+                            st_f(o + 3 * (size_t)d, o3);
+                        } else {
+                            float* o = reinterpret_cast<float*>(a.sout) + o_base + (size_t)i * 4 * d;
+                            o[0] = o0;
+                            o[d] = o1;
+                            o[2 * (size_t)d] = o2;
+                            o[3 * (size_t)d] = o3;
+                        }
+                    }
+                }
+                if (r == n_rounds - 1 && warp == W - 1 && a.tail_out && ch_ok) {
+                    a.tail_out[((size_t)b * 4 + 0) * d + ch] = xc;
+                    a.tail_out[((size_t)b * 4 + 1) * d + ch] = xn;
+                    a.tail_out[((size_t)b * 4 + 2) * d + ch] = xm;
+                    a.tail_out[((size_t)b * 4 + 3) * d + ch] = xh;
+                }
+            };
+            if (t0 + L <= a.T)
+                round_body(std::true_type{});
+            else
+                round_body(std::false_type{});
         }
     }
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
@@ -321,88 +332,97 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
             const int row_hi = (W - 1 - warp) * L + (L - 1);
             const int t_hi = tile_t * LT + row_hi;
 
-            SlstmAct act[L];
-            float g[L][4];
-#pragma unroll
-            for (int i = 0; i < L; ++i) {
-                const int row = row_hi - i;
-                const int t = t_hi - i;
-                float w[4], prev[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) w[q] = (float)t_wx[(row * 4 + q) * kLanes + lane];
-                if (t == 0) {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        prev[q] = a.halo ? __ldg(a.halo + (size_t)b * a.halo_stride + (size_t)q * d + chl) : 0.f;
-                } else {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) prev[q] = (float)t_st[(row * 4 + q) * kLanes + lane];
-                }
-#pragma unroll
-                for (int q = 0; q < 4; ++q) g[i][q] = (float)t_g[(row * 4 + q) * kLanes + lane];
-                slstm_acts(prev, w, r4, a.eps, act[i]);
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-
-            if (!(r == 0 && warp == 0)) named_sync(1 + warp, 64);
-            float nc = slot_in[0], nn = slot_in[kLanes], nm = slot_in[2 * kLanes], nh = slot_in[3 * kLanes];
-            float dz[L][4];
-#pragma unroll
-            for (int i = 0; i < L; ++i) {
-                const int t = t_hi - i;
-                if (t < a.T) {
-                    const SlstmAct& sa = act[i];
-                    const float mc = nc + g[i][0], mn_ = nn + g[i][1], mm = nm + g[i][2], mh = nh + g[i][3];
-                    const float cn = fmaf(sa.f, sa.c, sa.i * sa.z);
-                    const float u = cn * sa.invD;
-                    const float d_o = mh * u;
-                    const float d_cn = fmaf(mh, sa.o * sa.invD, mc);
-                    const float d_nn = fmaf(mh, -(sa.o * u) * sa.invD, mn_);
-                    const float d_f = fmaf(d_cn, sa.c, d_nn * sa.n);
-                    const float d_i = fmaf(d_cn, sa.z, d_nn);
-                    const float d_z = d_cn * sa.i;
-                    const float d_zo = d_o * sa.o * (1.f - sa.o);
-                    const float d_zz = d_z * (1.f - sa.z * sa.z);
-                    const float d_mn = mm - d_i * sa.i - d_f * sa.f;
-                    const float d_zi = fmaf(d_i, sa.i, d_mn * (1.f - sa.alpha));
-                    const float d_zf = fmaf(d_f, sa.f, d_mn * sa.alpha);
-                    dz[i][0] = d_zi; dz[i][1] = d_zf; dz[i][2] = d_zz; dz[i][3] = d_zo;
-                    nc = d_cn * sa.f;
-                    nn = d_nn * sa.f;
-                    nm = d_zf;
-                    nh = fmaf(r4[0], d_zi, fmaf(r4[1], d_zf, fmaf(r4[2], d_zz, r4[3] * d_zo)));
-                } else {
-                    dz[i][0] = dz[i][1] = dz[i][2] = dz[i][3] = 0.f;
-                }
-            }
-            slot_out[0] = nc;
-            slot_out[kLanes] = nn;
-            slot_out[2 * kLanes] = nm;
-            slot_out[3 * kLanes] = nh;
-            if (!(r == n_rounds - 1 && warp == W - 1)) named_arrive(1 + next, 64);
-
-#pragma unroll
-            for (int i = 0; i < L; ++i) {
-                const int t = t_hi - i;
-                if (t < a.T) {
-                    if (ch_ok) {
-                        TIO* o = gwx + (size_t)t * 4 * d;
-                        st_f(o, dz[i][0]);
-                        st_f(o + d, dz[i][1]);
-                        st_f(o + 2 * (size_t)d, dz[i][2]);
-                        st_f(o + 3 * (size_t)d, dz[i][3]);
+            // Rounds that lie fully inside the sequence take a variant without range checks.
+            auto round_body = [&](auto full_c) {
+                constexpr bool FULL = decltype(full_c)::value;
+                SlstmAct act[L];
+                float g[L][4];
+    #pragma unroll
+                for (int i = 0; i < L; ++i) {
+                    const int row = row_hi - i;
+                    const int t = t_hi - i;
+                    float w[4], prev[4];
+    #pragma unroll
+                    for (int q = 0; q < 4; ++q) w[q] = (float)t_wx[(row * 4 + q) * kLanes + lane];
+                    if (i == L - 1 && t == 0) {
+    #pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            prev[q] = a.halo ? __ldg(a.halo + (size_t)b * a.halo_stride + (size_t)q * d + chl) : 0.f;
+                    } else {
+    #pragma unroll
+                        for (int q = 0; q < 4; ++q) prev[q] = (float)t_st[(row * 4 + q) * kLanes + lane];
                     }
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) gr[q] = fmaf(dz[i][q], act[i].hp, gr[q]);
+    #pragma unroll
+                    for (int q = 0; q < 4; ++q) g[i][q] = (float)t_g[(row * 4 + q) * kLanes + lane];
+                    slstm_acts(prev, w, r4, a.eps, act[i]);
                 }
-            }
-            if (r == n_rounds - 1 && warp == W - 1 && a.g_h0 && ch_ok) {
-                a.g_h0[((size_t)b * 4 + 0) * d + ch] = nc;
-                a.g_h0[((size_t)b * 4 + 1) * d + ch] = nn;
-                a.g_h0[((size_t)b * 4 + 2) * d + ch] = nm;
-                a.g_h0[((size_t)b * 4 + 3) * d + ch] = nh;
-            }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+
+                if (!(r == 0 && warp == 0)) named_sync(1 + warp, 64);
+                float nc = slot_in[0], nn = slot_in[kLanes], nm = slot_in[2 * kLanes], nh = slot_in[3 * kLanes];
+                float dz[L][4];
+    #pragma unroll
+                for (int i = 0; i < L; ++i) {
+                    const int t = t_hi - i;
+                    if (FULL || t < a.T) {
+                        const SlstmAct& sa = act[i];
+                        const float mc = nc + g[i][0], mn_ = nn + g[i][1], mm = nm + g[i][2], mh = nh + g[i][3];
+                        const float cn = fmaf(sa.f, sa.c, sa.i * sa.z);
+                        const float u = cn * sa.invD;
+                        const float d_o = mh * u;
+                        const float d_cn = fmaf(mh, sa.o * sa.invD, mc);
+                        const float d_nn = fmaf(mh, -(sa.o * u) * sa.invD, mn_);
+                        const float d_f = fmaf(d_cn, sa.c, d_nn * sa.n);
+                        const float d_i = fmaf(d_cn, sa.z, d_nn);
+                        const float d_z = d_cn * sa.i;
+                        const float d_zo = d_o * sa.o * (1.f - sa.o);
+                        const float d_zz = d_z * (1.f - sa.z * sa.z);
+                        const float d_mn = mm - d_i * sa.i - d_f * sa.f;
+                        const float d_zi = fmaf(d_i, sa.i, d_mn * (1.f - sa.alpha));
+                        const float d_zf = fmaf(d_f, sa.f, d_mn * sa.alpha);
+                        dz[i][0] = d_zi; dz[i][1] = d_zf; dz[i][2] = d_zz; dz[i][3] = d_zo;
+                        nc = d_cn * sa.f;
+                        nn = d_nn * sa.f;
+                        nm = d_zf;
+                        nh = fmaf(r4[0], d_zi, fmaf(r4[1], d_zf, fmaf(r4[2], d_zz, r4[3] * d_zo)));
+                    } else {
+                        dz[i][0] = dz[i][1] = dz[i][2] = dz[i][3] = 0.f;
+                    }
+                }
+                slot_out[0] = nc;
+                slot_out[kLanes] = nn;
+                slot_out[2 * kLanes] = nm;
+                slot_out[3 * kLanes] = nh;
+                if (!(r == n_rounds - 1 && warp == W - 1)) named_arrive(1 + next, 64);
+
+                TIO* gw_hi = gwx + (size_t)t_hi * 4 * d;
+    #pragma unroll
+                for (int i = 0; i < L; ++i) {
+                    const int t = t_hi - i;
+                    if (FULL || t < a.T) {
+                        if (ch_ok) {
+                            TIO* o = gw_hi - (size_t)i * 4 * d;
+                            st_f(o, dz[i][0]);
+                            st_f(o + d, dz[i][1]);
+                            st_f(o + 2 * (size_t)d, dz[i][2]);
+                            st_f(o + 3 * (size_t)d, dz[i][3]);
+                        }
+    #pragma unroll
+                        for (int q = 0; q < 4; ++q) gr[q] = fmaf(dz[i][q], act[i].hp, gr[q]);
+                    }
+                }
+                if (r == n_rounds - 1 && warp == W - 1 && a.g_h0 && ch_ok) {
+                    a.g_h0[((size_t)b * 4 + 0) * d + ch] = nc;
+                    a.g_h0[((size_t)b * 4 + 1) * d + ch] = nn;
+                    a.g_h0[((size_t)b * 4 + 2) * d + ch] = nm;
+                    a.g_h0[((size_t)b * 4 + 3) * d + ch] = nh;
+                }
+            };
+            if (t_hi < a.T)
+                round_body(std::true_type{});
+            else
+                round_body(std::false_type{});
         }
 #pragma unroll
         for (int p = 0; p < 4; ++p) s_gp[(warp * 4 + p) * kLanes + lane] = gr[p];
@@ -510,92 +530,102 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
             const float* t_h = reinterpret_cast<const float*>(smem + s * S::STAGE + S::WX_BYTES);
             const int t0 = r * LT + warp * L;
 
-            float zi[L], zf[L], zz[L], og[L];
-#pragma unroll
-            for (int i = 0; i < L; ++i) {
-                float hp = 0.f;
-                if (HAS_H) {
-                    hp = (t0 + i == 0) ? (a.h_halo ? __ldg(a.h_halo + (size_t)b * a.halo_stride + chl) : 0.f)
-                                       : t_h[(warp * L + i) * kLanes + lane];
+            // Rounds that lie fully inside the sequence take a variant without range checks.
+            auto round_body = [&](auto full_c) {
+                constexpr bool FULL = decltype(full_c)::value;
+                float zi[L], zf[L], zz[L], og[L];
+    #pragma unroll
+                for (int i = 0; i < L; ++i) {
+                    float hp = 0.f;
+                    if (HAS_H) {
+                        hp = (i == 0 && t0 == 0) ? (a.h_halo ? __ldg(a.h_halo + (size_t)b * a.halo_stride + chl) : 0.f)
+                                           : t_h[(warp * L + i) * kLanes + lane];
+                    }
+                    const int row = warp * L + i;
+                    zi[i] = fmaf(r4[0], hp, (float)t_wx[(row * 4 + 0) * kLanes + lane]);
+                    zf[i] = fmaf(r4[1], hp, (float)t_wx[(row * 4 + 1) * kLanes + lane]);
+                    zz[i] = fmaf(r4[2], hp, (float)t_wx[(row * 4 + 2) * kLanes + lane]);
+                    og[i] = fmaf(r4[3], hp, (float)t_wx[(row * 4 + 3) * kLanes + lane]);
                 }
-                const int row = warp * L + i;
-                zi[i] = fmaf(r4[0], hp, (float)t_wx[(row * 4 + 0) * kLanes + lane]);
-                zf[i] = fmaf(r4[1], hp, (float)t_wx[(row * 4 + 1) * kLanes + lane]);
-                zz[i] = fmaf(r4[2], hp, (float)t_wx[(row * 4 + 2) * kLanes + lane]);
-                og[i] = fmaf(r4[3], hp, (float)t_wx[(row * 4 + 3) * kLanes + lane]);
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-#pragma unroll
-            for (int i = 0; i < L; ++i) {
-                zz[i] = tanh_f(zz[i]);
-                og[i] = 1.0f + ex2_approx(-1.4426950216293335f * og[i]);  // 1 / sigmoid
-            }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+    #pragma unroll
+                for (int i = 0; i < L; ++i) {
+                    zz[i] = tanh_f(zz[i]);
+                    og[i] = 1.0f + ex2_approx(-1.4426950216293335f * og[i]);  // 1 / sigmoid
+                }
 
-            if (!(r == 0 && warp == 0)) named_sync(1 + warp, 64);
-            float m = slot_in[2 * kLanes];
-            float dlt[L], ms[L];
-#pragma unroll
-            for (int i = 0; i < L; ++i) {
-                if (t0 + i < a.T) {
-                    const float left = zf[i] + m;
-                    dlt[i] = left - zi[i];
-                    m = fmaxf(left, zi[i]);
-                } else {
-                    dlt[i] = 0.f;
-                }
-                ms[i] = m;
-            }
-            slot_out[2 * kLanes] = m;
-            if (!(r == n_rounds - 1 && warp == W - 1)) named_arrive(1 + next, 64);
-            float e[L];
-#pragma unroll
-            for (int i = 0; i < L; ++i) e[i] = exp_f(-fabsf(dlt[i]));
-            // (c, n) from the previous warp: its r-th hand-over for warps > 0, the last warp's
-            // (r-1)-th for warp 0
-            if (!(r == 0 && warp == 0)) {
-                const uint32_t par = (warp == 0 ? r - 1 : r) & 1;
-                if (!mbar_wait_bounded(&cnbar[warp], par, kPipeWaitLimit)) timed_out = true;
-            }
-            float c = slot_in[0], n = slot_in[kLanes];
-            float cs[L], ns[L];
-#pragma unroll
-            for (int i = 0; i < L; ++i) {
-                if (t0 + i < a.T) {
-                    const bool lw = dlt[i] >= 0.f;
-                    const float ft = lw ? 1.f : e[i], it = lw ? e[i] : 1.f;
-                    n = fmaf(ft, n, it);
-                    c = fmaf(ft, c, it * zz[i]);
-                }
-                cs[i] = c;
-                ns[i] = n;
-            }
-            slot_out[0] = c;
-            slot_out[kLanes] = n;
-            __syncwarp();
-            if (lane == 0 && !(r == n_rounds - 1 && warp == W - 1)) mbar_arrive(&cnbar[next]);
-
-#pragma unroll
-            for (int i = 0; i < L; ++i) {
-                const int t = t0 + i;
-                if (t < a.T && ch_ok) {
-                    const float h = cs[i] * rcp_f(og[i] * (ns[i] + a.eps));
-                    if (a.state_out) {
-                        float* o = a.state_out + ((size_t)b * a.T + t) * 4 * d + ch;
-                        o[0] = cs[i];
-                        o[d] = ns[i];
-                        o[2 * (size_t)d] = ms[i];
-                        o[3 * (size_t)d] = h;
+                if (!(r == 0 && warp == 0)) named_sync(1 + warp, 64);
+                float m = slot_in[2 * kLanes];
+                float dlt[L], ms[L];
+    #pragma unroll
+                for (int i = 0; i < L; ++i) {
+                    if (FULL || t0 + i < a.T) {
+                        const float left = zf[i] + m;
+                        dlt[i] = left - zi[i];
+                        m = fmaxf(left, zi[i]);
                     } else {
-                        a.h_out[((size_t)b * a.T + t) * d + ch] = h;
+                        dlt[i] = 0.f;
+                    }
+                    ms[i] = m;
+                }
+                slot_out[2 * kLanes] = m;
+                if (!(r == n_rounds - 1 && warp == W - 1)) named_arrive(1 + next, 64);
+                float e[L];
+    #pragma unroll
+                for (int i = 0; i < L; ++i) e[i] = exp_f(-fabsf(dlt[i]));
+                // (c, n) from the previous warp: its r-th hand-over for warps > 0, the last warp's
+                // (r-1)-th for warp 0
+                if (!(r == 0 && warp == 0)) {
+                    const uint32_t par = (warp == 0 ? r - 1 : r) & 1;
+                    if (!mbar_wait_bounded(&cnbar[warp], par, kPipeWaitLimit)) timed_out = true;
+                }
+                float c = slot_in[0], n = slot_in[kLanes];
+                float cs[L], ns[L];
+    #pragma unroll
+                for (int i = 0; i < L; ++i) {
+                    if (FULL || t0 + i < a.T) {
+                        const bool lw = dlt[i] >= 0.f;
+                        const float ft = lw ? 1.f : e[i], it = lw ? e[i] : 1.f;
+                        n = fmaf(ft, n, it);
+                        c = fmaf(ft, c, it * zz[i]);
+                    }
+                    cs[i] = c;
+                    ns[i] = n;
+                }
+                slot_out[0] = c;
+                slot_out[kLanes] = n;
+                __syncwarp();
+                if (lane == 0 && !(r == n_rounds - 1 && warp == W - 1)) mbar_arrive(&cnbar[next]);
+
+                const size_t o_base = ((size_t)b * a.T + t0) * d;
+
+    #pragma unroll
+                for (int i = 0; i < L; ++i) {
+                    const int t = t0 + i;
+                    if ((FULL || t < a.T) && ch_ok) {
+                        const float h = cs[i] * rcp_f(og[i] * (ns[i] + a.eps));
+                        if (a.state_out) {
+                            float* o = a.state_out + o_base * 4 + ch + (size_t)i * 4 * d;
+                            o[0] = cs[i];
+                            o[d] = ns[i];
+                            o[2 * (size_t)d] = ms[i];
+                            o[3 * (size_t)d] = h;
+                        } else {
+                            a.h_out[o_base + ch + (size_t)i * d] = h;
+                        }
                     }
                 }
-            }
-            if (r == n_rounds - 1 && warp == W - 1 && a.tail_out && ch_ok) {
-                a.tail_out[((size_t)b * 3 + 0) * d + ch] = c;
-                a.tail_out[((size_t)b * 3 + 1) * d + ch] = n;
-                a.tail_out[((size_t)b * 3 + 2) * d + ch] = m;
-            }
+                if (r == n_rounds - 1 && warp == W - 1 && a.tail_out && ch_ok) {
+                    a.tail_out[((size_t)b * 3 + 0) * d + ch] = c;
+                    a.tail_out[((size_t)b * 3 + 1) * d + ch] = n;
+                    a.tail_out[((size_t)b * 3 + 2) * d + ch] = m;
+                }
+            };
+            if (t0 + L <= a.T)
+                round_body(std::true_type{});
+            else
+                round_body(std::false_type{});
         }
     }
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
