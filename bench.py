@@ -39,12 +39,16 @@ DEFAULT_T = T_PER_GPU
 SEED = 1
 # algorithmic bytes per (token, channel): bf16 I/O (a=2), fp32 work state (w=4), G=S=4
 BYTES_PICARD_MID = 4 * 2 + 4 + 4          # read wx + h, write h
+BYTES_PICARD_PHASE = 12 + 4 * 16 + 28     # the six separate passes of the warm start (P = 5)
+BYTES_PICARD_SWEEP = 4 * 2 + 16           # what the fused sweep has to move: read wx, write state
 BYTES_NEWTON_MID = 4 * 2 + 16 + 16        # read wx + state, write state
+BYTES_NEWTON_LAST = 4 * 2 + 16 + 4 * 2    # read wx + state, write the I/O-dtype state
 BYTES_BWD = 4 * 2 + 4 * 2 + 4 * 2 + 4 * 2  # read states, wx, cotangent; write g_wx
 BYTES_STEP = 224                          # all passes of one forward + backward
 # DRAM bytes per (token, channel) of each kernel from the committed ncu capture
 # (profiles/slstm_pipe_kernels_B8_T4096_d1024_bf16.md); traffic grows in proportion to the units
-NCU_TRAFFIC_PER_UNIT = {"slstm_picard_kernel": 15.44, "slstm_newton_kernel": 39.02, "slstm_bwd_kernel": 31.37}
+NCU_TRAFFIC_PER_UNIT = {"slstm_picard_pipe_kernel": 15.44, "slstm_newton_pipe_kernel": 39.02,
+                        "slstm_bwd_pipe_kernel": 31.37}
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
@@ -253,6 +257,7 @@ def kernel_rooflines(wx, r32, states32, states_io, G_io, peak):
     hbuf = torch.empty(B, T_PER_GPU, D, dtype=torch.float32, device=dev)
     hbuf2 = torch.empty_like(hbuf)
     sout = torch.empty_like(states32)
+    states_out = torch.empty_like(states_io)
     g_wx = torch.empty_like(wx)
     g_r = torch.empty(4, D, dtype=torch.float32, device=dev)
     g_h0 = torch.empty(B, 4, D, dtype=torch.float32, device=dev)
@@ -262,6 +267,17 @@ def kernel_rooflines(wx, r32, states32, states_io, G_io, peak):
     def picard():
         rc = lib.prb_slstm_picard_pass(P(wx), P(r32), P(hbuf), None, None, P(hbuf2), None, None, None, 0,
                                        B, T_PER_GPU, D, L.PRB_BF16, 1e-6, P(ws), ws.numel(), P(st.buf), stream)
+        assert rc == 0, rc
+
+    def picard_sweep():
+        rc = lib.prb_slstm_picard_sweep(P(wx), P(r32), None, None, P(sout), None, P_PICARD + 1, B, T_PER_GPU, D,
+                                        L.PRB_BF16, 1e-6, P(ws), ws.numel(), P(st.buf), stream)
+        assert rc == 0, rc
+
+    def newton_last():
+        rc = lib.prb_slstm_newton_pass(P(wx), P(r32), P(states32), None, None, P(states_out), None, None, 1, B,
+                                       T_PER_GPU, D, L.PRB_BF16, 1.0, 1e-6, P(ws), ws.numel(), P(st.buf),
+                                       1, stream)
         assert rc == 0, rc
 
     def newton():
@@ -278,15 +294,26 @@ def kernel_rooflines(wx, r32, states32, states_io, G_io, peak):
 
     n_units = B * T_PER_GPU * D
     out = {}
-    for name, fn, nbytes, per_step in (("slstm_picard_kernel", picard, BYTES_PICARD_MID, P_PICARD + 1),
-                                       ("slstm_newton_kernel", newton, BYTES_NEWTON_MID, K_NEWTON),
-                                       ("slstm_bwd_kernel", bwd, BYTES_BWD, 1)):
+    # One training step = 1 fused Picard sweep + (K-1) Newton passes + 1 last Newton pass (with the
+    # fused final residual) + 1 backward launch.  The per-pass Picard kernel (used by the sharded
+    # path) is timed too, with launches_per_step 0.
+    for name, fn, nbytes, per_step in (("slstm_picard_fused_kernel", picard_sweep, BYTES_PICARD_SWEEP, 1),
+                                       ("slstm_picard_pipe_kernel", picard, BYTES_PICARD_MID, 0),
+                                       ("slstm_newton_pipe_kernel", newton, BYTES_NEWTON_MID, K_NEWTON - 1),
+                                       ("slstm_newton_pipe_kernel_last", newton_last, BYTES_NEWTON_LAST, 1),
+                                       ("slstm_bwd_pipe_kernel", bwd, BYTES_BWD, 1)):
         for _ in range(3):
             fn()
         sec = time_region(fn, 10, None) / 10
         gbs = n_units * nbytes / sec / 1e9
         out[name] = {"ms_per_launch": sec * 1e3, "achieved": gbs, "frac": gbs / peak,
                      "launches_per_step": per_step, "algorithmic_bytes_per_launch": n_units * nbytes}
+        if fn is picard_sweep:
+            # the same work as six separate passes (104 B per token-channel by the per-pass
+            # accounting); the sweep is bound by instruction issue, not by HBM
+            out[name]["bound"] = "issue"
+            out[name]["separate_passes_bytes"] = n_units * BYTES_PICARD_PHASE
+            out[name]["achieved_vs_separate_passes"] = n_units * BYTES_PICARD_PHASE / sec / 1e9
     return out
 
 
@@ -382,15 +409,32 @@ def run_gpu_single(args):
     states_io = keep["H"]
     states32 = states_io.float()
     roofs = kernel_rooflines(wx, r_io.float().contiguous(), states32, states_io, G_io, peak)
-    total = {k: v["ms_per_launch"] * v["launches_per_step"] for k, v in roofs.items()}
+    n_units = tokens * D
+    # the dominant kernel by time per step; the two instantiations of the Newton kernel (middle
+    # pass, last pass with the fused final residual) count as one kernel with K launches
+    groups = {"slstm_picard_fused_kernel": ["slstm_picard_fused_kernel"],
+              "slstm_newton_pipe_kernel": ["slstm_newton_pipe_kernel", "slstm_newton_pipe_kernel_last"],
+              "slstm_bwd_pipe_kernel": ["slstm_bwd_pipe_kernel"]}
+    total = {g: sum(roofs[k]["ms_per_launch"] * roofs[k]["launches_per_step"] for k in ks)
+             for g, ks in groups.items()}
     top = max(total, key=total.get)
-    roofline = {"bound": "hbm", "kernel": top, "achieved": roofs[top]["achieved"], "peak": peak,
-                "unit": "GB/s", "frac": roofs[top]["achieved"] / peak, "peak_kind": peak_kind,
-                "traffic": NCU_TRAFFIC_PER_UNIT[top] * B * T_PER_GPU * D, "kernels": roofs,
-                "step": {"algorithmic_bytes": BYTES_STEP * tokens * D,
-                         "achieved": BYTES_STEP * tokens * D / (ms / 1e3) / 1e9,
-                         "frac": BYTES_STEP * tokens * D / (ms / 1e3) / 1e9 / peak,
-                         "frac_of_nominal_8TBs": BYTES_STEP * tokens * D / (ms / 1e3) / 1e9 / NOMINAL_HBM_GBS}}
+    n_launch = sum(roofs[k]["launches_per_step"] for k in groups[top])
+    top_bytes = sum(roofs[k]["algorithmic_bytes_per_launch"] * roofs[k]["launches_per_step"]
+                    for k in groups[top]) / n_launch
+    top_ms = total[top] / n_launch
+    top_gbs = top_bytes / (top_ms / 1e3) / 1e9
+    per_unit = NCU_TRAFFIC_PER_UNIT.get(top)
+    roofline = {"bound": "hbm", "kernel": top, "launches_per_step": n_launch, "ms_per_launch": top_ms,
+                "achieved": top_gbs, "peak": peak, "unit": "GB/s", "frac": top_gbs / peak,
+                "peak_kind": peak_kind, "traffic": per_unit * n_units if per_unit else None,
+                "ms_per_step_by_kernel": total, "kernels": roofs,
+                "step": {"algorithmic_bytes": BYTES_STEP * n_units,
+                         "achieved": BYTES_STEP * n_units / (ms / 1e3) / 1e9,
+                         "frac": BYTES_STEP * n_units / (ms / 1e3) / 1e9 / peak,
+                         "frac_of_nominal_8TBs": BYTES_STEP * n_units / (ms / 1e3) / 1e9 / NOMINAL_HBM_GBS,
+                         "note": "224 B per token-channel counts six separate Picard passes (104 B); the "
+                                 "fused sweep does their work moving 24 B, so this fraction is not "
+                                 "bounded by 1"}}
 
     # CPU baseline on a bounded sample (rank 0, N = 1 only)
     threads = os.cpu_count() or 1
@@ -411,7 +455,8 @@ def run_gpu_single(args):
                 "ms_per_step": e2e_sec * 1e3,
                 "includes": "H2D of x (double-buffered on a copy stream, one copy per step), 3 W_x GEMMs "
                             "(cuBLAS), Newton+scan fwd, reverse scan + VJP, D2H of loss"},
-        "gpu_launches": 12 * args.steps,
+        # per step: fp32 copy of R (x2), fused Picard sweep, 2 Newton passes, backward, reduction
+        "gpu_launches": 7 * args.steps,
         "roofline": roofline,
         "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": "1 of 8 batch rows (rows are independent), full T=16384, d=1024, "

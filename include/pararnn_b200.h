@@ -184,6 +184,17 @@ int prb_diag_bwd_pass(int cell, const void* states, const void* wx, const float*
                       int dtype, void* workspace, size_t workspace_bytes, prb_stats* stats,
                       prb_stream_t stream);
 
+/* All n_passes frozen-gate passes of the sLSTM warm start (the zero-hidden pass first) in one
+ * sweep over the sequence: pass p follows pass p-1 a few steps behind, hidden states never leave
+ * the chip.  Replaces slstm_picard_init, solvers/slstm_picard.py:158-181 (P+1 separate scans
+ * there).  h_halo (B,d), carry_in (B,3,d) = (c,n,m) preceding step 0 or NULL; writes the full
+ * state (B,T,4,d) fp32 of the last pass.  PRB_ERR_UNSUPPORTED when n_passes > 6 or the arrays do
+ * not meet the 16-byte stride rule of the bulk tensor loads (use prb_slstm_picard_pass then). */
+int prb_slstm_picard_sweep(const void* wx, const float* r, const float* h_halo, const float* carry_in,
+                           float* state_out, float* tail_out, int n_passes, int B, int T, int d,
+                           int dtype, float eps, void* workspace, size_t workspace_bytes,
+                           prb_stats* stats, prb_stream_t stream);
+
 /* sLSTM frozen-gate pass: h_prev (B,T,d) hidden trajectory of the previous pass or NULL
  * (zero-hidden pass); h_halo (B,d); carry (B,3,d) = (c,n,m); aggregate (B,4,d) = (a,b,N,C);
  * writes h_out (B,T,d) or, when state_out is given, the full state (B,T,4,d) */

@@ -331,7 +331,28 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
     if (guess) {
         to_f32(guess, p.sb[0], nst, dtype, s);
     } else {
-        for (int pass = 0; pass <= P; ++pass) {
+        // the pipelined family runs all P+1 passes in one sweep when it can
+        bool fused_done = false;
+        const char* fenv = getenv("PRB_PICARD_FUSED");
+        if (path == 2 && P + 1 <= slstm_picard_fused_max_passes() && !(fenv && fenv[0] == '0')) {
+            SlstmPicardArgs a{};
+            a.wx = wx;
+            a.r = p.r;
+            a.h_halo = h0f ? h0f + 3 * (size_t)d : nullptr;
+            a.halo_stride = 4 * d;
+            a.carry_in = h0f;
+            a.carry_stride = 4 * d;
+            a.state_out = p.sb[0];
+            a.B = B;
+            a.T = T;
+            a.d = d;
+            a.eps = eps;
+            a.chain = next_chain(p.chain, T, slstm_picard_tile_steps(), &st->status);
+            const cudaError_t e = launch_slstm_picard_fused(dtype, a, P + 1, s);
+            if (e == cudaSuccess) fused_done = true;
+            else if (e != cudaErrorNotSupported) return PRB_ERR_LAUNCH;
+        }
+        for (int pass = 0; pass <= P && !fused_done; ++pass) {
             SlstmPicardArgs a{};
             a.wx = wx;
             a.r = p.r;
@@ -832,6 +853,37 @@ int prb_slstm_picard_pass(const void* wx, const float* r, const float* h_prev, c
     if (mode == 0 && path == 2) e = launch_slstm_picard_pipe(dtype, a, s);
     if (mode == 0 && path == 1) e = launch_slstm_picard_persist(dtype, a, s);
     if (e == cudaErrorNotSupported) e = launch_slstm_picard(dtype, a, mode == 2, s);
+    return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+}
+
+int prb_slstm_picard_sweep(const void* wx, const float* r, const float* h_halo, const float* carry_in,
+                           float* state_out, float* tail_out, int n_passes, int B, int T, int d,
+                           int dtype, float eps, void* workspace, size_t workspace_bytes,
+                           prb_stats* stats, prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!wx || !r || !state_out || !stats || B < 1 || T < 1 || d < 1 || n_passes < 1 || bad_dtype(dtype))
+        return PRB_ERR_BAD_ARG;
+    if (n_passes > slstm_picard_fused_max_passes() || !slstm_persist_ok(dtype, B, T, d))
+        return PRB_ERR_UNSUPPORTED;
+    PassWs w;
+    if (int e = pass_ws(kCellSlstmDiag, B, T, d, workspace, workspace_bytes, s, w)) return e;
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    SlstmPicardArgs a{};
+    a.wx = wx;
+    a.r = r;
+    a.h_halo = h_halo;
+    a.halo_stride = d;
+    a.carry_in = carry_in;
+    a.carry_stride = 3 * d;
+    a.state_out = state_out;
+    a.tail_out = tail_out;
+    a.B = B;
+    a.T = T;
+    a.d = d;
+    a.eps = eps;
+    a.chain = next_chain(w.chain, T, slstm_picard_tile_steps(), &st->status);
+    const cudaError_t e = launch_slstm_picard_fused(dtype, a, n_passes, s);
+    if (e == cudaErrorNotSupported) return PRB_ERR_UNSUPPORTED;
     return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
 

@@ -10,3 +10,45 @@ from test_gpu_slstm import pytestmark  # noqa: F401
 @pytest.fixture(autouse=True)
 def _force_pipelined_kernels(monkeypatch):
     monkeypatch.setenv("PRB_KERNEL_PATH", "pipe")
+
+
+# ---- the fused sweep (all Picard passes in one launch) against the per-pass kernels
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+from gpu_util import dev, make_problem  # noqa: E402
+
+
+@pytest.mark.parametrize("P", [0, 1, 3, 5])
+@pytest.mark.parametrize("B,T,d,h0", [(1, 1, 32, False), (2, 57, 64, True), (2, 1000, 96, True),
+                                      (1, 4099, 40, False)])
+def test_fused_picard_sweep_equals_separate_passes(P, B, T, d, h0, monkeypatch):
+    from pararnn_b200 import ops
+
+    wx, r, h0a = make_problem("slstm_diag", B, T, d, seed=P + T, h0=h0, x_scale=0.7, bias_f=2.0, rec_scale=2.0)
+
+    def guess():
+        return ops.newton_slstm_fused(dev(wx), dev(r), dev(h0a), None, max_iters=0, picard_iters=P,
+                                      want_residual=False).float().cpu().numpy()
+
+    fused = guess()
+    monkeypatch.setenv("PRB_PICARD_FUSED", "0")
+    separate = guess()
+    for slot in range(4):
+        scale = max(1.0, float(np.abs(separate[:, :, slot]).max()))
+        assert np.abs(fused[:, :, slot] - separate[:, :, slot]).max() <= 1e-6 * scale, slot
+
+
+def test_seven_passes_fall_back_to_separate_kernels():
+    from oracle import oracle
+    from pararnn_b200 import ops
+
+    wx, r, _ = make_problem("slstm_diag", 2, 300, 64, seed=3, x_scale=0.7, bias_f=2.0, rec_scale=2.0)
+    want = oracle.guess(oracle.SLSTM_DIAG, wx, r, None, picard=6)
+    got = ops.newton_slstm_fused(dev(wx), dev(r), None, None, max_iters=0, picard_iters=6,
+                                 want_residual=False).float().cpu().numpy()
+    for slot in range(4):
+        scale = max(1.0, float(np.abs(want[:, :, slot]).max()))
+        # a guess, not a fixed point: chained summaries and the reference's cumsum / cummax form
+        # round differently, a little more with every pass
+        assert np.abs(got[:, :, slot] - want[:, :, slot]).max() <= 1e-4 * scale
