@@ -378,7 +378,30 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
         }
     }
     if (K == 0) from_f32(p.sb[0], out, nst, dtype, s);
-    for (int k = 0; k < K; ++k) {
+    // the pipelined family runs all K iterations in one sweep when it can
+    bool newton_done = false;
+    const char* nenv = getenv("PRB_NEWTON_FUSED");
+    if (path == 2 && K >= 1 && K <= slstm_newton_fused_max_iters() && !(nenv && nenv[0] == '0')) {
+        SlstmNewtonArgs a{};
+        a.wx = wx;
+        a.r = p.r;
+        a.sin = p.sb[0];
+        a.halo = h0f;
+        a.halo_stride = 4 * d;
+        a.sout = out;
+        a.resid_bits = &st->hist_bits[0];
+        a.final_bits = want_residual ? &st->final_bits : nullptr;
+        a.B = B;
+        a.T = T;
+        a.d = d;
+        a.omega = omega;
+        a.eps = eps;
+        a.chain = next_chain(p.chain, T, slstm_tile_steps(), &st->status);
+        const cudaError_t e = launch_slstm_newton_fused(dtype, a, K, s);
+        if (e == cudaSuccess) newton_done = true;
+        else if (e != cudaErrorNotSupported) return PRB_ERR_LAUNCH;
+    }
+    for (int k = 0; k < K && !newton_done; ++k) {
         SlstmNewtonArgs a{};
         a.wx = wx;
         a.r = p.r;

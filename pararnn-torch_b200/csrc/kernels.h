@@ -123,6 +123,9 @@ cudaError_t launch_slstm_bwd(int dtype, const SlstmBwdArgs& a, bool agg_only, cu
 
 // persistent-chain variants (slstm_persist.cu); cudaErrorNotSupported when TMA rules are not met
 bool slstm_persist_ok(int dtype, int B, int T, int d);
+// all Newton iterations in one sweep (slstm_newton_fused.cu)
+int slstm_newton_fused_max_iters();
+cudaError_t launch_slstm_newton_fused(int dtype, const SlstmNewtonArgs& a, int n_iters, cudaStream_t s);
 // all Picard passes of the warm start in one sweep (slstm_picard_fused.cu)
 int slstm_picard_fused_max_passes();
 cudaError_t launch_slstm_picard_fused(int dtype, const SlstmPicardArgs& a, int n_pass, cudaStream_t s);
