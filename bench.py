@@ -43,12 +43,16 @@ BYTES_PICARD_PHASE = 12 + 4 * 16 + 28     # the six separate passes of the warm 
 BYTES_PICARD_SWEEP = 4 * 2 + 16           # what the fused sweep has to move: read wx, write state
 BYTES_NEWTON_MID = 4 * 2 + 16 + 16        # read wx + state, write state
 BYTES_NEWTON_LAST = 4 * 2 + 16 + 4 * 2    # read wx + state, write the I/O-dtype state
+BYTES_NEWTON_PHASE = 40 + 32 + 16         # K = 2 separate passes and the separate residual gate
+BYTES_NEWTON_SWEEP = 4 * 2 + 16 + 4 * 2   # what the fused sweep has to move
 BYTES_BWD = 4 * 2 + 4 * 2 + 4 * 2 + 4 * 2  # read states, wx, cotangent; write g_wx
 BYTES_STEP = 224                          # all passes of one forward + backward
 # DRAM bytes per (token, channel) of each kernel from the committed ncu capture
 # (profiles/slstm_pipe_kernels_B8_T4096_d1024_bf16.md); traffic grows in proportion to the units
 NCU_TRAFFIC_PER_UNIT = {"slstm_picard_pipe_kernel": 15.44, "slstm_newton_pipe_kernel": 39.02,
-                        "slstm_bwd_pipe_kernel": 31.37}
+                        "slstm_bwd_pipe_kernel": 31.37,
+                        # profiles/slstm_fused_sweeps_B8_T4096_d1024_bf16.md
+                        "slstm_picard_fused_kernel": 22.42, "slstm_newton_fused_kernel": 31.56}
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
@@ -274,6 +278,12 @@ def kernel_rooflines(wx, r32, states32, states_io, G_io, peak):
                                         L.PRB_BF16, 1e-6, P(ws), ws.numel(), P(st.buf), stream)
         assert rc == 0, rc
 
+    def newton_sweep():
+        rc = lib.prb_slstm_newton_sweep(P(wx), P(r32), P(states32), None, P(states_out), K_NEWTON, 1, B,
+                                        T_PER_GPU, D, L.PRB_BF16, 1.0, 1e-6, P(ws), ws.numel(), P(st.buf),
+                                        stream)
+        assert rc == 0, rc
+
     def newton_last():
         rc = lib.prb_slstm_newton_pass(P(wx), P(r32), P(states32), None, None, P(states_out), None, None, 1, B,
                                        T_PER_GPU, D, L.PRB_BF16, 1.0, 1e-6, P(ws), ws.numel(), P(st.buf),
@@ -294,26 +304,29 @@ def kernel_rooflines(wx, r32, states32, states_io, G_io, peak):
 
     n_units = B * T_PER_GPU * D
     out = {}
-    # One training step = 1 fused Picard sweep + (K-1) Newton passes + 1 last Newton pass (with the
-    # fused final residual) + 1 backward launch.  The per-pass Picard kernel (used by the sharded
-    # path) is timed too, with launches_per_step 0.
+    # One training step = 1 fused Picard sweep + 1 fused Newton sweep (K iterations and the final
+    # residual) + 1 backward launch.  The per-pass kernels (used by the time-sharded path) are
+    # timed too, with launches_per_step 0.
     for name, fn, nbytes, per_step in (("slstm_picard_fused_kernel", picard_sweep, BYTES_PICARD_SWEEP, 1),
+                                       ("slstm_newton_fused_kernel", newton_sweep, BYTES_NEWTON_SWEEP, 1),
+                                       ("slstm_bwd_pipe_kernel", bwd, BYTES_BWD, 1),
                                        ("slstm_picard_pipe_kernel", picard, BYTES_PICARD_MID, 0),
-                                       ("slstm_newton_pipe_kernel", newton, BYTES_NEWTON_MID, K_NEWTON - 1),
-                                       ("slstm_newton_pipe_kernel_last", newton_last, BYTES_NEWTON_LAST, 1),
-                                       ("slstm_bwd_pipe_kernel", bwd, BYTES_BWD, 1)):
+                                       ("slstm_newton_pipe_kernel", newton, BYTES_NEWTON_MID, 0),
+                                       ("slstm_newton_pipe_kernel_last", newton_last, BYTES_NEWTON_LAST, 0)):
         for _ in range(3):
             fn()
         sec = time_region(fn, 10, None) / 10
         gbs = n_units * nbytes / sec / 1e9
         out[name] = {"ms_per_launch": sec * 1e3, "achieved": gbs, "frac": gbs / peak,
                      "launches_per_step": per_step, "algorithmic_bytes_per_launch": n_units * nbytes}
-        if fn is picard_sweep:
-            # the same work as six separate passes (104 B per token-channel by the per-pass
-            # accounting); the sweep is bound by instruction issue, not by HBM
+        if fn is picard_sweep or fn is newton_sweep:
+            # the same work as the separate passes of the per-pass accounting (104 B per
+            # token-channel for the six Picard passes, 88 B for two Newton passes and the residual
+            # gate); the sweeps are bound by instruction issue, not by HBM
+            phase = BYTES_PICARD_PHASE if fn is picard_sweep else BYTES_NEWTON_PHASE
             out[name]["bound"] = "issue"
-            out[name]["separate_passes_bytes"] = n_units * BYTES_PICARD_PHASE
-            out[name]["achieved_vs_separate_passes"] = n_units * BYTES_PICARD_PHASE / sec / 1e9
+            out[name]["separate_passes_bytes"] = n_units * phase
+            out[name]["achieved_vs_separate_passes"] = n_units * phase / sec / 1e9
     return out
 
 
@@ -410,31 +423,30 @@ def run_gpu_single(args):
     states32 = states_io.float()
     roofs = kernel_rooflines(wx, r_io.float().contiguous(), states32, states_io, G_io, peak)
     n_units = tokens * D
-    # the dominant kernel by time per step; the two instantiations of the Newton kernel (middle
-    # pass, last pass with the fused final residual) count as one kernel with K launches
-    groups = {"slstm_picard_fused_kernel": ["slstm_picard_fused_kernel"],
-              "slstm_newton_pipe_kernel": ["slstm_newton_pipe_kernel", "slstm_newton_pipe_kernel_last"],
-              "slstm_bwd_pipe_kernel": ["slstm_bwd_pipe_kernel"]}
-    total = {g: sum(roofs[k]["ms_per_launch"] * roofs[k]["launches_per_step"] for k in ks)
-             for g, ks in groups.items()}
+    # The dominant kernel by time per step.  `achieved` follows the per-pass accounting of the
+    # algorithm (the bytes the separate passes this launch replaces would move), `traffic` is what
+    # ncu saw it move: for the fused sweeps traffic is far BELOW the algorithmic bytes, because the
+    # intermediate trajectories stay on chip, and the fraction is not bounded by 1.
+    total = {k: v["ms_per_launch"] * v["launches_per_step"] for k, v in roofs.items()}
     top = max(total, key=total.get)
-    n_launch = sum(roofs[k]["launches_per_step"] for k in groups[top])
-    top_bytes = sum(roofs[k]["algorithmic_bytes_per_launch"] * roofs[k]["launches_per_step"]
-                    for k in groups[top]) / n_launch
-    top_ms = total[top] / n_launch
-    top_gbs = top_bytes / (top_ms / 1e3) / 1e9
+    top_bytes = roofs[top].get("separate_passes_bytes", roofs[top]["algorithmic_bytes_per_launch"])
+    top_gbs = top_bytes / (roofs[top]["ms_per_launch"] / 1e3) / 1e9
     per_unit = NCU_TRAFFIC_PER_UNIT.get(top)
-    roofline = {"bound": "hbm", "kernel": top, "launches_per_step": n_launch, "ms_per_launch": top_ms,
+    roofline = {"bound": "hbm", "kernel": top, "ms_per_launch": roofs[top]["ms_per_launch"],
                 "achieved": top_gbs, "peak": peak, "unit": "GB/s", "frac": top_gbs / peak,
                 "peak_kind": peak_kind, "traffic": per_unit * n_units if per_unit else None,
-                "ms_per_step_by_kernel": total, "kernels": roofs,
+                "note": "fused sweep: does the work of several HBM-bound passes while moving "
+                        "bytes_moved_per_launch; limited by instruction issue",
+                "bytes_moved_per_launch": roofs[top]["algorithmic_bytes_per_launch"],
+                "achieved_on_bytes_moved": roofs[top]["achieved"],
+                "ms_per_step_by_kernel": {k: v for k, v in total.items() if v > 0}, "kernels": roofs,
                 "step": {"algorithmic_bytes": BYTES_STEP * n_units,
                          "achieved": BYTES_STEP * n_units / (ms / 1e3) / 1e9,
                          "frac": BYTES_STEP * n_units / (ms / 1e3) / 1e9 / peak,
                          "frac_of_nominal_8TBs": BYTES_STEP * n_units / (ms / 1e3) / 1e9 / NOMINAL_HBM_GBS,
-                         "note": "224 B per token-channel counts six separate Picard passes (104 B); the "
-                                 "fused sweep does their work moving 24 B, so this fraction is not "
-                                 "bounded by 1"}}
+                         "bytes_moved": (BYTES_PICARD_SWEEP + BYTES_NEWTON_SWEEP + BYTES_BWD) * n_units,
+                         "note": "224 B per token-channel is the per-pass accounting (9 sweeps); the "
+                                 "three launches of a step move 88 B"}}
 
     # CPU baseline on a bounded sample (rank 0, N = 1 only)
     threads = os.cpu_count() or 1
@@ -455,8 +467,8 @@ def run_gpu_single(args):
                 "ms_per_step": e2e_sec * 1e3,
                 "includes": "H2D of x (double-buffered on a copy stream, one copy per step), 3 W_x GEMMs "
                             "(cuBLAS), Newton+scan fwd, reverse scan + VJP, D2H of loss"},
-        # per step: fp32 copy of R (x2), fused Picard sweep, 2 Newton passes, backward, reduction
-        "gpu_launches": 7 * args.steps,
+        # per step: fp32 copy of R (x2), Picard sweep, Newton sweep, backward, reduction
+        "gpu_launches": 6 * args.steps,
         "roofline": roofline,
         "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": "1 of 8 batch rows (rows are independent), full T=16384, d=1024, "

@@ -195,6 +195,19 @@ int prb_slstm_picard_sweep(const void* wx, const float* r, const float* h_halo, 
                            int dtype, float eps, void* workspace, size_t workspace_bytes,
                            prb_stats* stats, prb_stream_t stream);
 
+/* All n_iters Newton iterations of a whole sequence in one sweep (iteration k+1 follows iteration
+ * k a few steps behind; intermediate iterates never leave the chip), with the residual of the
+ * result when want_residual is set.  Replaces the K passes of _newton_slstm_fused_impl,
+ * kernels/newton_slstm.py:2696-2939, and the eager residual of _fill_stats,
+ * solvers/newton/__init__.py:582-636.  sin (B,T,4,d) fp32 warm start, halo (B,4,d) state preceding
+ * step 0 or NULL, sout (B,T,4,d) in the I/O dtype; stats->hist_bits[k] = max|F(H^k)|.
+ * PRB_ERR_UNSUPPORTED when n_iters > 4 or the arrays do not meet the 16-byte stride rule of the
+ * bulk tensor loads (use prb_slstm_newton_pass then). */
+int prb_slstm_newton_sweep(const void* wx, const float* r, const float* sin, const float* halo, void* sout,
+                           int n_iters, int want_residual, int B, int T, int d, int dtype, float omega,
+                           float eps, void* workspace, size_t workspace_bytes, prb_stats* stats,
+                           prb_stream_t stream);
+
 /* sLSTM frozen-gate pass: h_prev (B,T,d) hidden trajectory of the previous pass or NULL
  * (zero-hidden pass); h_halo (B,d); carry (B,3,d) = (c,n,m); aggregate (B,4,d) = (a,b,N,C);
  * writes h_out (B,T,d) or, when state_out is given, the full state (B,T,4,d) */

@@ -910,6 +910,38 @@ int prb_slstm_picard_sweep(const void* wx, const float* r, const float* h_halo, 
     return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
 
+int prb_slstm_newton_sweep(const void* wx, const float* r, const float* sin, const float* halo, void* sout,
+                           int n_iters, int want_residual, int B, int T, int d, int dtype, float omega,
+                           float eps, void* workspace, size_t workspace_bytes, prb_stats* stats,
+                           prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!wx || !r || !sin || !sout || !stats || B < 1 || T < 1 || d < 1 || n_iters < 1 || bad_dtype(dtype))
+        return PRB_ERR_BAD_ARG;
+    if (n_iters > slstm_newton_fused_max_iters() || !slstm_persist_ok(dtype, B, T, d))
+        return PRB_ERR_UNSUPPORTED;
+    PassWs w;
+    if (int e = pass_ws(kCellSlstmDiag, B, T, d, workspace, workspace_bytes, s, w)) return e;
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    SlstmNewtonArgs a{};
+    a.wx = wx;
+    a.r = r;
+    a.sin = sin;
+    a.halo = halo;
+    a.halo_stride = 4 * d;
+    a.sout = sout;
+    a.resid_bits = &st->hist_bits[0];
+    a.final_bits = want_residual ? &st->final_bits : nullptr;
+    a.B = B;
+    a.T = T;
+    a.d = d;
+    a.omega = omega;
+    a.eps = eps;
+    a.chain = next_chain(w.chain, T, slstm_tile_steps(), &st->status);
+    const cudaError_t e = launch_slstm_newton_fused(dtype, a, n_iters, s);
+    if (e == cudaErrorNotSupported) return PRB_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+}
+
 int prb_slstm_newton_pass(const void* wx, const float* r, const float* sin, const float* halo,
                           const float* carry_in, void* sout, float* tail_out, float* agg_out, int mode,
                           int B, int T, int d, int dtype, float omega, float eps, void* workspace,

@@ -47,6 +47,7 @@ _SIGNATURES = {
     "prb_diag_bwd_pass": (_INT, [_INT] + [_VOIDP] * 10 + [_INT] * 5 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_slstm_picard_pass": (_INT, [_VOIDP] * 9 + [_INT] * 5 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_slstm_picard_sweep": (_INT, [_VOIDP] * 6 + [_INT] * 5 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
+    "prb_slstm_newton_sweep": (_INT, [_VOIDP] * 5 + [_INT] * 6 + [_FLOAT, _FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_slstm_newton_pass": (_INT, [_VOIDP] * 8 + [_INT] * 5 + [_FLOAT, _FLOAT, _VOIDP, _SIZE, _VOIDP, _INT, _VOIDP]),
     "prb_slstm_bwd_pass": (_INT, [_VOIDP] * 10 + [_INT] * 5 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_fold_carries": (_INT, [_INT, _VOIDP, _INT, _INT, _INT, _VOIDP, _INT, _INT, _VOIDP]),

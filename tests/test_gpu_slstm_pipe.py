@@ -52,3 +52,30 @@ def test_seven_passes_fall_back_to_separate_kernels():
         # a guess, not a fixed point: chained summaries and the reference's cumsum / cummax form
         # round differently, a little more with every pass
         assert np.abs(got[:, :, slot] - want[:, :, slot]).max() <= 1e-4 * scale
+
+
+@pytest.mark.parametrize("K", [1, 2, 3, 4, 5])
+@pytest.mark.parametrize("B,T,d,h0", [(1, 1, 32, False), (2, 57, 64, True), (2, 1000, 96, True),
+                                      (1, 4099, 40, False)])
+def test_fused_newton_sweep_equals_separate_passes(K, B, T, d, h0, monkeypatch):
+    """K = 5 exceeds what one sweep takes and runs the separate passes in both cases."""
+    from pararnn_b200 import ops
+
+    wx, r, h0a = make_problem("slstm_diag", B, T, d, seed=K + T, h0=h0, x_scale=0.5, bias_f=3.0)
+
+    def solve():
+        st = ops.DeviceStats("cuda", K)
+        H = ops.newton_slstm_fused(dev(wx), dev(r), dev(h0a), None, max_iters=K, picard_iters=2, stats=st)
+        hist, res, status = st.read()
+        assert status == 0
+        return H.float().cpu().numpy(), np.asarray(hist), res
+
+    fused, hist_f, res_f = solve()
+    monkeypatch.setenv("PRB_NEWTON_FUSED", "0")
+    separate, hist_s, res_s = solve()
+    amp = max(1.0, float(hist_s.max()))
+    for slot in range(4):
+        scale = max(1.0, float(np.abs(separate[:, :, slot]).max()))
+        assert np.abs(fused[:, :, slot] - separate[:, :, slot]).max() <= 2e-6 * scale * amp, slot
+    np.testing.assert_allclose(hist_f, hist_s, rtol=1e-3, atol=1e-6)
+    assert abs(res_f - res_s) <= 1e-3 * res_s + 2e-6
