@@ -14,6 +14,8 @@
 #include "slstm_cell.cuh"
 #include "tma.cuh"
 
+#include <type_traits>
+
 namespace prb {
 
 constexpr int kAggW = 8;
@@ -133,37 +135,45 @@ slstm_newton_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
         if (!ring.wait(k)) timed_out = true;
         const TIO* t_wx = reinterpret_cast<const TIO*>(ring.stage(k));
         const float* t_st = reinterpret_cast<const float*>(ring.stage(k) + S::WX);
-#pragma unroll
-        for (int i = 0; i < U; ++i) {
-            if (lo + k * U + i < hi) {
-                float w[4], cur[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    w[q] = (float)t_wx[(i * 4 + q) * kLanes + lane];
-                    cur[q] = t_st[(i * 4 + q) * kLanes + lane];
-                }
-                SlstmLin lin;
-                slstm_linearize(prev, w, r4, a.eps, lin);
-                const float fc = lin.pc - cur[0], fn = lin.pn - cur[1];
-                const float fm = lin.pm - cur[2], fh = lin.ph - cur[3];
-                const float fh2 = fh - lin.ia * fc - lin.ib * fn;
-#pragma unroll
-                for (int c5 = 0; c5 < 5; ++c5) {
-                    const bool off = (c5 == 4);
-                    float xc = off ? mp[16] : mp[0 * 4 + c5], xn = off ? mp[17] : mp[1 * 4 + c5];
-                    float xm = off ? mp[18] : mp[2 * 4 + c5], xh = off ? mp[19] : mp[3 * 4 + c5];
-                    slstm_apply(lin, off ? fc : 0.f, off ? fn : 0.f, off ? fm : 0.f, off ? fh2 : 0.f, xc, xn,
-                                xm, xh);
-                    if (off) {
-                        mp[16] = xc; mp[17] = xn; mp[18] = xm; mp[19] = xh;
-                    } else {
-                        mp[0 * 4 + c5] = xc; mp[1 * 4 + c5] = xn; mp[2 * 4 + c5] = xm; mp[3 * 4 + c5] = xh;
+        // chunks that lie fully inside the warp's range take a variant without range checks
+        auto chunk_body = [&](auto full_c) {
+            constexpr bool FULL = decltype(full_c)::value;
+    #pragma unroll
+            for (int i = 0; i < U; ++i) {
+                if (FULL || lo + k * U + i < hi) {
+                    float w[4], cur[4];
+    #pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        w[q] = (float)t_wx[(i * 4 + q) * kLanes + lane];
+                        cur[q] = t_st[(i * 4 + q) * kLanes + lane];
                     }
+                    SlstmLin lin;
+                    slstm_linearize(prev, w, r4, a.eps, lin);
+                    const float fc = lin.pc - cur[0], fn = lin.pn - cur[1];
+                    const float fm = lin.pm - cur[2], fh = lin.ph - cur[3];
+                    const float fh2 = fh - lin.ia * fc - lin.ib * fn;
+    #pragma unroll
+                    for (int c5 = 0; c5 < 5; ++c5) {
+                        const bool off = (c5 == 4);
+                        float xc = off ? mp[16] : mp[0 * 4 + c5], xn = off ? mp[17] : mp[1 * 4 + c5];
+                        float xm = off ? mp[18] : mp[2 * 4 + c5], xh = off ? mp[19] : mp[3 * 4 + c5];
+                        slstm_apply(lin, off ? fc : 0.f, off ? fn : 0.f, off ? fm : 0.f, off ? fh2 : 0.f, xc, xn,
+                                    xm, xh);
+                        if (off) {
+                            mp[16] = xc; mp[17] = xn; mp[18] = xm; mp[19] = xh;
+                        } else {
+                            mp[0 * 4 + c5] = xc; mp[1 * 4 + c5] = xn; mp[2 * 4 + c5] = xm; mp[3 * 4 + c5] = xh;
+                        }
+                    }
+    #pragma unroll
+                    for (int q = 0; q < 4; ++q) prev[q] = cur[q];
                 }
-#pragma unroll
-                for (int q = 0; q < 4; ++q) prev[q] = cur[q];
             }
-        }
+        };
+        if (lo + (k + 1) * U <= hi)
+            chunk_body(std::true_type{});
+        else
+            chunk_body(std::false_type{});
         __syncwarp();
         if (lane == 0 && k + NST < n_chunks) {
             fence_proxy_async();
@@ -225,27 +235,35 @@ slstm_picard_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
         if (!ring.wait(k)) timed_out = true;
         const TIO* t_wx = reinterpret_cast<const TIO*>(ring.stage(k));
         const float* t_h = reinterpret_cast<const float*>(ring.stage(k) + S::WX);
-#pragma unroll
-        for (int i = 0; i < U; ++i) {
-            const int t = lo + k * U + i;
-            if (t < hi) {
-                float hp = 0.f;
-                if (HAS_H)
-                    hp = (t == 0) ? (a.h_halo ? __ldg(a.h_halo + (size_t)b * a.halo_stride + chl) : 0.f)
-                                  : t_h[i * kLanes + lane];
-                const float zi = fmaf(r4[0], hp, (float)t_wx[(i * 4 + 0) * kLanes + lane]);
-                const float zf = fmaf(r4[1], hp, (float)t_wx[(i * 4 + 1) * kLanes + lane]);
-                const float zz = tanh_f(fmaf(r4[2], hp, (float)t_wx[(i * 4 + 2) * kLanes + lane]));
-                const float b1a = mp[1] + zf;
-                const float e = exp_f(-fabsf(b1a - zi));
-                const bool left = b1a >= zi;
-                const float s1 = left ? 1.f : e, s2 = left ? e : 1.f;
-                mp[0] += zf;
-                mp[1] = left ? b1a : zi;
-                mp[2] = fmaf(mp[2], s1, s2);
-                mp[3] = fmaf(mp[3], s1, s2 * zz);
+        // chunks that lie fully inside the warp's range take a variant without range checks
+        auto chunk_body = [&](auto full_c) {
+            constexpr bool FULL = decltype(full_c)::value;
+    #pragma unroll
+            for (int i = 0; i < U; ++i) {
+                const int t = lo + k * U + i;
+                if (FULL || t < hi) {
+                    float hp = 0.f;
+                    if (HAS_H)
+                        hp = (t == 0) ? (a.h_halo ? __ldg(a.h_halo + (size_t)b * a.halo_stride + chl) : 0.f)
+                                      : t_h[i * kLanes + lane];
+                    const float zi = fmaf(r4[0], hp, (float)t_wx[(i * 4 + 0) * kLanes + lane]);
+                    const float zf = fmaf(r4[1], hp, (float)t_wx[(i * 4 + 1) * kLanes + lane]);
+                    const float zz = tanh_f(fmaf(r4[2], hp, (float)t_wx[(i * 4 + 2) * kLanes + lane]));
+                    const float b1a = mp[1] + zf;
+                    const float e = exp_f(-fabsf(b1a - zi));
+                    const bool left = b1a >= zi;
+                    const float s1 = left ? 1.f : e, s2 = left ? e : 1.f;
+                    mp[0] += zf;
+                    mp[1] = left ? b1a : zi;
+                    mp[2] = fmaf(mp[2], s1, s2);
+                    mp[3] = fmaf(mp[3], s1, s2 * zz);
+                }
             }
-        }
+        };
+        if (lo + (k + 1) * U <= hi)
+            chunk_body(std::true_type{});
+        else
+            chunk_body(std::false_type{});
         __syncwarp();
         if (lane == 0 && k + NST < n_chunks) {
             fence_proxy_async();

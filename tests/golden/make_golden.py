@@ -95,7 +95,9 @@ def run_case(name, cell, x, *, K, P=None, h0=None, omega=1.0):
 
 
 def main():
-    ref_src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src"
+    ref_src = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("PARARNN_REFERENCE_SRC")
+    if not ref_src:
+        raise SystemExit("usage: make_golden.py /path/to/reference/src")
     sys.path.insert(0, ref_src)
     warnings.filterwarnings("ignore")
     import logging
