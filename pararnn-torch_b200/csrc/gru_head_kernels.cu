@@ -39,100 +39,104 @@ __device__ __forceinline__ void stage_bar(int id) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(kHG) : "memory");
 }
 
-// dot products of two broadcast vectors with two register-resident columns.  Every product is
-// split over four partial accumulators: with one warp per scheduler the latency of the dependent
-// FMA chain, not the issue rate, sets the pace.
+// Dot products of broadcast vectors (shared memory) with register-resident columns.  The
+// products run on packed fp32 FMAs (fma.rn.f32x2: two lanes per instruction, sm_100), pairing
+// consecutive elements; every product keeps two packed accumulators, i.e. four partial sums,
+// because with one warp per scheduler the latency of a dependent FMA chain, not the issue rate,
+// sets the pace.
+__device__ __forceinline__ float hsum2(float2 a, float2 b) { return (a.x + a.y) + (b.x + b.y); }
+
 template <int DH>
 __device__ __forceinline__ void dot2x2(const float* va, const float* vb, const float (&c0)[DH],
                                        const float (&c1)[DH], float& a0, float& a1, float& b0, float& b1) {
-    float pa0[4] = {0.f, 0.f, 0.f, 0.f}, pa1[4] = {0.f, 0.f, 0.f, 0.f};
-    float pb0[4] = {0.f, 0.f, 0.f, 0.f}, pb1[4] = {0.f, 0.f, 0.f, 0.f};
+    float2 pa0[2] = {{0.f, 0.f}, {0.f, 0.f}}, pa1[2] = {{0.f, 0.f}, {0.f, 0.f}};
+    float2 pb0[2] = {{0.f, 0.f}, {0.f, 0.f}}, pb1[2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
     for (int i = 0; i < DH; i += 4) {
         const float4 x = *reinterpret_cast<const float4*>(va + i);
         const float4 y = *reinterpret_cast<const float4*>(vb + i);
-        const float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+        const float2 xs[2] = {{x.x, x.y}, {x.z, x.w}}, ys[2] = {{y.x, y.y}, {y.z, y.w}};
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            pa0[k] = fmaf(xs[k], c0[i + k], pa0[k]);
-            pa1[k] = fmaf(xs[k], c1[i + k], pa1[k]);
-            pb0[k] = fmaf(ys[k], c0[i + k], pb0[k]);
-            pb1[k] = fmaf(ys[k], c1[i + k], pb1[k]);
+        for (int k = 0; k < 2; ++k) {
+            const float2 k0 = make_float2(c0[i + 2 * k], c0[i + 2 * k + 1]);
+            const float2 k1 = make_float2(c1[i + 2 * k], c1[i + 2 * k + 1]);
+            pa0[k] = __ffma2_rn(xs[k], k0, pa0[k]);
+            pa1[k] = __ffma2_rn(xs[k], k1, pa1[k]);
+            pb0[k] = __ffma2_rn(ys[k], k0, pb0[k]);
+            pb1[k] = __ffma2_rn(ys[k], k1, pb1[k]);
         }
     }
-    a0 = (pa0[0] + pa0[1]) + (pa0[2] + pa0[3]);
-    a1 = (pa1[0] + pa1[1]) + (pa1[2] + pa1[3]);
-    b0 = (pb0[0] + pb0[1]) + (pb0[2] + pb0[3]);
-    b1 = (pb1[0] + pb1[1]) + (pb1[2] + pb1[3]);
+    a0 = hsum2(pa0[0], pa0[1]);
+    a1 = hsum2(pa1[0], pa1[1]);
+    b0 = hsum2(pb0[0], pb0[1]);
+    b1 = hsum2(pb1[0], pb1[1]);
 }
 template <int DH>
 __device__ __forceinline__ void dot2x1(const float* va, const float* vb, const float (&c)[DH], float& a,
                                        float& b) {
-    float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
+    float2 pa[2] = {{0.f, 0.f}, {0.f, 0.f}}, pb[2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
     for (int i = 0; i < DH; i += 4) {
         const float4 x = *reinterpret_cast<const float4*>(va + i);
         const float4 y = *reinterpret_cast<const float4*>(vb + i);
-        const float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+        const float2 xs[2] = {{x.x, x.y}, {x.z, x.w}}, ys[2] = {{y.x, y.y}, {y.z, y.w}};
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            pa[k] = fmaf(xs[k], c[i + k], pa[k]);
-            pb[k] = fmaf(ys[k], c[i + k], pb[k]);
+        for (int k = 0; k < 2; ++k) {
+            const float2 kk = make_float2(c[i + 2 * k], c[i + 2 * k + 1]);
+            pa[k] = __ffma2_rn(xs[k], kk, pa[k]);
+            pb[k] = __ffma2_rn(ys[k], kk, pb[k]);
         }
     }
-    a = (pa[0] + pa[1]) + (pa[2] + pa[3]);
-    b = (pb[0] + pb[1]) + (pb[2] + pb[3]);
+    a = hsum2(pa[0], pa[1]);
+    b = hsum2(pb[0], pb[1]);
 }
 // two products with two different row sets (reverse kernel)
 template <int DH>
 __device__ __forceinline__ void dot1x1x2(const float* va, const float* vb, const float (&c0)[DH],
                                          const float (&c1)[DH], float& a, float& b) {
-    float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
+    float2 pa[2] = {{0.f, 0.f}, {0.f, 0.f}}, pb[2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
     for (int i = 0; i < DH; i += 4) {
         const float4 x = *reinterpret_cast<const float4*>(va + i);
         const float4 y = *reinterpret_cast<const float4*>(vb + i);
-        const float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+        const float2 xs[2] = {{x.x, x.y}, {x.z, x.w}}, ys[2] = {{y.x, y.y}, {y.z, y.w}};
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            pa[k] = fmaf(xs[k], c0[i + k], pa[k]);
-            pb[k] = fmaf(ys[k], c1[i + k], pb[k]);
+        for (int k = 0; k < 2; ++k) {
+            pa[k] = __ffma2_rn(xs[k], make_float2(c0[i + 2 * k], c0[i + 2 * k + 1]), pa[k]);
+            pb[k] = __ffma2_rn(ys[k], make_float2(c1[i + 2 * k], c1[i + 2 * k + 1]), pb[k]);
         }
     }
-    a = (pa[0] + pa[1]) + (pa[2] + pa[3]);
-    b = (pb[0] + pb[1]) + (pb[2] + pb[3]);
+    a = hsum2(pa[0], pa[1]);
+    b = hsum2(pb[0], pb[1]);
 }
-
 // one broadcast vector against two / one register-resident columns
 template <int DH>
 __device__ __forceinline__ void dot1x2(const float* va, const float (&c0)[DH], const float (&c1)[DH],
                                        float& a0, float& a1) {
-    float p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f};
+    float2 p0[2] = {{0.f, 0.f}, {0.f, 0.f}}, p1[2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
     for (int i = 0; i < DH; i += 4) {
         const float4 x = *reinterpret_cast<const float4*>(va + i);
-        const float xs[4] = {x.x, x.y, x.z, x.w};
+        const float2 xs[2] = {{x.x, x.y}, {x.z, x.w}};
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            p0[k] = fmaf(xs[k], c0[i + k], p0[k]);
-            p1[k] = fmaf(xs[k], c1[i + k], p1[k]);
+        for (int k = 0; k < 2; ++k) {
+            p0[k] = __ffma2_rn(xs[k], make_float2(c0[i + 2 * k], c0[i + 2 * k + 1]), p0[k]);
+            p1[k] = __ffma2_rn(xs[k], make_float2(c1[i + 2 * k], c1[i + 2 * k + 1]), p1[k]);
         }
     }
-    a0 = (p0[0] + p0[1]) + (p0[2] + p0[3]);
-    a1 = (p1[0] + p1[1]) + (p1[2] + p1[3]);
+    a0 = hsum2(p0[0], p0[1]);
+    a1 = hsum2(p1[0], p1[1]);
 }
 template <int DH>
 __device__ __forceinline__ float dot1x1(const float* va, const float (&c)[DH]) {
-    float p[4] = {0.f, 0.f, 0.f, 0.f};
+    float2 p[2] = {{0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
     for (int i = 0; i < DH; i += 4) {
         const float4 x = *reinterpret_cast<const float4*>(va + i);
-        p[0] = fmaf(x.x, c[i], p[0]);
-        p[1] = fmaf(x.y, c[i + 1], p[1]);
-        p[2] = fmaf(x.z, c[i + 2], p[2]);
-        p[3] = fmaf(x.w, c[i + 3], p[3]);
+        p[0] = __ffma2_rn(make_float2(x.x, x.y), make_float2(c[i], c[i + 1]), p[0]);
+        p[1] = __ffma2_rn(make_float2(x.z, x.w), make_float2(c[i + 2], c[i + 3]), p[1]);
     }
-    return (p[0] + p[1]) + (p[2] + p[3]);
+    return hsum2(p[0], p[1]);
 }
 
 struct HeadFwdArgs {
@@ -436,16 +440,21 @@ __global__ void __launch_bounds__(192, 1) gru_head_bwd_kernel(HeadBwdArgs a) {
                     const float dz = s_d[(k + 1) & 1][0][o], dr = s_d[(k + 1) & 1][1][o];
                     const float dn = s_d[(k + 1) & 1][2][o];
                     const int slot = ring == 2 ? 0 : ring + 1;  // (k - 2) % 3
+                    const float2 dz2 = make_float2(dz, dz), dr2 = make_float2(dr, dr), dn2 = make_float2(dn, dn);
 #pragma unroll
                     for (int i = 0; i < DH; i += 4) {
                         const float4 x = *reinterpret_cast<const float4*>(&s_h[slot][i]);
                         const float4 y = *reinterpret_cast<const float4*>(&s_u[slot][i]);
-                        const float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+                        const float2 xs[2] = {{x.x, x.y}, {x.z, x.w}}, ys[2] = {{y.x, y.y}, {y.z, y.w}};
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            m0[i + q] = fmaf(xs[q], dz, m0[i + q]);
-                            m1[i + q] = fmaf(xs[q], dr, m1[i + q]);
-                            m2[i + q] = fmaf(ys[q], dn, m2[i + q]);
+                        for (int q = 0; q < 2; ++q) {
+                            const int j = i + 2 * q;
+                            const float2 r0 = __ffma2_rn(xs[q], dz2, make_float2(m0[j], m0[j + 1]));
+                            const float2 r1 = __ffma2_rn(xs[q], dr2, make_float2(m1[j], m1[j + 1]));
+                            const float2 r2 = __ffma2_rn(ys[q], dn2, make_float2(m2[j], m2[j + 1]));
+                            m0[j] = r0.x; m0[j + 1] = r0.y;
+                            m1[j] = r1.x; m1[j + 1] = r1.y;
+                            m2[j] = r2.x; m2[j + 1] = r2.y;
                         }
                     }
                 }
