@@ -90,6 +90,27 @@ __device__ __forceinline__ float sigmoid_f(float x) {
 __device__ __forceinline__ float tanh_f(float x) {
     return fmaf(-2.0f, rcp_f(ex2_approx(2.885390043258667f * x) + 1.0f), 1.0f);
 }
+// ---- packed fp32 (fma.rn.f32x2 family, sm_100): two independent time steps per instruction for
+// the add / multiply / fma part of the math; the SFU ops stay one per lane.  Each lane computes
+// exactly what the scalar function above computes (same operations, same rounding).
+__device__ __forceinline__ float2 splat2(float x) { return make_float2(x, x); }
+__device__ __forceinline__ float2 ex2_2(float2 v) { return make_float2(ex2_approx(v.x), ex2_approx(v.y)); }
+__device__ __forceinline__ float2 rcp_2(float2 v) { return make_float2(rcp_f(v.x), rcp_f(v.y)); }
+__device__ __forceinline__ float2 tanh_f2(float2 x) {
+    const float2 t = ex2_2(__fmul2_rn(x, splat2(2.885390043258667f)));
+    return __ffma2_rn(splat2(-2.0f), rcp_2(__fadd2_rn(t, splat2(1.0f))), splat2(1.0f));
+}
+__device__ __forceinline__ float2 exp_f2(float2 x) {
+    x.x = x.x < -88.f ? -88.f : x.x;
+    x.y = x.y < -88.f ? -88.f : x.y;
+    const float kL2E = 1.4426950216293335f, kL2E_LO = 1.9259629911e-8f;
+    const float2 hi = __fmul2_rn(x, splat2(kL2E));
+    const float2 nhi = __fmul2_rn(x, splat2(-kL2E));  // = -hi exactly
+    float2 lo = __ffma2_rn(x, splat2(kL2E), nhi);
+    lo = __ffma2_rn(x, splat2(kL2E_LO), lo);
+    const float2 r = ex2_2(hi);
+    return __ffma2_rn(r, __fmul2_rn(lo, splat2(0.6931471805599453f)), r);
+}
 __device__ __forceinline__ unsigned absbits(float v) { return __float_as_uint(v) & 0x7fffffffu; }
 
 // Block-wide max of |F| bit patterns, then one atomicMax into global memory.

@@ -78,7 +78,7 @@ struct FusedPicardSmem {
 };
 
 template <typename TIO, int L, int W, int NSTAGE>
-__global__ void __launch_bounds__((W + 1) * 32, 2)
+__global__ void __launch_bounds__(W * 32, 2)
 slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicardArgs a, int n_pass) {
     using S = FusedPicardSmem<TIO, L, W, NSTAGE>;
     constexpr int LT = S::LT;
@@ -123,17 +123,17 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
     __syncthreads();
     bool timed_out = false;
 
-    if (warp == W) {
-        if (lane == 0) {
-            for (int r = 0; r < n_rounds; ++r) {
-                const int s = r % NSTAGE;
-                if (r >= NSTAGE && !mbar_wait_bounded(&empty[s], ((r / NSTAGE) - 1) & 1, kFusedWaitLimit))
-                    timed_out = true;
-                mbar_expect_tx(&full[s], S::STAGE);
-                tma_load_3d(smem + s * S::STAGE, &tm_wx, &full[s], cb * kLanes, 0, row0 + r * LT);
-            }
-        }
-    } else {
+    // No dedicated producer warp (it would cost an eighth of the register file): lane 0 of warp 0
+    // keeps the TMA ring full.  At the start of round r it refills the stage of round r-1, which
+    // every warp has copied to registers long before (the warps are at most half a round apart).
+    auto issue = [&](int r) {
+        const int s = r % NSTAGE;
+        mbar_expect_tx(&full[s], S::STAGE);
+        tma_load_3d(smem + s * S::STAGE, &tm_wx, &full[s], cb * kLanes, 0, row0 + r * LT);
+    };
+    if (threadIdx.x == 0)
+        for (int r = 0; r < NSTAGE && r < n_rounds; ++r) issue(r);
+    {
         float r4[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) r4[q] = __ldg(a.r + (size_t)q * d + chl);
@@ -141,6 +141,12 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
 
         for (int r = 0; r < n_rounds; ++r) {
             const int s = r % NSTAGE;
+            if (threadIdx.x == 0 && r >= 1 && r - 1 + NSTAGE < n_rounds) {
+                if (!mbar_wait_bounded(&empty[(r - 1) % NSTAGE], ((r - 1) / NSTAGE) & 1, kFusedWaitLimit))
+                    timed_out = true;
+                issue(r - 1 + NSTAGE);
+            }
+            __syncwarp();
             if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, kFusedWaitLimit)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const int t0 = r * LT + warp * L;
@@ -164,13 +170,22 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
                     float* slot_in = s_slot + ((g * W + warp) * 4) * kLanes + lane;
                     float* slot_out = s_slot + ((g * W + next) * 4) * kLanes + lane;
                     float zi[L], zf[L], zz[L], og[L];
+                    // two steps per packed instruction
 #pragma unroll
-                    for (int i = 0; i < L; ++i) {
+                    for (int i = 0; i < L; i += 2) {
                         wxr[i].pin();
-                        zi[i] = fmaf(r4[0], hp[i], wxr[i].get(0));
-                        zf[i] = fmaf(r4[1], hp[i], wxr[i].get(1));
-                        zz[i] = tanh_f(fmaf(r4[2], hp[i], wxr[i].get(2)));
-                        og[i] = 1.0f + ex2_approx(-1.4426950216293335f * fmaf(r4[3], hp[i], wxr[i].get(3)));
+                        wxr[i + 1].pin();
+                        const float2 hp2 = make_float2(hp[i], hp[i + 1]);
+                        const float2 vi = __ffma2_rn(splat2(r4[0]), hp2, make_float2(wxr[i].get(0), wxr[i + 1].get(0)));
+                        const float2 vf = __ffma2_rn(splat2(r4[1]), hp2, make_float2(wxr[i].get(1), wxr[i + 1].get(1)));
+                        const float2 vz = tanh_f2(
+                            __ffma2_rn(splat2(r4[2]), hp2, make_float2(wxr[i].get(2), wxr[i + 1].get(2))));
+                        const float2 vo = __ffma2_rn(splat2(r4[3]), hp2, make_float2(wxr[i].get(3), wxr[i + 1].get(3)));
+                        const float2 go = __fadd2_rn(splat2(1.0f), ex2_2(__fmul2_rn(splat2(-1.4426950216293335f), vo)));
+                        zi[i] = vi.x; zi[i + 1] = vi.y;
+                        zf[i] = vf.x; zf[i + 1] = vf.y;
+                        zz[i] = vz.x; zz[i + 1] = vz.y;
+                        og[i] = go.x; og[i + 1] = go.y;
                     }
                     // ---- m: max-plus recurrence
                     if (!first && !mbar_wait_bounded(&mbar_m[g * W + warp], par, kFusedWaitLimit))
@@ -193,7 +208,11 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
                     if (lane == 0 && !last) fp_mbar_arrive(&mbar_m[g * W + next]);
                     float e[L];
 #pragma unroll
-                    for (int i = 0; i < L; ++i) e[i] = exp_f(-fabsf(dlt[i]));
+                    for (int i = 0; i < L; i += 2) {
+                        const float2 ev = exp_f2(make_float2(-fabsf(dlt[i]), -fabsf(dlt[i + 1])));
+                        e[i] = ev.x;
+                        e[i + 1] = ev.y;
+                    }
                     // ---- (c, n): multiply-add recurrences
                     if (!first && !mbar_wait_bounded(&mbar_cn[g * W + warp], par, kFusedWaitLimit))
                         timed_out = true;
@@ -213,7 +232,13 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
                     }
                     float h[L];
 #pragma unroll
-                    for (int i = 0; i < L; ++i) h[i] = cs[i] * rcp_f(og[i] * (ns[i] + a.eps));
+                    for (int i = 0; i < L; i += 2) {
+                        const float2 den = __fmul2_rn(make_float2(og[i], og[i + 1]),
+                                                      __fadd2_rn(make_float2(ns[i], ns[i + 1]), splat2(a.eps)));
+                        const float2 hv = __fmul2_rn(make_float2(cs[i], cs[i + 1]), rcp_2(den));
+                        h[i] = hv.x;
+                        h[i + 1] = hv.y;
+                    }
                     slot_out[0] = c;
                     slot_out[kLanes] = n;
                     slot_out[3 * kLanes] = h[L - 1];
@@ -258,8 +283,8 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
 
 template <typename TIO, int NSTAGE>
 cudaError_t launch_t(const SlstmPicardArgs& a, int n_pass, cudaStream_t s) {
-    // 7 compute warps + the producer = 256 threads: two CTAs per SM leave 128 registers per thread
-    constexpr int L = 8, W = 7;
+    // 8 warps = 256 threads: two CTAs per SM leave 128 registers per thread
+    constexpr int L = 8, W = 8;
     using S = FusedPicardSmem<TIO, L, W, NSTAGE>;
     CUtensorMap tm_wx;
     const uint64_t rows = (uint64_t)a.B * a.T;
@@ -267,7 +292,7 @@ cudaError_t launch_t(const SlstmPicardArgs& a, int n_pass, cudaStream_t s) {
     const int grid = a.B * ((a.d + kLanes - 1) / kLanes);
     auto k = slstm_picard_fused_kernel<TIO, L, W, NSTAGE>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    k<<<grid, (W + 1) * 32, S::TOTAL, s>>>(tm_wx, a, n_pass);
+    k<<<grid, W * 32, S::TOTAL, s>>>(tm_wx, a, n_pass);
     return cudaGetLastError();
 }
 
