@@ -49,7 +49,7 @@ struct NewtonFusedSmem {
 };
 
 template <typename TIO, int L, int W, int NSTAGE>
-__global__ void __launch_bounds__((W + 1) * 32, 2)
+__global__ void __launch_bounds__(W * 32, 2)
 slstm_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_st,
                           SlstmNewtonArgs a, int n_iters) {
     using S = NewtonFusedSmem<TIO, L, W, NSTAGE>;
@@ -94,19 +94,19 @@ slstm_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, const __gri
     unsigned fmax = 0u;
     bool timed_out = false;
 
-    if (warp == W) {
-        if (lane == 0) {
-            for (int r = 0; r < n_rounds; ++r) {
-                const int s = r % NSTAGE;
-                if (r >= NSTAGE && !mbar_wait_bounded(&empty[s], ((r / NSTAGE) - 1) & 1, kNfWaitLimit))
-                    timed_out = true;
-                unsigned char* base = smem + s * S::STAGE;
-                mbar_expect_tx(&full[s], S::WX_TX + S::ST_TX);
-                tma_load_3d(base, &tm_wx, &full[s], cb * kLanes, 0, row0 + r * LT);
-                tma_load_3d(base + S::WX_BYTES, &tm_st, &full[s], cb * kLanes, 0, row0 + r * LT - 1);
-            }
-        }
-    } else {
+    // No dedicated producer warp (it would cost an eighth of the register file): lane 0 of warp 0
+    // keeps the TMA ring full.  At the start of round r it refills the stage of round r-1, which
+    // every warp has copied to registers long before (the warps are at most half a round apart).
+    auto issue = [&](int r) {
+        const int s = r % NSTAGE;
+        unsigned char* base = smem + s * S::STAGE;
+        mbar_expect_tx(&full[s], S::WX_TX + S::ST_TX);
+        tma_load_3d(base, &tm_wx, &full[s], cb * kLanes, 0, row0 + r * LT);
+        tma_load_3d(base + S::WX_BYTES, &tm_st, &full[s], cb * kLanes, 0, row0 + r * LT - 1);
+    };
+    if (threadIdx.x == 0)
+        for (int r = 0; r < NSTAGE && r < n_rounds; ++r) issue(r);
+    {
         float r4[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) r4[q] = __ldg(a.r + (size_t)q * d + chl);
@@ -115,6 +115,12 @@ slstm_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, const __gri
 
         for (int r = 0; r < n_rounds; ++r) {
             const int s = r % NSTAGE;
+            if (threadIdx.x == 0 && r >= 1 && r - 1 + NSTAGE < n_rounds) {
+                if (!mbar_wait_bounded(&empty[(r - 1) % NSTAGE], ((r - 1) / NSTAGE) & 1, kNfWaitLimit))
+                    timed_out = true;
+                issue(r - 1 + NSTAGE);
+            }
+            __syncwarp();
             if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, kNfWaitLimit)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const float* t_st = reinterpret_cast<const float*>(smem + s * S::STAGE + S::WX_BYTES);
@@ -245,7 +251,7 @@ slstm_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, const __gri
 
 template <typename TIO, int NSTAGE>
 cudaError_t launch_t(const SlstmNewtonArgs& a, int n_iters, cudaStream_t s) {
-    constexpr int L = 4, W = 7;  // 7 compute warps + the producer: 128 registers with two CTAs per SM
+    constexpr int L = 4, W = 8;  // 8 warps: 128 registers per thread with two CTAs per SM
     using S = NewtonFusedSmem<TIO, L, W, NSTAGE>;
     CUtensorMap tm_wx, tm_st;
     const uint64_t rows = (uint64_t)a.B * a.T;
@@ -255,7 +261,7 @@ cudaError_t launch_t(const SlstmNewtonArgs& a, int n_iters, cudaStream_t s) {
     const int grid = a.B * ((a.d + kLanes - 1) / kLanes);
     auto k = slstm_newton_fused_kernel<TIO, L, W, NSTAGE>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    k<<<grid, (W + 1) * 32, S::TOTAL, s>>>(tm_wx, tm_st, a, n_iters);
+    k<<<grid, W * 32, S::TOTAL, s>>>(tm_wx, tm_st, a, n_iters);
     return cudaGetLastError();
 }
 
