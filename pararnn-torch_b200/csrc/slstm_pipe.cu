@@ -257,7 +257,7 @@ struct PipeBwdSmem {
 // nu_{t-1} = J_t^T (nu_t + g_t) is evaluated through the packed-VJP quantities:
 // (d_cn f, d_nn f, d_zf, sum_g r_g d_zg).
 template <typename TIO, int L, int W, int NSTAGE>
-__global__ void __launch_bounds__((W + 1) * 32, 2)
+__global__ void __launch_bounds__(W * 32, 2)
 slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_st,
                       const __grid_constant__ CUtensorMap tm_g, SlstmBwdArgs a) {
     using S = PipeBwdSmem<TIO, L, W, NSTAGE>;
@@ -298,22 +298,20 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
     bool timed_out = false;
     float gr[4] = {0.f, 0.f, 0.f, 0.f};
 
-    if (warp == W) {
-        if (lane == 0) {
-            for (int r = 0; r < n_rounds; ++r) {
-                const int s = r % NSTAGE;
-                const int tile_t = n_rounds - 1 - r;
-                if (r >= NSTAGE && !mbar_wait_bounded(&empty[s], ((r / NSTAGE) - 1) & 1, kPipeWaitLimit))
-                    timed_out = true;
-                unsigned char* base = smem + s * S::STAGE;
-                mbar_expect_tx(&full[s], S::WX_BYTES + (LT + 1) * 4 * kLanes * (int)sizeof(TIO) + S::G_BYTES);
-                tma_load_3d(base, &tm_wx, &full[s], cb * kLanes, 0, row0 + tile_t * LT);
-                tma_load_3d(base + S::WX_BYTES, &tm_st, &full[s], cb * kLanes, 0, row0 + tile_t * LT - 1);
-                tma_load_3d(base + S::WX_BYTES + S::ST_BYTES, &tm_g, &full[s], cb * kLanes, 0,
-                            row0 + tile_t * LT);
-            }
-        }
-    } else {
+    // No dedicated producer warp: lane 0 of warp 0 keeps the TMA ring full.  At the start of round r
+    // it refills the stage of round r-1, which every warp has copied to registers by then.
+    auto issue = [&](int r) {
+        const int s = r % NSTAGE;
+        const int tile_t = n_rounds - 1 - r;
+        unsigned char* base = smem + s * S::STAGE;
+        mbar_expect_tx(&full[s], S::WX_BYTES + (LT + 1) * 4 * kLanes * (int)sizeof(TIO) + S::G_BYTES);
+        tma_load_3d(base, &tm_wx, &full[s], cb * kLanes, 0, row0 + tile_t * LT);
+        tma_load_3d(base + S::WX_BYTES, &tm_st, &full[s], cb * kLanes, 0, row0 + tile_t * LT - 1);
+        tma_load_3d(base + S::WX_BYTES + S::ST_BYTES, &tm_g, &full[s], cb * kLanes, 0, row0 + tile_t * LT);
+    };
+    if (threadIdx.x == 0)
+        for (int r = 0; r < NSTAGE && r < n_rounds; ++r) issue(r);
+    {
         float r4[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) r4[q] = __ldg(a.r + (size_t)q * d + chl);
@@ -325,6 +323,12 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
         for (int r = 0; r < n_rounds; ++r) {
             const int s = r % NSTAGE;
             const int tile_t = n_rounds - 1 - r;
+            if (threadIdx.x == 0 && r >= 1 && r - 1 + NSTAGE < n_rounds) {
+                if (!mbar_wait_bounded(&empty[(r - 1) % NSTAGE], ((r - 1) / NSTAGE) & 1, kPipeWaitLimit))
+                    timed_out = true;
+                issue(r - 1 + NSTAGE);
+            }
+            __syncwarp();
             if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, kPipeWaitLimit)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const TIO* t_st = reinterpret_cast<const TIO*>(smem + s * S::STAGE + S::WX_BYTES);
@@ -667,7 +671,7 @@ static cudaError_t launch_bwd_pipe_t(const SlstmBwdArgs& a, cudaStream_t s) {
     const int grid = a.B * ((a.d + kLanes - 1) / kLanes);
     auto k = slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    k<<<grid, (kQW + 1) * 32, S::TOTAL, s>>>(tm_wx, tm_st, tm_g, a);
+    k<<<grid, kQW * 32, S::TOTAL, s>>>(tm_wx, tm_st, tm_g, a);
     return cudaGetLastError();
 }
 
