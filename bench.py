@@ -52,7 +52,7 @@ BYTES_STEP = 224                          # all passes of one forward + backward
 NCU_TRAFFIC_PER_UNIT = {"slstm_picard_pipe_kernel": 15.44, "slstm_newton_pipe_kernel": 39.02,
                         "slstm_bwd_pipe_kernel": 31.37,
                         # profiles/slstm_fused_sweeps_B8_T4096_d1024_bf16.md
-                        "slstm_picard_fused_kernel": 22.42, "slstm_newton_fused_kernel": 31.56}
+                        "slstm_picard_fused_kernel": 22.44, "slstm_newton_fused_kernel": 31.53}
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
@@ -364,10 +364,10 @@ def run_gpu_single(args):
 
     for _ in range(max(args.warmup, 3)):
         step()
+    # clocks are sampled over all timed regions of this run (step, end-to-end, kernels in isolation)
     sampler = ClockSampler(0)
     sampler.start()
     sec = time_region(step, args.steps, None)
-    clocks = sampler.stop()
     hist, res, status = stats.read()
     assert status == 0, "chain wait timed out"
     ms = sec / args.steps * 1e3
@@ -403,7 +403,7 @@ def run_gpu_single(args):
         prefetch(i + 1)
         xd = x_bufs[i % 2].detach().requires_grad_(True)
         Hs = prb.newton_apply(cell, xd, cfg)
-        loss = Hs[:, :, 3].float().sum()
+        loss = Hs[:, :, 3].sum(dtype=torch.float32)
         loss.backward()
         consumed[i % 2].record()
         loss_host.copy_(loss.detach(), non_blocking=True)
@@ -447,6 +447,8 @@ def run_gpu_single(args):
                          "bytes_moved": (BYTES_PICARD_SWEEP + BYTES_NEWTON_SWEEP + BYTES_BWD) * n_units,
                          "note": "224 B per token-channel is the per-pass accounting (9 sweeps); the "
                                  "three launches of a step move 88 B"}}
+
+    clocks = sampler.stop()
 
     # CPU baseline on a bounded sample (rank 0, N = 1 only)
     threads = os.cpu_count() or 1
@@ -565,7 +567,7 @@ def run_gpu_sharded(args):
         prefetch(i + 1)
         xd = x_bufs[i % 2].detach().requires_grad_(True)
         Hs = prb.newton_apply(cell, xd, cfg)
-        loss = Hs[:, :, 3].float().sum()
+        loss = Hs[:, :, 3].sum(dtype=torch.float32)
         loss.backward()
         consumed[i % 2].record()
         loss_host.copy_(loss.detach(), non_blocking=True)
