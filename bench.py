@@ -574,6 +574,28 @@ def run_gpu_sharded(args):
         cell.zero_grad(set_to_none=True)
         e2e_state["i"] = i + 1
 
+    # For comparison only: the same GPUs used batch-parallel (every rank solves its own B rows of
+    # T_PER_GPU steps with the single-GPU kernels; the only exchange is the all-reduce of grad R).
+    # It is not the time-sharded path this line measures and never enters `value`.
+    from pararnn_b200 import ops as _ops
+
+    r_io = rec[0]
+    dp_stats = _ops.DeviceStats(dev, K_NEWTON)
+
+    def dp_step():
+        H = _ops.newton_slstm_fused(wx, r_io, None, None, max_iters=K_NEWTON, picard_iters=P_PICARD,
+                                    stats=dp_stats, want_residual=True)
+        out = _ops.slstm_reverse_vjp(H, wx, r_io, G_io)
+        dist.all_reduce(out[1])
+        keep["dp"] = out
+
+    for _ in range(3):
+        dp_step()
+    dp_sec = time_region(dp_step, args.steps, None, barrier)
+    t = torch.tensor([dp_sec], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dp_sec = float(t.item()) / args.steps
+
     e2e_sec = float("nan")
     if not args.no_e2e:
         for _ in range(2):
@@ -607,6 +629,10 @@ def run_gpu_sharded(args):
                          "traffic": None,
                          "note": "ranks other than the first sweep each pass twice (aggregate, then apply)"},
             "newton": {"iters": K_NEWTON, "residual_history": list(hist), "max_residual": res_final},
+            "batch_parallel_for_comparison": {
+                "value": B * T_PER_GPU * world / dp_sec, "unit": "tokens/s", "ms_per_step": dp_sec * 1e3,
+                "workload": f"B={B * world} rows split over the ranks, T={T_PER_GPU}: independent rows, "
+                            "fused single-GPU sweeps, all-reduce of grad R only"},
         }
         print(json.dumps(line))
     dist.barrier(device_ids=[local])
