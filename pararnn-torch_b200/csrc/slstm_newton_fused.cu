@@ -49,7 +49,7 @@ struct NewtonFusedSmem {
 };
 
 template <typename TIO, int L, int W, int NSTAGE>
-__global__ void __launch_bounds__(W * 32, 2)
+__global__ void __launch_bounds__(W * 32, W > 8 ? 1 : 2)
 slstm_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_st,
                           SlstmNewtonArgs a, int n_iters) {
     using S = NewtonFusedSmem<TIO, L, W, NSTAGE>;
@@ -249,9 +249,8 @@ slstm_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, const __gri
     }
 }
 
-template <typename TIO, int NSTAGE>
-cudaError_t launch_t(const SlstmNewtonArgs& a, int n_iters, cudaStream_t s) {
-    constexpr int L = 4, W = 8;  // 8 warps: 128 registers per thread with two CTAs per SM
+template <typename TIO, int NSTAGE, int L, int W>
+cudaError_t launch_lw(const SlstmNewtonArgs& a, int n_iters, cudaStream_t s) {
     using S = NewtonFusedSmem<TIO, L, W, NSTAGE>;
     CUtensorMap tm_wx, tm_st;
     const uint64_t rows = (uint64_t)a.B * a.T;
@@ -263,6 +262,15 @@ cudaError_t launch_t(const SlstmNewtonArgs& a, int n_iters, cudaStream_t s) {
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     k<<<grid, W * 32, S::TOTAL, s>>>(tm_wx, tm_st, a, n_iters);
     return cudaGetLastError();
+}
+
+// 8 warps x 4 steps, two CTAs per SM (128 registers per thread) when there are more chains than
+// SMs; with fewer chains a CTA has an SM to itself and a single chain's walk is bound by latency,
+// so 16 warps put twice as many warps on a round of twice the steps.
+template <typename TIO, int NSTAGE>
+cudaError_t launch_t(const SlstmNewtonArgs& a, int n_iters, cudaStream_t s) {
+    const int chains = a.B * ((a.d + kLanes - 1) / kLanes);
+    return chains > 148 ? launch_lw<TIO, NSTAGE, 4, 8>(a, n_iters, s) : launch_lw<TIO, NSTAGE, 4, 16>(a, n_iters, s);
 }
 
 }  // namespace

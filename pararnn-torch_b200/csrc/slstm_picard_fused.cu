@@ -78,7 +78,7 @@ struct FusedPicardSmem {
 };
 
 template <typename TIO, int L, int W, int NSTAGE>
-__global__ void __launch_bounds__(W * 32, 2)
+__global__ void __launch_bounds__(W * 32, W > 8 ? 1 : 2)
 slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicardArgs a, int n_pass) {
     using S = FusedPicardSmem<TIO, L, W, NSTAGE>;
     constexpr int LT = S::LT;
@@ -281,10 +281,8 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
 }
 
-template <typename TIO, int NSTAGE>
-cudaError_t launch_t(const SlstmPicardArgs& a, int n_pass, cudaStream_t s) {
-    // 8 warps = 256 threads: two CTAs per SM leave 128 registers per thread
-    constexpr int L = 8, W = 8;
+template <typename TIO, int NSTAGE, int L, int W>
+cudaError_t launch_lw(const SlstmPicardArgs& a, int n_pass, cudaStream_t s) {
     using S = FusedPicardSmem<TIO, L, W, NSTAGE>;
     CUtensorMap tm_wx;
     const uint64_t rows = (uint64_t)a.B * a.T;
@@ -294,6 +292,15 @@ cudaError_t launch_t(const SlstmPicardArgs& a, int n_pass, cudaStream_t s) {
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     k<<<grid, W * 32, S::TOTAL, s>>>(tm_wx, a, n_pass);
     return cudaGetLastError();
+}
+
+// 8 warps x 8 steps, two CTAs per SM (128 registers per thread) when there are more chains than
+// SMs; with fewer chains a CTA has an SM to itself and a single chain's walk is bound by latency,
+// so 16 warps x 4 steps put twice as many warps on the same round.
+template <typename TIO, int NSTAGE>
+cudaError_t launch_t(const SlstmPicardArgs& a, int n_pass, cudaStream_t s) {
+    const int chains = a.B * ((a.d + kLanes - 1) / kLanes);
+    return chains > 148 ? launch_lw<TIO, NSTAGE, 8, 8>(a, n_pass, s) : launch_lw<TIO, NSTAGE, 4, 16>(a, n_pass, s);
 }
 
 }  // namespace
