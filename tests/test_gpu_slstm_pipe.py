@@ -79,3 +79,40 @@ def test_fused_newton_sweep_equals_separate_passes(K, B, T, d, h0, monkeypatch):
         assert np.abs(fused[:, :, slot] - separate[:, :, slot]).max() <= 2e-6 * scale * amp, slot
     np.testing.assert_allclose(hist_f, hist_s, rtol=1e-3, atol=1e-6)
     assert abs(res_f - res_s) <= 1e-3 * res_s + 2e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_sweeps_with_damping_eps_and_h0(dtype, monkeypatch):
+    """omega != 1, a non-default eps, a start state and both I/O dtypes through the fused sweeps,
+    against the separate passes (fp32: also against the oracle)."""
+    from gpu_util import bf16_round
+    from oracle import oracle
+    from pararnn_b200 import ops
+
+    wx, r, h0a = make_problem("slstm_diag", 3, 777, 64, seed=21, h0=True, x_scale=0.5, bias_f=3.0)
+    if dtype == torch.bfloat16:
+        wx, r, h0a = bf16_round(wx), bf16_round(r), bf16_round(h0a)
+
+    def solve():
+        st = ops.DeviceStats("cuda", 3)
+        H = ops.newton_slstm_fused(dev(wx, dtype), dev(r, dtype), dev(h0a, dtype), None, max_iters=3,
+                                   omega=0.8, eps=1e-4, picard_iters=4, stats=st)
+        hist, res, status = st.read()
+        assert status == 0
+        return H.float().cpu().numpy(), np.asarray(hist), res
+
+    fused, hist_f, res_f = solve()
+    monkeypatch.setenv("PRB_NEWTON_FUSED", "0")
+    monkeypatch.setenv("PRB_PICARD_FUSED", "0")
+    separate, hist_s, res_s = solve()
+    tol = 2e-6 if dtype == torch.float32 else 1e-2
+    for slot in range(4):
+        scale = max(1.0, float(np.abs(separate[:, :, slot]).max()))
+        assert np.abs(fused[:, :, slot] - separate[:, :, slot]).max() <= tol * scale, slot
+    np.testing.assert_allclose(hist_f, hist_s, rtol=2e-3, atol=1e-6)
+    if dtype == torch.float32:
+        want = oracle.newton(oracle.SLSTM_DIAG, wx, r, h0a, max_iters=3, picard=4, omega=0.8, eps=1e-4)
+        amp = max(1.0, max(want.history))
+        assert np.abs(fused[:, :, 3] - want.states[:, :, 3]).max() <= 1e-5 * amp
+        # the histories sit at the fp32 floor of the stabiliser slot (|m| ~ 2e3: one ulp = 2.4e-4)
+        np.testing.assert_allclose(hist_f, np.asarray(want.history), rtol=1e-2, atol=5e-4)
