@@ -500,19 +500,33 @@ def run_gpu_sharded(args):
     dist.init_process_group("nccl", device_id=dev)
     comm = DistComm()
     peak, peak_kind = measured_peaks()
-    x, W, bias, R = make_inputs(T_PER_GPU, SEED + 1000 * rank)
+    # Shard lengths: the first rank knows the state entering its shard and sweeps once per pass,
+    # the others sweep twice (aggregate, then apply), so the first shard is made
+    # `--first-shard-weight` times as long as the others (1.0 = equal shards).  The total stays
+    # T_PER_GPU * N.
+    from pararnn_b200.seq_shard import balanced_shard_bounds
+
+    t_total = T_PER_GPU * world
+    lo, hi = balanced_shard_bounds(t_total, rank, world, args.first_shard_weight, 64)
+    t_local = hi - lo
+    t_first = balanced_shard_bounds(t_total, 0, world, args.first_shard_weight, 64)[1]
+    t_other = (t_total - t_first) // (world - 1)
+    x, W, bias, R = make_inputs(max(t_local, T_PER_GPU), SEED + 1000 * rank)
     cell = prb.ParaSLSTM(D, D).to(dev)
     with torch.no_grad():
         cell.W_x.weight.copy_(W)
         cell.W_x.bias.copy_(bias)
         cell.R.copy_(R)
     cell = cell.bfloat16()
-    x_host = x.bfloat16().pin_memory()
+    x_host = x[:, :t_local].bfloat16().contiguous().pin_memory()
     x_dev = x_host.to(dev)
     with torch.no_grad():
         wx = cell.W_x(x_dev).contiguous()
-    G_io = torch.zeros(B, T_PER_GPU, 4, D, dtype=torch.bfloat16, device=dev)
+        wx_dp = cell.W_x(x[:, :T_PER_GPU].bfloat16().to(dev)).contiguous()
+    G_io = torch.zeros(B, t_local, 4, D, dtype=torch.bfloat16, device=dev)
     G_io[:, :, 3] = 1.0
+    G_dp = torch.zeros(B, T_PER_GPU, 4, D, dtype=torch.bfloat16, device=dev)
+    G_dp[:, :, 3] = 1.0
     rec = (cell.clipped_r().detach(),)
     keep = {}
 
@@ -583,9 +597,9 @@ def run_gpu_sharded(args):
     dp_stats = _ops.DeviceStats(dev, K_NEWTON)
 
     def dp_step():
-        H = _ops.newton_slstm_fused(wx, r_io, None, None, max_iters=K_NEWTON, picard_iters=P_PICARD,
+        H = _ops.newton_slstm_fused(wx_dp, r_io, None, None, max_iters=K_NEWTON, picard_iters=P_PICARD,
                                     stats=dp_stats, want_residual=True)
-        out = _ops.slstm_reverse_vjp(H, wx, r_io, G_io)
+        out = _ops.slstm_reverse_vjp(H, wx_dp, r_io, G_dp)
         dist.all_reduce(out[1])
         keep["dp"] = out
 
@@ -615,9 +629,10 @@ def run_gpu_sharded(args):
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32 scan arithmetic, bf16 I/O", "data": "synthetic",
-            "config": workload_config(world), "clocks": clocks,
+            "config": dict(workload_config(world), shard_lengths=[t_first] + [t_other] * (world - 1)),
+            "clocks": clocks,
             "e2e": {"value": tokens / e2e_sec, "unit": "tokens/s",
-                    "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": 4 * world,
+                    "h2d_bytes_per_step": B * t_total * D * 2, "d2h_bytes_per_step": 4 * world,
                     "ms_per_step": e2e_sec * 1e3,
                     "includes": "per rank: H2D of its x shard, 3 W_x GEMMs, sharded Newton+scan fwd and "
                                 "reverse scan + VJP with NCCL carry exchange and gradient all-reduce, "
@@ -732,6 +747,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--seq-len", type=int, default=T_PER_GPU,
                     help="time steps per GPU (profiling captures use a smaller case)")
+    ap.add_argument("--first-shard-weight", type=float, default=1.8,
+                    help="N > 1: length of the first time shard relative to the others")
     ap.add_argument("--workload", default="c2", choices=("c2", "c1", "c3", "c5"),
                     help="c2 (default) is the headline line; the others print secondary lines")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

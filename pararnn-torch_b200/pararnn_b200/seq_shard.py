@@ -43,6 +43,24 @@ def time_shard_bounds(time: int, rank: int, world_size: int) -> tuple[int, int]:
 
 # ------------------------------------------------------------------------------- comms
 
+def balanced_shard_bounds(time: int, rank: int, world_size: int, first_weight: float = 1.8,
+                          multiple: int = 1) -> tuple[int, int]:
+    """Contiguous ``[start, end)`` with the first shard ``first_weight`` times as long as each of
+    the others (their length a multiple of ``multiple``).  The first rank knows the state entering
+    its shard and sweeps once per pass while the others sweep twice (aggregate, then apply), so a
+    longer first shard evens out the time per pass.  ``first_weight=1`` gives equal shards with
+    the remainder on the first rank."""
+    if world_size < 1 or not 0 <= rank < world_size or time < 0 or first_weight <= 0 or multiple < 1:
+        raise ValueError("bad arguments to balanced_shard_bounds")
+    if world_size == 1:
+        return 0, time
+    other = int(time / (first_weight + world_size - 1)) // multiple * multiple
+    first = time - (world_size - 1) * other
+    if rank == 0:
+        return 0, first
+    return first + (rank - 1) * other, first + rank * other
+
+
 class DistComm:
     """Collectives over a ``torch.distributed`` process group."""
 
@@ -520,13 +538,18 @@ class _Ctx:
 
 def emulate_sharded(kind: str, wx: Tensor, rec, *, world: int, K: int, P: int = 0, h0=None,
                     eps: float = 1e-6, omega: float = 1.0, grad_states: Tensor | None = None,
-                    ops_factory=None):
+                    ops_factory=None, bounds=None):
     """Run the time-sharded programs of ``world`` virtual ranks in one process on one device
-    (shards of ``wx`` along time per ``time_shard_bounds``).  Returns the concatenated states,
-    the statistics bits and, when ``grad_states`` is given, ``(g_wx, g_params, g_h0)``."""
+    (shards of ``wx`` along time per ``time_shard_bounds``, or the contiguous ``bounds`` given:
+    shards need not have equal lengths).  Returns the concatenated states, the statistics bits and,
+    when ``grad_states`` is given, ``(g_wx, g_params, g_h0)``."""
     factory = ops_factory or CudaShardOps
     T = wx.shape[1]
-    bounds = [time_shard_bounds(T, r, world) for r in range(world)]
+    if bounds is None:
+        bounds = [time_shard_bounds(T, r, world) for r in range(world)]
+    if len(bounds) != world or bounds[0][0] != 0 or bounds[-1][1] != T or any(
+            bounds[i][1] != bounds[i + 1][0] for i in range(world - 1)):
+        raise ValueError(f"bounds must be {world} contiguous [start, end) pairs covering [0, {T})")
     ops = [factory(kind, wx[:, s:e].contiguous(), rec, eps, omega) for s, e in bounds]
     res = run_lockstep([forward_program(ops[r], r, world, K, P, _h0_f32(h0)) for r in range(world)])
     states = torch.cat([r.states for r in res], dim=1)

@@ -55,3 +55,26 @@ def test_sharded_equals_unsharded_bf16():
     one = ops.newton_slstm_fused(wxd, rd, None, None, max_iters=2, picard_iters=5)
     many, _ = emulate_sharded("slstm_diag", wxd, (rd,), world=4, K=2, P=5)
     assert rel_err(many[:, :, 3].float().cpu().numpy(), one[:, :, 3].float().cpu().numpy()) <= 2e-2
+
+
+@pytest.mark.parametrize("kind,K,P", [("slstm_diag", 2, 3), ("gru_diag", 3, 0), ("nlru", 2, 0)])
+def test_unequal_shards_match_oracle(kind, K, P, monkeypatch):
+    """The first rank sweeps once per pass, the others twice, so a balanced split gives the first
+    rank a longer shard; the programs make no assumption on shard lengths."""
+    from pararnn_b200.seq_shard import _bits_to_stats, emulate_sharded
+
+    monkeypatch.setenv("PRB_KERNEL_PATH", "pipe")
+    B, T, d = 2, 1000, 64
+    bounds = [(0, 470), (470, 730), (730, 731), (731, 1000)]
+    wx, params, h0 = make_problem(kind, B, T, d, seed=17, h0=True, x_scale=0.6, bias_f=1.0)
+    want = oracle.newton(oracle.KIND[kind], wx, params, h0, max_iters=K, picard=P)
+    G = np.random.default_rng(2).standard_normal(want.states.shape).astype(np.float32)
+    states, bits, grads = emulate_sharded(kind, dev(wx), _rec(kind, params), world=4, K=K, P=P, h0=dev(h0),
+                                          grad_states=dev(G), bounds=bounds)
+    amp = max(1.0, max(want.history))
+    scale = max(1.0, float(np.abs(want.states).max()))
+    assert np.abs(states.cpu().numpy() - want.states).max() <= 1e-5 * amp * scale
+    assert _bits_to_stats(bits, K)[2] == 0
+    want_g = oracle.backward(oracle.KIND[kind], states.cpu().numpy(), wx, params, G, h0)
+    assert rel_err(grads[0].cpu().numpy(), want_g[0]) <= 5e-5
+    assert rel_err(grads[1].cpu().numpy().reshape(-1), np.asarray(want_g[1]).reshape(-1)) <= 1e-4
