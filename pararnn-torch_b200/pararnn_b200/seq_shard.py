@@ -47,9 +47,10 @@ def balanced_shard_bounds(time: int, rank: int, world_size: int, first_weight: f
                           multiple: int = 1) -> tuple[int, int]:
     """Contiguous ``[start, end)`` with the first shard ``first_weight`` times as long as each of
     the others (their length a multiple of ``multiple``).  The first rank knows the state entering
-    its shard and sweeps once per pass while the others sweep twice (aggregate, then apply), so a
-    longer first shard evens out the time per pass.  ``first_weight=1`` gives equal shards with
-    the remainder on the first rank."""
+    its shard and sweeps once per pass while the others sweep twice (aggregate, then apply); the
+    others' apply sweep waits for the first rank's result, so the best weight depends on the ratio
+    of the sweep costs and is close to 1 for ParaSLSTM (measured).  ``first_weight=1`` gives equal
+    shards with the remainder on the first rank."""
     if world_size < 1 or not 0 <= rank < world_size or time < 0 or first_weight <= 0 or multiple < 1:
         raise ValueError("bad arguments to balanced_shard_bounds")
     if world_size == 1:
