@@ -291,18 +291,8 @@ def _sharded_scan(ops, rank, world, reverse, monoid, boundary, sweep):
     if world == 1:
         return boundary, sweep(False, boundary)
     if rank == first:
-        # The other ranks cannot start their apply sweep before they know what leaves this shard.
-        # An aggregate-only sweep is cheaper than the apply sweep, so the first rank publishes
-        # map(boundary) from its aggregate first and runs its own apply sweep while the others
-        # run theirs.
-        agg = sweep(True, None)
-        slots = agg.new_zeros(3, *agg.shape)
-        if boundary is not None:
-            slots[2 if reverse else 0, :, : boundary.shape[1]] = boundary
-        slots[1] = agg
-        early = ops.fold(monoid, slots, 0 if reverse else 2, 3, reverse)
-        gathered = yield ("gather", _pad(early, NV[monoid]))
         leaving = sweep(False, boundary)
+        gathered = yield ("gather", _pad(leaving, NV[monoid]))
         return boundary, leaving
     agg = sweep(True, None)
     gathered = yield ("gather", agg)
