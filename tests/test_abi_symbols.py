@@ -46,3 +46,23 @@ def test_workspace_queries_are_pure():
     assert 0 < a < b
     assert lib.prb_newton_workspace_bytes(_lib.CELL_GRU_DIAG, 0, 0, 10, 8, 1, 3, 0) == 0
     assert lib.prb_error_string(-2).decode().startswith("workspace")
+
+
+def test_sweep_entry_points_validate_arguments_before_any_gpu_work():
+    """Argument checks come first, so they can be exercised without a GPU."""
+    from pararnn_b200 import _lib
+
+    lib = _lib.lib()
+    null = None
+    # missing pointers
+    assert lib.prb_slstm_picard_sweep(null, null, null, null, null, null, 6, 1, 8, 32, _lib.PRB_F32, 1e-6,
+                                      null, 0, null, null) == -1
+    assert lib.prb_slstm_newton_sweep(null, null, null, null, null, 2, 1, 1, 8, 32, _lib.PRB_F32, 1.0, 1e-6,
+                                      null, 0, null, null) == -1
+    # more passes than one sweep takes (pointers only need to be non-null to get that far)
+    buf = ctypes.create_string_buffer(256)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert lib.prb_slstm_picard_sweep(p, p, null, null, p, null, 7, 1, 8, 32, _lib.PRB_F32, 1e-6, null, 0,
+                                      p, null) == -3
+    assert lib.prb_slstm_newton_sweep(p, p, p, null, p, 5, 1, 1, 8, 32, _lib.PRB_F32, 1.0, 1e-6, null, 0, p,
+                                      null) == -3
