@@ -300,7 +300,7 @@ cudaError_t launch_lw(const SlstmPicardArgs& a, int n_pass, cudaStream_t s) {
 template <typename TIO, int NSTAGE>
 cudaError_t launch_t(const SlstmPicardArgs& a, int n_pass, cudaStream_t s) {
     const int chains = a.B * ((a.d + kLanes - 1) / kLanes);
-    return chains > 148 ? launch_lw<TIO, NSTAGE, 8, 8>(a, n_pass, s) : launch_lw<TIO, NSTAGE, 4, 16>(a, n_pass, s);
+    return chains > 148 ? launch_lw<TIO, NSTAGE, 8, 8>(a, n_pass, s) : launch_lw<TIO, NSTAGE, 8, 16>(a, n_pass, s);
 }
 
 }  // namespace
