@@ -24,7 +24,7 @@ namespace prb {
 
 namespace {
 
-constexpr uint32_t kDiagPipeWaitLimit = 1u << 26;
+constexpr uint32_t kDiagPipeWaitLimit = 1u << 24;
 
 __device__ __forceinline__ void dp_mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");

@@ -19,7 +19,7 @@
 namespace prb {
 
 constexpr int kAggW = 8;
-constexpr uint32_t kAggWaitLimit = 1u << 26;
+constexpr uint32_t kAggWaitLimit = 1u << 24;
 
 // compose the W warp maps (time order = warp order) and write the result
 template <class M>

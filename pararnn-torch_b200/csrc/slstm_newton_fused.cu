@@ -25,7 +25,7 @@ namespace prb {
 
 namespace {
 
-constexpr uint32_t kNfWaitLimit = 1u << 26;
+constexpr uint32_t kNfWaitLimit = 1u << 24;
 constexpr int kNfMaxIters = 4;
 
 __device__ __forceinline__ void nf_mbar_arrive(uint64_t* bar) {

@@ -18,7 +18,7 @@
 
 namespace prb {
 
-constexpr uint32_t kTmaWaitLimit = 1u << 26;
+constexpr uint32_t kTmaWaitLimit = 1u << 24;
 
 // ------------------------------------------------------------------ host: tensor maps
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

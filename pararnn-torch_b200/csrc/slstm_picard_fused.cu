@@ -26,7 +26,7 @@ namespace prb {
 
 namespace {
 
-constexpr uint32_t kFusedWaitLimit = 1u << 26;
+constexpr uint32_t kFusedWaitLimit = 1u << 24;
 constexpr int kFusedMaxPass = 6;
 
 // Gate pre-activations of one step as the warp keeps them between passes: fp32 inputs as they

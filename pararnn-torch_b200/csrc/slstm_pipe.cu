@@ -21,7 +21,7 @@
 
 namespace prb {
 
-constexpr uint32_t kPipeWaitLimit = 1u << 26;
+constexpr uint32_t kPipeWaitLimit = 1u << 24;
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
