@@ -270,7 +270,7 @@ def kernel_rooflines(wx, r32, states32, states_io, G_io, peak):
 
     def picard():
         rc = lib.prb_slstm_picard_pass(P(wx), P(r32), P(hbuf), None, None, P(hbuf2), None, None, None, 0,
-                                       B, T_PER_GPU, D, L.PRB_BF16, 1e-6, P(ws), ws.numel(), P(st.buf), stream)
+                                       1, T_PER_GPU, B, T_PER_GPU, D, L.PRB_BF16, 1e-6, P(ws), ws.numel(), P(st.buf), stream)
         assert rc == 0, rc
 
     def picard_sweep():
@@ -285,20 +285,20 @@ def kernel_rooflines(wx, r32, states32, states_io, G_io, peak):
         assert rc == 0, rc
 
     def newton_last():
-        rc = lib.prb_slstm_newton_pass(P(wx), P(r32), P(states32), None, None, P(states_out), None, None, 1, B,
-                                       T_PER_GPU, D, L.PRB_BF16, 1.0, 1e-6, P(ws), ws.numel(), P(st.buf),
+        rc = lib.prb_slstm_newton_pass(P(wx), P(r32), P(states32), None, None, P(states_out), None, None, 1, 1,
+                                       T_PER_GPU, B, T_PER_GPU, D, L.PRB_BF16, 1.0, 1e-6, P(ws), ws.numel(), P(st.buf),
                                        1, stream)
         assert rc == 0, rc
 
     def newton():
-        rc = lib.prb_slstm_newton_pass(P(wx), P(r32), P(states32), None, None, P(sout), None, None, 0, B,
-                                       T_PER_GPU, D, L.PRB_BF16, 1.0, 1e-6, P(ws), ws.numel(), P(st.buf),
+        rc = lib.prb_slstm_newton_pass(P(wx), P(r32), P(states32), None, None, P(sout), None, None, 0, 1,
+                                       T_PER_GPU, B, T_PER_GPU, D, L.PRB_BF16, 1.0, 1e-6, P(ws), ws.numel(), P(st.buf),
                                        0, stream)
         assert rc == 0, rc
 
     def bwd():
         rc = lib.prb_slstm_bwd_pass(P(states_io), P(wx), P(r32), None, None, P(G_io), P(g_wx), P(g_r),
-                                    P(g_h0), None, 0, B, T_PER_GPU, D, L.PRB_BF16, 1e-6, P(ws), ws.numel(),
+                                    P(g_h0), None, 0, 1, T_PER_GPU, B, T_PER_GPU, D, L.PRB_BF16, 1e-6, P(ws), ws.numel(),
                                     P(st.buf), stream)
         assert rc == 0, rc
 

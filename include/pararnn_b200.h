@@ -62,6 +62,18 @@ typedef struct prb_stats {
 const char* prb_version(void);
 const char* prb_error_string(int code);
 
+/* Test and profiling hook, no counterpart in the reference: process-wide switches that force a
+ * kernel family or a wait limit so that small test shapes reach code that normally serves large
+ * ones.  Not thread-safe; call it while no other call of this library is in progress.  Every
+ * option's default is what production calls use.
+ *   PRB_OPT_KERNEL_FAMILY  -1 choose by shape (default), 0 look-back kernels, 2 pipelined kernels
+ *   PRB_OPT_PICARD_FUSED    1 (default) / 0: all Picard passes in one sweep when the shape allows
+ *   PRB_OPT_NEWTON_FUSED    1 (default) / 0: all Newton iterations in one sweep when it allows
+ *   PRB_OPT_SPIN_LIMIT      polls after which a look-back wait gives up and reports
+ *                           PRB_STATUS_CHAIN_TIMEOUT; <= 0 restores the default */
+enum { PRB_OPT_KERNEL_FAMILY = 0, PRB_OPT_PICARD_FUSED = 1, PRB_OPT_NEWTON_FUSED = 2, PRB_OPT_SPIN_LIMIT = 3 };
+int prb_debug_set(int option, long long value);
+
 /* Scratch sizes.  `n_heads` is ignored by the diagonal cells. */
 size_t prb_newton_workspace_bytes(int cell, int dtype, int B, int T, int d, int n_heads,
                                   int max_iters, int picard_iters);
@@ -161,6 +173,13 @@ int prb_residual(int cell, const void* wx, const void* params, const void* h0, c
  * the shard, `carry_in` the scan carry entering step 0 (NULL = zeros).
  * mode: 0 = apply, fp32 work trajectory out; 1 = apply, last pass, output in the I/O
  * dtype; 2 = aggregate only: nothing but the shard's aggregate map is written.
+ * Time segments (sLSTM passes): with n_seg > 1 the shard's time axis is cut into n_seg pieces of
+ * seg_len steps ((n_seg-1)*seg_len < T <= n_seg*seg_len) that are swept by different thread
+ * blocks at the same time, which is what fills the GPU when there are fewer (batch row, channel
+ * block) chains than SMs.  carry_in then is (n_seg, B, NS, d) (the carry entering each segment,
+ * from prb_segment_carries), agg_out (n_seg, B, NV, d); tail_out / head_out stay (B, NS, d) and
+ * are written by the segment that ends the scan.  prb_plan_segments proposes n_seg / seg_len for
+ * a shape (1 / T when segments would not help or the kernels that support them cannot run).
  * The workspace (prb_pass_workspace_bytes) holds the chain scratch of one pass.
  * prb_stats is NOT cleared by these calls: hist_bits[hist_slot] / final_bits are
  * max-accumulated, so the caller zeroes the block once per solve. */
@@ -213,22 +232,22 @@ int prb_slstm_newton_sweep(const void* wx, const float* r, const float* sin, con
  * writes h_out (B,T,d) or, when state_out is given, the full state (B,T,4,d) */
 int prb_slstm_picard_pass(const void* wx, const float* r, const float* h_prev, const float* h_halo,
                           const float* carry_in, float* h_out, float* state_out, float* tail_out,
-                          float* agg_out, int mode, int B, int T, int d, int dtype, float eps,
-                          void* workspace, size_t workspace_bytes, prb_stats* stats,
+                          float* agg_out, int mode, int n_seg, int seg_len, int B, int T, int d, int dtype,
+                          float eps, void* workspace, size_t workspace_bytes, prb_stats* stats,
                           prb_stream_t stream);
 
 /* sLSTM Newton pass: halo, carry (B,4,d); aggregate (B,20,d) = 4x4 row-major M, then v */
 int prb_slstm_newton_pass(const void* wx, const float* r, const float* sin, const float* halo,
                           const float* carry_in, void* sout, float* tail_out, float* agg_out, int mode,
-                          int B, int T, int d, int dtype, float omega, float eps, void* workspace,
-                          size_t workspace_bytes, prb_stats* stats, int hist_slot,
+                          int n_seg, int seg_len, int B, int T, int d, int dtype, float omega, float eps,
+                          void* workspace, size_t workspace_bytes, prb_stats* stats, int hist_slot,
                           prb_stream_t stream);
 
 int prb_slstm_bwd_pass(const void* states, const void* wx, const float* r, const float* halo,
                        const float* carry_in, const void* grad_states, void* g_wx, float* g_params,
-                       float* head_out, float* agg_out, int mode, int B, int T, int d, int dtype,
-                       float eps, void* workspace, size_t workspace_bytes, prb_stats* stats,
-                       prb_stream_t stream);
+                       float* head_out, float* agg_out, int mode, int n_seg, int seg_len, int B, int T,
+                       int d, int dtype, float eps, void* workspace, size_t workspace_bytes,
+                       prb_stats* stats, prb_stream_t stream);
 
 /* Carry entering `rank` from the all-gathered per-rank slots (world, B, NV, d): the first
  * rank in scan order (rank 0, or world-1 when reverse != 0) stores the exact carry leaving it
@@ -237,6 +256,22 @@ int prb_slstm_bwd_pass(const void* states, const void* wx, const float* r, const
  * serial fold of solvers/seq_parallel.py:185-191. */
 int prb_fold_carries(int monoid, const float* gathered, int rank, int world, int reverse,
                      float* carry_out, int B, int d, prb_stream_t stream);
+
+/* Segment plan for the pass-level sLSTM entry points (see "Time segments" above). */
+int prb_plan_segments(int cell, int dtype, int B, int T, int d, int* n_seg, int* seg_len);
+
+/* Map of a whole shard from its segment maps agg (n_seg, B, NV, d), composed in scan order
+ * (time order, or backwards when reverse != 0) into slot (B, NV, d): what a rank that does not
+ * know its entering carry puts into the all-gather.  Same role as the local scan of
+ * solvers/seq_parallel.py:175-183, one level down. */
+int prb_fold_segments(int monoid, const float* agg, int n_seg, int reverse, float* slot, int B, int d,
+                      prb_stream_t stream);
+
+/* Carries entering every segment, given the carry entering the shard (carry0 (B, NS, d), NULL =
+ * zeros): carries (n_seg + 1, B, NS, d); carries[j] enters segment j (at its last step when
+ * reverse != 0), carries[n_seg] leaves the shard. */
+int prb_segment_carries(int monoid, const float* agg, int n_seg, int reverse, const float* carry0,
+                        float* carries, int B, int d, prb_stream_t stream);
 
 /* residual of a shard with an fp32 halo; states fp32 (states_f32 != 0) or I/O dtype */
 int prb_residual_pass(int cell, const void* wx, const float* params, const float* halo,

@@ -1,10 +1,8 @@
 // extern "C" entry points declared in include/pararnn_b200.h.  This file owns
 // argument validation, the workspace layout and the sequence of launches that
-// make up one fused forward or backward call; the kernels live in
-// diag_kernels.cu and slstm_kernels.cu.
+// make up one fused forward or backward call; the kernels live in the other .cu files.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
-#include <stdlib.h>
 
 #include "../../include/pararnn_b200.h"
 #include "kernels.h"
@@ -65,6 +63,7 @@ Chain next_chain(ChainScratch& c, int T, int tile_steps, int* status) {
     ch.ticket = c.tickets + (c.next_ticket++ % kTickets);
     ch.status = status;
     ch.epoch = c.next_epoch++;
+    ch.spin_limit = options().spin_limit;
     ch.n_chains = c.n_chains;
     ch.n_tt = (T + tile_steps - 1) / tile_steps;
     return ch;
@@ -84,55 +83,53 @@ __global__ void cvt_from_f32_kernel(const float* src, T* dst, size_t n) {
 }
 
 void to_f32(const void* src, float* dst, size_t n, int dtype, cudaStream_t s) {
-    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    const size_t cap = (size_t)sm_count() * 8;
+    const int blocks = (int)((n + 255) / 256 < cap ? (n + 255) / 256 : cap);
     if (dtype == kF32)
         cvt_to_f32_kernel<float><<<blocks, 256, 0, s>>>((const float*)src, dst, n);
     else
         cvt_to_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)src, dst, n);
 }
 void from_f32(const float* src, void* dst, size_t n, int dtype, cudaStream_t s) {
-    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    const size_t cap = (size_t)sm_count() * 8;
+    const int blocks = (int)((n + 255) / 256 < cap ? (n + 255) / 256 : cap);
     if (dtype == kF32)
         cvt_from_f32_kernel<float><<<blocks, 256, 0, s>>>(src, (float*)dst, n);
     else
         cvt_from_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(src, (__nv_bfloat16*)dst, n);
 }
 
-// Kernel family for a sLSTM pass: 0 = look-back kernels (any shape), 1 = persistent-chain
-// kernels with per-thread map composition, 2 = warp-pipelined persistent kernels.  The
-// persistent families need enough independent chains to fill the GPU (one CTA per chain) and
-// TMA-compatible strides.  PRB_KERNEL_PATH=lookback|persist|pipe overrides the choice (used by
-// the tests to cover every family on small shapes).
-// One CTA walks a whole chain, so the persistent families need a minimum of chains to win over the
-// look-back kernels, which also split the time axis: measured cross-over at about 32 chains
-// (B=1, T=65536, d=1024: 12.1 ms against 13.7 ms per forward + backward).
+// Kernel family for a sLSTM pass: 0 = look-back kernels (any shape), 2 = warp-pipelined
+// persistent kernels (one CTA per chain, TMA-fed).  One CTA walks a whole chain, so the
+// pipelined family needs a minimum of chains to win over the look-back kernels, which also split
+// the time axis: measured cross-over at about 32 chains (B=1, T=65536, d=1024: 12.1 ms against
+// 13.7 ms per forward + backward).  prb_debug_set(PRB_OPT_KERNEL_FAMILY) overrides the choice so
+// that the tests can cover both families on small shapes.
 constexpr int kMinChainsPersistent = 32;
 
 int kernel_path(int dtype, int B, int T, int d) {
-    const char* env = getenv("PRB_KERNEL_PATH");
-    if (env && env[0] == 'l') return 0;
-    if (!slstm_persist_ok(dtype, B, T, d)) return 0;
-    if (env && env[0] == 'p' && env[1] == 'e') return 1;
-    if (env && env[0] == 'p') return 2;
+    const int forced = options().kernel_family;
+    if (forced == 0) return 0;
+    if (!tma_addressable(dtype, B, T, d)) return 0;
+    if (forced == 2) return 2;
     return B * ((d + kLanes - 1) / kLanes) >= kMinChainsPersistent ? 2 : 0;
 }
-bool use_persist(int dtype, int B, int T, int d) { return kernel_path(dtype, B, T, d) != 0; }
-// aggregate-only sweeps: one CTA per chain when there are enough chains (or when a persistent
+// aggregate-only sweeps: one CTA per chain when there are enough chains (or when the pipelined
 // family is forced), else the look-back kernels with map carries
 bool agg_seg(int B, int d) {
-    const char* env = getenv("PRB_KERNEL_PATH");
-    if (env && env[0] == 'l') return false;
-    if (env && env[0] == 'p') return true;
+    const int forced = options().kernel_family;
+    if (forced == 0) return false;
+    if (forced == 2) return true;
     return B * ((d + kLanes - 1) / kLanes) >= kMinChainsPersistent;
 }
 
 // scalar-diagonal cells: pipelined persistent kernels when TMA can address the arrays and there
 // are enough chains to occupy a good part of the GPU (one CTA per chain); else look-back kernels
 bool diag_pipe(int dtype, int B, int T, int d) {
-    const char* env = getenv("PRB_KERNEL_PATH");
-    if (env && env[0] == 'l') return false;
-    if (!slstm_persist_ok(dtype, B, T, d)) return false;
-    if (env && env[0] == 'p') return true;
+    const int forced = options().kernel_family;
+    if (forced == 0) return false;
+    if (!tma_addressable(dtype, B, T, d)) return false;
+    if (forced == 2) return true;
     return B * ((d + kLanes - 1) / kLanes) >= 48;
 }
 
@@ -207,9 +204,9 @@ int run_diag_fwd(int cell, const void* wx, const void* const* pars, const void* 
         a.d = d;
         a.omega = omega;
         a.chain = next_chain(p.chain, T, diag_tile_steps(), &st->status);
-        const cudaError_t e = diag_pipe(dtype, B, T, d)
-                                  ? launch_diag_newton_pipe(cell, dtype, a, k == 0, k == K - 1, s)
-                                  : launch_diag_newton(cell, dtype, a, k == 0, k == K - 1, s);
+        cudaError_t e = cudaErrorNotSupported;
+        if (diag_pipe(dtype, B, T, d)) e = launch_diag_newton_pipe(cell, dtype, a, k == 0, k == K - 1, s);
+        if (e == cudaErrorNotSupported) e = launch_diag_newton(cell, dtype, a, k == 0, k == K - 1, s);
         if (e != cudaSuccess) return PRB_ERR_LAUNCH;
     }
     if (want_residual && K == 0)
@@ -274,10 +271,14 @@ int run_diag_bwd(int cell, const void* states, const void* wx, const void* const
     a.T = T;
     a.d = d;
     a.chain = next_chain(p.chain, T, diag_tile_steps(), &st->status);
-    const bool pipe = diag_pipe(dtype, B, T, d);
-    if ((pipe ? launch_diag_bwd_pipe(cell, dtype, a, s) : launch_diag_bwd(cell, dtype, a, false, s)) !=
-        cudaSuccess)
-        return PRB_ERR_LAUNCH;
+    bool pipe = diag_pipe(dtype, B, T, d);
+    cudaError_t e = cudaErrorNotSupported;
+    if (pipe) e = launch_diag_bwd_pipe(cell, dtype, a, s);
+    if (e == cudaErrorNotSupported) {
+        pipe = false;
+        e = launch_diag_bwd(cell, dtype, a, false, s);
+    }
+    if (e != cudaSuccess) return PRB_ERR_LAUNCH;
     // one partial row per tile (look-back) or per batch row (one CTA per chain)
     if (launch_reduce_partials(p.partial, pipe ? B : B * a.chain.n_tt, np * d, g_params, s) != cudaSuccess)
         return PRB_ERR_LAUNCH;
@@ -315,8 +316,9 @@ SlstmPlan plan_slstm_fwd(void* ws, int B, int T, int d, int K, int P, bool has_g
 int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* guess, void* out, int B,
                   int T, int d, int dtype, int K, int P, float omega, float eps, int want_residual,
                   void* ws, size_t ws_bytes, prb_stats* stats, cudaStream_t s) {
+    // every pass of the look-back family takes its own ticket counter
     if (!wx || !r || !out || !stats || B < 1 || T < 1 || d < 1 || K < 0 || K > kMaxIters || P < 0 ||
-        bad_dtype(dtype))
+        P + 1 + K > kTickets || bad_dtype(dtype))
         return PRB_ERR_BAD_ARG;
     SlstmPlan p = plan_slstm_fwd(nullptr, B, T, d, K, P, guess != nullptr);
     if (int e = check_ws(ws, ws_bytes, p.total)) return e;
@@ -332,14 +334,12 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
     }
     const size_t nst = (size_t)B * T * 4 * d;
     const int path = kernel_path(dtype, B, T, d);
-    const bool persist = path != 0;
     if (guess) {
         to_f32(guess, p.sb[0], nst, dtype, s);
     } else {
         // the pipelined family runs all P+1 passes in one sweep when it can
         bool fused_done = false;
-        const char* fenv = getenv("PRB_PICARD_FUSED");
-        if (path == 2 && P + 1 <= slstm_picard_fused_max_passes() && !(fenv && fenv[0] == '0')) {
+        if (path == 2 && P + 1 <= slstm_picard_fused_max_passes() && options().picard_fused) {
             SlstmPicardArgs a{};
             a.wx = wx;
             a.r = p.r;
@@ -377,7 +377,6 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
             a.chain = next_chain(p.chain, T, slstm_picard_tile_steps(), &st->status);
             cudaError_t e = cudaErrorNotSupported;
             if (path == 2) e = launch_slstm_picard_pipe(dtype, a, s);
-            if (path == 1) e = launch_slstm_picard_persist(dtype, a, s);
             if (e == cudaErrorNotSupported) e = launch_slstm_picard(dtype, a, false, s);
             if (e != cudaSuccess) return PRB_ERR_LAUNCH;
         }
@@ -385,8 +384,7 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
     if (K == 0) from_f32(p.sb[0], out, nst, dtype, s);
     // the pipelined family runs all K iterations in one sweep when it can
     bool newton_done = false;
-    const char* nenv = getenv("PRB_NEWTON_FUSED");
-    if (path == 2 && K >= 1 && K <= slstm_newton_fused_max_iters() && !(nenv && nenv[0] == '0')) {
+    if (path == 2 && K >= 1 && K <= slstm_newton_fused_max_iters() && options().newton_fused) {
         SlstmNewtonArgs a{};
         a.wx = wx;
         a.r = p.r;
@@ -424,7 +422,6 @@ int run_slstm_fwd(const void* wx, const void* r, const void* h0, const void* gue
         a.chain = next_chain(p.chain, T, slstm_tile_steps(), &st->status);
         cudaError_t e = cudaErrorNotSupported;
         if (path == 2) e = launch_slstm_newton_pipe(dtype, a, k == K - 1, s);
-        if (path == 1) e = launch_slstm_newton_persist(dtype, a, k == K - 1, s);
         if (e == cudaErrorNotSupported) e = launch_slstm_newton(dtype, a, k == K - 1, false, s);
         if (e != cudaSuccess) return PRB_ERR_LAUNCH;
     }
@@ -483,11 +480,83 @@ __global__ void fold_carries_kernel(const float* gathered, int rank, int world, 
     for (int i = 0; i < M::NS; ++i) out[((size_t)b * M::NS + i) * d + ch] = vec[i];
 }
 
+// Carries entering the time segments of one rank (segments in time order; the scan runs through
+// them forwards, or backwards when reverse != 0).  out[j] (j < n_seg) is the carry entering
+// segment j, out[n_seg] the carry leaving the rank.  carry0 == nullptr means a zero carry.
+template <class M>
+__global__ void segment_carries_kernel(const float* agg, int n_seg, int reverse, const float* carry0,
+                                       float* out, int B, int d) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= B * d) return;
+    const int b = idx / d, ch = idx % d;
+    float vec[M::NS];
+#pragma unroll
+    for (int i = 0; i < M::NS; ++i) vec[i] = carry0 ? carry0[((size_t)b * M::NS + i) * d + ch] : 0.f;
+    for (int k = 0; k < n_seg; ++k) {
+        const int j = reverse ? n_seg - 1 - k : k;
+#pragma unroll
+        for (int i = 0; i < M::NS; ++i) out[(((size_t)j * B + b) * M::NS + i) * d + ch] = vec[i];
+        float m[M::NV];
+        const float* p = agg + ((size_t)j * B + b) * M::NV * d + ch;
+#pragma unroll
+        for (int i = 0; i < M::NV; ++i) m[i] = p[(size_t)i * d];
+        M::apply(m, vec);
+    }
+#pragma unroll
+    for (int i = 0; i < M::NS; ++i) out[(((size_t)n_seg * B + b) * M::NS + i) * d + ch] = vec[i];
+}
+
+// Map of a whole rank = composition of its segment maps in scan order.
+template <class M>
+__global__ void fold_segments_kernel(const float* agg, int n_seg, int reverse, float* out, int B, int d) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= B * d) return;
+    const int b = idx / d, ch = idx % d;
+    float acc[M::NV];
+    for (int k = 0; k < n_seg; ++k) {
+        const int j = reverse ? n_seg - 1 - k : k;
+        float m[M::NV];
+        const float* p = agg + ((size_t)j * B + b) * M::NV * d + ch;
+#pragma unroll
+        for (int i = 0; i < M::NV; ++i) m[i] = p[(size_t)i * d];
+        if (k == 0) {
+#pragma unroll
+            for (int i = 0; i < M::NV; ++i) acc[i] = m[i];
+        } else {
+            M::compose(acc, m);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < M::NV; ++i) out[((size_t)b * M::NV + i) * d + ch] = acc[i];
+}
+
+bool bad_segments(int T, int n_seg, int seg_len) {
+    if (n_seg < 1 || seg_len < 1) return true;
+    if (n_seg == 1) return false;
+    return (long long)(n_seg - 1) * seg_len >= T || (long long)n_seg * seg_len < T;
+}
+
 }  // namespace
 
 extern "C" {
 
-const char* prb_version(void) { return "pararnn_b200 0.1 (sm_100a)"; }
+const char* prb_version(void) { return "pararnn_b200 0.2 (sm_100a)"; }
+
+int prb_debug_set(int option, long long value) {
+    Options& o = options();
+    switch (option) {
+        case PRB_OPT_KERNEL_FAMILY:
+            if (value != -1 && value != 0 && value != 2) return PRB_ERR_BAD_ARG;
+            o.kernel_family = (int)value;
+            return PRB_OK;
+        case PRB_OPT_PICARD_FUSED: o.picard_fused = value != 0; return PRB_OK;
+        case PRB_OPT_NEWTON_FUSED: o.newton_fused = value != 0; return PRB_OK;
+        case PRB_OPT_SPIN_LIMIT:
+            o.spin_limit = value <= 0 ? kSpinLimit : (unsigned)(value > 0x7fffffffLL ? 0x7fffffffLL : value);
+            return PRB_OK;
+        default: return PRB_ERR_BAD_ARG;
+    }
+}
 
 const char* prb_error_string(int code) {
     switch (code) {
@@ -606,8 +675,7 @@ int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void*
     const int path = kernel_path(dtype, B, T, d);
     cudaError_t e = cudaErrorNotSupported;
     if (path == 2) e = launch_slstm_bwd_pipe(dtype, a, s);
-    if (path == 1) e = launch_slstm_bwd_persist(dtype, a, s);
-    if (e == cudaSuccess) rows = B;  // the persistent kernel writes one partial per batch row
+    if (e == cudaSuccess) rows = B;  // the pipelined kernel writes one partial per batch row
     if (e == cudaErrorNotSupported) e = launch_slstm_bwd(dtype, a, false, s);
     if (e != cudaSuccess) return PRB_ERR_LAUNCH;
     if (launch_reduce_partials(p.partial, rows, 4 * d, g_params, s) != cudaSuccess)
@@ -848,11 +916,12 @@ int prb_diag_bwd_pass(int cell, const void* states, const void* wx, const float*
 
 int prb_slstm_picard_pass(const void* wx, const float* r, const float* h_prev, const float* h_halo,
                           const float* carry_in, float* h_out, float* state_out, float* tail_out,
-                          float* agg_out, int mode, int B, int T, int d, int dtype, float eps,
-                          void* workspace, size_t workspace_bytes, prb_stats* stats,
+                          float* agg_out, int mode, int n_seg, int seg_len, int B, int T, int d, int dtype,
+                          float eps, void* workspace, size_t workspace_bytes, prb_stats* stats,
                           prb_stream_t stream) {
     cudaStream_t s = (cudaStream_t)stream;
-    if (!wx || !r || !stats || B < 1 || T < 1 || d < 1 || bad_dtype(dtype) || (mode != 0 && mode != 2))
+    if (!wx || !r || !stats || B < 1 || T < 1 || d < 1 || bad_dtype(dtype) || (mode != 0 && mode != 2) ||
+        bad_segments(T, n_seg, seg_len))
         return PRB_ERR_BAD_ARG;
     if ((mode == 2 && !agg_out) || (mode == 0 && !h_out && !state_out)) return PRB_ERR_BAD_ARG;
     PassWs w;
@@ -874,12 +943,14 @@ int prb_slstm_picard_pass(const void* wx, const float* r, const float* h_prev, c
     a.T = T;
     a.d = d;
     a.eps = eps;
+    a.n_seg = n_seg;
+    a.seg_len = seg_len;
     a.chain = next_chain(w.chain, T, slstm_picard_tile_steps(), &st->status);
     const int path = kernel_path(dtype, B, T, d);
     cudaError_t e = cudaErrorNotSupported;
-    if (mode == 2 && agg_seg(B, d)) e = launch_slstm_picard_agg_seg(dtype, a, s);
+    if (mode == 2 && (agg_seg(B, d) || n_seg > 1)) e = launch_slstm_picard_agg_seg(dtype, a, s);
     if (mode == 0 && path == 2) e = launch_slstm_picard_pipe(dtype, a, s);
-    if (mode == 0 && path == 1) e = launch_slstm_picard_persist(dtype, a, s);
+    if (e == cudaErrorNotSupported && n_seg > 1) return PRB_ERR_UNSUPPORTED;  // look-back kernels: one segment
     if (e == cudaErrorNotSupported) e = launch_slstm_picard(dtype, a, mode == 2, s);
     return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
@@ -891,7 +962,7 @@ int prb_slstm_picard_sweep(const void* wx, const float* r, const float* h_halo, 
     cudaStream_t s = (cudaStream_t)stream;
     if (!wx || !r || !state_out || !stats || B < 1 || T < 1 || d < 1 || n_passes < 1 || bad_dtype(dtype))
         return PRB_ERR_BAD_ARG;
-    if (n_passes > slstm_picard_fused_max_passes() || !slstm_persist_ok(dtype, B, T, d))
+    if (n_passes > slstm_picard_fused_max_passes() || !tma_addressable(dtype, B, T, d))
         return PRB_ERR_UNSUPPORTED;
     PassWs w;
     if (int e = pass_ws(kCellSlstmDiag, B, T, d, workspace, workspace_bytes, s, w)) return e;
@@ -922,7 +993,7 @@ int prb_slstm_newton_sweep(const void* wx, const float* r, const float* sin, con
     cudaStream_t s = (cudaStream_t)stream;
     if (!wx || !r || !sin || !sout || !stats || B < 1 || T < 1 || d < 1 || n_iters < 1 || bad_dtype(dtype))
         return PRB_ERR_BAD_ARG;
-    if (n_iters > slstm_newton_fused_max_iters() || !slstm_persist_ok(dtype, B, T, d))
+    if (n_iters > slstm_newton_fused_max_iters() || !tma_addressable(dtype, B, T, d))
         return PRB_ERR_UNSUPPORTED;
     PassWs w;
     if (int e = pass_ws(kCellSlstmDiag, B, T, d, workspace, workspace_bytes, s, w)) return e;
@@ -949,12 +1020,12 @@ int prb_slstm_newton_sweep(const void* wx, const float* r, const float* sin, con
 
 int prb_slstm_newton_pass(const void* wx, const float* r, const float* sin, const float* halo,
                           const float* carry_in, void* sout, float* tail_out, float* agg_out, int mode,
-                          int B, int T, int d, int dtype, float omega, float eps, void* workspace,
-                          size_t workspace_bytes, prb_stats* stats, int hist_slot,
+                          int n_seg, int seg_len, int B, int T, int d, int dtype, float omega, float eps,
+                          void* workspace, size_t workspace_bytes, prb_stats* stats, int hist_slot,
                           prb_stream_t stream) {
     cudaStream_t s = (cudaStream_t)stream;
     if (!wx || !r || !sin || !stats || B < 1 || T < 1 || d < 1 || bad_dtype(dtype) || mode < 0 ||
-        mode > 2 || hist_slot < 0 || hist_slot >= kMaxIters)
+        mode > 2 || hist_slot < 0 || hist_slot >= kMaxIters || bad_segments(T, n_seg, seg_len))
         return PRB_ERR_BAD_ARG;
     if ((mode == 2 && !agg_out) || (mode != 2 && !sout)) return PRB_ERR_BAD_ARG;
     PassWs w;
@@ -977,24 +1048,26 @@ int prb_slstm_newton_pass(const void* wx, const float* r, const float* sin, cons
     a.d = d;
     a.omega = omega;
     a.eps = eps;
+    a.n_seg = n_seg;
+    a.seg_len = seg_len;
     a.chain = next_chain(w.chain, T, slstm_tile_steps(), &st->status);
     const int path = kernel_path(dtype, B, T, d);
     cudaError_t e = cudaErrorNotSupported;
-    if (mode == 2 && agg_seg(B, d)) e = launch_slstm_newton_agg_seg(dtype, a, s);
+    if (mode == 2 && (agg_seg(B, d) || n_seg > 1)) e = launch_slstm_newton_agg_seg(dtype, a, s);
     if (mode != 2 && path == 2) e = launch_slstm_newton_pipe(dtype, a, mode == 1, s);
-    if (mode != 2 && path == 1) e = launch_slstm_newton_persist(dtype, a, mode == 1, s);
+    if (e == cudaErrorNotSupported && n_seg > 1) return PRB_ERR_UNSUPPORTED;
     if (e == cudaErrorNotSupported) e = launch_slstm_newton(dtype, a, mode == 1, mode == 2, s);
     return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
 
 int prb_slstm_bwd_pass(const void* states, const void* wx, const float* r, const float* halo,
                        const float* carry_in, const void* grad_states, void* g_wx, float* g_params,
-                       float* head_out, float* agg_out, int mode, int B, int T, int d, int dtype,
-                       float eps, void* workspace, size_t workspace_bytes, prb_stats* stats,
-                       prb_stream_t stream) {
+                       float* head_out, float* agg_out, int mode, int n_seg, int seg_len, int B, int T,
+                       int d, int dtype, float eps, void* workspace, size_t workspace_bytes,
+                       prb_stats* stats, prb_stream_t stream) {
     cudaStream_t s = (cudaStream_t)stream;
     if (!states || !wx || !r || !grad_states || !stats || B < 1 || T < 1 || d < 1 || bad_dtype(dtype) ||
-        (mode != 0 && mode != 2))
+        (mode != 0 && mode != 2) || bad_segments(T, n_seg, seg_len))
         return PRB_ERR_BAD_ARG;
     if ((mode == 2 && !agg_out) || (mode == 0 && (!g_wx || !g_params))) return PRB_ERR_BAD_ARG;
     PassWs w;
@@ -1016,14 +1089,16 @@ int prb_slstm_bwd_pass(const void* states, const void* wx, const float* r, const
     a.T = T;
     a.d = d;
     a.eps = eps;
+    a.n_seg = n_seg;
+    a.seg_len = seg_len;
     a.chain = next_chain(w.chain, T, slstm_tile_steps(), &st->status);
     int rows = B * a.chain.n_tt;
     const int path = kernel_path(dtype, B, T, d);
     cudaError_t e = cudaErrorNotSupported;
-    if (mode == 2 && agg_seg(B, d)) e = launch_slstm_bwd_agg_seg(dtype, a, s);
+    if (mode == 2 && (agg_seg(B, d) || n_seg > 1)) e = launch_slstm_bwd_agg_seg(dtype, a, s);
     if (mode == 0 && path == 2) e = launch_slstm_bwd_pipe(dtype, a, s);
-    if (mode == 0 && path == 1) e = launch_slstm_bwd_persist(dtype, a, s);
-    if (e == cudaSuccess) rows = B;
+    if (e == cudaSuccess) rows = B * n_seg;  // one partial row per (segment, batch row)
+    if (e == cudaErrorNotSupported && n_seg > 1) return PRB_ERR_UNSUPPORTED;
     if (e == cudaErrorNotSupported) e = launch_slstm_bwd(dtype, a, mode == 2, s);
     if (e != cudaSuccess) return PRB_ERR_LAUNCH;
     if (mode == 0 && launch_reduce_partials(w.partial, rows, 4 * d, g_params, s) != cudaSuccess)
@@ -1063,6 +1138,58 @@ int prb_fold_carries(int monoid, const float* gathered, int rank, int world, int
         fold_carries_kernel<Affine4><<<grid, blk, 0, s>>>(gathered, rank, world, reverse, carry_out, B, d, 20);
     else if (monoid == 2)
         fold_carries_kernel<PicardMonoid><<<grid, blk, 0, s>>>(gathered, rank, world, reverse, carry_out, B, d, 4);
+    else
+        return PRB_ERR_BAD_ARG;
+    return cudaGetLastError() == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+}
+
+int prb_plan_segments(int cell, int dtype, int B, int T, int d, int* n_seg, int* seg_len) {
+    if (!n_seg || !seg_len || B < 1 || T < 1 || d < 1 || bad_dtype(dtype)) return PRB_ERR_BAD_ARG;
+    *n_seg = 1;
+    *seg_len = T;
+    if (cell != kCellSlstmDiag || kernel_path(dtype, B, T, d) != 2) return PRB_OK;
+    // aim at two CTAs per SM, keep segments long enough that the two extra tiny launches per
+    // pass (segment fold, segment carries) and the pipeline fill stay negligible
+    const int chains = B * ((d + kLanes - 1) / kLanes);
+    const int target = 2 * sm_count();
+    int n = (target + chains - 1) / chains;
+    const int min_len = 1024;
+    if (n > T / min_len) n = T / min_len;
+    if (n < 2) return PRB_OK;
+    int len = (T + n - 1) / n;
+    len = (len + 63) / 64 * 64;
+    *seg_len = len;
+    *n_seg = (T + len - 1) / len;
+    return PRB_OK;
+}
+
+int prb_fold_segments(int monoid, const float* agg, int n_seg, int reverse, float* slot, int B, int d,
+                      prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!agg || !slot || n_seg < 1 || B < 1 || d < 1) return PRB_ERR_BAD_ARG;
+    const int n = B * d, blk = 128, grid = (n + blk - 1) / blk;
+    if (monoid == 0)
+        fold_segments_kernel<Affine1><<<grid, blk, 0, s>>>(agg, n_seg, reverse, slot, B, d);
+    else if (monoid == 1)
+        fold_segments_kernel<Affine4><<<grid, blk, 0, s>>>(agg, n_seg, reverse, slot, B, d);
+    else if (monoid == 2)
+        fold_segments_kernel<PicardMonoid><<<grid, blk, 0, s>>>(agg, n_seg, reverse, slot, B, d);
+    else
+        return PRB_ERR_BAD_ARG;
+    return cudaGetLastError() == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+}
+
+int prb_segment_carries(int monoid, const float* agg, int n_seg, int reverse, const float* carry0,
+                        float* carries, int B, int d, prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!agg || !carries || n_seg < 1 || B < 1 || d < 1) return PRB_ERR_BAD_ARG;
+    const int n = B * d, blk = 128, grid = (n + blk - 1) / blk;
+    if (monoid == 0)
+        segment_carries_kernel<Affine1><<<grid, blk, 0, s>>>(agg, n_seg, reverse, carry0, carries, B, d);
+    else if (monoid == 1)
+        segment_carries_kernel<Affine4><<<grid, blk, 0, s>>>(agg, n_seg, reverse, carry0, carries, B, d);
+    else if (monoid == 2)
+        segment_carries_kernel<PicardMonoid><<<grid, blk, 0, s>>>(agg, n_seg, reverse, carry0, carries, B, d);
     else
         return PRB_ERR_BAD_ARG;
     return cudaGetLastError() == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;

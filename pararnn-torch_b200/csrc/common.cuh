@@ -34,6 +34,24 @@ struct DeviceStats {
     int reserved[2];
 };
 
+// Time segment of a CTA: blockIdx.y selects one of n_seg contiguous pieces of the time axis.
+struct SegRange {
+    int seg, lo, hi;
+};
+__device__ __forceinline__ SegRange seg_range(int T, int n_seg, int seg_len) {
+    SegRange s;
+    if (n_seg <= 1) {
+        s.seg = 0;
+        s.lo = 0;
+        s.hi = T;
+    } else {
+        s.seg = blockIdx.y;
+        s.lo = min(T, s.seg * seg_len);
+        s.hi = min(T, s.lo + seg_len);
+    }
+    return s;
+}
+
 // ---------------------------------------------------------------- I/O dtype
 template <typename T>
 __device__ __forceinline__ float ld_f(const T* p);
@@ -149,6 +167,7 @@ struct Chain {
     unsigned* ticket;  // one counter, zero at launch
     int* status;       // device status word
     unsigned epoch;    // distinguishes passes that share the flag array
+    unsigned spin_limit;  // polls after which a look-back wait gives up
     int n_chains;
     int n_tt;
 };
@@ -204,7 +223,7 @@ __device__ __forceinline__ void chain_lookback(const Chain& c, size_t tile0, int
             --k;
             continue;
         }
-        if (++spins > kSpinLimit) {
+        if (++spins > c.spin_limit) {
             ok = false;
             break;
         }

@@ -464,7 +464,7 @@ template <int CELL, typename TIO, typename TOUT>
 static void launch_guess_t(const void* wx, const float* par, const float* h0, void* out, int B, int T,
                            int d, cudaStream_t s) {
     const size_t n = (size_t)B * T * d;
-    const int blocks = (int)min((size_t)148 * 16, (n + 255) / 256);
+    const int blocks = (int)min((size_t)sm_count() * 16, (n + 255) / 256);
     diag_guess_kernel<CELL, TIO, TOUT><<<blocks, 256, 0, s>>>(
         reinterpret_cast<const TIO*>(wx), par, h0, reinterpret_cast<TOUT*>(out), B, T, d);
 }

@@ -7,6 +7,19 @@
 
 namespace prb {
 
+// SM count of the current device (queried once per device).
+int sm_count();
+
+// Process-wide switches set through prb_debug_set (tests and profiling only); the defaults are
+// what every normal call uses.
+struct Options {
+    int kernel_family = -1;            // -1 choose by shape, 0 look-back kernels, 2 pipelined kernels
+    bool picard_fused = true;          // all Picard passes in one sweep when the shape allows
+    bool newton_fused = true;          // all Newton iterations in one sweep when the shape allows
+    unsigned spin_limit = kSpinLimit;  // poll limit of the look-back waits
+};
+Options& options();
+
 enum Cell : int { kCellGruDiag = 0, kCellNlru = 1, kCellSlstmDiag = 2, kCellGruHead = 3 };
 enum DType : int { kF32 = 0, kBF16 = 1 };
 
@@ -74,6 +87,9 @@ struct SlstmPicardArgs {
     int carry_stride;      // batch stride (floats) of carry_in, slots (c,n,m) d apart
     int B, T, d;
     float eps;
+    // time segments: CTA (chain, seg) owns steps [seg*seg_len, min(T, (seg+1)*seg_len)); carry_in
+    // and agg_out then have a leading n_seg dimension.  n_seg <= 1 means one segment of T steps.
+    int n_seg, seg_len;
     Chain chain;
 };
 
@@ -91,6 +107,9 @@ struct SlstmNewtonArgs {
     int halo_stride;        // batch stride (floats) of halo
     int B, T, d;
     float omega, eps;
+    // time segments: CTA (chain, seg) owns steps [seg*seg_len, min(T, (seg+1)*seg_len)); carry_in
+    // and agg_out then have a leading n_seg dimension.  n_seg <= 1 means one segment of T steps.
+    int n_seg, seg_len;
     Chain chain;
 };
 
@@ -108,6 +127,9 @@ struct SlstmBwdArgs {
     int halo_stride;
     int B, T, d;
     float eps;
+    // time segments: CTA (chain, seg) owns steps [seg*seg_len, min(T, (seg+1)*seg_len)); carry_in
+    // and agg_out then have a leading n_seg dimension.  n_seg <= 1 means one segment of T steps.
+    int n_seg, seg_len;
     Chain chain;
 };
 
@@ -121,17 +143,14 @@ cudaError_t launch_slstm_residual(int dtype, bool st_f32, const void* wx, const 
                                   int d, float eps, unsigned* dst, cudaStream_t s);
 cudaError_t launch_slstm_bwd(int dtype, const SlstmBwdArgs& a, bool agg_only, cudaStream_t s);
 
-// persistent-chain variants (slstm_persist.cu); cudaErrorNotSupported when TMA rules are not met
-bool slstm_persist_ok(int dtype, int B, int T, int d);
+// true when TMA tile loads can address the (B,T,G*d) / (B,T,S,d) arrays of this shape and dtype
+bool tma_addressable(int dtype, int B, int T, int d);
 // all Newton iterations in one sweep (slstm_newton_fused.cu)
 int slstm_newton_fused_max_iters();
 cudaError_t launch_slstm_newton_fused(int dtype, const SlstmNewtonArgs& a, int n_iters, cudaStream_t s);
 // all Picard passes of the warm start in one sweep (slstm_picard_fused.cu)
 int slstm_picard_fused_max_passes();
 cudaError_t launch_slstm_picard_fused(int dtype, const SlstmPicardArgs& a, int n_pass, cudaStream_t s);
-cudaError_t launch_slstm_picard_persist(int dtype, const SlstmPicardArgs& a, cudaStream_t s);
-cudaError_t launch_slstm_newton_persist(int dtype, const SlstmNewtonArgs& a, bool last, cudaStream_t s);
-cudaError_t launch_slstm_bwd_persist(int dtype, const SlstmBwdArgs& a, cudaStream_t s);
 
 // warp-pipelined variants (slstm_pipe.cu)
 cudaError_t launch_slstm_newton_pipe(int dtype, const SlstmNewtonArgs& a, bool last, cudaStream_t s);

@@ -45,10 +45,11 @@ __device__ __forceinline__ void finish_agg(float* smem, const float (&mp)[M::NV]
     }
 }
 
-__device__ __forceinline__ void seg_bounds(int T, int warp, int& lo, int& hi) {
-    const int seg = (T + kAggW - 1) / kAggW;
-    lo = min(T, warp * seg);
-    hi = min(T, lo + seg);
+// the warp's share of the CTA's time segment [t_lo, t_hi)
+__device__ __forceinline__ void seg_bounds(int t_lo, int t_hi, int warp, int& lo, int& hi) {
+    const int seg = (t_hi - t_lo + kAggW - 1) / kAggW;
+    lo = min(t_hi, t_lo + warp * seg);
+    hi = min(t_hi, lo + seg);
 }
 
 // Warp-private TMA ring: NST stages of STAGE_BYTES each, one mbarrier per stage.
@@ -68,8 +69,8 @@ struct WarpRing {
         __syncwarp();
     }
     __device__ __forceinline__ unsigned char* stage(int k) const { return base + (k % NST) * stage_bytes; }
-    __device__ __forceinline__ bool wait(int k) const {
-        return mbar_wait_bounded(&bars[k % NST], (k / NST) & 1, kAggWaitLimit);
+    __device__ __forceinline__ bool wait(int k, volatile int* abort_word) const {
+        return mbar_wait_abortable(&bars[k % NST], (k / NST) & 1, kAggWaitLimit, abort_word);
     }
 };
 
@@ -98,8 +99,12 @@ slstm_newton_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
     const int ch = cb * kLanes + lane;
     const bool ch_ok = ch < d;
     const int chl = ch_ok ? ch : d - 1;
+    const SegRange sg = seg_range(a.T, a.n_seg, a.seg_len);
+    __shared__ volatile int s_abort;
+    if (threadIdx.x == 0) s_abort = 0;
+    __syncthreads();
     int lo, hi;
-    seg_bounds(a.T, warp, lo, hi);
+    seg_bounds(sg.lo, sg.hi, warp, lo, hi);
     WarpRing<NST> ring;
     ring.init(smem + warp * S::RING, reinterpret_cast<uint64_t*>(smem + S::BAR_OFF) + warp * NST, S::STAGE, lane);
     const int n_chunks = (hi - lo + U - 1) / U;
@@ -110,8 +115,12 @@ slstm_newton_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
         tma_load_3d(st, &tm_wx, &ring.bars[k % NST], cb * kLanes, 0, row0 + lo + k * U);
         tma_load_3d(st + S::WX, &tm_st, &ring.bars[k % NST], cb * kLanes, 0, row0 + lo + k * U);
     };
+    int issued = 0;
     if (lane == 0)
-        for (int k = 0; k < NST && k < n_chunks; ++k) issue(k);
+        for (int k = 0; k < NST && k < n_chunks; ++k) {
+            issue(k);
+            issued = k + 1;
+        }
     float r4[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) r4[q] = __ldg(a.r + (size_t)q * d + chl);
@@ -132,7 +141,10 @@ slstm_newton_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
     }
     bool timed_out = false;
     for (int k = 0; k < n_chunks; ++k) {
-        if (!ring.wait(k)) timed_out = true;
+        if (!ring.wait(k, &s_abort)) {
+            timed_out = true;
+            break;
+        }
         const TIO* t_wx = reinterpret_cast<const TIO*>(ring.stage(k));
         const float* t_st = reinterpret_cast<const float*>(ring.stage(k) + S::WX);
         // chunks that lie fully inside the warp's range take a variant without range checks
@@ -178,10 +190,13 @@ slstm_newton_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
         if (lane == 0 && k + NST < n_chunks) {
             fence_proxy_async();
             issue(k + NST);
+            issued = k + NST + 1;
         }
     }
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
-    finish_agg<Affine4>(reinterpret_cast<float*>(smem + S::MAPS_OFF), mp, warp, lane, a.agg_out, b, d, ch, ch_ok);
+    if (lane == 0 && s_abort) drain_ring(ring.bars, NST, issued, kAggWaitLimit);
+    finish_agg<Affine4>(reinterpret_cast<float*>(smem + S::MAPS_OFF), mp, warp, lane,
+                        a.agg_out + (size_t)sg.seg * a.B * 20 * d, b, d, ch, ch_ok);
 }
 
 // ------------------------------------------------------------------ Picard
@@ -209,8 +224,12 @@ slstm_picard_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
     const int ch = cb * kLanes + lane;
     const bool ch_ok = ch < d;
     const int chl = ch_ok ? ch : d - 1;
+    const SegRange sg = seg_range(a.T, a.n_seg, a.seg_len);
+    __shared__ volatile int s_abort;
+    if (threadIdx.x == 0) s_abort = 0;
+    __syncthreads();
     int lo, hi;
-    seg_bounds(a.T, warp, lo, hi);
+    seg_bounds(sg.lo, sg.hi, warp, lo, hi);
     WarpRing<NST> ring;
     ring.init(smem + warp * S::RING, reinterpret_cast<uint64_t*>(smem + S::BAR_OFF) + warp * NST, S::STAGE, lane);
     const int n_chunks = (hi - lo + U - 1) / U;
@@ -222,8 +241,12 @@ slstm_picard_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
         // hidden state of the PREVIOUS step: rows shifted by one
         if (HAS_H) tma_load_3d(st + S::WX, &tm_h, &ring.bars[k % NST], cb * kLanes, 0, row0 + lo + k * U - 1);
     };
+    int issued = 0;
     if (lane == 0)
-        for (int k = 0; k < NST && k < n_chunks; ++k) issue(k);
+        for (int k = 0; k < NST && k < n_chunks; ++k) {
+            issue(k);
+            issued = k + 1;
+        }
     float r4[4] = {0.f, 0.f, 0.f, 0.f};
     if (HAS_H) {
 #pragma unroll
@@ -232,7 +255,10 @@ slstm_picard_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
     float mp[4] = {0.f, -CUDART_INF_F, 0.f, 0.f};
     bool timed_out = false;
     for (int k = 0; k < n_chunks; ++k) {
-        if (!ring.wait(k)) timed_out = true;
+        if (!ring.wait(k, &s_abort)) {
+            timed_out = true;
+            break;
+        }
         const TIO* t_wx = reinterpret_cast<const TIO*>(ring.stage(k));
         const float* t_h = reinterpret_cast<const float*>(ring.stage(k) + S::WX);
         // chunks that lie fully inside the warp's range take a variant without range checks
@@ -268,11 +294,13 @@ slstm_picard_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
         if (lane == 0 && k + NST < n_chunks) {
             fence_proxy_async();
             issue(k + NST);
+            issued = k + NST + 1;
         }
     }
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
-    finish_agg<PicardMonoid>(reinterpret_cast<float*>(smem + S::MAPS_OFF), mp, warp, lane, a.agg_out, b, d, ch,
-                             ch_ok);
+    if (lane == 0 && s_abort) drain_ring(ring.bars, NST, issued, kAggWaitLimit);
+    finish_agg<PicardMonoid>(reinterpret_cast<float*>(smem + S::MAPS_OFF), mp, warp, lane,
+                             a.agg_out + (size_t)sg.seg * a.B * 4 * d, b, d, ch, ch_ok);
 }
 
 // ------------------------------------------------------------------ backward
@@ -301,8 +329,12 @@ slstm_bwd_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid
     const int ch = cb * kLanes + lane;
     const bool ch_ok = ch < d;
     const int chl = ch_ok ? ch : d - 1;
+    const SegRange sg = seg_range(a.T, a.n_seg, a.seg_len);
+    __shared__ volatile int s_abort;
+    if (threadIdx.x == 0) s_abort = 0;
+    __syncthreads();
     int lo, hi;
-    seg_bounds(a.T, kAggW - 1 - warp, lo, hi);
+    seg_bounds(sg.lo, sg.hi, kAggW - 1 - warp, lo, hi);
     WarpRing<NST> ring;
     ring.init(smem + warp * S::RING, reinterpret_cast<uint64_t*>(smem + S::BAR_OFF) + warp * NST, S::STAGE, lane);
     const int n_chunks = (hi - lo + U - 1) / U;
@@ -315,8 +347,12 @@ slstm_bwd_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid
         tma_load_3d(st + S::WX, &tm_st, &ring.bars[k % NST], cb * kLanes, 0, row0 + t_first - 1);
         tma_load_3d(st + 2 * S::WX, &tm_g, &ring.bars[k % NST], cb * kLanes, 0, row0 + t_first);
     };
+    int issued = 0;
     if (lane == 0)
-        for (int k = 0; k < NST && k < n_chunks; ++k) issue(k);
+        for (int k = 0; k < NST && k < n_chunks; ++k) {
+            issue(k);
+            issued = k + 1;
+        }
     float r4[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) r4[q] = __ldg(a.r + (size_t)q * d + chl);
@@ -326,7 +362,10 @@ slstm_bwd_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid
     mp[0] = mp[5] = mp[10] = mp[15] = 1.f;
     bool timed_out = false;
     for (int k = 0; k < n_chunks; ++k) {
-        if (!ring.wait(k)) timed_out = true;
+        if (!ring.wait(k, &s_abort)) {
+            timed_out = true;
+            break;
+        }
         const TIO* t_wx = reinterpret_cast<const TIO*>(ring.stage(k));
         const TIO* t_st = reinterpret_cast<const TIO*>(ring.stage(k) + S::WX);
         const TIO* t_g = reinterpret_cast<const TIO*>(ring.stage(k) + 2 * S::WX);
@@ -363,10 +402,13 @@ slstm_bwd_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid
         if (lane == 0 && k + NST < n_chunks) {
             fence_proxy_async();
             issue(k + NST);
+            issued = k + NST + 1;
         }
     }
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
-    finish_agg<Affine4>(reinterpret_cast<float*>(smem + S::MAPS_OFF), mp, warp, lane, a.agg_out, b, d, ch, ch_ok);
+    if (lane == 0 && s_abort) drain_ring(ring.bars, NST, issued, kAggWaitLimit);
+    finish_agg<Affine4>(reinterpret_cast<float*>(smem + S::MAPS_OFF), mp, warp, lane,
+                        a.agg_out + (size_t)sg.seg * a.B * 20 * d, b, d, ch, ch_ok);
 }
 
 // ------------------------------------------------------------------ launchers
@@ -381,7 +423,7 @@ static cudaError_t agg_newton_t(const SlstmNewtonArgs& a, cudaStream_t s) {
         return cudaErrorNotSupported;
     auto k = slstm_newton_agg_seg_kernel<TIO, U, NST>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    k<<<a.B * ((a.d + kLanes - 1) / kLanes), kAggW * 32, S::TOTAL, s>>>(tm_wx, tm_st, a);
+    k<<<dim3(a.B * ((a.d + kLanes - 1) / kLanes), a.n_seg > 1 ? a.n_seg : 1), kAggW * 32, S::TOTAL, s>>>(tm_wx, tm_st, a);
     return cudaGetLastError();
 }
 cudaError_t launch_slstm_newton_agg_seg(int dtype, const SlstmNewtonArgs& a, cudaStream_t s) {
@@ -395,7 +437,7 @@ static cudaError_t agg_picard_t(const SlstmPicardArgs& a, cudaStream_t s) {
     CUtensorMap tm_wx, tm_h;
     const uint64_t rows = (uint64_t)a.B * a.T;
     if (!make_tile_map(&tm_wx, a.wx, sizeof(TIO), rows, 4, a.d, U)) return cudaErrorNotSupported;
-    const int grid = a.B * ((a.d + kLanes - 1) / kLanes);
+    const dim3 grid(a.B * ((a.d + kLanes - 1) / kLanes), a.n_seg > 1 ? a.n_seg : 1);
     if (a.h_prev) {
         if (!make_tile_map(&tm_h, a.h_prev, 4, rows, 1, a.d, U)) return cudaErrorNotSupported;
         auto k = slstm_picard_agg_seg_kernel<TIO, U, NST, true>;
@@ -424,7 +466,7 @@ static cudaError_t agg_bwd_t(const SlstmBwdArgs& a, cudaStream_t s) {
         return cudaErrorNotSupported;
     auto k = slstm_bwd_agg_seg_kernel<TIO, U, NST>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    k<<<a.B * ((a.d + kLanes - 1) / kLanes), kAggW * 32, S::TOTAL, s>>>(tm_wx, tm_st, tm_g, a);
+    k<<<dim3(a.B * ((a.d + kLanes - 1) / kLanes), a.n_seg > 1 ? a.n_seg : 1), kAggW * 32, S::TOTAL, s>>>(tm_wx, tm_st, tm_g, a);
     return cudaGetLastError();
 }
 cudaError_t launch_slstm_bwd_agg_seg(int dtype, const SlstmBwdArgs& a, cudaStream_t s) {

@@ -10,7 +10,7 @@
 // the warps like a baton; no affine maps are composed and the arithmetic per step is the
 // sequential algorithm's, while the expensive carry-independent part runs W-way in parallel.
 //
-// Same math as slstm_kernels.cu / slstm_persist.cu (slstm_cell.cuh); reference behaviour
+// Same math as slstm_kernels.cu (slstm_cell.cuh); reference behaviour
 // restated there.
 #include "common.cuh"
 #include "kernels.h"
@@ -67,10 +67,13 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
     const int ch = cb * kLanes + lane;
     const bool ch_ok = ch < d;
     const int chl = ch_ok ? ch : d - 1;
-    const int n_rounds = (a.T + LT - 1) / LT;
-    const int row0 = b * a.T;
+    const SegRange sg = seg_range(a.T, a.n_seg, a.seg_len);
+    const int n_rounds = (sg.hi - sg.lo + LT - 1) / LT;
+    const int row0 = b * a.T + sg.lo;
+    __shared__ volatile int s_abort;
 
     if (threadIdx.x == 0) {
+        s_abort = 0;
         tma_prefetch_desc(&tm_wx);
         tma_prefetch_desc(&tm_st);
         for (int s = 0; s < NSTAGE; ++s) {
@@ -83,7 +86,7 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
 #pragma unroll
         for (int q = 0; q < 4; ++q)
             s_slot[(0 * 4 + q) * kLanes + lane] =
-                a.carry_in ? __ldg(a.carry_in + ((size_t)b * 4 + q) * d + chl) : 0.f;
+                a.carry_in ? __ldg(a.carry_in + (((size_t)sg.seg * a.B + b) * 4 + q) * d + chl) : 0.f;
     }
     __syncthreads();
 
@@ -93,15 +96,19 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
     if (warp == W) {
         // ---------------- producer warp: one lane streams the rounds into the ring
         if (lane == 0) {
+            int issued = 0;
             for (int r = 0; r < n_rounds; ++r) {
                 const int s = r % NSTAGE;
-                if (r >= NSTAGE && !mbar_wait_bounded(&empty[s], ((r / NSTAGE) - 1) & 1, kPipeWaitLimit))
+                if (r >= NSTAGE && !mbar_wait_abortable(&empty[s], ((r / NSTAGE) - 1) & 1, kPipeWaitLimit, &s_abort))
                     timed_out = true;
+                if (s_abort) break;
                 unsigned char* base = smem + s * S::STAGE;
                 mbar_expect_tx(&full[s], S::STAGE);
                 tma_load_3d(base, &tm_wx, &full[s], cb * kLanes, 0, row0 + r * LT);
                 tma_load_3d(base + S::WX_BYTES, &tm_st, &full[s], cb * kLanes, 0, row0 + r * LT - 1);
+                issued = r + 1;
             }
+            if (s_abort) drain_ring(full, NSTAGE, issued, kPipeWaitLimit);
         }
     } else {
         // ---------------- compute warps
@@ -115,10 +122,12 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
 
         for (int r = 0; r < n_rounds; ++r) {
             const int s = r % NSTAGE;
-            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, kPipeWaitLimit)) timed_out = true;
+            // after a time-out the warps keep walking (the named-barrier hand-over needs every
+            // warp) but no wait takes more than a few polls: the result is void, status says so
+            if (!mbar_wait_abortable(&full[s], (r / NSTAGE) & 1, kPipeWaitLimit, &s_abort)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const float* t_st = reinterpret_cast<const float*>(smem + s * S::STAGE + S::WX_BYTES);
-            const int t0 = r * LT + warp * L;
+            const int t0 = sg.lo + r * LT + warp * L;
 
             // Rounds that lie fully inside the sequence take a variant without range checks.
             auto round_body = [&](auto full_c) {
@@ -150,7 +159,7 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
     #pragma unroll
                 for (int i = 0; i < L; ++i) {
                     slstm_linearize(st[i], w[i], r4, a.eps, lin[i]);
-                    const bool ok = FULL || t0 + i < a.T;
+                    const bool ok = FULL || t0 + i < sg.hi;
                     float fc = lin[i].pc - st[i + 1][0], fn = lin[i].pn - st[i + 1][1];
                     float fm = lin[i].pm - st[i + 1][2], fh = lin[i].ph - st[i + 1][3];
                     if (!ok) {
@@ -189,7 +198,7 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
     #pragma unroll
                 for (int i = 0; i < L; ++i) {
                     const int t = t0 + i;
-                    if ((FULL || t < a.T) && ch_ok) {
+                    if ((FULL || t < sg.hi) && ch_ok) {
                         const float o0 = fmaf(a.omega, dl[i][0], st[i + 1][0]);
                         const float o1 = fmaf(a.omega, dl[i][1], st[i + 1][1]);
                         const float o2 = fmaf(a.omega, dl[i][2], st[i + 1][2]);
@@ -216,14 +225,14 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
                         }
                     }
                 }
-                if (r == n_rounds - 1 && warp == W - 1 && a.tail_out && ch_ok) {
+                if (r == n_rounds - 1 && warp == W - 1 && a.tail_out && ch_ok && sg.hi == a.T) {
                     a.tail_out[((size_t)b * 4 + 0) * d + ch] = xc;
                     a.tail_out[((size_t)b * 4 + 1) * d + ch] = xn;
                     a.tail_out[((size_t)b * 4 + 2) * d + ch] = xm;
                     a.tail_out[((size_t)b * 4 + 3) * d + ch] = xh;
                 }
             };
-            if (t0 + L <= a.T)
+            if (t0 + L <= sg.hi)
                 round_body(std::true_type{});
             else
                 round_body(std::false_type{});
@@ -276,10 +285,13 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
     const int ch = cb * kLanes + lane;
     const bool ch_ok = ch < d;
     const int chl = ch_ok ? ch : d - 1;
-    const int n_rounds = (a.T + LT - 1) / LT;
-    const int row0 = b * a.T;
+    const SegRange sg = seg_range(a.T, a.n_seg, a.seg_len);
+    const int n_rounds = (sg.hi - sg.lo + LT - 1) / LT;
+    const int row0 = b * a.T + sg.lo;
+    __shared__ volatile int s_abort;
 
     if (threadIdx.x == 0) {
+        s_abort = 0;
         tma_prefetch_desc(&tm_wx);
         tma_prefetch_desc(&tm_st);
         tma_prefetch_desc(&tm_g);
@@ -292,7 +304,8 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
     if (warp == 0) {
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-            s_slot[q * kLanes + lane] = a.carry_in ? __ldg(a.carry_in + ((size_t)b * 4 + q) * d + chl) : 0.f;
+            s_slot[q * kLanes + lane] =
+                a.carry_in ? __ldg(a.carry_in + (((size_t)sg.seg * a.B + b) * 4 + q) * d + chl) : 0.f;
     }
     __syncthreads();
     bool timed_out = false;
@@ -309,8 +322,12 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
         tma_load_3d(base + S::WX_BYTES, &tm_st, &full[s], cb * kLanes, 0, row0 + tile_t * LT - 1);
         tma_load_3d(base + S::WX_BYTES + S::ST_BYTES, &tm_g, &full[s], cb * kLanes, 0, row0 + tile_t * LT);
     };
+    int issued = 0;
     if (threadIdx.x == 0)
-        for (int r = 0; r < NSTAGE && r < n_rounds; ++r) issue(r);
+        for (int r = 0; r < NSTAGE && r < n_rounds; ++r) {
+            issue(r);
+            issued = r + 1;
+        }
     {
         float r4[4];
 #pragma unroll
@@ -324,17 +341,22 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
             const int s = r % NSTAGE;
             const int tile_t = n_rounds - 1 - r;
             if (threadIdx.x == 0 && r >= 1 && r - 1 + NSTAGE < n_rounds) {
-                if (!mbar_wait_bounded(&empty[(r - 1) % NSTAGE], ((r - 1) / NSTAGE) & 1, kPipeWaitLimit))
+                if (!mbar_wait_abortable(&empty[(r - 1) % NSTAGE], ((r - 1) / NSTAGE) & 1, kPipeWaitLimit, &s_abort))
                     timed_out = true;
-                issue(r - 1 + NSTAGE);
+                if (!s_abort) {
+                    issue(r - 1 + NSTAGE);
+                    issued = r + NSTAGE;
+                }
             }
             __syncwarp();
-            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, kPipeWaitLimit)) timed_out = true;
+            // after a time-out the warps keep walking (the named-barrier hand-over needs every
+            // warp) but no wait takes more than a few polls: the result is void, status says so
+            if (!mbar_wait_abortable(&full[s], (r / NSTAGE) & 1, kPipeWaitLimit, &s_abort)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const TIO* t_st = reinterpret_cast<const TIO*>(smem + s * S::STAGE + S::WX_BYTES);
             const TIO* t_g = reinterpret_cast<const TIO*>(smem + s * S::STAGE + S::WX_BYTES + S::ST_BYTES);
             const int row_hi = (W - 1 - warp) * L + (L - 1);
-            const int t_hi = tile_t * LT + row_hi;
+            const int t_hi = sg.lo + tile_t * LT + row_hi;
 
             // Rounds that lie fully inside the sequence take a variant without range checks.
             auto round_body = [&](auto full_c) {
@@ -369,7 +391,7 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
     #pragma unroll
                 for (int i = 0; i < L; ++i) {
                     const int t = t_hi - i;
-                    if (FULL || t < a.T) {
+                    if (FULL || t < sg.hi) {
                         const SlstmAct& sa = act[i];
                         const float mc = nc + g[i][0], mn_ = nn + g[i][1], mm = nm + g[i][2], mh = nh + g[i][3];
                         const float cn = fmaf(sa.f, sa.c, sa.i * sa.z);
@@ -404,7 +426,7 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
     #pragma unroll
                 for (int i = 0; i < L; ++i) {
                     const int t = t_hi - i;
-                    if (FULL || t < a.T) {
+                    if (FULL || t < sg.hi) {
                         if (ch_ok) {
                             TIO* o = gw_hi - (size_t)i * 4 * d;
                             st_f(o, dz[i][0]);
@@ -416,14 +438,14 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
                         for (int q = 0; q < 4; ++q) gr[q] = fmaf(dz[i][q], act[i].hp, gr[q]);
                     }
                 }
-                if (r == n_rounds - 1 && warp == W - 1 && a.g_h0 && ch_ok) {
+                if (r == n_rounds - 1 && warp == W - 1 && a.g_h0 && ch_ok && sg.lo == 0) {
                     a.g_h0[((size_t)b * 4 + 0) * d + ch] = nc;
                     a.g_h0[((size_t)b * 4 + 1) * d + ch] = nn;
                     a.g_h0[((size_t)b * 4 + 2) * d + ch] = nm;
                     a.g_h0[((size_t)b * 4 + 3) * d + ch] = nh;
                 }
             };
-            if (t_hi < a.T)
+            if (t_hi < sg.hi)
                 round_body(std::true_type{});
             else
                 round_body(std::false_type{});
@@ -432,6 +454,7 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
         for (int p = 0; p < 4; ++p) s_gp[(warp * 4 + p) * kLanes + lane] = gr[p];
     }
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
+    if (threadIdx.x == 0 && s_abort) drain_ring(full, NSTAGE, issued, kPipeWaitLimit);
     __syncthreads();
     if (warp == 0 && ch_ok) {
 #pragma unroll
@@ -439,7 +462,7 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
             float sum = 0.f;
 #pragma unroll
             for (int w2 = 0; w2 < W; ++w2) sum += s_gp[(w2 * 4 + p) * kLanes + lane];
-            a.gp_partial[((size_t)b * 4 + p) * d + ch] = sum;
+            a.gp_partial[(((size_t)sg.seg * a.B + b) * 4 + p) * d + ch] = sum;
         }
     }
 }
@@ -483,10 +506,13 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
     const int ch = cb * kLanes + lane;
     const bool ch_ok = ch < d;
     const int chl = ch_ok ? ch : d - 1;
-    const int n_rounds = (a.T + LT - 1) / LT;
-    const int row0 = b * a.T;
+    const SegRange sg = seg_range(a.T, a.n_seg, a.seg_len);
+    const int n_rounds = (sg.hi - sg.lo + LT - 1) / LT;
+    const int row0 = b * a.T + sg.lo;
+    __shared__ volatile int s_abort;
 
     if (threadIdx.x == 0) {
+        s_abort = 0;
         tma_prefetch_desc(&tm_wx);
         if (HAS_H) tma_prefetch_desc(&tm_h);
         for (int s = 0; s < NSTAGE; ++s) {
@@ -500,22 +526,27 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
 #pragma unroll
         for (int q = 0; q < 3; ++q)
             s_slot[q * kLanes + lane] =
-                a.carry_in ? __ldg(a.carry_in + (size_t)b * a.carry_stride + (size_t)q * d + chl) : 0.f;
+                a.carry_in ? __ldg(a.carry_in + ((size_t)sg.seg * a.B + b) * a.carry_stride + (size_t)q * d + chl)
+                           : 0.f;
     }
     __syncthreads();
     bool timed_out = false;
 
     if (warp == W) {
         if (lane == 0) {
+            int issued = 0;
             for (int r = 0; r < n_rounds; ++r) {
                 const int s = r % NSTAGE;
-                if (r >= NSTAGE && !mbar_wait_bounded(&empty[s], ((r / NSTAGE) - 1) & 1, kPipeWaitLimit))
+                if (r >= NSTAGE && !mbar_wait_abortable(&empty[s], ((r / NSTAGE) - 1) & 1, kPipeWaitLimit, &s_abort))
                     timed_out = true;
+                if (s_abort) break;
                 unsigned char* base = smem + s * S::STAGE;
                 mbar_expect_tx(&full[s], S::WX_BYTES + (HAS_H ? (LT + 1) * kLanes * 4 : 0));
                 tma_load_3d(base, &tm_wx, &full[s], cb * kLanes, 0, row0 + r * LT);
                 if (HAS_H) tma_load_3d(base + S::WX_BYTES, &tm_h, &full[s], cb * kLanes, 0, row0 + r * LT - 1);
+                issued = r + 1;
             }
+            if (s_abort) drain_ring(full, NSTAGE, issued, kPipeWaitLimit);
         }
     } else {
         float r4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -529,10 +560,10 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
 
         for (int r = 0; r < n_rounds; ++r) {
             const int s = r % NSTAGE;
-            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, kPipeWaitLimit)) timed_out = true;
+            if (!mbar_wait_abortable(&full[s], (r / NSTAGE) & 1, kPipeWaitLimit, &s_abort)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const float* t_h = reinterpret_cast<const float*>(smem + s * S::STAGE + S::WX_BYTES);
-            const int t0 = r * LT + warp * L;
+            const int t0 = sg.lo + r * LT + warp * L;
 
             // Rounds that lie fully inside the sequence take a variant without range checks.
             auto round_body = [&](auto full_c) {
@@ -564,7 +595,7 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
                 float dlt[L], ms[L];
     #pragma unroll
                 for (int i = 0; i < L; ++i) {
-                    if (FULL || t0 + i < a.T) {
+                    if (FULL || t0 + i < sg.hi) {
                         const float left = zf[i] + m;
                         dlt[i] = left - zi[i];
                         m = fmaxf(left, zi[i]);
@@ -582,13 +613,13 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
                 // (r-1)-th for warp 0
                 if (!(r == 0 && warp == 0)) {
                     const uint32_t par = (warp == 0 ? r - 1 : r) & 1;
-                    if (!mbar_wait_bounded(&cnbar[warp], par, kPipeWaitLimit)) timed_out = true;
+                    if (!mbar_wait_abortable(&cnbar[warp], par, kPipeWaitLimit, &s_abort)) timed_out = true;
                 }
                 float c = slot_in[0], n = slot_in[kLanes];
                 float cs[L], ns[L];
     #pragma unroll
                 for (int i = 0; i < L; ++i) {
-                    if (FULL || t0 + i < a.T) {
+                    if (FULL || t0 + i < sg.hi) {
                         const bool lw = dlt[i] >= 0.f;
                         const float ft = lw ? 1.f : e[i], it = lw ? e[i] : 1.f;
                         n = fmaf(ft, n, it);
@@ -607,7 +638,7 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
     #pragma unroll
                 for (int i = 0; i < L; ++i) {
                     const int t = t0 + i;
-                    if ((FULL || t < a.T) && ch_ok) {
+                    if ((FULL || t < sg.hi) && ch_ok) {
                         const float h = cs[i] * rcp_f(og[i] * (ns[i] + a.eps));
                         if (a.state_out) {
                             float* o = a.state_out + o_base * 4 + ch + (size_t)i * 4 * d;
@@ -620,13 +651,13 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
                         }
                     }
                 }
-                if (r == n_rounds - 1 && warp == W - 1 && a.tail_out && ch_ok) {
+                if (r == n_rounds - 1 && warp == W - 1 && a.tail_out && ch_ok && sg.hi == a.T) {
                     a.tail_out[((size_t)b * 3 + 0) * d + ch] = c;
                     a.tail_out[((size_t)b * 3 + 1) * d + ch] = n;
                     a.tail_out[((size_t)b * 3 + 2) * d + ch] = m;
                 }
             };
-            if (t0 + L <= a.T)
+            if (t0 + L <= sg.hi)
                 round_body(std::true_type{});
             else
                 round_body(std::false_type{});
@@ -646,7 +677,7 @@ static cudaError_t launch_newton_pipe_t(const SlstmNewtonArgs& a, bool last, cud
     if (!make_tile_map(&tm_wx, a.wx, sizeof(TIO), rows, 4, a.d, S::LT) ||
         !make_tile_map(&tm_st, a.sin, 4, rows, 4, a.d, S::LT + 1))
         return cudaErrorNotSupported;
-    const int grid = a.B * ((a.d + kLanes - 1) / kLanes);
+    const dim3 grid(a.B * ((a.d + kLanes - 1) / kLanes), a.n_seg > 1 ? a.n_seg : 1);
     if (last) {
         auto k = slstm_newton_pipe_kernel<TIO, kQL, kQW, NSTAGE, true>;
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
@@ -668,7 +699,7 @@ static cudaError_t launch_bwd_pipe_t(const SlstmBwdArgs& a, cudaStream_t s) {
         !make_tile_map(&tm_st, a.states, sizeof(TIO), rows, 4, a.d, S::LT + 1) ||
         !make_tile_map(&tm_g, a.grad_states, sizeof(TIO), rows, 4, a.d, S::LT))
         return cudaErrorNotSupported;
-    const int grid = a.B * ((a.d + kLanes - 1) / kLanes);
+    const dim3 grid(a.B * ((a.d + kLanes - 1) / kLanes), a.n_seg > 1 ? a.n_seg : 1);
     auto k = slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     k<<<grid, kQW * 32, S::TOTAL, s>>>(tm_wx, tm_st, tm_g, a);
@@ -687,7 +718,7 @@ static cudaError_t launch_picard_pipe_t(const SlstmPicardArgs& a, cudaStream_t s
     CUtensorMap tm_wx, tm_h;
     const uint64_t rows = (uint64_t)a.B * a.T;
     if (!make_tile_map(&tm_wx, a.wx, sizeof(TIO), rows, 4, a.d, S::LT)) return cudaErrorNotSupported;
-    const int grid = a.B * ((a.d + kLanes - 1) / kLanes);
+    const dim3 grid(a.B * ((a.d + kLanes - 1) / kLanes), a.n_seg > 1 ? a.n_seg : 1);
     if (a.h_prev) {
         if (!make_tile_map(&tm_h, a.h_prev, 4, rows, 1, a.d, S::LT + 1)) return cudaErrorNotSupported;
         auto k = slstm_picard_pipe_kernel<TIO, L, W, NSTAGE, true>;

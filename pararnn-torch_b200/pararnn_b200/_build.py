@@ -15,7 +15,6 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(os.path.dirname(HERE), "csrc")
 LIB = os.path.join(HERE, "libpararnn_b200.so")
 OBJ_DIR = os.path.join(CSRC, "build")
-SOURCES = ("capi.cu", "diag_kernels.cu", "slstm_kernels.cu")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

@@ -29,6 +29,7 @@ _FLOAT = ctypes.c_float
 _SIGNATURES = {
     "prb_version": (ctypes.c_char_p, []),
     "prb_error_string": (ctypes.c_char_p, [_INT]),
+    "prb_debug_set": (_INT, [_INT, ctypes.c_longlong]),
     "prb_newton_workspace_bytes": (_SIZE, [_INT] * 8),
     "prb_bwd_workspace_bytes": (_SIZE, [_INT] * 6),
     "prb_newton_gru_fused": (_INT, [_VOIDP] * 6 + [_INT] * 5 + [_FLOAT, _INT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
@@ -45,11 +46,14 @@ _SIGNATURES = {
     "prb_diag_guess": (_INT, [_INT] + [_VOIDP] * 4 + [_INT] * 4 + [_VOIDP]),
     "prb_diag_newton_pass": (_INT, [_INT] + [_VOIDP] * 8 + [_INT] * 5 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _INT, _VOIDP]),
     "prb_diag_bwd_pass": (_INT, [_INT] + [_VOIDP] * 10 + [_INT] * 5 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
-    "prb_slstm_picard_pass": (_INT, [_VOIDP] * 9 + [_INT] * 5 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
+    "prb_slstm_picard_pass": (_INT, [_VOIDP] * 9 + [_INT] * 7 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_slstm_picard_sweep": (_INT, [_VOIDP] * 6 + [_INT] * 5 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_slstm_newton_sweep": (_INT, [_VOIDP] * 5 + [_INT] * 6 + [_FLOAT, _FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
-    "prb_slstm_newton_pass": (_INT, [_VOIDP] * 8 + [_INT] * 5 + [_FLOAT, _FLOAT, _VOIDP, _SIZE, _VOIDP, _INT, _VOIDP]),
-    "prb_slstm_bwd_pass": (_INT, [_VOIDP] * 10 + [_INT] * 5 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
+    "prb_slstm_newton_pass": (_INT, [_VOIDP] * 8 + [_INT] * 7 + [_FLOAT, _FLOAT, _VOIDP, _SIZE, _VOIDP, _INT, _VOIDP]),
+    "prb_slstm_bwd_pass": (_INT, [_VOIDP] * 10 + [_INT] * 7 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
+    "prb_plan_segments": (_INT, [_INT] * 5 + [_VOIDP, _VOIDP]),
+    "prb_fold_segments": (_INT, [_INT, _VOIDP, _INT, _INT, _VOIDP, _INT, _INT, _VOIDP]),
+    "prb_segment_carries": (_INT, [_INT, _VOIDP, _INT, _INT, _VOIDP, _VOIDP, _INT, _INT, _VOIDP]),
     "prb_fold_carries": (_INT, [_INT, _VOIDP, _INT, _INT, _INT, _VOIDP, _INT, _INT, _VOIDP]),
     "prb_static_scratch_bytes": (_SIZE, []),
     "prb_bwd_nlru_static": (_INT, [_VOIDP] * 8 + [_INT] * 4 + [_VOIDP, _VOIDP]),
@@ -79,6 +83,25 @@ def lib() -> ctypes.CDLL:
             fn.argtypes = args
         _lib = handle
     return _lib
+
+
+OPTIONS = {"kernel_family": 0, "picard_fused": 1, "newton_fused": 2, "spin_limit": 3}
+KERNEL_FAMILY = {"auto": -1, "lookback": 0, "pipe": 2}
+_DEFAULTS = {"kernel_family": -1, "picard_fused": 1, "newton_fused": 1, "spin_limit": 0}
+
+
+def debug_set(option: str, value) -> None:
+    """Test / profiling hook (``prb_debug_set``): force a kernel family or a wait limit."""
+    if option == "kernel_family" and isinstance(value, str):
+        value = KERNEL_FAMILY[value]
+    rc = lib().prb_debug_set(OPTIONS[option], int(value))
+    if rc != 0:
+        raise ValueError(f"prb_debug_set({option}, {value}) failed: {error_string(rc)}")
+
+
+def debug_reset() -> None:
+    for name, value in _DEFAULTS.items():
+        debug_set(name, value)
 
 
 def error_string(code: int) -> str:

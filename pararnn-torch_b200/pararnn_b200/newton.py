@@ -162,6 +162,7 @@ def _forward_once(cell, kind, x, cfg, h0, stats, wx=None):
         states = _solve_window(cell, kind, wx, h0, cfg, ds, need_stats)
         if need_stats:
             hist, res, status = ds.read()
+            ops.check_pending_backward()
             _gate(cell, x, cfg, res, _emulated_iters(hist, cfg), hist, stats, status)
         return states, wx
     # windowed solve: the last state of a window is the next window's h0
@@ -176,6 +177,7 @@ def _forward_once(cell, kind, x, cfg, h0, stats, wx=None):
         carry = piece[:, -1]
     states = torch.cat(parts, dim=1)
     if need_stats:
+        ops.check_pending_backward()
         res, iters, status = 0.0, 0, 0
         for ds in blocks:
             hist, r, st = ds.read()

@@ -93,6 +93,37 @@ class DeviceStats:
         return tuple(hist[: self.max_iters]), final, status
 
 
+# Statistics blocks of reverse-scan calls whose status word nobody has looked at yet.  Reading one
+# costs a device-to-host copy, so the backward functions do not do it themselves: the next forward
+# that reads its own statistics checks them in the same breath (check_pending_backward).
+_pending_backward: list[DeviceStats] = []
+
+
+def _track_backward(sb: DeviceStats) -> None:
+    _pending_backward.append(sb)
+    if len(_pending_backward) > 64:
+        del _pending_backward[0]
+
+
+def check_pending_backward() -> None:
+    """Raise if a reverse scan issued since the last check ran into a bounded device-side wait
+    that gave up (its gradients are not valid).  One small device-to-host copy per device."""
+    if not _pending_backward:
+        return
+    pending, _pending_backward[:] = list(_pending_backward), []
+    by_dev: dict = {}
+    for sb in pending:
+        by_dev.setdefault(sb.buf.device, []).append(sb.buf)
+    for bufs in by_dev.values():
+        raw = torch.stack(bufs).cpu().numpy()
+        for row in raw:
+            status = struct.unpack("<i", row.tobytes()[4 * L.MAX_ITERS + 4: 4 * L.MAX_ITERS + 8])[0]
+            if status != 0:
+                raise RuntimeError(
+                    "pararnn_b200: a bounded device-side wait ran out during an earlier reverse scan "
+                    f"(status {status}); the gradients of that backward call are not valid")
+
+
 def _reject_packed(cu_seqlens, block_table) -> None:
     if cu_seqlens is not None:
         raise NotImplementedError("packed cu_seqlens batches are not covered by the CUDA backend yet")
@@ -262,6 +293,7 @@ def gru_reverse_vjp(states: Tensor, wx: Tensor, a_z: Tensor, a_r: Tensor, a_n: T
                              _ptr(g_h0), B, T, d, code, _ptr(ws), ws.numel(), _ptr(sb.buf),
                              _stream(dev))
     _raise(rc, "gru_reverse_vjp")
+    _track_backward(sb)
     return g_wx, g_par[0], g_par[1], g_par[2], g_h0
 
 
@@ -285,6 +317,7 @@ def nlru_reverse_vjp(states: Tensor, wx: Tensor, u: Tensor, grad_states: Tensor,
                               _ptr(g_wx), _ptr(g_par), _ptr(g_h0), B, T, d, code, _ptr(ws),
                               ws.numel(), _ptr(sb.buf), _stream(dev))
     _raise(rc, "nlru_reverse_vjp")
+    _track_backward(sb)
     return g_wx, g_par[0], g_h0
 
 
@@ -309,6 +342,7 @@ def slstm_reverse_vjp(states: Tensor, wx: Tensor, r: Tensor, grad_states: Tensor
                                _ptr(g_wx), _ptr(g_par), _ptr(g_h0), B, T, d, code, float(eps),
                                _ptr(ws), ws.numel(), _ptr(sb.buf), _stream(dev))
     _raise(rc, "slstm_reverse_vjp")
+    _track_backward(sb)
     return g_wx, g_par, g_h0
 
 

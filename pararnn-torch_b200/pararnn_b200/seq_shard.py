@@ -9,7 +9,11 @@ is sharded, trajectories stay sharded, and one pass costs one small all-gather:
 * the first rank in scan direction knows the carry entering its shard and sweeps once;
 * every other rank first runs an aggregate-only sweep (mode 2 of the pass-level C ABI) that
   yields the affine map of its whole shard, the maps are all-gathered, ``prb_fold_carries`` turns
-  them into the carry entering the rank, and a second sweep applies it.
+  them into the carry entering the rank, and a second sweep applies it;
+* when a rank has fewer (batch row, channel block) chains than its GPU has SMs, its shard is cut
+  further into time segments that different thread blocks sweep at the same time (ParaSLSTM
+  passes): the same aggregate / carry / apply scheme one level down, folded on the device by
+  ``prb_fold_segments`` and ``prb_segment_carries`` with no further collective.
 
 The per-rank algorithm is written as a generator that yields its collectives.  ``DistComm``
 fulfils them with ``torch.distributed`` (one process per GPU); ``run_lockstep`` fulfils them for
@@ -150,7 +154,8 @@ class ShardResult:
 class CudaShardOps:
     """Local scan passes of one rank on its GPU, through the pass-level C ABI."""
 
-    def __init__(self, kind: str, wx: Tensor, rec: tuple[Tensor, ...], eps: float, omega: float):
+    def __init__(self, kind: str, wx: Tensor, rec: tuple[Tensor, ...], eps: float, omega: float,
+                 segments: int | None = None):
         from . import _lib as L
         from . import ops
 
@@ -170,6 +175,19 @@ class CudaShardOps:
         self.ws = torch.empty(max(n, 256), dtype=torch.uint8, device=self.dev)
         self.stats = ops.DeviceStats(self.dev, L.MAX_ITERS)
         self.monoid = "affine4" if kind == "slstm_diag" else "affine1"
+        # time segments inside this rank's shard: the library's plan, or `segments` pieces (tests)
+        self.n_seg, self.seg_len = 1, int(self.T)
+        if kind == "slstm_diag":
+            if segments is None:
+                n, ln = ctypes.c_int(1), ctypes.c_int(int(self.T))
+                with torch.cuda.device(self.dev):
+                    rc = self.lib.prb_plan_segments(self.cell, self.code, self.B, self.T, self.d,
+                                                    ctypes.byref(n), ctypes.byref(ln))
+                self._check(rc, "plan_segments")
+                self.n_seg, self.seg_len = n.value, ln.value
+            elif segments > 1 and self.T >= 2:
+                ln = -(-int(self.T) // int(segments))
+                self.n_seg, self.seg_len = -(-int(self.T) // ln), ln
 
     # helpers
     def _p(self, t):
@@ -189,6 +207,25 @@ class CudaShardOps:
         shape = (self.B, self.T, 4, self.d) if self.slots == 4 else (self.B, self.T, self.d)
         return torch.empty(shape, dtype=self.wx.dtype, device=self.dev)
 
+    def fold_segments(self, monoid: str, agg: Tensor, reverse: bool) -> Tensor:
+        """Map of the whole shard from its segment maps ``(n_seg, B, NV, d)``."""
+        out = torch.empty(self.B, NV[monoid], self.d, dtype=torch.float32, device=self.dev)
+        with torch.cuda.device(self.dev):
+            rc = self.lib.prb_fold_segments(MONOID[monoid], self._p(agg), agg.shape[0], int(reverse),
+                                            self._p(out), self.B, self.d, self._stream())
+        self._check(rc, "fold_segments")
+        return out
+
+    def segment_carries(self, monoid: str, agg: Tensor, reverse: bool, carry0: Tensor | None) -> Tensor:
+        """``(n_seg + 1, B, NS, d)``: the carry entering every segment, then the one leaving the shard."""
+        n = agg.shape[0]
+        out = torch.empty(n + 1, self.B, NS[monoid], self.d, dtype=torch.float32, device=self.dev)
+        with torch.cuda.device(self.dev):
+            rc = self.lib.prb_segment_carries(MONOID[monoid], self._p(agg), n, int(reverse), self._p(carry0),
+                                              self._p(out), self.B, self.d, self._stream())
+        self._check(rc, "segment_carries")
+        return out
+
     def fold(self, monoid: str, gathered: Tensor, rank: int, world: int, reverse: bool) -> Tensor:
         out = torch.empty(self.B, NS[monoid], self.d, dtype=torch.float32, device=self.dev)
         with torch.cuda.device(self.dev):
@@ -206,16 +243,21 @@ class CudaShardOps:
         return out
 
     def newton_pass(self, traj, halo, carry, mode, out, hist_slot):
-        """mode 0/1: returns the carry leaving the shard; mode 2: returns the shard aggregate."""
+        """mode 0/1: applies ``carry`` (per segment: ``(n_seg, B, NS, d)``) and returns the carry
+        leaving the shard; mode 2: returns the segment aggregates ``(n_seg, B, NV, d)``."""
         nv, ns = NV[self.monoid], NS[self.monoid]
-        res = torch.empty(self.B, nv if mode == 2 else ns, self.d, dtype=torch.float32, device=self.dev)
+        if mode == 2:
+            res = torch.empty(self.n_seg, self.B, nv, self.d, dtype=torch.float32, device=self.dev)
+        else:
+            res = torch.empty(self.B, ns, self.d, dtype=torch.float32, device=self.dev)
         tail = None if mode == 2 else res
         agg = res if mode == 2 else None
         with torch.cuda.device(self.dev):
             if self.kind == "slstm_diag":
                 rc = self.lib.prb_slstm_newton_pass(
                     self._p(self.wx), self._p(self.par), self._p(traj), self._p(halo), self._p(carry),
-                    self._p(out), self._p(tail), self._p(agg), mode, self.B, self.T, self.d, self.code,
+                    self._p(out), self._p(tail), self._p(agg), mode, self.n_seg, self.seg_len, self.B,
+                    self.T, self.d, self.code,
                     self.omega, self.eps, self._p(self.ws), self.ws.numel(), self._p(self.stats.buf),
                     hist_slot, self._stream())
             else:
@@ -228,12 +270,16 @@ class CudaShardOps:
         return res
 
     def picard_pass(self, h_prev, h_halo, carry, mode, h_out, state_out):
-        res = torch.empty(self.B, 4 if mode == 2 else 3, self.d, dtype=torch.float32, device=self.dev)
+        if mode == 2:
+            res = torch.empty(self.n_seg, self.B, 4, self.d, dtype=torch.float32, device=self.dev)
+        else:
+            res = torch.empty(self.B, 3, self.d, dtype=torch.float32, device=self.dev)
         with torch.cuda.device(self.dev):
             rc = self.lib.prb_slstm_picard_pass(
                 self._p(self.wx), self._p(self.par), self._p(h_prev), self._p(h_halo), self._p(carry),
                 self._p(h_out), self._p(state_out), self._p(None if mode == 2 else res),
-                self._p(res if mode == 2 else None), mode, self.B, self.T, self.d, self.code, self.eps,
+                self._p(res if mode == 2 else None), mode, self.n_seg, self.seg_len, self.B, self.T, self.d,
+                self.code, self.eps,
                 self._p(self.ws), self.ws.numel(), self._p(self.stats.buf), self._stream())
         self._check(rc, "picard_pass")
         return res
@@ -245,7 +291,7 @@ class CudaShardOps:
         st = states.to(self.wx.dtype).contiguous()
         gs = grad_states.to(self.wx.dtype).contiguous()
         if mode == 2:
-            agg = torch.empty(self.B, nv, self.d, dtype=torch.float32, device=self.dev)
+            agg = torch.empty(self.n_seg, self.B, nv, self.d, dtype=torch.float32, device=self.dev)
             g_wx = g_par = head = None
         else:
             agg = None
@@ -256,9 +302,9 @@ class CudaShardOps:
             if self.kind == "slstm_diag":
                 rc = self.lib.prb_slstm_bwd_pass(
                     self._p(st), self._p(self.wx), self._p(self.par), self._p(halo), self._p(carry),
-                    self._p(gs), self._p(g_wx), self._p(g_par), self._p(head), self._p(agg), mode, self.B,
-                    self.T, self.d, self.code, self.eps, self._p(self.ws), self.ws.numel(),
-                    self._p(self.stats.buf), self._stream())
+                    self._p(gs), self._p(g_wx), self._p(g_par), self._p(head), self._p(agg), mode, self.n_seg,
+                    self.seg_len, self.B, self.T, self.d, self.code, self.eps, self._p(self.ws),
+                    self.ws.numel(), self._p(self.stats.buf), self._stream())
             else:
                 rc = self.lib.prb_diag_bwd_pass(
                     self.cell, self._p(st), self._p(self.wx), self._p(self.par), self._p(halo),
@@ -283,22 +329,36 @@ def _pad(t: Tensor, nv: int) -> Tensor:
     return out
 
 
-def _sharded_scan(ops, rank, world, reverse, monoid, boundary, sweep):
-    """One sharded scan pass.  ``sweep(mode, carry)`` runs the local kernel: mode 2 returns the
-    shard aggregate, otherwise it applies ``carry`` and returns the carry leaving the shard.
-    Yields one gather; returns ``(carry entering this rank, carry leaving it)``."""
+def _sharded_scan(ops, rank, world, reverse, monoid, boundary, sweep, extra=None):
+    """One sharded scan pass.  ``sweep(True, None)`` returns the aggregates of the rank's time
+    segments ``(n_seg, B, NV, d)``; ``sweep(False, carries)`` applies the carries entering the
+    segments ``(n_seg, B, NS, d)`` (None = zeros) and returns the carry leaving the shard.
+    ``extra`` (B, E, d) rides along in the rank's gather slot.  Yields at most one gather; returns
+    ``(carry entering this rank, carry leaving it, gathered slots or None)``."""
     first = world - 1 if reverse else 0
-    if world == 1:
-        return boundary, sweep(False, boundary)
+    n_seg = getattr(ops, "n_seg", 1)
+    nv = NV[monoid]
+    gathered = None
     if rank == first:
-        leaving = sweep(False, boundary)
-        gathered = yield ("gather", _pad(leaving, NV[monoid]))
-        return boundary, leaving
+        if n_seg == 1:
+            leaving = sweep(False, boundary)
+        else:
+            agg = sweep(True, None)
+            carries = ops.segment_carries(monoid, agg, reverse, boundary)
+            sweep(False, carries)
+            leaving = carries[n_seg]
+        if world > 1:
+            slot = _pad(leaving, nv)
+            gathered = yield ("gather", slot if extra is None else torch.cat([slot, extra], dim=1))
+        return boundary, leaving, gathered
     agg = sweep(True, None)
-    gathered = yield ("gather", agg)
-    carry = ops.fold(monoid, gathered, rank, world, reverse)
-    leaving = sweep(False, carry)
-    return carry, leaving
+    slot = agg[0] if n_seg == 1 else ops.fold_segments(monoid, agg, reverse)
+    gathered = yield ("gather", slot if extra is None else torch.cat([slot, extra], dim=1))
+    maps = gathered if extra is None else gathered[:, :, :nv].contiguous()
+    carry = ops.fold(monoid, maps, rank, world, reverse)
+    carries = carry if n_seg == 1 else ops.segment_carries(monoid, agg, reverse, carry)
+    leaving = sweep(False, carries)
+    return carry, leaving, gathered
 
 
 def forward_program(ops, rank: int, world: int, K: int, P: int, h0: Tensor | None):
@@ -336,25 +396,20 @@ def forward_program(ops, rank: int, world: int, K: int, P: int, h0: Tensor | Non
                 zo_last = wx_o_last + r_o * h_prev[:, -2]
             else:
                 zo_last = wx_o_last + r_o * (h_halo if h_halo is not None else 0.0)
-            carry = carry0
-            if world > 1:
-                if rank == 0:
-                    leaving = ops.picard_pass(h_prev, h_halo, carry0, 0, h_out, state_out)
-                    slot = torch.cat([leaving, leaving.new_zeros(B, 1, d), zo_last[:, None]], dim=1)
-                    gathered = yield ("gather", slot)
-                else:
-                    agg = ops.picard_pass(h_prev, h_halo, None, 2, None, None)
-                    gathered = yield ("gather", torch.cat([agg, zo_last[:, None]], dim=1))
-                    carry = ops.fold("picard", gathered[:, :, :4].contiguous(), rank, world, False)
-                    ops.picard_pass(h_prev, h_halo, carry, 0, h_out, state_out)
-                    # hidden state at the previous rank's last step under the new trajectory
-                    zo_prev = gathered[rank - 1][:, 4]
-                    h_end = torch.sigmoid(zo_prev) * carry[:, 0] / (carry[:, 1] + ops.eps)
-                    h_halo = h_end
-                    if last:
-                        halo = torch.cat([carry, h_end[:, None]], dim=1)
-            else:
-                ops.picard_pass(h_prev, h_halo, carry0, 0, h_out, state_out)
+            def sweep(agg_only, carry, h_prev=h_prev, h_halo=h_halo, h_out=h_out, state_out=state_out):
+                if agg_only:
+                    return ops.picard_pass(h_prev, h_halo, None, 2, None, None)
+                return ops.picard_pass(h_prev, h_halo, carry, 0, h_out, state_out)
+
+            carry, _, gathered = yield from _sharded_scan(ops, rank, world, False, "picard", carry0, sweep,
+                                                          extra=zo_last[:, None] if world > 1 else None)
+            if rank > 0:
+                # hidden state at the previous rank's last step under the new trajectory
+                zo_prev = gathered[rank - 1][:, 4]
+                h_end = torch.sigmoid(zo_prev) * carry[:, 0] / (carry[:, 1] + ops.eps)
+                h_halo = h_end
+                if last:
+                    halo = torch.cat([carry, h_end[:, None]], dim=1)
             h_prev = h_out
             traj = state_out
         if rank == 0:
@@ -377,7 +432,7 @@ def forward_program(ops, rank: int, world: int, K: int, P: int, h0: Tensor | Non
         def sweep(agg_only, carry, traj=traj, halo=halo, dst=dst, last=last, k=k):
             return ops.newton_pass(traj, halo, carry, 2 if agg_only else (1 if last else 0), dst, k)
 
-        carry, _ = yield from _sharded_scan(ops, rank, world, False, ops.monoid, None, sweep)
+        carry, _, _ = yield from _sharded_scan(ops, rank, world, False, ops.monoid, None, sweep)
         if rank > 0 and carry is not None:
             # the carry entering the shard is the update of the previous rank's last step
             c = carry if ops.slots == 4 else carry[:, 0]
@@ -539,7 +594,7 @@ class _Ctx:
 
 def emulate_sharded(kind: str, wx: Tensor, rec, *, world: int, K: int, P: int = 0, h0=None,
                     eps: float = 1e-6, omega: float = 1.0, grad_states: Tensor | None = None,
-                    ops_factory=None, bounds=None):
+                    ops_factory=None, bounds=None, segments=None):
     """Run the time-sharded programs of ``world`` virtual ranks in one process on one device
     (shards of ``wx`` along time per ``time_shard_bounds``, or the contiguous ``bounds`` given:
     shards need not have equal lengths).  Returns the concatenated states, the statistics bits and,
@@ -551,7 +606,8 @@ def emulate_sharded(kind: str, wx: Tensor, rec, *, world: int, K: int, P: int = 
     if len(bounds) != world or bounds[0][0] != 0 or bounds[-1][1] != T or any(
             bounds[i][1] != bounds[i + 1][0] for i in range(world - 1)):
         raise ValueError(f"bounds must be {world} contiguous [start, end) pairs covering [0, {T})")
-    ops = [factory(kind, wx[:, s:e].contiguous(), rec, eps, omega) for s, e in bounds]
+    extra = {} if segments is None else {"segments": segments}
+    ops = [factory(kind, wx[:, s:e].contiguous(), rec, eps, omega, **extra) for s, e in bounds]
     res = run_lockstep([forward_program(ops[r], r, world, K, P, _h0_f32(h0)) for r in range(world)])
     states = torch.cat([r.states for r in res], dim=1)
     out = [states, res[0].stats_bits]

@@ -33,3 +33,13 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture
+def prb_options():
+    """Setter for the library's test hook (``prb_debug_set``); every option is restored to its
+    default after the test."""
+    from pararnn_b200 import _lib
+
+    yield _lib.debug_set
+    _lib.debug_reset()

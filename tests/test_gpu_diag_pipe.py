@@ -1,5 +1,5 @@
 """The GRU-diag / NLRU parity tests once more, forced onto the pipelined persistent kernels
-(PRB_KERNEL_PATH=pipe), plus shapes chosen for that family: channel counts TMA can address
+(kernel family forced through prb_debug_set), plus shapes chosen for that family: channel counts TMA can address
 (d a multiple of 4 in fp32, of 8 in bf16), sequence lengths around the 64-step round, a ragged
 last channel block.  Shapes TMA cannot address fall back to the look-back kernels."""
 
@@ -14,8 +14,8 @@ from test_gpu_diag import _bwd, _fwd, pytestmark  # noqa: F401
 
 
 @pytest.fixture(autouse=True)
-def _force_pipelined_kernels(monkeypatch):
-    monkeypatch.setenv("PRB_KERNEL_PATH", "pipe")
+def _force_pipelined_kernels(prb_options):
+    prb_options("kernel_family", "pipe")
 
 
 PIPE_SHAPES = [(1, 1, 32), (2, 63, 64), (1, 64, 40), (3, 65, 96), (2, 128, 36), (1, 1000, 64), (4, 4097, 72)]
@@ -49,11 +49,11 @@ def test_pipe_backward_vs_oracle_fp32(kind, B, T, d):
 
 
 @pytest.mark.parametrize("kind", ["gru_diag", "nlru"])
-def test_pipe_bf16_matches_lookback_family(kind, monkeypatch):
+def test_pipe_bf16_matches_lookback_family(kind, prb_options):
     """Two independent implementations on the same bf16 problem."""
     wx, params, h0 = make_problem(kind, 2, 777, 64, seed=9, h0=True)
     wx, params, h0 = bf16_round(wx), bf16_round(params), bf16_round(h0)
     a, _, _ = _fwd(kind, wx, params, h0, 2, dtype=torch.bfloat16)
-    monkeypatch.setenv("PRB_KERNEL_PATH", "lookback")
+    prb_options("kernel_family", "lookback")
     b, _, _ = _fwd(kind, wx, params, h0, 2, dtype=torch.bfloat16)
     assert rel_err(a, b) <= 1e-2

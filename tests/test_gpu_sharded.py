@@ -19,11 +19,11 @@ def _rec(kind, params):
 
 @pytest.mark.parametrize("kind,K,P", [("gru_diag", 3, 0), ("nlru", 2, 0), ("slstm_diag", 2, 3)])
 @pytest.mark.parametrize("world,T", [(2, 257), (3, 100), (4, 1024)])
-@pytest.mark.parametrize("path", ["lookback", "persist"])
-def test_sharded_matches_oracle(kind, K, P, world, T, path, monkeypatch):
+@pytest.mark.parametrize("path", ["lookback", "pipe"])
+def test_sharded_matches_oracle(kind, K, P, world, T, path, prb_options):
     from pararnn_b200.seq_shard import _bits_to_stats, emulate_sharded
 
-    monkeypatch.setenv("PRB_KERNEL_PATH", path)
+    prb_options("kernel_family", path)
     B, d = 2, 40
     wx, params, h0 = make_problem(kind, B, T, d, seed=T + world, h0=True, x_scale=0.6, bias_f=1.0)
     want = oracle.newton(oracle.KIND[kind], wx, params, h0, max_iters=K, picard=P)
@@ -58,12 +58,12 @@ def test_sharded_equals_unsharded_bf16():
 
 
 @pytest.mark.parametrize("kind,K,P", [("slstm_diag", 2, 3), ("gru_diag", 3, 0), ("nlru", 2, 0)])
-def test_unequal_shards_match_oracle(kind, K, P, monkeypatch):
+def test_unequal_shards_match_oracle(kind, K, P, prb_options):
     """The first rank sweeps once per pass, the others twice, so a balanced split gives the first
     rank a longer shard; the programs make no assumption on shard lengths."""
     from pararnn_b200.seq_shard import _bits_to_stats, emulate_sharded
 
-    monkeypatch.setenv("PRB_KERNEL_PATH", "pipe")
+    prb_options("kernel_family", "pipe")
     B, T, d = 2, 1000, 64
     bounds = [(0, 470), (470, 730), (730, 731), (731, 1000)]
     wx, params, h0 = make_problem(kind, B, T, d, seed=17, h0=True, x_scale=0.6, bias_f=1.0)
@@ -78,3 +78,52 @@ def test_unequal_shards_match_oracle(kind, K, P, monkeypatch):
     want_g = oracle.backward(oracle.KIND[kind], states.cpu().numpy(), wx, params, G, h0)
     assert rel_err(grads[0].cpu().numpy(), want_g[0]) <= 5e-5
     assert rel_err(grads[1].cpu().numpy().reshape(-1), np.asarray(want_g[1]).reshape(-1)) <= 1e-4
+
+
+@pytest.mark.parametrize("world,segments,T", [(1, 3, 1000), (2, 2, 777), (3, 5, 2050), (2, 4, 131)])
+def test_time_segments_match_oracle(world, segments, T, prb_options):
+    """ParaSLSTM passes with the shard of every rank cut into time segments that are swept by
+    different thread blocks (aggregate sweep, device-side fold, apply sweep with per-segment
+    carries): same result as the oracle's unsharded solve, forward and backward."""
+    from pararnn_b200.seq_shard import _bits_to_stats, emulate_sharded
+
+    prb_options("kernel_family", "pipe")
+    B, d, K, P = 2, 64, 2, 3
+    wx, params, h0 = make_problem("slstm_diag", B, T, d, seed=T + segments, h0=True, x_scale=0.6, bias_f=1.0)
+    want = oracle.newton(oracle.SLSTM_DIAG, wx, params, h0, max_iters=K, picard=P)
+    G = np.random.default_rng(4).standard_normal(want.states.shape).astype(np.float32)
+    states, bits, grads = emulate_sharded("slstm_diag", dev(wx), (dev(params),), world=world, K=K, P=P,
+                                          h0=dev(h0), grad_states=dev(G), segments=segments)
+    amp = max(1.0, max(want.history))
+    scale = max(1.0, float(np.abs(want.states).max()))
+    assert np.abs(states.cpu().numpy() - want.states).max() <= 1e-5 * amp * scale
+    hist, final, status = _bits_to_stats(bits, K)
+    assert status == 0
+    np.testing.assert_allclose(np.asarray(hist), np.asarray(want.history), rtol=2e-2, atol=4e-6 * scale)
+    want_g = oracle.backward(oracle.SLSTM_DIAG, states.cpu().numpy(), wx, params, G, h0)
+    assert rel_err(grads[0].cpu().numpy(), want_g[0]) <= 5e-5
+    assert rel_err(grads[1].cpu().numpy().reshape(-1), np.asarray(want_g[1]).reshape(-1)) <= 1e-4
+    assert rel_err(grads[2].cpu().numpy().reshape(want_g[2].shape), want_g[2]) <= 5e-5
+
+
+def test_segment_plan_and_argument_checks():
+    import ctypes
+
+    from pararnn_b200 import _lib
+
+    lib = _lib.lib()
+    n, ln = ctypes.c_int(0), ctypes.c_int(0)
+    # few chains, long shard: several segments that tile T exactly once
+    assert lib.prb_plan_segments(_lib.CELL_SLSTM_DIAG, _lib.PRB_BF16, 1, 16384, 2048, ctypes.byref(n),
+                                 ctypes.byref(ln)) == 0
+    assert n.value > 1 and (n.value - 1) * ln.value < 16384 <= n.value * ln.value
+    # enough chains to fill the GPU: one segment
+    assert lib.prb_plan_segments(_lib.CELL_SLSTM_DIAG, _lib.PRB_BF16, 8, 16384, 2048, ctypes.byref(n),
+                                 ctypes.byref(ln)) == 0
+    assert (n.value, ln.value) == (1, 16384)
+    # a segment layout that does not cover T is refused before anything is launched
+    one = torch.zeros(64, device="cuda")
+    p = ctypes.c_void_p(one.data_ptr())
+    rc = lib.prb_slstm_newton_pass(p, p, p, None, None, p, None, None, 0, 3, 100, 1, 1000, 32, _lib.PRB_F32, 1.0,
+                                   1e-6, p, 256, p, 0, None)
+    assert rc == -1

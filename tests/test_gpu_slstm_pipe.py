@@ -1,5 +1,5 @@
 """The sLSTM parity tests once more, forced onto the warp-pipelined persistent kernels
-(PRB_KERNEL_PATH=pipe); passes that have no pipelined variant fall back to the other families."""
+(kernel family forced through prb_debug_set); passes that have no pipelined variant fall back to the other families."""
 
 import pytest
 
@@ -8,8 +8,8 @@ from test_gpu_slstm import pytestmark  # noqa: F401
 
 
 @pytest.fixture(autouse=True)
-def _force_pipelined_kernels(monkeypatch):
-    monkeypatch.setenv("PRB_KERNEL_PATH", "pipe")
+def _force_pipelined_kernels(prb_options):
+    prb_options("kernel_family", "pipe")
 
 
 # ---- the fused sweep (all Picard passes in one launch) against the per-pass kernels
@@ -22,7 +22,7 @@ from gpu_util import dev, make_problem  # noqa: E402
 @pytest.mark.parametrize("P", [0, 1, 3, 5])
 @pytest.mark.parametrize("B,T,d,h0", [(1, 1, 32, False), (2, 57, 64, True), (2, 1000, 96, True),
                                       (1, 4099, 40, False)])
-def test_fused_picard_sweep_equals_separate_passes(P, B, T, d, h0, monkeypatch):
+def test_fused_picard_sweep_equals_separate_passes(P, B, T, d, h0, prb_options):
     from pararnn_b200 import ops
 
     wx, r, h0a = make_problem("slstm_diag", B, T, d, seed=P + T, h0=h0, x_scale=0.7, bias_f=2.0, rec_scale=2.0)
@@ -32,7 +32,7 @@ def test_fused_picard_sweep_equals_separate_passes(P, B, T, d, h0, monkeypatch):
                                       want_residual=False).float().cpu().numpy()
 
     fused = guess()
-    monkeypatch.setenv("PRB_PICARD_FUSED", "0")
+    prb_options("picard_fused", 0)
     separate = guess()
     for slot in range(4):
         scale = max(1.0, float(np.abs(separate[:, :, slot]).max()))
@@ -57,7 +57,7 @@ def test_seven_passes_fall_back_to_separate_kernels():
 @pytest.mark.parametrize("K", [1, 2, 3, 4, 5])
 @pytest.mark.parametrize("B,T,d,h0", [(1, 1, 32, False), (2, 57, 64, True), (2, 1000, 96, True),
                                       (1, 4099, 40, False)])
-def test_fused_newton_sweep_equals_separate_passes(K, B, T, d, h0, monkeypatch):
+def test_fused_newton_sweep_equals_separate_passes(K, B, T, d, h0, prb_options):
     """K = 5 exceeds what one sweep takes and runs the separate passes in both cases."""
     from pararnn_b200 import ops
 
@@ -71,7 +71,7 @@ def test_fused_newton_sweep_equals_separate_passes(K, B, T, d, h0, monkeypatch):
         return H.float().cpu().numpy(), np.asarray(hist), res
 
     fused, hist_f, res_f = solve()
-    monkeypatch.setenv("PRB_NEWTON_FUSED", "0")
+    prb_options("newton_fused", 0)
     separate, hist_s, res_s = solve()
     amp = max(1.0, float(hist_s.max()))
     for slot in range(4):
@@ -82,7 +82,7 @@ def test_fused_newton_sweep_equals_separate_passes(K, B, T, d, h0, monkeypatch):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_fused_sweeps_with_damping_eps_and_h0(dtype, monkeypatch):
+def test_fused_sweeps_with_damping_eps_and_h0(dtype, prb_options):
     """omega != 1, a non-default eps, a start state and both I/O dtypes through the fused sweeps,
     against the separate passes (fp32: also against the oracle)."""
     from gpu_util import bf16_round
@@ -102,8 +102,8 @@ def test_fused_sweeps_with_damping_eps_and_h0(dtype, monkeypatch):
         return H.float().cpu().numpy(), np.asarray(hist), res
 
     fused, hist_f, res_f = solve()
-    monkeypatch.setenv("PRB_NEWTON_FUSED", "0")
-    monkeypatch.setenv("PRB_PICARD_FUSED", "0")
+    prb_options("newton_fused", 0)
+    prb_options("picard_fused", 0)
     separate, hist_s, res_s = solve()
     tol = 2e-6 if dtype == torch.float32 else 1e-2
     for slot in range(4):
