@@ -87,10 +87,8 @@ diag_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_
     const int chl = ch_ok ? ch : d - 1;
     const int n_rounds = (a.T + LT - 1) / LT;
     const int row0 = b * a.T;
-    __shared__ volatile int s_abort;
 
     if (threadIdx.x == 0) {
-        s_abort = 0;
         tma_prefetch_desc(&tm_wx);
         if (!FIRST) tma_prefetch_desc(&tm_h);
         for (int s = 0; s < NSTAGE; ++s) {
@@ -107,19 +105,16 @@ diag_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_
     if (warp == W) {
         // ---------------- producer warp: one lane streams the rounds into the ring
         if (lane == 0) {
-            int issued = 0;
             for (int r = 0; r < n_rounds; ++r) {
                 const int s = r % NSTAGE;
-                if (r >= NSTAGE && !mbar_wait_abortable(&empty[s], ((r / NSTAGE) - 1) & 1, kDiagPipeWaitLimit, &s_abort))
+                if (r >= NSTAGE && !mbar_wait_bounded(&empty[s], ((r / NSTAGE) - 1) & 1, timed_out ? kWaitLimitAfterTimeout : kDiagPipeWaitLimit))
                     timed_out = true;
-                if (s_abort) break;
                 unsigned char* base = smem + s * S::STAGE;
                 mbar_expect_tx(&full[s], FIRST ? S::WX_TX : S::WX_TX + S::H_TX);
                 tma_load_3d(base, &tm_wx, &full[s], cb * kLanes, 0, row0 + r * LT - 1);
                 if (!FIRST) tma_load_3d(base + S::WX_BYTES, &tm_h, &full[s], cb * kLanes, 0, row0 + r * LT - 1);
-                issued = r + 1;
             }
-            if (s_abort) drain_ring(full, NSTAGE, issued, kDiagPipeWaitLimit);
+            if (timed_out) drain_ring(full, NSTAGE, n_rounds, kDrainLimit);
         }
     } else {
         // ---------------- compute warps
@@ -132,7 +127,7 @@ diag_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_
 
         for (int r = 0; r < n_rounds; ++r) {
             const int s = r % NSTAGE;
-            if (!mbar_wait_abortable(&full[s], (r / NSTAGE) & 1, kDiagPipeWaitLimit, &s_abort)) timed_out = true;
+            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kDiagPipeWaitLimit)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const float* t_h = reinterpret_cast<const float*>(smem + s * S::STAGE + S::WX_BYTES);
             const int t0 = r * LT + warp * L;
@@ -285,10 +280,8 @@ diag_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
     const int chl = ch_ok ? ch : d - 1;
     const int n_rounds = (a.T + LT - 1) / LT;
     const int row0 = b * a.T;
-    __shared__ volatile int s_abort;
 
     if (threadIdx.x == 0) {
-        s_abort = 0;
         tma_prefetch_desc(&tm_wx);
         tma_prefetch_desc(&tm_st);
         tma_prefetch_desc(&tm_g);
@@ -306,22 +299,19 @@ diag_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
 
     if (warp == W) {
         if (lane == 0) {
-            int issued = 0;
             for (int r = 0; r < n_rounds; ++r) {
                 const int s = r % NSTAGE;
                 const int tile_t = n_rounds - 1 - r;
-                if (r >= NSTAGE && !mbar_wait_abortable(&empty[s], ((r / NSTAGE) - 1) & 1, kDiagPipeWaitLimit, &s_abort))
+                if (r >= NSTAGE && !mbar_wait_bounded(&empty[s], ((r / NSTAGE) - 1) & 1, timed_out ? kWaitLimitAfterTimeout : kDiagPipeWaitLimit))
                     timed_out = true;
-                if (s_abort) break;
                 unsigned char* base = smem + s * S::STAGE;
                 mbar_expect_tx(&full[s], S::WX_TX + S::ST_TX + S::G_TX);
                 tma_load_3d(base, &tm_wx, &full[s], cb * kLanes, 0, row0 + tile_t * LT);
                 tma_load_3d(base + S::WX_BYTES, &tm_st, &full[s], cb * kLanes, 0, row0 + tile_t * LT - 1);
                 tma_load_3d(base + S::WX_BYTES + S::ST_BYTES, &tm_g, &full[s], cb * kLanes, 0,
                             row0 + tile_t * LT);
-                issued = r + 1;
             }
-            if (s_abort) drain_ring(full, NSTAGE, issued, kDiagPipeWaitLimit);
+            if (timed_out) drain_ring(full, NSTAGE, n_rounds, kDrainLimit);
         }
     } else {
         float par[NP];
@@ -334,7 +324,7 @@ diag_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
         for (int r = 0; r < n_rounds; ++r) {
             const int s = r % NSTAGE;
             const int tile_t = n_rounds - 1 - r;
-            if (!mbar_wait_abortable(&full[s], (r / NSTAGE) & 1, kDiagPipeWaitLimit, &s_abort)) timed_out = true;
+            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kDiagPipeWaitLimit)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const TIO* t_st = reinterpret_cast<const TIO*>(smem + s * S::STAGE + S::WX_BYTES);
             const TIO* t_g = reinterpret_cast<const TIO*>(smem + s * S::STAGE + S::WX_BYTES + S::ST_BYTES);

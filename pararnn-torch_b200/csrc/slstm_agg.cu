@@ -69,8 +69,9 @@ struct WarpRing {
         __syncwarp();
     }
     __device__ __forceinline__ unsigned char* stage(int k) const { return base + (k % NST) * stage_bytes; }
-    __device__ __forceinline__ bool wait(int k, volatile int* abort_word) const {
-        return mbar_wait_abortable(&bars[k % NST], (k / NST) & 1, kAggWaitLimit, abort_word);
+    __device__ __forceinline__ bool wait(int k, bool timed_out) const {
+        return mbar_wait_bounded(&bars[k % NST], (k / NST) & 1,
+                                 timed_out ? kWaitLimitAfterTimeout : kAggWaitLimit);
     }
 };
 
@@ -100,9 +101,6 @@ slstm_newton_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
     const bool ch_ok = ch < d;
     const int chl = ch_ok ? ch : d - 1;
     const SegRange sg = seg_range(a.T, a.n_seg, a.seg_len);
-    __shared__ volatile int s_abort;
-    if (threadIdx.x == 0) s_abort = 0;
-    __syncthreads();
     int lo, hi;
     seg_bounds(sg.lo, sg.hi, warp, lo, hi);
     WarpRing<NST> ring;
@@ -115,12 +113,8 @@ slstm_newton_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
         tma_load_3d(st, &tm_wx, &ring.bars[k % NST], cb * kLanes, 0, row0 + lo + k * U);
         tma_load_3d(st + S::WX, &tm_st, &ring.bars[k % NST], cb * kLanes, 0, row0 + lo + k * U);
     };
-    int issued = 0;
     if (lane == 0)
-        for (int k = 0; k < NST && k < n_chunks; ++k) {
-            issue(k);
-            issued = k + 1;
-        }
+        for (int k = 0; k < NST && k < n_chunks; ++k) issue(k);
     float r4[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) r4[q] = __ldg(a.r + (size_t)q * d + chl);
@@ -141,10 +135,7 @@ slstm_newton_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
     }
     bool timed_out = false;
     for (int k = 0; k < n_chunks; ++k) {
-        if (!ring.wait(k, &s_abort)) {
-            timed_out = true;
-            break;
-        }
+        if (!ring.wait(k, timed_out)) timed_out = true;
         const TIO* t_wx = reinterpret_cast<const TIO*>(ring.stage(k));
         const float* t_st = reinterpret_cast<const float*>(ring.stage(k) + S::WX);
         // chunks that lie fully inside the warp's range take a variant without range checks
@@ -190,11 +181,10 @@ slstm_newton_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
         if (lane == 0 && k + NST < n_chunks) {
             fence_proxy_async();
             issue(k + NST);
-            issued = k + NST + 1;
         }
     }
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
-    if (lane == 0 && s_abort) drain_ring(ring.bars, NST, issued, kAggWaitLimit);
+    if (lane == 0 && timed_out) drain_ring(ring.bars, NST, n_chunks, kDrainLimit);
     finish_agg<Affine4>(reinterpret_cast<float*>(smem + S::MAPS_OFF), mp, warp, lane,
                         a.agg_out + (size_t)sg.seg * a.B * 20 * d, b, d, ch, ch_ok);
 }
@@ -225,9 +215,6 @@ slstm_picard_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
     const bool ch_ok = ch < d;
     const int chl = ch_ok ? ch : d - 1;
     const SegRange sg = seg_range(a.T, a.n_seg, a.seg_len);
-    __shared__ volatile int s_abort;
-    if (threadIdx.x == 0) s_abort = 0;
-    __syncthreads();
     int lo, hi;
     seg_bounds(sg.lo, sg.hi, warp, lo, hi);
     WarpRing<NST> ring;
@@ -241,12 +228,8 @@ slstm_picard_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
         // hidden state of the PREVIOUS step: rows shifted by one
         if (HAS_H) tma_load_3d(st + S::WX, &tm_h, &ring.bars[k % NST], cb * kLanes, 0, row0 + lo + k * U - 1);
     };
-    int issued = 0;
     if (lane == 0)
-        for (int k = 0; k < NST && k < n_chunks; ++k) {
-            issue(k);
-            issued = k + 1;
-        }
+        for (int k = 0; k < NST && k < n_chunks; ++k) issue(k);
     float r4[4] = {0.f, 0.f, 0.f, 0.f};
     if (HAS_H) {
 #pragma unroll
@@ -255,10 +238,7 @@ slstm_picard_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
     float mp[4] = {0.f, -CUDART_INF_F, 0.f, 0.f};
     bool timed_out = false;
     for (int k = 0; k < n_chunks; ++k) {
-        if (!ring.wait(k, &s_abort)) {
-            timed_out = true;
-            break;
-        }
+        if (!ring.wait(k, timed_out)) timed_out = true;
         const TIO* t_wx = reinterpret_cast<const TIO*>(ring.stage(k));
         const float* t_h = reinterpret_cast<const float*>(ring.stage(k) + S::WX);
         // chunks that lie fully inside the warp's range take a variant without range checks
@@ -294,11 +274,10 @@ slstm_picard_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
         if (lane == 0 && k + NST < n_chunks) {
             fence_proxy_async();
             issue(k + NST);
-            issued = k + NST + 1;
         }
     }
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
-    if (lane == 0 && s_abort) drain_ring(ring.bars, NST, issued, kAggWaitLimit);
+    if (lane == 0 && timed_out) drain_ring(ring.bars, NST, n_chunks, kDrainLimit);
     finish_agg<PicardMonoid>(reinterpret_cast<float*>(smem + S::MAPS_OFF), mp, warp, lane,
                              a.agg_out + (size_t)sg.seg * a.B * 4 * d, b, d, ch, ch_ok);
 }
@@ -330,9 +309,6 @@ slstm_bwd_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid
     const bool ch_ok = ch < d;
     const int chl = ch_ok ? ch : d - 1;
     const SegRange sg = seg_range(a.T, a.n_seg, a.seg_len);
-    __shared__ volatile int s_abort;
-    if (threadIdx.x == 0) s_abort = 0;
-    __syncthreads();
     int lo, hi;
     seg_bounds(sg.lo, sg.hi, kAggW - 1 - warp, lo, hi);
     WarpRing<NST> ring;
@@ -347,12 +323,8 @@ slstm_bwd_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid
         tma_load_3d(st + S::WX, &tm_st, &ring.bars[k % NST], cb * kLanes, 0, row0 + t_first - 1);
         tma_load_3d(st + 2 * S::WX, &tm_g, &ring.bars[k % NST], cb * kLanes, 0, row0 + t_first);
     };
-    int issued = 0;
     if (lane == 0)
-        for (int k = 0; k < NST && k < n_chunks; ++k) {
-            issue(k);
-            issued = k + 1;
-        }
+        for (int k = 0; k < NST && k < n_chunks; ++k) issue(k);
     float r4[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) r4[q] = __ldg(a.r + (size_t)q * d + chl);
@@ -362,10 +334,7 @@ slstm_bwd_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid
     mp[0] = mp[5] = mp[10] = mp[15] = 1.f;
     bool timed_out = false;
     for (int k = 0; k < n_chunks; ++k) {
-        if (!ring.wait(k, &s_abort)) {
-            timed_out = true;
-            break;
-        }
+        if (!ring.wait(k, timed_out)) timed_out = true;
         const TIO* t_wx = reinterpret_cast<const TIO*>(ring.stage(k));
         const TIO* t_st = reinterpret_cast<const TIO*>(ring.stage(k) + S::WX);
         const TIO* t_g = reinterpret_cast<const TIO*>(ring.stage(k) + 2 * S::WX);
@@ -402,11 +371,10 @@ slstm_bwd_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid
         if (lane == 0 && k + NST < n_chunks) {
             fence_proxy_async();
             issue(k + NST);
-            issued = k + NST + 1;
         }
     }
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
-    if (lane == 0 && s_abort) drain_ring(ring.bars, NST, issued, kAggWaitLimit);
+    if (lane == 0 && timed_out) drain_ring(ring.bars, NST, n_chunks, kDrainLimit);
     finish_agg<Affine4>(reinterpret_cast<float*>(smem + S::MAPS_OFF), mp, warp, lane,
                         a.agg_out + (size_t)sg.seg * a.B * 20 * d, b, d, ch, ch_ok);
 }

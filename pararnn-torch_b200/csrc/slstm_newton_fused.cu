@@ -71,10 +71,8 @@ slstm_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, const __gri
     const int chl = ch_ok ? ch : d - 1;
     const int n_rounds = (a.T + LT - 1) / LT;
     const int row0 = b * a.T;
-    __shared__ volatile int s_abort;
 
     if (threadIdx.x == 0) {
-        s_abort = 0;
         tma_prefetch_desc(&tm_wx);
         tma_prefetch_desc(&tm_st);
         for (int s = 0; s < NSTAGE; ++s) {
@@ -106,12 +104,8 @@ slstm_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, const __gri
         tma_load_3d(base, &tm_wx, &full[s], cb * kLanes, 0, row0 + r * LT);
         tma_load_3d(base + S::WX_BYTES, &tm_st, &full[s], cb * kLanes, 0, row0 + r * LT - 1);
     };
-    int issued = 0;
     if (threadIdx.x == 0)
-        for (int r = 0; r < NSTAGE && r < n_rounds; ++r) {
-            issue(r);
-            issued = r + 1;
-        }
+        for (int r = 0; r < NSTAGE && r < n_rounds; ++r) issue(r);
     {
         float r4[4];
 #pragma unroll
@@ -121,17 +115,13 @@ slstm_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, const __gri
 
         for (int r = 0; r < n_rounds; ++r) {
             const int s = r % NSTAGE;
-            if (s_abort) break;  // a wait ran out somewhere in the CTA: every warp leaves
             if (threadIdx.x == 0 && r >= 1 && r - 1 + NSTAGE < n_rounds) {
-                if (!mbar_wait_abortable(&empty[(r - 1) % NSTAGE], ((r - 1) / NSTAGE) & 1, kNfWaitLimit, &s_abort))
+                if (!mbar_wait_bounded(&empty[(r - 1) % NSTAGE], ((r - 1) / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kNfWaitLimit))
                     timed_out = true;
-                if (!s_abort) {
-                    issue(r - 1 + NSTAGE);
-                    issued = r + NSTAGE;
-                }
+                issue(r - 1 + NSTAGE);
             }
             __syncwarp();
-            if (!mbar_wait_abortable(&full[s], (r / NSTAGE) & 1, kNfWaitLimit, &s_abort)) timed_out = true;
+            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kNfWaitLimit)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const float* t_st = reinterpret_cast<const float*>(smem + s * S::STAGE + S::WX_BYTES);
             const int t0 = r * LT + warp * L;
@@ -190,7 +180,7 @@ slstm_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, const __gri
                     for (int kk = 0; kk < kNfMaxIters; ++kk) rm[kk] = (kk == k) ? max(rm[kk], rmax) : rm[kk];
 
                     // ---- the baton of iteration k
-                    if (!first && !mbar_wait_abortable(&baton[k * W + warp], par, kNfWaitLimit, &s_abort)) timed_out = true;
+                    if (!first && !mbar_wait_bounded(&baton[k * W + warp], par, timed_out ? kWaitLimitAfterTimeout : kNfWaitLimit)) timed_out = true;
                     float xc = slot_in[0], xn = slot_in[kLanes], xm = slot_in[2 * kLanes], xh = slot_in[3 * kLanes];
                     // the state preceding the sub-tile moves by the incoming carry
                     st[0][0] = fmaf(a.omega, xc, st[0][0]);
@@ -246,7 +236,7 @@ slstm_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, const __gri
         }
     }
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
-    if (threadIdx.x == 0 && s_abort) drain_ring(full, NSTAGE, issued, kNfWaitLimit);
+    if (threadIdx.x == 0 && timed_out) drain_ring(full, NSTAGE, n_rounds, kDrainLimit);
     for (int k = 0; k < n_iters; ++k) {
         __syncthreads();
         unsigned v = 0u;

@@ -99,10 +99,8 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
     const int chl = ch_ok ? ch : d - 1;
     const int n_rounds = (a.T + LT - 1) / LT;
     const int row0 = b * a.T;
-    __shared__ volatile int s_abort;
 
     if (threadIdx.x == 0) {
-        s_abort = 0;
         tma_prefetch_desc(&tm_wx);
         for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(&full[s], 1);
@@ -133,12 +131,8 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
         mbar_expect_tx(&full[s], S::STAGE);
         tma_load_3d(smem + s * S::STAGE, &tm_wx, &full[s], cb * kLanes, 0, row0 + r * LT);
     };
-    int issued = 0;
     if (threadIdx.x == 0)
-        for (int r = 0; r < NSTAGE && r < n_rounds; ++r) {
-            issue(r);
-            issued = r + 1;
-        }
+        for (int r = 0; r < NSTAGE && r < n_rounds; ++r) issue(r);
     {
         float r4[4];
 #pragma unroll
@@ -147,17 +141,13 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
 
         for (int r = 0; r < n_rounds; ++r) {
             const int s = r % NSTAGE;
-            if (s_abort) break;  // a wait ran out somewhere in the CTA: every warp leaves
             if (threadIdx.x == 0 && r >= 1 && r - 1 + NSTAGE < n_rounds) {
-                if (!mbar_wait_abortable(&empty[(r - 1) % NSTAGE], ((r - 1) / NSTAGE) & 1, kFusedWaitLimit, &s_abort))
+                if (!mbar_wait_bounded(&empty[(r - 1) % NSTAGE], ((r - 1) / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kFusedWaitLimit))
                     timed_out = true;
-                if (!s_abort) {
-                    issue(r - 1 + NSTAGE);
-                    issued = r + NSTAGE;
-                }
+                issue(r - 1 + NSTAGE);
             }
             __syncwarp();
-            if (!mbar_wait_abortable(&full[s], (r / NSTAGE) & 1, kFusedWaitLimit, &s_abort)) timed_out = true;
+            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kFusedWaitLimit)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const int t0 = r * LT + warp * L;
             const bool first = (r == 0 && warp == 0);
@@ -198,7 +188,7 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
                         og[i] = go.x; og[i + 1] = go.y;
                     }
                     // ---- m: max-plus recurrence
-                    if (!first && !mbar_wait_abortable(&mbar_m[g * W + warp], par, kFusedWaitLimit, &s_abort))
+                    if (!first && !mbar_wait_bounded(&mbar_m[g * W + warp], par, timed_out ? kWaitLimitAfterTimeout : kFusedWaitLimit))
                         timed_out = true;
                     float m = slot_in[2 * kLanes];
                     float dlt[L], ms[L];
@@ -224,7 +214,7 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
                         e[i + 1] = ev.y;
                     }
                     // ---- (c, n): multiply-add recurrences
-                    if (!first && !mbar_wait_abortable(&mbar_cn[g * W + warp], par, kFusedWaitLimit, &s_abort))
+                    if (!first && !mbar_wait_bounded(&mbar_cn[g * W + warp], par, timed_out ? kWaitLimitAfterTimeout : kFusedWaitLimit))
                         timed_out = true;
                     float c = slot_in[0], n = slot_in[kLanes];
                     const float h_before = slot_in[3 * kLanes];  // this pass's h at step t0-1
@@ -289,7 +279,7 @@ slstm_picard_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, SlstmPicard
         }
     }
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
-    if (threadIdx.x == 0 && s_abort) drain_ring(full, NSTAGE, issued, kFusedWaitLimit);
+    if (threadIdx.x == 0 && timed_out) drain_ring(full, NSTAGE, n_rounds, kDrainLimit);
 }
 
 template <typename TIO, int NSTAGE, int L, int W>

@@ -70,10 +70,8 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
     const SegRange sg = seg_range(a.T, a.n_seg, a.seg_len);
     const int n_rounds = (sg.hi - sg.lo + LT - 1) / LT;
     const int row0 = b * a.T + sg.lo;
-    __shared__ volatile int s_abort;
 
     if (threadIdx.x == 0) {
-        s_abort = 0;
         tma_prefetch_desc(&tm_wx);
         tma_prefetch_desc(&tm_st);
         for (int s = 0; s < NSTAGE; ++s) {
@@ -96,19 +94,16 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
     if (warp == W) {
         // ---------------- producer warp: one lane streams the rounds into the ring
         if (lane == 0) {
-            int issued = 0;
             for (int r = 0; r < n_rounds; ++r) {
                 const int s = r % NSTAGE;
-                if (r >= NSTAGE && !mbar_wait_abortable(&empty[s], ((r / NSTAGE) - 1) & 1, kPipeWaitLimit, &s_abort))
+                if (r >= NSTAGE && !mbar_wait_bounded(&empty[s], ((r / NSTAGE) - 1) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit))
                     timed_out = true;
-                if (s_abort) break;
                 unsigned char* base = smem + s * S::STAGE;
                 mbar_expect_tx(&full[s], S::STAGE);
                 tma_load_3d(base, &tm_wx, &full[s], cb * kLanes, 0, row0 + r * LT);
                 tma_load_3d(base + S::WX_BYTES, &tm_st, &full[s], cb * kLanes, 0, row0 + r * LT - 1);
-                issued = r + 1;
             }
-            if (s_abort) drain_ring(full, NSTAGE, issued, kPipeWaitLimit);
+            if (timed_out) drain_ring(full, NSTAGE, n_rounds, kDrainLimit);
         }
     } else {
         // ---------------- compute warps
@@ -122,9 +117,9 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
 
         for (int r = 0; r < n_rounds; ++r) {
             const int s = r % NSTAGE;
-            // after a time-out the warps keep walking (the named-barrier hand-over needs every
-            // warp) but no wait takes more than a few polls: the result is void, status says so
-            if (!mbar_wait_abortable(&full[s], (r / NSTAGE) & 1, kPipeWaitLimit, &s_abort)) timed_out = true;
+            // after a time-out the warp keeps walking (the named-barrier hand-over needs every
+            // warp) but its waits give up after a few polls: the result is void, status says so
+            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const float* t_st = reinterpret_cast<const float*>(smem + s * S::STAGE + S::WX_BYTES);
             const int t0 = sg.lo + r * LT + warp * L;
@@ -288,10 +283,8 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
     const SegRange sg = seg_range(a.T, a.n_seg, a.seg_len);
     const int n_rounds = (sg.hi - sg.lo + LT - 1) / LT;
     const int row0 = b * a.T + sg.lo;
-    __shared__ volatile int s_abort;
 
     if (threadIdx.x == 0) {
-        s_abort = 0;
         tma_prefetch_desc(&tm_wx);
         tma_prefetch_desc(&tm_st);
         tma_prefetch_desc(&tm_g);
@@ -322,12 +315,8 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
         tma_load_3d(base + S::WX_BYTES, &tm_st, &full[s], cb * kLanes, 0, row0 + tile_t * LT - 1);
         tma_load_3d(base + S::WX_BYTES + S::ST_BYTES, &tm_g, &full[s], cb * kLanes, 0, row0 + tile_t * LT);
     };
-    int issued = 0;
     if (threadIdx.x == 0)
-        for (int r = 0; r < NSTAGE && r < n_rounds; ++r) {
-            issue(r);
-            issued = r + 1;
-        }
+        for (int r = 0; r < NSTAGE && r < n_rounds; ++r) issue(r);
     {
         float r4[4];
 #pragma unroll
@@ -341,17 +330,14 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
             const int s = r % NSTAGE;
             const int tile_t = n_rounds - 1 - r;
             if (threadIdx.x == 0 && r >= 1 && r - 1 + NSTAGE < n_rounds) {
-                if (!mbar_wait_abortable(&empty[(r - 1) % NSTAGE], ((r - 1) / NSTAGE) & 1, kPipeWaitLimit, &s_abort))
+                if (!mbar_wait_bounded(&empty[(r - 1) % NSTAGE], ((r - 1) / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit))
                     timed_out = true;
-                if (!s_abort) {
-                    issue(r - 1 + NSTAGE);
-                    issued = r + NSTAGE;
-                }
+                issue(r - 1 + NSTAGE);
             }
             __syncwarp();
-            // after a time-out the warps keep walking (the named-barrier hand-over needs every
-            // warp) but no wait takes more than a few polls: the result is void, status says so
-            if (!mbar_wait_abortable(&full[s], (r / NSTAGE) & 1, kPipeWaitLimit, &s_abort)) timed_out = true;
+            // after a time-out the warp keeps walking (the named-barrier hand-over needs every
+            // warp) but its waits give up after a few polls: the result is void, status says so
+            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const TIO* t_st = reinterpret_cast<const TIO*>(smem + s * S::STAGE + S::WX_BYTES);
             const TIO* t_g = reinterpret_cast<const TIO*>(smem + s * S::STAGE + S::WX_BYTES + S::ST_BYTES);
@@ -454,7 +440,7 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
         for (int p = 0; p < 4; ++p) s_gp[(warp * 4 + p) * kLanes + lane] = gr[p];
     }
     if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
-    if (threadIdx.x == 0 && s_abort) drain_ring(full, NSTAGE, issued, kPipeWaitLimit);
+    if (threadIdx.x == 0 && timed_out) drain_ring(full, NSTAGE, n_rounds, kDrainLimit);
     __syncthreads();
     if (warp == 0 && ch_ok) {
 #pragma unroll
@@ -509,10 +495,8 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
     const SegRange sg = seg_range(a.T, a.n_seg, a.seg_len);
     const int n_rounds = (sg.hi - sg.lo + LT - 1) / LT;
     const int row0 = b * a.T + sg.lo;
-    __shared__ volatile int s_abort;
 
     if (threadIdx.x == 0) {
-        s_abort = 0;
         tma_prefetch_desc(&tm_wx);
         if (HAS_H) tma_prefetch_desc(&tm_h);
         for (int s = 0; s < NSTAGE; ++s) {
@@ -534,19 +518,16 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
 
     if (warp == W) {
         if (lane == 0) {
-            int issued = 0;
             for (int r = 0; r < n_rounds; ++r) {
                 const int s = r % NSTAGE;
-                if (r >= NSTAGE && !mbar_wait_abortable(&empty[s], ((r / NSTAGE) - 1) & 1, kPipeWaitLimit, &s_abort))
+                if (r >= NSTAGE && !mbar_wait_bounded(&empty[s], ((r / NSTAGE) - 1) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit))
                     timed_out = true;
-                if (s_abort) break;
                 unsigned char* base = smem + s * S::STAGE;
                 mbar_expect_tx(&full[s], S::WX_BYTES + (HAS_H ? (LT + 1) * kLanes * 4 : 0));
                 tma_load_3d(base, &tm_wx, &full[s], cb * kLanes, 0, row0 + r * LT);
                 if (HAS_H) tma_load_3d(base + S::WX_BYTES, &tm_h, &full[s], cb * kLanes, 0, row0 + r * LT - 1);
-                issued = r + 1;
             }
-            if (s_abort) drain_ring(full, NSTAGE, issued, kPipeWaitLimit);
+            if (timed_out) drain_ring(full, NSTAGE, n_rounds, kDrainLimit);
         }
     } else {
         float r4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -560,7 +541,7 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
 
         for (int r = 0; r < n_rounds; ++r) {
             const int s = r % NSTAGE;
-            if (!mbar_wait_abortable(&full[s], (r / NSTAGE) & 1, kPipeWaitLimit, &s_abort)) timed_out = true;
+            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const float* t_h = reinterpret_cast<const float*>(smem + s * S::STAGE + S::WX_BYTES);
             const int t0 = sg.lo + r * LT + warp * L;
@@ -613,7 +594,7 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
                 // (r-1)-th for warp 0
                 if (!(r == 0 && warp == 0)) {
                     const uint32_t par = (warp == 0 ? r - 1 : r) & 1;
-                    if (!mbar_wait_abortable(&cnbar[warp], par, kPipeWaitLimit, &s_abort)) timed_out = true;
+                    if (!mbar_wait_bounded(&cnbar[warp], par, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit)) timed_out = true;
                 }
                 float c = slot_in[0], n = slot_in[kLanes];
                 float cs[L], ns[L];

@@ -41,20 +41,12 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
     return false;
 }
-// Bounded wait that a whole CTA gives up together.  `abort_word` lives in shared memory, is zero
-// at the start of the kernel and is set by the first wait that runs out; every other wait looks at
-// it every 64 polls and then returns false at once.  A CTA whose input stalled therefore leaves
-// after about ONE limit, not one limit per remaining wait.
-__device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, uint32_t limit,
-                                                    volatile int* abort_word) {
-    for (uint32_t i = 0; i < limit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u && *abort_word) return false;
-    }
-    *abort_word = 1;
-    return false;
-}
-// After an abort: the thread that issued the bulk loads waits (bounded) until the loads already
+// Once a thread has seen one of its bounded waits run out it passes this limit to its later waits
+// (`timed_out ? kWaitLimitAfterTimeout : limit`): a CTA whose input stalled then leaves after about
+// one full limit per warp, not one per remaining wait, and the normal path pays nothing for it.
+constexpr uint32_t kWaitLimitAfterTimeout = 64;
+constexpr uint32_t kDrainLimit = 1u << 20;
+// After a time-out: the thread that issued the bulk loads waits (bounded) until the loads already
 // issued into the ring have landed, so the CTA does not exit with copies in flight into its
 // shared memory.  `n_issued` = number of stages issued so far (round r went to stage r % nstage).
 __device__ __forceinline__ void drain_ring(uint64_t* full, int nstage, int n_issued, uint32_t limit) {
