@@ -13,6 +13,12 @@ so per-GPU work is fixed (weak scaling) and N = 8 is the T = 131072 case.
 cotangent -> gradients of the pre-activations and of R), timed with CUDA events.
 `e2e` is the same metric through `newton_apply` + autograd with host-resident inputs,
 including the three W_x GEMMs and the host<->device copies.
+`roofline` is computed on the bytes the dominant launch really moves; the figure the
+separate passes it replaces would need is reported beside it under its own name.
+`parity` compares a 32-channel slice of this run's own result with the CPU oracle.
+`sustained` repeats the step back to back for at least three seconds.
+With N > 1 the line also carries `c4_strong` (B=1, T=131072, d=2048 sharded over the N
+ranks against the same shape on one GPU) and `c5_sharded` (12 x ParaNLRU stack).
 The CPU arm (`--impl reference`, and `cpu_baseline` at N = 1) times the C restatement of
 the reference's eager algorithm (oracle/) on the host cores.
 """
@@ -47,12 +53,16 @@ BYTES_NEWTON_PHASE = 40 + 32 + 16         # K = 2 separate passes and the separa
 BYTES_NEWTON_SWEEP = 4 * 2 + 16 + 4 * 2   # what the fused sweep has to move
 BYTES_BWD = 4 * 2 + 4 * 2 + 4 * 2 + 4 * 2  # read states, wx, cotangent; write g_wx
 BYTES_STEP = 224                          # all passes of one forward + backward
-# DRAM bytes per (token, channel) of each kernel from the committed ncu capture
-# (profiles/slstm_pipe_kernels_B8_T4096_d1024_bf16.md); traffic grows in proportion to the units
+# DRAM bytes per (token, channel) of each kernel as ncu counted them in an earlier capture of the
+# same kernels at a quarter of this sequence length (traffic grows in proportion to the units);
+# NOT measured by this run: a run under a profiler is never a bench run
 NCU_TRAFFIC_PER_UNIT = {"slstm_picard_pipe_kernel": 15.44, "slstm_newton_pipe_kernel": 39.02,
                         "slstm_bwd_pipe_kernel": 31.37,
-                        # profiles/slstm_fused_sweeps_B8_T4096_d1024_bf16.md
                         "slstm_picard_fused_kernel": 22.44, "slstm_newton_fused_kernel": 31.53}
+# issue-slot utilisation of the fused sweeps in the same capture (they are bound by it, not by HBM)
+NCU_ISSUE_ACTIVE = {"slstm_picard_fused_kernel": 0.61, "slstm_newton_fused_kernel": 0.72}
+PARITY_TOL = 2e-2     # bf16 I/O against the fp32 oracle on bf16-rounded inputs, relative to max|.|
+PARITY_CH = 32
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
@@ -209,7 +219,9 @@ def run_reference_arm(args):
         "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus),
+        # the CPU arm always times the same one-row, T = T_PER_GPU sample, whatever N is
+        "config": dict(workload_config(1), timed_sample="1 batch row, T=%d" % T_PER_GPU,
+                       requested_gpus=args.gpus),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": "1 of 8 batch rows per step (rows are independent), full T=16384, "
                                    "d=1024, fp32 arithmetic on bf16-rounded inputs"},
@@ -227,6 +239,57 @@ def workload_config(n):
 
 
 # ----------------------------------------------------------------------------- GPU arm
+
+def slice_parity(wx_rows, r, H_rows, gwx_rows, d, K, P, eps=1e-6):
+    """Max relative error of this run's own result against the CPU oracle on a slice: one batch
+    row, the first PARITY_CH channels, the whole sequence.  `wx_rows` (T, 4, C), `H_rows`
+    (T, 4, C), `gwx_rows` (T, 4, C) are that slice (any float dtype, CPU or GPU), `r` (4, C).
+    The cotangent is 1 on the hidden slot, 0 elsewhere (what the bench's loss produces)."""
+    import numpy as np
+
+    from oracle import oracle
+
+    wx_np = wx_rows.float().cpu().numpy()
+    T, _, C = wx_np.shape
+    wx_np = np.ascontiguousarray(wx_np.reshape(1, T, 4 * C))
+    r_np = np.ascontiguousarray(r.float().cpu().numpy())
+    want = oracle.newton(oracle.SLSTM_DIAG, wx_np, r_np, None, max_iters=K, picard=P, eps=eps)
+    got_H = H_rows.float().cpu().numpy().reshape(1, T, 4, C)
+    G = np.zeros((1, T, 4, C), dtype=np.float32)
+    G[:, :, 3] = 1.0
+    want_g, _, _ = oracle.backward(oracle.SLSTM_DIAG, got_H, wx_np, r_np, G, None, eps=eps)
+    got_g = gwx_rows.float().cpu().numpy().reshape(1, T, 4 * C)
+    rel_h = float(np.abs(got_H[:, :, 3] - want.states[:, :, 3]).max() / max(1e-30, np.abs(want.states[:, :, 3]).max()))
+    rel_g = float(np.abs(got_g - want_g).max() / max(1e-30, np.abs(want_g).max()))
+    return {"max_rel_h": rel_h, "max_rel_gwx": rel_g, "tol": PARITY_TOL, "ok": bool(rel_h <= PARITY_TOL and rel_g <= PARITY_TOL),
+            "slice": f"batch row 0, channels 0..{C - 1}, all {T} steps, against the fp32 CPU oracle on the same "
+                     "bf16-rounded inputs", "oracle_residual_history": [float(v) for v in want.history]}
+
+
+def gate_slice(t, d, n_ch=PARITY_CH):
+    """(T, 4, n_ch) slice of a (T, 4*d) gate-major row or of a (T, 4, d) state row."""
+    T = t.shape[0]
+    return t.reshape(T, 4, d)[:, :, :n_ch]
+
+
+def sustained_run(step, device_index, seconds=3.0):
+    """The step back to back for at least `seconds`: what it costs once the burst clock is gone."""
+    import torch
+
+    sampler = ClockSampler(device_index)
+    sampler.start()
+    n, total = 0, 0.0
+    chunk = 50
+    t_start = time.perf_counter()
+    while time.perf_counter() - t_start < seconds:
+        total += time_region(step, chunk, None)
+        n += chunk
+    clocks = sampler.stop()
+    ms = total / n * 1e3
+    mhz = clocks.get("sm_mhz")
+    return {"ms_per_step": ms, "steps": n, "seconds": total, "sm_mhz_median": mhz,
+            "ms_times_mhz": (ms * mhz) if mhz else None, "reasons": clocks.get("reasons")}
+
 
 def time_region(fn, steps, stream_sync, barrier=None):
     import torch
@@ -423,30 +486,42 @@ def run_gpu_single(args):
     states32 = states_io.float()
     roofs = kernel_rooflines(wx, r_io.float().contiguous(), states32, states_io, G_io, peak)
     n_units = tokens * D
-    # The dominant kernel by time per step.  `achieved` follows the per-pass accounting of the
-    # algorithm (the bytes the separate passes this launch replaces would move), `traffic` is what
-    # ncu saw it move: for the fused sweeps traffic is far BELOW the algorithmic bytes, because the
-    # intermediate trajectories stay on chip, and the fraction is not bounded by 1.
+    # The dominant kernel by time per step.  `achieved` / `frac` are computed on the bytes the
+    # launch really moves (its inputs once, its outputs once).  A fused sweep replaces several
+    # HBM-bound passes while moving a fraction of their bytes, so its fraction of the HBM peak is
+    # low by construction: it is bound by instruction issue (`binding_resource`).  What the
+    # separate passes would have needed is kept under `equivalent_per_pass_gbs`.
     total = {k: v["ms_per_launch"] * v["launches_per_step"] for k, v in roofs.items()}
     top = max(total, key=total.get)
-    top_bytes = roofs[top].get("separate_passes_bytes", roofs[top]["algorithmic_bytes_per_launch"])
-    top_gbs = top_bytes / (roofs[top]["ms_per_launch"] / 1e3) / 1e9
     per_unit = NCU_TRAFFIC_PER_UNIT.get(top)
+    moved_step = (BYTES_PICARD_SWEEP + BYTES_NEWTON_SWEEP + BYTES_BWD) * n_units
     roofline = {"bound": "hbm", "kernel": top, "ms_per_launch": roofs[top]["ms_per_launch"],
-                "achieved": top_gbs, "peak": peak, "unit": "GB/s", "frac": top_gbs / peak,
-                "peak_kind": peak_kind, "traffic": per_unit * n_units if per_unit else None,
-                "note": "fused sweep: does the work of several HBM-bound passes while moving "
-                        "bytes_moved_per_launch; limited by instruction issue",
-                "bytes_moved_per_launch": roofs[top]["algorithmic_bytes_per_launch"],
-                "achieved_on_bytes_moved": roofs[top]["achieved"],
+                "achieved": roofs[top]["achieved"], "peak": peak, "unit": "GB/s",
+                "frac": roofs[top]["achieved"] / peak, "peak_kind": peak_kind,
+                "algorithmic_bytes_per_launch": roofs[top]["algorithmic_bytes_per_launch"],
+                "traffic": per_unit * n_units if per_unit else None,
+                "traffic_source": "ncu capture of the same kernel at T=4096 scaled by the units; not measured "
+                                  "by this run",
+                "binding_resource": ("instruction issue: %.0f %% of issue slots active in the ncu capture"
+                                     % (100 * NCU_ISSUE_ACTIVE[top])) if top in NCU_ISSUE_ACTIVE else "hbm",
+                "equivalent_per_pass_gbs": roofs[top].get("achieved_vs_separate_passes"),
                 "ms_per_step_by_kernel": {k: v for k, v in total.items() if v > 0}, "kernels": roofs,
-                "step": {"algorithmic_bytes": BYTES_STEP * n_units,
-                         "achieved": BYTES_STEP * n_units / (ms / 1e3) / 1e9,
-                         "frac": BYTES_STEP * n_units / (ms / 1e3) / 1e9 / peak,
-                         "frac_of_nominal_8TBs": BYTES_STEP * n_units / (ms / 1e3) / 1e9 / NOMINAL_HBM_GBS,
-                         "bytes_moved": (BYTES_PICARD_SWEEP + BYTES_NEWTON_SWEEP + BYTES_BWD) * n_units,
-                         "note": "224 B per token-channel is the per-pass accounting (9 sweeps); the "
-                                 "three launches of a step move 88 B"}}
+                "step": {"bytes_moved": moved_step, "achieved": moved_step / (ms / 1e3) / 1e9,
+                         "frac": moved_step / (ms / 1e3) / 1e9 / peak,
+                         "per_pass_accounting_bytes": BYTES_STEP * n_units,
+                         "equivalent_per_pass_gbs": BYTES_STEP * n_units / (ms / 1e3) / 1e9,
+                         "equivalent_per_pass_frac": BYTES_STEP * n_units / (ms / 1e3) / 1e9 / peak,
+                         "equivalent_per_pass_frac_of_nominal_8TBs": BYTES_STEP * n_units / (ms / 1e3) / 1e9 / NOMINAL_HBM_GBS,
+                         "note": "the three launches of a step move 88 B per token-channel; 224 B is what "
+                                 "the nine separate sweeps of the per-pass formulation move"}}
+
+    # parity of THIS run's result (seed-1 inputs of the bench) against the CPU oracle
+    g_wx_run = keep["out"][0]
+    parity = slice_parity(gate_slice(wx[0], D), r_io[:, :PARITY_CH], gate_slice(keep["H"][0], D),
+                          gate_slice(g_wx_run[0], D), D, K_NEWTON, P_PICARD)
+    assert parity["ok"], parity
+
+    sustained = None if args.no_sustained else sustained_run(step, 0)
 
     clocks = sampler.stop()
 
@@ -475,7 +550,10 @@ def run_gpu_single(args):
         "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": "1 of 8 batch rows (rows are independent), full T=16384, d=1024, "
                                    "fp32 arithmetic on bf16-rounded inputs, one forward+backward"},
-        "newton": {"iters": K_NEWTON, "residual_history": list(hist), "max_residual": res},
+        "parity": parity, "sustained": sustained,
+        "newton": {"iters": K_NEWTON, "residual_history": list(hist), "max_residual": res,
+                   "note": "max_iters is mandated by the configuration; the warm start already lands at "
+                           "1e-7 and the Newton iterations move the stabiliser m by one ulp"},
     }
     print(json.dumps(line))
 
@@ -619,8 +697,22 @@ def run_gpu_sharded(args):
         t = torch.tensor([e2e_sec], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_sec = float(t.item())
+    # parity of this run's own (sharded, NCCL) result: the slice of every rank goes to rank 0,
+    # which runs the CPU oracle over the whole T = T_PER_GPU * N sequence of that slice
+    sl_wx = gather_time(dist, dev, world, gate_slice(wx[0], D).contiguous())
+    sl_H = gather_time(dist, dev, world, gate_slice(keep["res"].states[0], D).contiguous())
+    sl_g = gather_time(dist, dev, world, gate_slice(keep["bwd"][0][0], D).contiguous())
+    parity = None
+    if rank == 0:
+        parity = slice_parity(sl_wx, rec[0][:, :PARITY_CH], sl_H, sl_g, D, K_NEWTON, P_PICARD)
+        parity["path"] = f"time-sharded over {world} ranks, NCCL carry exchange"
+    extra = {}
+    if not args.no_extra:
+        extra["c4_strong"] = c4_strong_record(args, rank, world, dev, dist, comm, barrier)
+        extra["c5_sharded"] = c5_sharded_record(args, rank, world, dev, dist, barrier)
     if rank == 0:
         assert status == 0, "chain wait timed out"
+        assert parity["ok"], parity
         ms = sec / args.steps * 1e3
         tokens = B * T_PER_GPU * world
         step_bytes = BYTES_STEP * tokens * D
@@ -644,6 +736,7 @@ def run_gpu_sharded(args):
                          "traffic": None,
                          "note": "ranks other than the first sweep each pass twice (aggregate, then apply)"},
             "newton": {"iters": K_NEWTON, "residual_history": list(hist), "max_residual": res_final},
+            "parity": parity, **extra,
             "batch_parallel_for_comparison": {
                 "value": B * T_PER_GPU * world / dp_sec, "unit": "tokens/s", "ms_per_step": dp_sec * 1e3,
                 "workload": f"B={B * world} rows split over the ranks, T={T_PER_GPU}: independent rows, "
@@ -652,6 +745,191 @@ def run_gpu_sharded(args):
         print(json.dumps(line))
     dist.barrier(device_ids=[local])
     dist.destroy_process_group()
+
+
+def gather_time(dist, dev, world, t):
+    """Slices (T_local, ...) of all ranks concatenated along time (shards may differ in length)."""
+    import torch
+
+    n_local = torch.tensor([t.shape[0]], device=dev)
+    sizes = [torch.zeros_like(n_local) for _ in range(world)]
+    dist.all_gather(sizes, n_local)
+    n_max = max(int(v.item()) for v in sizes)
+    pad = torch.zeros(n_max, *t.shape[1:], dtype=t.dtype, device=dev)
+    pad[: t.shape[0]] = t
+    parts = [torch.empty_like(pad) for _ in range(world)]
+    dist.all_gather(parts, pad)
+    return torch.cat([p_[: int(n.item())] for p_, n in zip(parts, sizes)], dim=0)
+
+
+def _max_over_ranks(dist, dev, sec):
+    import torch
+
+    t = torch.tensor([sec], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def c4_strong_record(args, rank, world, dev, dist, comm, barrier):
+    """Strong scaling of the T = 131072 configuration (ParaSLSTM mix='diag', bf16, B=1, d=2048,
+    picard_iters=5, max_iters=2, seed 3): the sequence sharded over the N ranks against the SAME
+    sequence on one GPU (rank 0, the other ranks idle), both at the op boundary, both checked."""
+    import torch
+
+    import pararnn_b200 as prb
+    from pararnn_b200 import ops as _ops
+    from pararnn_b200.seq_shard import (CudaShardOps, _bits_to_stats, backward_program, drive,
+                                        forward_program, time_shard_bounds)
+
+    Bc, Tc, Dc, seed = 1, 131072, 2048, 3
+    if args.c4_seq_len:
+        Tc = args.c4_seq_len
+    g = torch.Generator().manual_seed(seed)
+    bound = (6.0 / (Dc + 4 * Dc)) ** 0.5
+    W = (torch.rand(4 * Dc, Dc, generator=g) * 2 - 1) * bound
+    bias = torch.zeros(4 * Dc)
+    bias[Dc:2 * Dc] = 3.0
+    R = (torch.randn(4, Dc, generator=g) * (1.0 / (4 * Dc)) ** 0.5).clamp(-0.5, 0.5)
+    cell = prb.ParaSLSTM(Dc, Dc).to(dev)
+    with torch.no_grad():
+        cell.W_x.weight.copy_(W)
+        cell.W_x.bias.copy_(bias)
+        cell.R.copy_(R)
+    cell = cell.bfloat16()
+    rec = (cell.clipped_r().detach(),)
+
+    def x_shard(r):
+        lo, hi = time_shard_bounds(Tc, r, world)
+        gx = torch.Generator(device=dev).manual_seed(seed + 1000 * (r + 1))
+        return (0.5 * torch.randn(Bc, hi - lo, Dc, generator=gx, device=dev)).bfloat16()
+
+    with torch.no_grad():
+        wx = cell.W_x(x_shard(rank)).contiguous()
+    t_local = wx.shape[1]
+    G_io = torch.zeros(Bc, t_local, 4, Dc, dtype=torch.bfloat16, device=dev)
+    G_io[:, :, 3] = 1.0
+    keep = {}
+
+    def step():
+        sops = CudaShardOps("slstm_diag", wx, rec, 1e-6, 1.0)
+        res = drive(forward_program(sops, rank, world, K_NEWTON, P_PICARD, None), comm)
+        keep["bwd"] = drive(backward_program(sops, rank, world, res.states, G_io, res.halo), comm)
+        keep["res"], keep["segs"] = res, (sops.n_seg, sops.seg_len)
+
+    n_steps = max(3, min(args.steps, 10))
+    for _ in range(3):
+        step()
+    sec = _max_over_ranks(dist, dev, time_region(step, n_steps, None, barrier)) / n_steps
+    status = _bits_to_stats(keep["res"].stats_bits, K_NEWTON)[2]
+
+    # slices of the sharded result to rank 0
+    sl_wx = gather_time(dist, dev, world, gate_slice(wx[0], Dc).contiguous())
+    sl_H = gather_time(dist, dev, world, gate_slice(keep["res"].states[0], Dc).contiguous())
+    sl_g = gather_time(dist, dev, world, gate_slice(keep["bwd"][0][0], Dc).contiguous())
+    record = None
+    del keep["res"], keep["bwd"], G_io
+    if rank == 0:
+        parity = slice_parity(sl_wx, rec[0][:, :PARITY_CH], sl_H, sl_g, Dc, K_NEWTON, P_PICARD)
+        # the same sequence on one GPU: rank 0 rebuilds all shards of x
+        with torch.no_grad():
+            wx_full = torch.cat([cell.W_x(x_shard(r)) for r in range(world)], dim=1).contiguous()
+        G_full = torch.zeros(Bc, Tc, 4, Dc, dtype=torch.bfloat16, device=dev)
+        G_full[:, :, 3] = 1.0
+        st = _ops.DeviceStats(dev, K_NEWTON)
+
+        def one_gpu():
+            H = _ops.newton_slstm_fused(wx_full, rec[0], None, None, max_iters=K_NEWTON, picard_iters=P_PICARD,
+                                        stats=st, want_residual=True)
+            keep["one"] = (H, _ops.slstm_reverse_vjp(H, wx_full, rec[0], G_full))
+
+        for _ in range(2):
+            one_gpu()
+        one_sec = time_region(one_gpu, n_steps, None) / n_steps
+        H1, (g1, _, _) = keep["one"]
+        h_one = gate_slice(H1[0], Dc)[:, 3].float()
+        h_sh = sl_H[:, 3].float()
+        rel_vs_one = float((h_one - h_sh).abs().max() / h_one.abs().max())
+        g_one = gate_slice(g1[0], Dc).float()
+        rel_g_vs_one = float((g_one - sl_g.float()).abs().max() / g_one.abs().max())
+        units = Bc * Tc * Dc
+        record = {
+            "workload": f"ParaSLSTM mix=diag fwd+bwd, B={Bc}, T={Tc}, d={Dc}, bf16 I/O, picard_iters={P_PICARD}, "
+                        f"max_iters={K_NEWTON}, seed {seed}; op boundary",
+            "n_gpus": world, "ms_per_step": sec * 1e3, "tokens_per_s": Bc * Tc / sec,
+            "one_gpu_ms_per_step": one_sec * 1e3, "one_gpu_tokens_per_s": Bc * Tc / one_sec,
+            "speedup": one_sec / sec, "segments_per_rank": keep["segs"][0], "segment_steps": keep["segs"][1],
+            "status": status, "parity": parity,
+            "sharded_vs_one_gpu": {"max_rel_h": rel_vs_one, "max_rel_gwx": rel_g_vs_one},
+            "per_pass_accounting_gbs": BYTES_STEP * units / sec / 1e9,
+            "timing": "CUDA events, max over ranks; one-GPU time measured on rank 0 in the same run"}
+        assert parity["ok"] and status == 0, record
+        del keep["one"], wx_full, G_full
+    torch.cuda.empty_cache()
+    barrier()
+    return record
+
+
+def c5_sharded_record(args, rank, world, dev, dist, barrier):
+    """The 12-layer ParaNLRU residual stack (d=768, bf16, B=4, T=8192, max_iters=2, seed 4) with
+    the sequence sharded over the N ranks, forward + backward through newton_apply, against the
+    same stack on one GPU.  Latency-dominated by construction (1024 steps per rank at N = 8)."""
+    import torch
+
+    import pararnn_b200 as prb
+    from pararnn_b200.seq_shard import time_shard_bounds
+
+    Bc, Tc, Dc, layers, vocab = 4, 8192, 768, 12, 50304
+    torch.manual_seed(4)
+    cells = []
+    for _ in range(layers):
+        c = prb.ParaNLRU(Dc, Dc)
+        with torch.no_grad():
+            a0 = torch.empty(Dc).uniform_(0.9, 0.999)
+            c.W_x.bias[:Dc] = torch.log(a0 / (1 - a0))
+        cells.append(c.to(dev, torch.bfloat16))
+    emb = (torch.randn(vocab, Dc) * 0.02).to(dev, torch.bfloat16)
+    ids = torch.randint(0, vocab, (Bc, Tc)).to(dev)
+    norm = torch.nn.RMSNorm(Dc).to(dev, torch.bfloat16)
+    lo, hi = time_shard_bounds(Tc, rank, world)
+    cfg_sh = prb.NewtonConfig(max_iters=2, scan_backend="context_parallel", residual_fail=None)
+    cfg_one = prb.NewtonConfig(max_iters=2, residual_fail=None)
+    keep = {}
+
+    def stack(ids_, cfg):
+        h = emb[ids_].requires_grad_(True)
+        for c in cells:
+            h = h + prb.newton_apply(c, norm(h), cfg)
+        keep["h"] = h.detach()
+        h.float().sum().backward()
+
+    def sharded():
+        stack(ids[:, lo:hi], cfg_sh)
+
+    n_steps = max(3, min(args.steps, 10))
+    for _ in range(3):
+        sharded()
+    sec = _max_over_ranks(dist, dev, time_region(sharded, n_steps, None, barrier)) / n_steps
+    h_all = gather_time(dist, dev, world, keep["h"][0, :, :PARITY_CH].float().contiguous())
+    record = None
+    if rank == 0:
+        def one_gpu():
+            stack(ids, cfg_one)
+
+        for _ in range(3):
+            one_gpu()
+        one_sec = time_region(one_gpu, n_steps, None) / n_steps
+        h_one = keep["h"][0, :, :PARITY_CH].float()
+        rel = float((h_all - h_one).abs().max() / h_one.abs().max())
+        record = {"workload": f"{layers} x ParaNLRU d={Dc} bf16 B={Bc} T={Tc} K=2 pre-norm residual stack, "
+                              "forward + backward through newton_apply (layer boundary)",
+                  "n_gpus": world, "ms_per_step": sec * 1e3, "tokens_per_s": Bc * Tc / sec,
+                  "one_gpu_ms_per_step": one_sec * 1e3, "one_gpu_tokens_per_s": Bc * Tc / one_sec,
+                  "speedup": one_sec / sec, "sharded_vs_one_gpu_max_rel_out": rel, "tol": PARITY_TOL}
+        assert rel <= PARITY_TOL, record
+    for c in cells:
+        c.zero_grad(set_to_none=True)
+    barrier()
+    return record
 
 
 def run_secondary(args):
@@ -748,12 +1026,16 @@ def main():
     ap.add_argument("--seq-len", type=int, default=T_PER_GPU,
                     help="time steps per GPU (profiling captures use a smaller case)")
     ap.add_argument("--first-shard-weight", type=float, default=1.0,
-                    help="N > 1: length of the first time shard relative to the others (measured at "
-                         "N = 2: 11.35 / 10.75 / 11.04 ms per step for 1.0 / 1.8 / 2.2)")
+                    help="N > 1: length of the first time shard relative to the others")
     ap.add_argument("--workload", default="c2", choices=("c2", "c1", "c3", "c5"),
                     help="c2 (default) is the headline line; the others print secondary lines")
+    ap.add_argument("--c4-seq-len", type=int, default=0,
+                    help="N > 1: sequence length of the c4_strong sub-record (default 131072)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the 3-second sustained leg")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="N > 1: skip the c4_strong and c5_sharded sub-records")
     args = ap.parse_args()
     T_PER_GPU = args.seq_len
     if args.impl == "reference":

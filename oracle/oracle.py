@@ -185,6 +185,49 @@ def backward(kind, states, wx, params, grad_states, h0=None, *, n_heads=1, eps=1
     return g_wx, g_params, g_h0
 
 
+# ---- packed batches (cu_seqlens): every sequence is its own scan from its own h0 row, nothing
+# crosses a segment head (reference layout.py:93-138, prepend_state_ragged).  wx is (1, N, G*d).
+
+def _segments(cu_seqlens, T):
+    cs = [int(v) for v in np.asarray(cu_seqlens).reshape(-1)]
+    assert cs[0] == 0 and cs[-1] == T and all(b > a for a, b in zip(cs[:-1], cs[1:])), cs
+    return list(zip(cs[:-1], cs[1:]))
+
+
+def _row(h0, i):
+    return None if h0 is None else np.ascontiguousarray(np.asarray(h0)[i:i + 1])
+
+
+def sequential_packed(kind, wx, params, h0, cu_seqlens, **kw):
+    segs = _segments(cu_seqlens, wx.shape[1])
+    return np.concatenate([sequential(kind, np.ascontiguousarray(wx[:, a:b]), params, _row(h0, i), **kw)
+                           for i, (a, b) in enumerate(segs)], axis=1)
+
+
+def newton_packed(kind, wx, params, h0, cu_seqlens, **kw) -> NewtonResult:
+    """The reference evaluates one residual maximum over the whole pack per iteration, so the
+    per-segment histories are merged with max."""
+    segs = _segments(cu_seqlens, wx.shape[1])
+    parts = [newton(kind, np.ascontiguousarray(wx[:, a:b]), params, _row(h0, i), **kw)
+             for i, (a, b) in enumerate(segs)]
+    n = max(len(p.history) for p in parts)
+    hist = tuple(max(p.history[k] for p in parts if len(p.history) > k) for k in range(n))
+    return NewtonResult(np.concatenate([p.states for p in parts], axis=1), max(p.iters for p in parts),
+                        max(p.max_residual for p in parts), hist)
+
+
+def backward_packed(kind, states, wx, params, grad_states, h0, cu_seqlens, **kw):
+    segs = _segments(cu_seqlens, wx.shape[1])
+    g_wx, g_par, heads = [], None, []
+    for i, (a, b) in enumerate(segs):
+        gw, gp, gh = backward(kind, np.ascontiguousarray(states[:, a:b]), np.ascontiguousarray(wx[:, a:b]),
+                              params, np.ascontiguousarray(grad_states[:, a:b]), _row(h0, i), **kw)
+        g_wx.append(gw)
+        heads.append(gh)
+        g_par = gp if g_par is None else g_par + gp
+    return np.concatenate(g_wx, axis=1), g_par, np.concatenate(heads, axis=0)
+
+
 def time_shard_bounds(T: int, world: int, rank: int) -> tuple[int, int]:
     s, e = ctypes.c_int(0), ctypes.c_int(0)
     _lib("f32").oracle_time_shard_bounds(T, world, rank, ctypes.byref(s), ctypes.byref(e))

@@ -10,7 +10,7 @@ import torch
 from torch import Tensor
 
 from . import _lib as L
-from .ops import (DeviceStats, _check_cuda, _check_iters, _dtype_code, _ptr, _raise, _reject_packed,
+from .ops import (DeviceStats, _check_cuda, _check_iters, _dtype_code, _ptr, _raise,
                   _same, _stream, _workspace)
 
 
@@ -31,7 +31,9 @@ def newton_gru_head_fused(wx: Tensor, a_z: Tensor, a_r: Tensor, a_n: Tensor, h0:
                           cu_seqlens: Tensor | None = None, *, max_iters: int, omega: float = 1.0,
                           stats: DeviceStats | None = None, want_residual: bool = True) -> Tensor:
     """Fused Newton for ``ParaGRU(mix='head')``: ``wx (B,T,3d)`` -> ``H (B,T,d)`` in ``wx.dtype``."""
-    _reject_packed(cu_seqlens, None)
+    if cu_seqlens is not None:
+        # same rule as the reference's dispatcher (kernels/custom_ops.py:323-328)
+        raise TypeError("ParaGRU(mix='head') takes rectangular batches only: pad the packed sequences")
     dev = _check_cuda(wx, a_z, a_r, a_n, h0)
     _check_iters(max_iters)
     B, T, d, H = _head_shape(wx, a_z)

@@ -91,19 +91,21 @@ def _recurrent_params(cell: nn.Module, kind: str):
 
 # --------------------------------------------------------------------------- forward
 
-def _solve_window(cell, kind, wx, h0, cfg, dstats, want_residual):
+def _solve_window(cell, kind, wx, h0, cfg, dstats, want_residual, cu_seqlens=None, block_table=None):
     rec = _recurrent_params(cell, kind)
     K = int(cfg.max_iters)
     if kind == "gru_diag":
-        return ops.newton_gru_fused(wx, *rec, h0, max_iters=K, omega=cfg.omega, stats=dstats,
-                                    want_residual=want_residual)
+        return ops.newton_gru_fused(wx, *rec, h0, cu_seqlens, block_table, max_iters=K, omega=cfg.omega,
+                                    stats=dstats, want_residual=want_residual)
     if kind == "nlru":
-        return ops.newton_nlru_fused(wx, rec[0], h0, max_iters=K, omega=cfg.omega, stats=dstats,
-                                     want_residual=want_residual)
+        return ops.newton_nlru_fused(wx, rec[0], h0, cu_seqlens, block_table, max_iters=K, omega=cfg.omega,
+                                     stats=dstats, want_residual=want_residual)
     if kind == "slstm_diag":
-        return ops.newton_slstm_fused(wx, rec[0], h0, max_iters=K, omega=cfg.omega,
+        return ops.newton_slstm_fused(wx, rec[0], h0, None, block_table, max_iters=K, omega=cfg.omega,
                                       eps=float(cell.eps), picard_iters=int(cfg.picard_iters or 0),
-                                      stats=dstats, want_residual=want_residual)
+                                      stats=dstats, want_residual=want_residual, cu_seqlens=cu_seqlens)
+    if cu_seqlens is not None or block_table is not None:
+        raise TypeError("ParaGRU(mix='head') takes rectangular batches with a dense h0 only")
     from . import head_ops
 
     return head_ops.newton_gru_head_fused(wx, *rec, h0, max_iters=K, omega=cfg.omega, stats=dstats,
@@ -150,7 +152,7 @@ def _emulated_iters(hist, cfg) -> int:
     return int(cfg.max_iters)
 
 
-def _forward_once(cell, kind, x, cfg, h0, stats, wx=None):
+def _forward_once(cell, kind, x, cfg, h0, stats, wx=None, cu_seqlens=None, block_table=None):
     """One full solve (all windows); returns ``(states, wx)``.  Reads the device statistics
     only when somebody consumes them."""
     if wx is None:
@@ -159,7 +161,7 @@ def _forward_once(cell, kind, x, cfg, h0, stats, wx=None):
     K = int(cfg.max_iters)
     if cfg.chunk_len is None:
         ds = ops.DeviceStats(x.device, K)
-        states = _solve_window(cell, kind, wx, h0, cfg, ds, need_stats)
+        states = _solve_window(cell, kind, wx, h0, cfg, ds, need_stats, cu_seqlens, block_table)
         if need_stats:
             hist, res, status = ds.read()
             ops.check_pending_backward()
@@ -188,15 +190,16 @@ def _forward_once(cell, kind, x, cfg, h0, stats, wx=None):
     return states, wx
 
 
-def _forward(cell, kind, x, cfg, h0, stats):
+def _forward(cell, kind, x, cfg, h0, stats, cu_seqlens=None, block_table=None):
     if not (cfg.picard_adapt and kind == "slstm_diag"):
-        return _forward_once(cell, kind, x, cfg, h0, stats)
+        return _forward_once(cell, kind, x, cfg, h0, stats, cu_seqlens=cu_seqlens, block_table=block_table)
     # Picard retry ladder: re-run at the next rung while the residual is outside the basin
     cur = cfg
     wx = None
     while True:
         st = stats if stats is not None else NewtonStats()
-        states, wx = _forward_once(cell, kind, x, replace(cur, residual_fail=None), h0, st, wx=wx)
+        states, wx = _forward_once(cell, kind, x, replace(cur, residual_fail=None), h0, st, wx=wx,
+                                   cu_seqlens=cu_seqlens, block_table=block_table)
         res = st.max_residual
         nxt = slstm_picard_next(int(cur.picard_iters or 0))
         retry = (not math.isfinite(res)
@@ -236,9 +239,23 @@ def _reverse_window(cell, kind, states, wx, grad_states, h0):
     return g_wx, {"A_z": gz, "A_r": gr, "A_n": gn}, g_h0
 
 
-def _backward(cell, kind, states, x, wx, grad_states, h0, chunk_len):
+def _backward(cell, kind, states, x, wx, grad_states, h0, chunk_len, cu_seqlens=None):
     """``(grad_x, grad_h0, {name: grad})`` — eq. 2.6 + packed VJP + the W_x GEMMs."""
-    if chunk_len is None:
+    if cu_seqlens is not None:
+        # packed sequences: independent reverse scans, grad_h0 (S, ...) row by row
+        cs = ops.validate_cu_seqlens(cu_seqlens, x.shape[1])
+        g_wx = torch.empty_like(wx)
+        rec_grads, heads = {}, []
+        for i in range(len(cs) - 1):
+            lo, hi = cs[i], cs[i + 1]
+            g_piece, rg, head = _reverse_window(cell, kind, states[:, lo:hi], wx[:, lo:hi],
+                                                grad_states[:, lo:hi], None if h0 is None else h0[i:i + 1])
+            g_wx[:, lo:hi] = g_piece
+            heads.append(head)
+            for k, v in rg.items():
+                rec_grads[k] = v if k not in rec_grads else rec_grads[k] + v
+        g_h0 = torch.cat(heads, dim=0)
+    elif chunk_len is None:
         g_wx, rec_grads, g_h0 = _reverse_window(cell, kind, states, wx, grad_states, h0)
     else:
         # same windows as the forward, walked backwards; grad_h0 of window i+1 is added to
@@ -284,12 +301,12 @@ class _NewtonFixedPoint(torch.autograd.Function):
     ``(grad_x, grad_h0, *param_grads)`` in ``cell.named_parameters()`` order."""
 
     @staticmethod
-    def forward(ctx, cell, kind, cfg, stats, has_h0, x_in, h0_in, *params):
+    def forward(ctx, cell, kind, cfg, stats, has_h0, cu_seqlens, x_in, h0_in, *params):
         del params
         h0 = h0_in if has_h0 else None
         with torch.no_grad():
-            states, wx = _forward(cell, kind, x_in, cfg, h0, stats)
-        ctx.cell, ctx.kind, ctx.cfg, ctx.has_h0 = cell, kind, cfg, has_h0
+            states, wx = _forward(cell, kind, x_in, cfg, h0, stats, cu_seqlens=cu_seqlens)
+        ctx.cell, ctx.kind, ctx.cfg, ctx.has_h0, ctx.cu_seqlens = cell, kind, cfg, has_h0, cu_seqlens
         if cfg.recompute:
             ctx.save_for_backward(x_in, h0_in)
         else:
@@ -304,13 +321,14 @@ class _NewtonFixedPoint(torch.autograd.Function):
             h0 = h0_in if ctx.has_h0 else None
             with torch.no_grad():
                 states, wx = _forward(cell, kind, x_in, replace(cfg, residual_fail=None,
-                                                                 picard_adapt=False), h0, None)
+                                                                 picard_adapt=False), h0, None,
+                                      cu_seqlens=ctx.cu_seqlens)
         else:
             x_in, h0_in, states, wx = ctx.saved_tensors
             h0 = h0_in if ctx.has_h0 else None
         with torch.no_grad():
             grad_x, g_h0, grads = _backward(cell, kind, states, x_in.detach(), wx,
-                                            grad_states, h0, cfg.chunk_len)
+                                            grad_states, h0, cfg.chunk_len, ctx.cu_seqlens)
         out_params = []
         for name, p in cell.named_parameters():
             g = grads.get(name)
@@ -320,7 +338,7 @@ class _NewtonFixedPoint(torch.autograd.Function):
         grad_h0 = None
         if ctx.has_h0 and h0_in.requires_grad and g_h0 is not None:
             grad_h0 = g_h0.to(h0_in.dtype)
-        return (None, None, None, None, None, grad_x, grad_h0, *out_params)
+        return (None, None, None, None, None, None, grad_x, grad_h0, *out_params)
 
 
 def newton_apply(cell: nn.Module, x: Tensor, config: NewtonConfig | None = None, *,
@@ -331,10 +349,23 @@ def newton_apply(cell: nn.Module, x: Tensor, config: NewtonConfig | None = None,
     Same call signature and return layout as the reference's ``newton_apply``:
     ``x (B, T, d_in)`` -> ``H (B, T, *state)`` (``(B,T,d)`` for GRU / NLRU, ``(B,T,4,d)`` for
     sLSTM).  Raises ``NewtonDivergenceError`` when the final ``max|F|`` is non-finite or above
-    ``config.residual_fail``."""
-    if cu_seqlens is not None or block_table is not None:
-        raise NotImplementedError("cu_seqlens / block_table are not covered by the CUDA backend yet")
+    ``config.residual_fail``.
+
+    ``cu_seqlens`` ``(S+1,)``: ``x`` is a packed ``(1, N, d_in)`` batch of S sequences, each its
+    own scan starting from ``h0[s]`` (``h0`` is ``(S, *state)``), differentiable.  ``block_table``
+    ``(B,)`` or ``(S,)``: ``h0`` is a pool ``(C, *state)`` and sequence ``i`` starts from
+    ``h0[block_table[i]]``; inference only, as in the reference
+    (``solvers/newton/__init__.py:286-304``)."""
     cfg, kind = _resolve(cell, x, config or NewtonConfig())
+    if cu_seqlens is not None or block_table is not None:
+        if kind == "gru_head":
+            raise TypeError("ParaGRU(mix='head') takes rectangular batches with a dense h0 only")
+        if cfg.chunk_len is not None:
+            raise ValueError("chunk_len cannot be combined with cu_seqlens / block_table")
+        if cfg.scan_backend == "context_parallel":
+            raise ValueError("cu_seqlens / block_table cannot be combined with scan_backend='context_parallel'")
+    if cu_seqlens is not None and x.shape[0] != 1:
+        raise ValueError(f"cu_seqlens packs x with batch=1, got batch={x.shape[0]}")
     if cfg.scan_backend == "context_parallel":
         from .seq_shard import newton_apply_sharded
 
@@ -349,9 +380,12 @@ def newton_apply(cell: nn.Module, x: Tensor, config: NewtonConfig | None = None,
     has_h0 = h0 is not None
     needs_grad = torch.is_grad_enabled() and (
         x.requires_grad or (has_h0 and h0.requires_grad) or any(p.requires_grad for p in params))
+    if block_table is not None and needs_grad:
+        raise RuntimeError("block_table newton is inference-only")
     with ctx_mgr:
         if not needs_grad:
             with torch.no_grad():
-                return _forward(cell, kind, x, cfg, h0, stats)[0]
+                return _forward(cell, kind, x, cfg, h0, stats, cu_seqlens=cu_seqlens,
+                                block_table=block_table)[0]
         h0_leaf = h0 if has_h0 else x.new_zeros(())
-        return _NewtonFixedPoint.apply(cell, kind, cfg, stats, has_h0, x, h0_leaf, *params)
+        return _NewtonFixedPoint.apply(cell, kind, cfg, stats, has_h0, cu_seqlens, x, h0_leaf, *params)

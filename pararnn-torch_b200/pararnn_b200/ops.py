@@ -78,18 +78,38 @@ def _raise(code: int, what: str) -> None:
 
 
 class DeviceStats:
-    """Handle on the device-side statistics block of one forward call."""
+    """Handle on the device-side statistics block of one forward call.  A packed (``cu_seqlens``)
+    call solves its segments one after the other; their blocks hang off ``parts`` and ``read``
+    merges them (max over segments, NaN wins, as one solve over the packed batch would report)."""
 
     def __init__(self, device, max_iters: int):
         self.buf = torch.zeros(L.STATS_BYTES, dtype=torch.uint8, device=device)
         self.max_iters = int(max_iters)
+        self.parts: list[DeviceStats] = []
 
-    def read(self) -> tuple[tuple[float, ...], float, int]:
-        """One small device-to-host copy: (residual_history, final max|F|, status)."""
-        raw = bytes(self.buf.cpu().numpy().tobytes())
+    @staticmethod
+    def _unpack(raw: bytes):
         hist = struct.unpack(f"<{L.MAX_ITERS}f", raw[: 4 * L.MAX_ITERS])
         final = struct.unpack("<f", raw[4 * L.MAX_ITERS: 4 * L.MAX_ITERS + 4])[0]
         status = struct.unpack("<i", raw[4 * L.MAX_ITERS + 4: 4 * L.MAX_ITERS + 8])[0]
+        return hist, final, status
+
+    def read(self) -> tuple[tuple[float, ...], float, int]:
+        """One small device-to-host copy: (residual_history, final max|F|, status)."""
+        if not self.parts:
+            hist, final, status = self._unpack(bytes(self.buf.cpu().numpy().tobytes()))
+            return tuple(hist[: self.max_iters]), final, status
+        rows = torch.stack([p.buf for p in self.parts]).cpu().numpy()
+
+        def worse(a, b):
+            return b if (b != b or (a == a and b > a)) else a
+
+        hist, final, status = [0.0] * L.MAX_ITERS, 0.0, 0
+        for row in rows:
+            h, f, st = self._unpack(row.tobytes())
+            hist = [worse(a, b) for a, b in zip(hist, h)]
+            final = worse(final, f)
+            status |= st
         return tuple(hist[: self.max_iters]), final, status
 
 
@@ -124,11 +144,67 @@ def check_pending_backward() -> None:
                     f"(status {status}); the gradients of that backward call are not valid")
 
 
-def _reject_packed(cu_seqlens, block_table) -> None:
-    if cu_seqlens is not None:
-        raise NotImplementedError("packed cu_seqlens batches are not covered by the CUDA backend yet")
-    if block_table is not None:
-        raise NotImplementedError("block_table (paged h0) is not covered by the CUDA backend yet")
+def validate_cu_seqlens(cu_seqlens: Tensor, time: int) -> list[int]:
+    """Exclusive prefix ``(S+1,)`` with ``[0] = 0``, strictly increasing, last ``= time``
+    (same checks and messages as the reference's ``layout.validate_cu_seqlens``,
+    ``layout.py:93-106``).  Returns the offsets as Python ints (one host read)."""
+    if cu_seqlens.dim() != 1 or cu_seqlens.numel() < 2:
+        raise ValueError(f"cu_seqlens must be (S+1,), got {tuple(cu_seqlens.shape)}")
+    cs = [int(v) for v in cu_seqlens.tolist()]
+    if cs[0] != 0:
+        raise ValueError(f"cu_seqlens[0] must be 0, got {cs[0]}")
+    if cs[-1] != int(time):
+        raise ValueError(f"cu_seqlens[-1] must equal time={time}, got {cs[-1]}")
+    if any(b <= a for a, b in zip(cs[:-1], cs[1:])):
+        raise ValueError("cu_seqlens must be strictly increasing")
+    return cs
+
+
+def gather_h0(h0: Tensor | None, block_table: Tensor | None, rows: int, tail: tuple[int, ...]) -> Tensor | None:
+    """Paged initial state: with ``block_table`` (``(rows,)`` slot ids) ``h0`` is a pool
+    ``(C, *tail)`` and row ``i`` of the batch starts from ``h0[block_table[i]]`` (reference
+    ``kernels/_fused_common.py:106-139``, same checks)."""
+    if block_table is None:
+        return h0
+    if h0 is None:
+        raise ValueError("block_table needs h0 as a pool (C, …)")
+    if block_table.dim() != 1:
+        raise ValueError(f"block_table must be 1-D (B,), got {tuple(block_table.shape)}")
+    if int(block_table.numel()) != rows:
+        raise ValueError(f"block_table B={int(block_table.numel())} != {rows}")
+    if tuple(h0.shape[1:]) != tuple(tail):
+        raise ValueError(f"pool h0 tail {tuple(h0.shape[1:])} != {tuple(tail)}")
+    if int(h0.shape[0]) < 1:
+        raise ValueError("pool h0 is empty")
+    bt = block_table.to(device=h0.device, dtype=torch.long)
+    mn, mx = int(bt.min().item()), int(bt.max().item())
+    if mn < 0 or mx >= int(h0.shape[0]):
+        raise ValueError(f"block_table slots [{mn}, {mx}] outside pool capacity {int(h0.shape[0])}")
+    return h0.index_select(0, bt)
+
+
+def _packed(fn, wx: Tensor, h0: Tensor | None, cu_seqlens: Tensor, block_table: Tensor | None,
+            tail: tuple[int, ...], stats: "DeviceStats | None", states: Tensor | None = None) -> Tensor:
+    """A packed batch ``(1, N, ...)`` of S sequences (``cu_seqlens``): every sequence is its own
+    scan with its own initial state ``h0[s]`` and nothing carried over the segment heads
+    (reference ``layout.py:121-138``, ``kernels/newton_gru.py:205-236``).  The segments are solved
+    one after the other with the rectangular kernels; ``fn(wx_seg, h0_seg, stats_seg, guess_seg)``."""
+    if wx.shape[0] != 1:
+        raise ValueError(f"cu_seqlens packs x with batch=1, got batch={wx.shape[0]}")
+    cs = validate_cu_seqlens(cu_seqlens, wx.shape[1])
+    n_seq = len(cs) - 1
+    h0 = gather_h0(h0, block_table, n_seq, tail)
+    if h0 is not None and h0.shape[0] != n_seq:
+        raise ValueError(f"h0 batch {h0.shape[0]} != n_seq {n_seq}")
+    outs = []
+    for i in range(n_seq):
+        st = None
+        if stats is not None:
+            st = DeviceStats(wx.device, stats.max_iters)
+            stats.parts.append(st)
+        outs.append(fn(wx[:, cs[i]:cs[i + 1]], None if h0 is None else h0[i:i + 1], st,
+                       None if states is None else states[:, cs[i]:cs[i + 1]]))
+    return torch.cat(outs, dim=1)
 
 
 def _check_iters(max_iters: int) -> None:
@@ -142,8 +218,17 @@ def newton_gru_fused(wx: Tensor, a_z: Tensor, a_r: Tensor, a_n: Tensor, h0: Tens
                      cu_seqlens: Tensor | None = None, block_table: Tensor | None = None, *,
                      max_iters: int, omega: float = 1.0, stats: DeviceStats | None = None,
                      want_residual: bool = True) -> Tensor:
-    """Fused Newton for ``ParaGRU(mix='diag')``: ``wx (B,T,3d)`` -> ``H (B,T,d)`` in ``wx.dtype``."""
-    _reject_packed(cu_seqlens, block_table)
+    """Fused Newton for ``ParaGRU(mix='diag')``: ``wx (B,T,3d)`` -> ``H (B,T,d)`` in ``wx.dtype``.
+    With ``cu_seqlens`` ``wx`` is a packed ``(1, N, 3d)`` batch and ``h0`` is ``(S, d)``; with
+    ``block_table`` ``h0`` is a pool ``(C, d)``."""
+    if cu_seqlens is not None:
+        if stats is not None:
+            stats.parts.clear()
+        return _packed(lambda w, h, st, _g: newton_gru_fused(w, a_z, a_r, a_n, h, max_iters=max_iters,
+                                                              omega=omega, stats=st,
+                                                              want_residual=want_residual),
+                       wx, h0, cu_seqlens, block_table, (a_z.numel(),), stats)
+    h0 = gather_h0(h0, block_table, wx.shape[0], (a_z.numel(),))
     dev = _check_cuda(wx, a_z, a_r, a_n, h0)
     _check_iters(max_iters)
     if wx.dim() != 3 or wx.shape[-1] % 3:
@@ -178,8 +263,15 @@ def newton_nlru_fused(wx: Tensor, u: Tensor, h0: Tensor | None = None,
                       cu_seqlens: Tensor | None = None, block_table: Tensor | None = None, *,
                       max_iters: int, omega: float = 1.0, stats: DeviceStats | None = None,
                       want_residual: bool = True) -> Tensor:
-    """Fused Newton for ``ParaNLRU``: ``wx (B,T,2d)`` -> ``H (B,T,d)``."""
-    _reject_packed(cu_seqlens, block_table)
+    """Fused Newton for ``ParaNLRU``: ``wx (B,T,2d)`` -> ``H (B,T,d)``.  ``cu_seqlens`` /
+    ``block_table`` as in ``newton_gru_fused``."""
+    if cu_seqlens is not None:
+        if stats is not None:
+            stats.parts.clear()
+        return _packed(lambda w, h, st, _g: newton_nlru_fused(w, u, h, max_iters=max_iters, omega=omega,
+                                                               stats=st, want_residual=want_residual),
+                       wx, h0, cu_seqlens, block_table, (u.numel(),), stats)
+    h0 = gather_h0(h0, block_table, wx.shape[0], (u.numel(),))
     dev = _check_cuda(wx, u, h0)
     _check_iters(max_iters)
     if wx.dim() != 3 or wx.shape[-1] % 2:
@@ -213,18 +305,26 @@ def newton_slstm_fused(wx: Tensor, r: Tensor, h0: Tensor | None = None,
                        max_iters: int, omega: float = 1.0, eps: float = 1e-6,
                        log_coords: bool = False, scan_tile: str = "assoc", time_loop: bool = False,
                        window_len: int = 0, picard_iters: int = 0,
-                       stats: DeviceStats | None = None, want_residual: bool = True) -> Tensor:
+                       stats: DeviceStats | None = None, want_residual: bool = True,
+                       cu_seqlens: Tensor | None = None) -> Tensor:
     """Fused Newton for ``ParaSLSTM(mix='diag')``: ``wx (B,T,4d)`` -> ``H (B,T,4,d)``.
 
     ``states`` is an optional initial guess (cloned, never modified).  Without it the
     kernel runs the zero-hidden frozen-gate scan followed by ``picard_iters`` Picard
     passes itself (the reference does this in ``slstm_picard_init`` before calling its op).
     """
-    _reject_packed(None, block_table)
     if log_coords:
         raise TypeError("coords='log' is not covered by the CUDA backend")
     if scan_tile != "assoc" or time_loop or window_len:
         raise TypeError("scan_tile / fused_time_loop / fused_window_len ablations are not available")
+    if cu_seqlens is not None:
+        if stats is not None:
+            stats.parts.clear()
+        return _packed(lambda w, h, st, g: newton_slstm_fused(w, r, h, g, max_iters=max_iters, omega=omega,
+                                                               eps=eps, picard_iters=picard_iters, stats=st,
+                                                               want_residual=want_residual),
+                       wx, h0, cu_seqlens, block_table, (4, r.shape[-1]), stats, states)
+    h0 = gather_h0(h0, block_table, wx.shape[0], (4, r.shape[-1]))
     dev = _check_cuda(wx, r, h0, states)
     _check_iters(max_iters)
     if wx.dim() != 3 or wx.shape[-1] % 4:

@@ -13,7 +13,16 @@ from .cells import zero_state
 def sequential_apply(cell: nn.Module, x: Tensor, h0: Tensor | None = None, *, step=None,
                      cu_seqlens: Tensor | None = None) -> Tensor:
     if cu_seqlens is not None:
-        raise NotImplementedError("packed cu_seqlens batches are not covered yet")
+        # packed (1, N, d_in): every sequence unrolled on its own from its own h0 row
+        from .ops import validate_cu_seqlens
+
+        if x.shape[0] != 1:
+            raise ValueError(f"cu_seqlens packs x with batch=1, got batch={x.shape[0]}")
+        cs = validate_cu_seqlens(cu_seqlens, x.shape[1])
+        if h0 is not None and h0.shape[0] != len(cs) - 1:
+            raise ValueError(f"h0 batch {h0.shape[0]} != n_seq {len(cs) - 1}")
+        return torch.cat([sequential_apply(cell, x[:, a:b], None if h0 is None else h0[i:i + 1], step=step)
+                          for i, (a, b) in enumerate(zip(cs[:-1], cs[1:]))], dim=1)
     batch, time, _ = x.shape
     if time < 1:
         raise ValueError(f"sequential_apply needs time >= 1, got {time}")

@@ -28,7 +28,7 @@ def _np(t):
     return None if t is None else t.detach().cpu().numpy()
 
 
-def run_case(name, cell, x, *, K, P=None, h0=None, omega=1.0):
+def run_case(name, cell, x, *, K, P=None, h0=None, omega=1.0, cu_seqlens=None):
     from pararnn import NewtonConfig, NewtonStats, newton_apply, sequential_apply
 
     torch.manual_seed(1234)
@@ -41,11 +41,17 @@ def run_case(name, cell, x, *, K, P=None, h0=None, omega=1.0):
         max_iters=K, scan_backend="eager", picard_iters=P, picard_adapt=False, omega=omega,
         residual_atol=1e-30, residual_fail=None,
     )
-    H = newton_apply(cell, x, cfg, h0=h0, stats=st)
+    cs = None if cu_seqlens is None else torch.tensor(cu_seqlens, dtype=torch.long)
+    H = newton_apply(cell, x, cfg, h0=h0, stats=st, cu_seqlens=cs)
     G = torch.randn_like(H)
     (H * G).sum().backward()
     with torch.no_grad():
-        H_seq = sequential_apply(cell, x.detach(), None if h0 is None else h0.detach())
+        if cs is None:
+            H_seq = sequential_apply(cell, x.detach(), None if h0 is None else h0.detach())
+        else:  # packed: every sequence unrolled on its own from its own h0 row
+            H_seq = torch.cat([sequential_apply(cell, x.detach()[:, a:b],
+                                                None if h0 is None else h0.detach()[i:i + 1])
+                               for i, (a, b) in enumerate(zip(cu_seqlens[:-1], cu_seqlens[1:]))], dim=1)
         wx = cell.W_x(x.detach())
     out = {
         "x": _np(x), "wx": _np(wx), "W": _np(cell.W_x.weight), "b": _np(cell.W_x.bias),
@@ -59,6 +65,8 @@ def run_case(name, cell, x, *, K, P=None, h0=None, omega=1.0):
     if h0 is not None:
         out["h0"] = _np(h0)
         out["g_h0"] = _np(h0.grad)
+    if cs is not None:
+        out["cu_seqlens"] = np.asarray(cu_seqlens, dtype=np.int64)
     kind = type(cell).__name__
     if kind == "ParaGRU" and cell.mix == "diag":
         az, ar, an = cell.clipped_a()
@@ -156,6 +164,29 @@ def main():
                 torch.nn.init.orthogonal_(A[hd], gain=0.9)
     run_case("gru_head_k3", cell, torch.randn(2, 48, 16), K=3)
     run_case("gru_head_k2_h0", cell, torch.randn(2, 17, 16), K=2, h0=0.5 * torch.randn(2, 16))
+
+    # --- packed batches (cu_seqlens): ragged sequences, one of length 1, own h0 per sequence ---
+    torch.manual_seed(20)
+    cell = ParaGRU(12, 16)
+    with torch.no_grad():
+        torch.nn.init.xavier_uniform_(cell.W_x.weight)
+    run_case("gru_diag_packed_k3_h0", cell, torch.randn(1, 61, 12), K=3, h0=0.5 * torch.randn(4, 16),
+             cu_seqlens=[0, 7, 8, 40, 61])
+    torch.manual_seed(21)
+    cell = ParaNLRU(10, 12)
+    with torch.no_grad():
+        a0 = torch.empty(12).uniform_(0.9, 0.999)
+        cell.W_x.bias[:12] = torch.log(a0 / (1 - a0))
+    run_case("nlru_packed_k2", cell, torch.randn(1, 50, 10), K=2, cu_seqlens=[0, 1, 20, 50])
+    torch.manual_seed(22)
+    cell = ParaSLSTM(8, 8, mix="diag")
+    with torch.no_grad():
+        torch.nn.init.xavier_uniform_(cell.W_x.weight)
+        cell.W_x.bias[8:16] = 1.0
+    run_case("slstm_packed_p2_k2_h0", cell, 0.6 * torch.randn(1, 45, 8), K=2, P=2,
+             h0=torch.stack([0.3 * torch.randn(3, 8), torch.rand(3, 8) + 0.5,
+                             0.2 * torch.randn(3, 8), 0.3 * torch.randn(3, 8)], dim=1),
+             cu_seqlens=[0, 16, 17, 45])
 
 
 if __name__ == "__main__":

@@ -26,7 +26,23 @@ def load_golden(name):
     g["eps"] = float(g.get("eps", 1e-6))
     g["n_heads"] = int(g.get("n_heads", 1))
     g.setdefault("h0", None)
+    g.setdefault("cu_seqlens", None)
     return g
+
+
+def oracle_calls(g):
+    """(sequential, newton, backward) of the oracle for a fixture: the packed variants when the
+    fixture carries ``cu_seqlens``."""
+    from functools import partial
+
+    from oracle import oracle
+
+    if g["cu_seqlens"] is None:
+        return oracle.sequential, oracle.newton, oracle.backward
+    cs = g["cu_seqlens"]
+    return (lambda kind, wx, params, h0, **kw: oracle.sequential_packed(kind, wx, params, h0, cs, **kw),
+            lambda kind, wx, params, h0, **kw: oracle.newton_packed(kind, wx, params, h0, cs, **kw),
+            lambda kind, st, wx, params, G, h0, **kw: oracle.backward_packed(kind, st, wx, params, G, h0, cs, **kw))
 
 
 def linear_grads(g_wx, x, W):

@@ -20,7 +20,8 @@ def test_newton_apply_and_grads_match_reference(name):
     st = prb.NewtonStats()
     cfg = prb.NewtonConfig(max_iters=g["K"], picard_iters=g["P"] if g["cell"] == "slstm_diag" else None,
                            picard_adapt=False, omega=g["omega"], residual_fail=None)
-    H = prb.newton_apply(cell, x, cfg, h0=h0, stats=st)
+    cs = None if g["cu_seqlens"] is None else torch.from_numpy(g["cu_seqlens"]).cuda()
+    H = prb.newton_apply(cell, x, cfg, h0=h0, stats=st, cu_seqlens=cs)
     amp = max(1.0, float(np.max(g["history"])))
     assert np.abs(H.detach().cpu().numpy() - g["H"]).max() <= 2e-5 * amp * max(1.0, np.abs(g["H"]).max())
     assert st.iters == g["K"] and st.scan_backend == "fused"

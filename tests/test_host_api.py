@@ -41,8 +41,9 @@ def test_sequential_apply_matches_reference(name):
     g = load_golden(name)
     cell = _cell_from_golden(g)
     h0 = None if g["h0"] is None else torch.from_numpy(g["h0"])
+    cs = None if g["cu_seqlens"] is None else torch.from_numpy(g["cu_seqlens"])
     with torch.no_grad():
-        H = prb.sequential_apply(cell, torch.from_numpy(g["x"]), h0).numpy()
+        H = prb.sequential_apply(cell, torch.from_numpy(g["x"]), h0, cu_seqlens=cs).numpy()
     scale = max(1.0, float(np.abs(g["H_seq"]).max()))
     assert np.abs(H - g["H_seq"]).max() <= 2e-6 * scale
 

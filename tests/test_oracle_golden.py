@@ -3,21 +3,21 @@
 import numpy as np
 import pytest
 
-from golden_util import clip_mask, golden_names, linear_grads, load_golden
+from golden_util import clip_mask, golden_names, linear_grads, load_golden, oracle_calls
 from oracle import oracle
 
 NAMES = golden_names()
 
 
 def test_fixtures_present():
-    assert len(NAMES) >= 11
+    assert len(NAMES) >= 14
 
 
 @pytest.mark.parametrize("name", NAMES)
 def test_sequential_matches_reference(name):
     g = load_golden(name)
     kind = oracle.KIND[g["cell"]]
-    H = oracle.sequential(kind, g["wx"], g["params"], g["h0"], n_heads=g["n_heads"], eps=g["eps"])
+    H = oracle_calls(g)[0](kind, g["wx"], g["params"], g["h0"], n_heads=g["n_heads"], eps=g["eps"])
     scale = max(1.0, float(np.abs(g["H_seq"]).max()))
     assert np.abs(H - g["H_seq"]).max() <= 2e-6 * scale
 
@@ -26,7 +26,7 @@ def test_sequential_matches_reference(name):
 def test_newton_matches_reference_eager(name):
     g = load_golden(name)
     kind = oracle.KIND[g["cell"]]
-    r = oracle.newton(kind, g["wx"], g["params"], g["h0"], n_heads=g["n_heads"], max_iters=g["K"],
+    r = oracle_calls(g)[1](kind, g["wx"], g["params"], g["h0"], n_heads=g["n_heads"], max_iters=g["K"],
                       picard=g["P"], omega=g["omega"], eps=g["eps"],
                       early_atol=1e-30 if g["iters"] < g["K"] else None)
     assert r.iters == g["iters"]
@@ -43,8 +43,8 @@ def test_newton_matches_reference_eager(name):
 def test_backward_matches_reference_autograd(name):
     g = load_golden(name)
     kind = oracle.KIND[g["cell"]]
-    g_wx, g_params, g_h0 = oracle.backward(kind, g["H"], g["wx"], g["params"], g["G"], g["h0"],
-                                           n_heads=g["n_heads"], eps=g["eps"])
+    g_wx, g_params, g_h0 = oracle_calls(g)[2](kind, g["H"], g["wx"], g["params"], g["G"], g["h0"],
+                                              n_heads=g["n_heads"], eps=g["eps"])
     gx, gW, gb = linear_grads(g_wx, g["x"], g["W"])
     for got, want in ((gx, g["g_x"]), (gW, g["g_W"]), (gb, g["g_b"])):
         tol = 2e-5 * max(1.0, float(np.abs(want).max()))
@@ -61,9 +61,9 @@ def test_backward_matches_reference_autograd(name):
 def test_f64_build_agrees_with_f32(name):
     g = load_golden(name)
     kind = oracle.KIND[g["cell"]]
-    a = oracle.sequential(kind, g["wx"], g["params"], g["h0"], n_heads=g["n_heads"], eps=g["eps"])
-    b = oracle.sequential(kind, g["wx"], g["params"], g["h0"], n_heads=g["n_heads"], eps=g["eps"],
-                          prec="f64")
+    seq = oracle_calls(g)[0]
+    a = seq(kind, g["wx"], g["params"], g["h0"], n_heads=g["n_heads"], eps=g["eps"])
+    b = seq(kind, g["wx"], g["params"], g["h0"], n_heads=g["n_heads"], eps=g["eps"], prec="f64")
     scale = max(1.0, float(np.abs(b).max()))
     assert np.abs(a - b).max() <= 5e-5 * scale
 
