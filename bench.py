@@ -365,6 +365,27 @@ def kernel_rooflines(wx, r32, states32, states_io, G_io, peak):
                                     P(st.buf), stream)
         assert rc == 0, rc
 
+    agg_n = torch.empty(1, B, 20, D, dtype=torch.float32, device=dev)
+    agg_p = torch.empty(1, B, 4, D, dtype=torch.float32, device=dev)
+
+    def newton_agg():
+        rc = lib.prb_slstm_newton_pass(P(wx), P(r32), P(states32), None, None, None, None, P(agg_n), 2, 1,
+                                       T_PER_GPU, B, T_PER_GPU, D, L.PRB_BF16, 1.0, 1e-6, P(ws), ws.numel(),
+                                       P(st.buf), 0, stream)
+        assert rc == 0, rc
+
+    def picard_agg():
+        rc = lib.prb_slstm_picard_pass(P(wx), P(r32), P(hbuf), None, None, None, None, None, P(agg_p), 2,
+                                       1, T_PER_GPU, B, T_PER_GPU, D, L.PRB_BF16, 1e-6, P(ws), ws.numel(),
+                                       P(st.buf), stream)
+        assert rc == 0, rc
+
+    def bwd_agg():
+        rc = lib.prb_slstm_bwd_pass(P(states_io), P(wx), P(r32), None, None, P(G_io), None, None, None,
+                                    P(agg_n), 2, 1, T_PER_GPU, B, T_PER_GPU, D, L.PRB_BF16, 1e-6, P(ws),
+                                    ws.numel(), P(st.buf), stream)
+        assert rc == 0, rc
+
     n_units = B * T_PER_GPU * D
     out = {}
     # One training step = 1 fused Picard sweep + 1 fused Newton sweep (K iterations and the final
@@ -375,7 +396,11 @@ def kernel_rooflines(wx, r32, states32, states_io, G_io, peak):
                                        ("slstm_bwd_pipe_kernel", bwd, BYTES_BWD, 1),
                                        ("slstm_picard_pipe_kernel", picard, BYTES_PICARD_MID, 0),
                                        ("slstm_newton_pipe_kernel", newton, BYTES_NEWTON_MID, 0),
-                                       ("slstm_newton_pipe_kernel_last", newton_last, BYTES_NEWTON_LAST, 0)):
+                                       ("slstm_newton_pipe_kernel_last", newton_last, BYTES_NEWTON_LAST, 0),
+                                       # aggregate-only sweeps of the time-sharded path: inputs only
+                                       ("slstm_picard_agg_seg_kernel", picard_agg, 4 * 2 + 4, 0),
+                                       ("slstm_newton_agg_seg_kernel", newton_agg, 4 * 2 + 16, 0),
+                                       ("slstm_bwd_agg_seg_kernel", bwd_agg, 4 * 2 * 3, 0)):
         for _ in range(3):
             fn()
         sec = time_region(fn, 10, None) / 10
@@ -566,8 +591,8 @@ def run_gpu_sharded(args):
     import torch.distributed as dist
 
     import pararnn_b200 as prb
-    from pararnn_b200.seq_shard import (CudaShardOps, DistComm, _bits_to_stats, backward_program, drive,
-                                        forward_program)
+    from pararnn_b200.seq_shard import (CudaShardOps, DistComm, GraphedShardedStep, _bits_to_stats,
+                                        backward_program, drive, forward_program)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -619,14 +644,27 @@ def run_gpu_sharded(args):
 
     for _ in range(max(args.warmup, 3)):
         step()
+    eager_sec = _max_over_ranks(dist, dev, time_region(step, args.steps, None, barrier))
+    # The timed step: the same programs captured once into a CUDA graph (kernels, device-side
+    # folds and the NCCL all-gathers) and replayed, which removes the host's per-launch cost.
+    graphed = not args.no_graph
+    if graphed:
+        gs = GraphedShardedStep("slstm_diag", wx, rec, G_io, comm, K=K_NEWTON, P=P_PICARD)
+        timed_step = gs.replay
+        for _ in range(3):
+            timed_step()
+    else:
+        timed_step = step
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    sec = time_region(step, args.steps, None, barrier)
+    sec = _max_over_ranks(dist, dev, time_region(timed_step, args.steps, None, barrier))
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([sec], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    sec = float(t.item())
+    if graphed:
+        from types import SimpleNamespace
+
+        keep["res"] = SimpleNamespace(states=gs.states, stats_bits=gs.stats_bits)
+        keep["bwd"] = (gs.g_wx, gs.g_params, gs.head)
     hist, res_final, status = _bits_to_stats(keep["res"].stats_bits, K_NEWTON)
 
     # end to end through the public API (host-resident shard of x per rank)
@@ -721,7 +759,10 @@ def run_gpu_sharded(args):
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32 scan arithmetic, bf16 I/O", "data": "synthetic",
-            "config": dict(workload_config(world), shard_lengths=[t_first] + [t_other] * (world - 1)),
+            "config": dict(workload_config(world), shard_lengths=[t_first] + [t_other] * (world - 1),
+                           step="CUDA graph replay of the sharded forward + backward programs" if graphed
+                           else "programs issued from Python"),
+            "eager_ms_per_step": eager_sec / args.steps * 1e3,
             "clocks": clocks,
             "e2e": {"value": tokens / e2e_sec, "unit": "tokens/s",
                     "h2d_bytes_per_step": B * t_total * D * 2, "d2h_bytes_per_step": 4 * world,
@@ -742,9 +783,21 @@ def run_gpu_sharded(args):
                 "workload": f"B={B * world} rows split over the ranks, T={T_PER_GPU}: independent rows, "
                             "fused single-GPU sweeps, all-reduce of grad R only"},
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    # release the captured graphs (they hold NCCL kernels) before the communicator goes away; a
+    # teardown that does not return must not keep the job alive after the line is out
+    gs = None
+    keep.clear()
+    import gc
+
+    gc.collect()
+    torch.cuda.synchronize()
     dist.barrier(device_ids=[local])
+    guard = threading.Timer(60.0, lambda: os._exit(0))
+    guard.daemon = True
+    guard.start()
     dist.destroy_process_group()
+    guard.cancel()
 
 
 def gather_time(dist, dev, world, t):
@@ -819,7 +872,22 @@ def c4_strong_record(args, rank, world, dev, dist, comm, barrier):
     n_steps = max(3, min(args.steps, 10))
     for _ in range(3):
         step()
-    sec = _max_over_ranks(dist, dev, time_region(step, n_steps, None, barrier)) / n_steps
+    eager_sec = _max_over_ranks(dist, dev, time_region(step, n_steps, None, barrier)) / n_steps
+    sec = eager_sec
+    if not args.no_graph:
+        from types import SimpleNamespace
+
+        from pararnn_b200.seq_shard import GraphedShardedStep
+
+        keep.pop("res", None)
+        keep.pop("bwd", None)
+        gs = GraphedShardedStep("slstm_diag", wx, rec, G_io, comm, K=K_NEWTON, P=P_PICARD)
+        for _ in range(3):
+            gs.replay()
+        sec = _max_over_ranks(dist, dev, time_region(gs.replay, n_steps, None, barrier)) / n_steps
+        keep["res"] = SimpleNamespace(states=gs.states, stats_bits=gs.stats_bits)
+        keep["bwd"] = (gs.g_wx, gs.g_params, gs.head)
+        keep["segs"] = (gs.ops.n_seg, gs.ops.seg_len)
     status = _bits_to_stats(keep["res"].stats_bits, K_NEWTON)[2]
 
     # slices of the sharded result to rank 0
@@ -827,7 +895,10 @@ def c4_strong_record(args, rank, world, dev, dist, comm, barrier):
     sl_H = gather_time(dist, dev, world, gate_slice(keep["res"].states[0], Dc).contiguous())
     sl_g = gather_time(dist, dev, world, gate_slice(keep["bwd"][0][0], Dc).contiguous())
     record = None
-    del keep["res"], keep["bwd"], G_io
+    del keep["res"], keep["bwd"]
+    if not args.no_graph:
+        del gs
+    torch.cuda.empty_cache()
     if rank == 0:
         parity = slice_parity(sl_wx, rec[0][:, :PARITY_CH], sl_H, sl_g, Dc, K_NEWTON, P_PICARD)
         # the same sequence on one GPU: rank 0 rebuilds all shards of x
@@ -856,6 +927,8 @@ def c4_strong_record(args, rank, world, dev, dist, comm, barrier):
             "workload": f"ParaSLSTM mix=diag fwd+bwd, B={Bc}, T={Tc}, d={Dc}, bf16 I/O, picard_iters={P_PICARD}, "
                         f"max_iters={K_NEWTON}, seed {seed}; op boundary",
             "n_gpus": world, "ms_per_step": sec * 1e3, "tokens_per_s": Bc * Tc / sec,
+            "eager_ms_per_step": eager_sec * 1e3,
+            "step": "CUDA graph replay" if not args.no_graph else "issued from Python",
             "one_gpu_ms_per_step": one_sec * 1e3, "one_gpu_tokens_per_s": Bc * Tc / one_sec,
             "speedup": one_sec / sec, "segments_per_rank": keep["segs"][0], "segment_steps": keep["segs"][1],
             "status": status, "parity": parity,
@@ -1034,6 +1107,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg")
     ap.add_argument("--no-sustained", action="store_true", help="skip the 3-second sustained leg")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="N > 1: issue the sharded programs from Python instead of replaying a CUDA graph")
     ap.add_argument("--no-extra", action="store_true",
                     help="N > 1: skip the c4_strong and c5_sharded sub-records")
     args = ap.parse_args()

@@ -530,9 +530,13 @@ __global__ void fold_segments_kernel(const float* agg, int n_seg, int reverse, f
     for (int i = 0; i < M::NV; ++i) out[((size_t)b * M::NV + i) * d + ch] = acc[i];
 }
 
+// Segments must tile [0, T) exactly once, and there may be no more of them than time tiles of the
+// look-back kernels: the per-pass workspace holds one parameter-partial row per tile.
 bool bad_segments(int T, int n_seg, int seg_len) {
     if (n_seg < 1 || seg_len < 1) return true;
     if (n_seg == 1) return false;
+    const int tile = slstm_tile_steps() < slstm_picard_tile_steps() ? slstm_tile_steps() : slstm_picard_tile_steps();
+    if (n_seg > (T + tile - 1) / tile) return true;
     return (long long)(n_seg - 1) * seg_len >= T || (long long)n_seg * seg_len < T;
 }
 
@@ -1148,11 +1152,11 @@ int prb_plan_segments(int cell, int dtype, int B, int T, int d, int* n_seg, int*
     *n_seg = 1;
     *seg_len = T;
     if (cell != kCellSlstmDiag || kernel_path(dtype, B, T, d) != 2) return PRB_OK;
-    // aim at two CTAs per SM, keep segments long enough that the two extra tiny launches per
-    // pass (segment fold, segment carries) and the pipeline fill stay negligible
+    // aim at two CTAs per SM in ONE wave, keep segments long enough that the two extra tiny
+    // launches per pass (segment fold, segment carries) and the pipeline fill stay negligible
     const int chains = B * ((d + kLanes - 1) / kLanes);
     const int target = 2 * sm_count();
-    int n = (target + chains - 1) / chains;
+    int n = target / chains;  // rounded down: one CTA more than fits costs a whole second wave
     const int min_len = 1024;
     if (n > T / min_len) n = T / min_len;
     if (n < 2) return PRB_OK;

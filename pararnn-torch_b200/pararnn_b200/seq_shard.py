@@ -185,8 +185,9 @@ class CudaShardOps:
                                                     ctypes.byref(n), ctypes.byref(ln))
                 self._check(rc, "plan_segments")
                 self.n_seg, self.seg_len = n.value, ln.value
-            elif segments > 1 and self.T >= 2:
-                ln = -(-int(self.T) // int(segments))
+            elif segments > 1 and self.T >= 64:
+                # at least 32 steps per segment (the workspace has one partial row per 32 steps)
+                ln = max(32, -(-int(self.T) // int(segments)))
                 self.n_seg, self.seg_len = -(-int(self.T) // ln), ln
 
     # helpers
@@ -467,6 +468,50 @@ def backward_program(ops, rank: int, world: int, states: Tensor, grad_states: Te
     if world > 1:
         g_par = yield ("reduce_sum", g_par)
     return g_wx, g_par, head
+
+
+# ------------------------------------------------------------------------------- graphed step
+
+class GraphedShardedStep:
+    """One rank's forward + backward programs captured ONCE into a CUDA graph and replayed.
+
+    A sharded step is a chain of ~20 short sweeps, ~20 tiny fold kernels and ~10 small NCCL
+    all-gathers; at 8 ranks each sweep lasts 0.1-0.4 ms, so issuing them from Python (ctypes calls,
+    allocations, slicing) costs as much as running them.  The graph holds the kernels of this
+    library, the device-side folds and the collectives (NCCL collectives can be captured), so a
+    replay costs one launch on the host.  Inputs are static: write the next step's ``wx`` and
+    cotangent into ``self.wx`` / ``self.grad_states`` (for example as the ``out=`` of the ``W_x``
+    GEMM) and call ``replay()``; results are in ``self.states``, ``self.g_wx``, ``self.g_params``,
+    ``self.head``.  Every rank must construct and replay it in step with the others."""
+
+    def __init__(self, kind: str, wx: Tensor, rec, grad_states: Tensor, comm: DistComm, *, K: int, P: int = 0,
+                 eps: float = 1e-6, omega: float = 1.0, h0: Tensor | None = None, warmup: int = 2,
+                 segments: int | None = None):
+        self.wx, self.grad_states, self.comm = wx.contiguous(), grad_states.contiguous(), comm
+        self.K, self.P, self.h0 = int(K), int(P), _h0_f32(h0)
+        self.ops = CudaShardOps(kind, self.wx, rec, eps, omega, segments=segments)
+        side = torch.cuda.Stream(device=wx.device)
+        side.wait_stream(torch.cuda.current_stream(wx.device))
+        with torch.cuda.stream(side):  # eager runs first: communicators, kernel attributes, allocator
+            for _ in range(max(1, warmup)):
+                self._run()
+        torch.cuda.current_stream(wx.device).wait_stream(side)
+        torch.cuda.synchronize(wx.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._run()
+
+    def _run(self):
+        self.ops.stats.buf.zero_()
+        res = drive(forward_program(self.ops, self.comm.rank, self.comm.world, self.K, self.P, self.h0),
+                    self.comm)
+        self.g_wx, self.g_params, self.head = drive(
+            backward_program(self.ops, self.comm.rank, self.comm.world, res.states, self.grad_states, res.halo),
+            self.comm)
+        self.states, self.stats_bits = res.states, res.stats_bits
+
+    def replay(self):
+        self.graph.replay()
 
 
 # ------------------------------------------------------------------------------- public entry

@@ -127,3 +127,41 @@ def test_segment_plan_and_argument_checks():
     rc = lib.prb_slstm_newton_pass(p, p, p, None, None, p, None, None, 0, 3, 100, 1, 1000, 32, _lib.PRB_F32, 1.0,
                                    1e-6, p, 256, p, 0, None)
     assert rc == -1
+
+
+def test_graphed_step_replays_with_new_inputs(prb_options):
+    """The forward + backward programs captured into a CUDA graph (one-rank NCCL group, three time
+    segments so that the device-side folds are part of it): a replay after new inputs were written
+    into the static buffers gives what the eager programs give for those inputs."""
+    import socket
+
+    import torch.distributed as dist
+
+    from pararnn_b200.seq_shard import DistComm, GraphedShardedStep, emulate_sharded
+
+    prb_options("kernel_family", "pipe")
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
+                            device_id=torch.device("cuda", 0))
+    try:
+        B, T, d, K, P = 2, 700, 64, 2, 2
+        wx1, r, _ = make_problem("slstm_diag", B, T, d, seed=1, x_scale=0.6, bias_f=1.0)
+        wx2, _, _ = make_problem("slstm_diag", B, T, d, seed=2, x_scale=0.6, bias_f=1.0)
+        G1 = np.random.default_rng(5).standard_normal((B, T, 4, d)).astype(np.float32)
+        G2 = np.random.default_rng(6).standard_normal((B, T, 4, d)).astype(np.float32)
+        wx_s, G_s = dev(wx1), dev(G1)
+        gs = GraphedShardedStep("slstm_diag", wx_s, (dev(r),), G_s, DistComm(), K=K, P=P, segments=3)
+        assert gs.ops.n_seg == 3
+        for wx, G in ((wx1, G1), (wx2, G2), (wx1, G1)):
+            gs.wx.copy_(dev(wx))
+            gs.grad_states.copy_(dev(G))
+            gs.replay()
+            torch.cuda.synchronize()
+            states, _, grads = emulate_sharded("slstm_diag", dev(wx), (dev(r),), world=1, K=K, P=P,
+                                               grad_states=dev(G), segments=3)
+            assert torch.equal(gs.states, states)
+            assert torch.equal(gs.g_wx, grads[0]) and torch.equal(gs.g_params, grads[1])
+    finally:
+        dist.destroy_process_group()
