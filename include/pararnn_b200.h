@@ -124,10 +124,11 @@ int prb_newton_gru_head_fused(const void* wx, const void* a_z, const void* a_r, 
  * gru_head_recurrence_vjp (kernels/vjp_gru.py:656-810).  g_wx (B,T,3d) I/O dtype;
  * g_a (3,H,dh,dh) fp32 = grad of (A_z, A_r, A_n), the outer-product sums
  * sum h_prev^T g_z, sum h_prev^T g_r, sum (h_prev r)^T g_n accumulated in the same sweep
- * (no clip mask applied); g_h0 (B,d) fp32 or NULL. */
+ * (no clip mask applied); g_h0 (B,d) fp32 or NULL; mu_out (B,T,d) fp32 or NULL receives the
+ * adjoint mu_t = J_{t+1}^T mu_{t+1} + g_t itself, the return value of the reference's op. */
 int prb_bwd_gru_head(const void* states, const void* wx, const void* a_z, const void* a_r,
                      const void* a_n, const void* h0, const void* grad_states, void* g_wx, float* g_a,
-                     float* g_h0, int B, int T, int d, int n_heads, int dtype, void* workspace,
+                     float* g_h0, float* mu_out, int B, int T, int d, int n_heads, int dtype, void* workspace,
                      size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
 
 /* ---- backward: eq. 2.6 reverse scan fused with the packed VJP ------------------- */
@@ -277,6 +278,19 @@ int prb_segment_carries(int monoid, const float* agg, int n_seg, int reverse, co
 int prb_residual_pass(int cell, const void* wx, const float* params, const float* halo,
                       const void* states, int states_f32, int B, int T, int d, int dtype, float eps,
                       prb_stats* stats, prb_stream_t stream);
+
+/* ---- T = 1 decode ----------------------------------------------------------------------
+ * One recurrent step of a whole batch in one launch (the serving path: .eval(), T = 1).  Replaces
+ * decode_step, kernels/decode.py:119-216 and its three step kernels (:294-475); W_x(x) stays a
+ * library GEMM on the caller's side.  state (B, S, d) or, with block_table (B,) int32 slot ids,
+ * a pool (C, S, d); wx (B, G*d); params_raw: the UNCLAMPED recurrent vectors (GRU (3,d), NLRU
+ * (1,d), sLSTM (4,d)) in the I/O dtype, clamped to [-cap, cap] in the kernel (cap < 0: no
+ * clamp), so a captured CUDA graph needs no extra kernel; out has the shape of state and may BE
+ * state (in-place update of the pool rows named by block_table).  Allocates nothing, takes no
+ * workspace, never synchronises: it can be captured in a CUDA graph. */
+int prb_decode_step(int cell, const void* state, const void* wx, const void* params_raw, float cap,
+                    const int* block_table, void* out, int B, int d, int dtype, float eps,
+                    prb_stream_t stream);
 
 /* ---- entry point that allocates nothing ------------------------------------------------
  * No counterpart in the reference (its ops allocate scratch through PyTorch on every call).

@@ -771,7 +771,7 @@ int prb_newton_gru_head_fused(const void* wx, const void* a_z, const void* a_r, 
 
 int prb_bwd_gru_head(const void* states, const void* wx, const void* a_z, const void* a_r,
                      const void* a_n, const void* h0, const void* grad_states, void* g_wx, float* g_a,
-                     float* g_h0, int B, int T, int d, int n_heads, int dtype, void* workspace,
+                     float* g_h0, float* mu_out, int B, int T, int d, int n_heads, int dtype, void* workspace,
                      size_t workspace_bytes, prb_stats* stats, prb_stream_t stream) {
     cudaStream_t s = (cudaStream_t)stream;
     if (!states || !wx || !a_z || !a_r || !a_n || !grad_states || !g_wx || !g_a || !stats || B < 1 ||
@@ -792,7 +792,7 @@ int prb_bwd_gru_head(const void* states, const void* wx, const void* a_z, const 
         to_f32(h0, p.h0, (size_t)B * d, dtype, s);
         h0f = p.h0;
     }
-    if (launch_gru_head_bwd(dtype, wx, states, grad_states, p.A, h0f, g_wx, p.gA_part, g_h0, B, T, d, H, s) !=
+    if (launch_gru_head_bwd(dtype, wx, states, grad_states, p.A, h0f, g_wx, p.gA_part, g_h0, mu_out, B, T, d, H, s) !=
         cudaSuccess)
         return PRB_ERR_LAUNCH;
     return launch_reduce_partials(p.gA_part, B, 3 * H * dh * dh, g_a, s) == cudaSuccess ? PRB_OK
@@ -1232,6 +1232,17 @@ int prb_residual(int cell, const void* wx, const void* params, const void* h0, c
     return e == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
 
+
+int prb_decode_step(int cell, const void* state, const void* wx, const void* params_raw, float cap,
+                    const int* block_table, void* out, int B, int d, int dtype, float eps,
+                    prb_stream_t stream) {
+    if (!state || !wx || !params_raw || !out || B < 1 || d < 1 || bad_dtype(dtype)) return PRB_ERR_BAD_ARG;
+    if (cell != kCellGruDiag && cell != kCellNlru && cell != kCellSlstmDiag) return PRB_ERR_UNSUPPORTED;
+    return launch_decode_step(cell, dtype, state, wx, params_raw, block_table, out, B, d, cap, eps,
+                              (cudaStream_t)stream) == cudaSuccess
+               ? PRB_OK
+               : PRB_ERR_LAUNCH;
+}
 
 /* ---- entry point that allocates nothing ---------------------------------------------- */
 

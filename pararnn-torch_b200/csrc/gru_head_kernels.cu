@@ -305,6 +305,7 @@ struct HeadBwdArgs {
     void* g_wx;               // (B,T,3d) I/O dtype
     float* gA_part;           // (B,3,H,dh,dh) fp32: this batch row's share of grad A
     float* g_h0;              // (B,d) fp32 or null
+    float* mu_out;            // (B,T,d) fp32 or null: mu_t = nu_t + g_t, the adjoint of eq. 2.6
     int B, T, d, H;
 };
 
@@ -425,6 +426,7 @@ __global__ void __launch_bounds__(192, 1) gru_head_bwd_kernel(HeadBwdArgs a) {
                     stage_bar(2);
                     const float t4 = dot1x1<DH>(s_v3, m1);
                     if (act) {
+                        if (a.mu_out) a.mu_out[base + (size_t)t * a.d] = mu;
                         st_f(gwx + (size_t)t * 3 * a.d, w_z);
                         st_f(gwx + (size_t)t * 3 * a.d + a.d, v3);
                         st_f(gwx + (size_t)t * 3 * a.d + 2 * (size_t)a.d, w_n);
@@ -516,8 +518,8 @@ static cudaError_t launch_head_bwd_t(const HeadBwdArgs& a, int dh, cudaStream_t 
 
 cudaError_t launch_gru_head_bwd(int dtype, const void* wx, const void* states, const void* grad_states,
                                 const float* A, const float* h0, void* g_wx, float* gA_part, float* g_h0,
-                                int B, int T, int d, int H, cudaStream_t s) {
-    HeadBwdArgs a{wx, states, grad_states, A, h0, g_wx, gA_part, g_h0, B, T, d, H};
+                                float* mu_out, int B, int T, int d, int H, cudaStream_t s) {
+    HeadBwdArgs a{wx, states, grad_states, A, h0, g_wx, gA_part, g_h0, mu_out, B, T, d, H};
     return dtype == kF32 ? launch_head_bwd_t<float>(a, d / H, s) : launch_head_bwd_t<__nv_bfloat16>(a, d / H, s);
 }
 

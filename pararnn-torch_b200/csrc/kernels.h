@@ -170,6 +170,11 @@ cudaError_t launch_gru_head_fwd(int dtype, const void* wx, const float* A, const
                                 float omega, cudaStream_t s);
 cudaError_t launch_gru_head_bwd(int dtype, const void* wx, const void* states, const void* grad_states,
                                 const float* A, const float* h0, void* g_wx, float* gA_part, float* g_h0,
-                                int B, int T, int d, int H, cudaStream_t s);
+                                float* mu_out, int B, int T, int d, int H, cudaStream_t s);
+
+// ---- T = 1 decode (decode.cu) ------------------------------------------------------------------
+cudaError_t launch_decode_step(int cell, int dtype, const void* state, const void* wx, const void* par,
+                               const int* block_table, void* out, int B, int d, float cap, float eps,
+                               cudaStream_t s);
 
 }  // namespace prb

@@ -37,7 +37,7 @@ _SIGNATURES = {
     "prb_newton_slstm_fused": (_INT, [_VOIDP] * 5 + [_INT] * 6 + [_FLOAT, _FLOAT, _INT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_gru_head_workspace_bytes": (_SIZE, [_INT] * 5),
     "prb_newton_gru_head_fused": (_INT, [_VOIDP] * 6 + [_INT] * 6 + [_FLOAT, _INT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
-    "prb_bwd_gru_head": (_INT, [_VOIDP] * 10 + [_INT] * 5 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
+    "prb_bwd_gru_head": (_INT, [_VOIDP] * 11 + [_INT] * 5 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_bwd_gru": (_INT, [_VOIDP] * 10 + [_INT] * 4 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_bwd_nlru": (_INT, [_VOIDP] * 8 + [_INT] * 4 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_bwd_slstm": (_INT, [_VOIDP] * 8 + [_INT] * 4 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
@@ -55,6 +55,7 @@ _SIGNATURES = {
     "prb_fold_segments": (_INT, [_INT, _VOIDP, _INT, _INT, _VOIDP, _INT, _INT, _VOIDP]),
     "prb_segment_carries": (_INT, [_INT, _VOIDP, _INT, _INT, _VOIDP, _VOIDP, _INT, _INT, _VOIDP]),
     "prb_fold_carries": (_INT, [_INT, _VOIDP, _INT, _INT, _INT, _VOIDP, _INT, _INT, _VOIDP]),
+    "prb_decode_step": (_INT, [_INT, _VOIDP, _VOIDP, _VOIDP, _FLOAT, _VOIDP, _VOIDP, _INT, _INT, _INT, _FLOAT, _VOIDP]),
     "prb_static_scratch_bytes": (_SIZE, []),
     "prb_bwd_nlru_static": (_INT, [_VOIDP] * 8 + [_INT] * 4 + [_VOIDP, _VOIDP]),
     "prb_residual_pass": (_INT, [_INT] + [_VOIDP] * 4 + [_INT] * 5 + [_FLOAT, _VOIDP, _VOIDP]),

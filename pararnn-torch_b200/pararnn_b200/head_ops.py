@@ -59,7 +59,7 @@ def newton_gru_head_fused(wx: Tensor, a_z: Tensor, a_r: Tensor, a_n: Tensor, h0:
 
 
 def gru_head_reverse_vjp(states: Tensor, wx: Tensor, a_z: Tensor, a_r: Tensor, a_n: Tensor,
-                         grad_states: Tensor, h0: Tensor | None = None):
+                         grad_states: Tensor, h0: Tensor | None = None, mu_out: Tensor | None = None):
     """Reverse walk with the factorised ``J^T`` fused with the gate part of the packed VJP.
     Returns ``(g_wx, g_Az, g_Ar, g_An, g_h0)``; the ``A`` gradients are fp32 ``(H, dh, dh)``
     outer-product sums accumulated by the same kernel (no clip mask applied)."""
@@ -81,7 +81,8 @@ def gru_head_reverse_vjp(states: Tensor, wx: Tensor, a_z: Tensor, a_r: Tensor, a
     with torch.cuda.device(dev):
         ws = _workspace(lib.prb_gru_head_workspace_bytes(B, T, d, H, 0), dev)
         rc = lib.prb_bwd_gru_head(_ptr(st), _ptr(wx_c), _ptr(az), _ptr(ar), _ptr(an), _ptr(h0c), _ptr(gs),
-                                  _ptr(g_wx), _ptr(g_a), _ptr(g_h0), B, T, d, H, code, _ptr(ws), ws.numel(),
+                                  _ptr(g_wx), _ptr(g_a), _ptr(g_h0), _ptr(mu_out), B, T, d, H, code, _ptr(ws),
+                                  ws.numel(),
                                   _ptr(sb.buf), _stream(dev))
     _raise(rc, "gru_head_reverse_vjp")
     g_az, g_ar, g_an = g_a.unbind(0)

@@ -28,6 +28,12 @@ def sequential_apply(cell: nn.Module, x: Tensor, h0: Tensor | None = None, *, st
         raise ValueError(f"sequential_apply needs time >= 1, got {time}")
     h = h0 if h0 is not None else zero_state(cell, batch, x)
     wx_all = cell.W_x(x) if step is None and hasattr(cell, "W_x") else None
+    if step is None and time == 1 and wx_all is not None and not torch.is_grad_enabled():
+        # T = 1 without a graph: the one-launch decode kernel (reference solvers/sequential.py:77-81)
+        from .decode import can_decode_step, decode_step
+
+        if can_decode_step(cell, wx_all):
+            return decode_step(cell, h, wx=wx_all[:, 0]).unsqueeze(1)
     step_fn = step or cell.step
     outs = []
     for t in range(time):
