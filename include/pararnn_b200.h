@@ -36,7 +36,8 @@ extern "C" {
 typedef struct CUstream_st* prb_stream_t; /* cudaStream_t */
 
 enum { PRB_F32 = 0, PRB_BF16 = 1 };
-enum { PRB_CELL_GRU_DIAG = 0, PRB_CELL_NLRU = 1, PRB_CELL_SLSTM_DIAG = 2, PRB_CELL_GRU_HEAD = 3 };
+enum { PRB_CELL_GRU_DIAG = 0, PRB_CELL_NLRU = 1, PRB_CELL_SLSTM_DIAG = 2, PRB_CELL_GRU_HEAD = 3,
+       PRB_CELL_TITANS = 4 };
 enum {
     PRB_OK = 0,
     PRB_ERR_BAD_ARG = -1,     /* null pointer, non-positive size, unknown enum */
@@ -96,6 +97,13 @@ int prb_newton_nlru_fused(const void* wx, const void* u, const void* h0, void* o
                           void* workspace, size_t workspace_bytes, prb_stats* stats,
                           prb_stream_t stream);
 
+/* ParaTitans (scalar-diagonal memory cell).  Replaces pararnn::newton_titans_fused,
+ * kernels/custom_ops.py:269-308 -> kernels/newton_titans.py.  wx (B,T,5d) gates
+ * (alpha_pre, theta_pre, k, v, n_pre); u, r (d) clamped; h0 (B,d) or NULL; out (B,T,d). */
+int prb_newton_titans_fused(const void* wx, const void* u, const void* r, const void* h0, void* out, int B,
+                            int T, int d, int dtype, int max_iters, float omega, int want_residual,
+                            void* workspace, size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
+
 /* ParaSLSTM mix='diag', including the frozen-gate Picard warm start.  Replaces
  * pararnn::newton_slstm_fused, kernels/custom_ops.py:486-540 ->
  * kernels/newton_slstm.py:2696-2939, and solvers/slstm_picard.py:158-181
@@ -148,6 +156,14 @@ int prb_bwd_nlru(const void* states, const void* wx, const void* u, const void* 
                  int d, int dtype, void* workspace, size_t workspace_bytes, prb_stats* stats,
                  prb_stream_t stream);
 
+/* ParaTitans: reverse_scan_diag (solvers/scan.py:126-148) + the VJP the reference takes by autograd
+ * through the cell step (solvers/vjp.py:77-98), in closed form.  g_wx (B,T,5d); g_params fp32
+ * (2,d) = grad of (u, r); g_h0 fp32 (B,d) or NULL. */
+int prb_bwd_titans(const void* states, const void* wx, const void* u, const void* r, const void* h0,
+                   const void* grad_states, void* g_wx, float* g_params, float* g_h0, int B, int T, int d,
+                   int dtype, void* workspace, size_t workspace_bytes, prb_stats* stats,
+                   prb_stream_t stream);
+
 /* Replaces reverse_scan_block4 + slstm_recurrence_vjp, solvers/scan.py:166-178,
  * kernels/vjp_slstm.py:234-293.  states, grad_states (B,T,4,d); g_wx (B,T,4d);
  * g_params fp32 (4,d); g_h0 fp32 (B,4,d) or NULL. */
@@ -160,7 +176,7 @@ int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void*
 
 /* max|f(H_{t-1},x_t) - H_t| into stats->final_bits.  Replaces the eager
  * evaluation in solvers/newton/__init__.py:602-606.  params: GRU (3,d) packed
- * a_z,a_r,a_n; NLRU (1,d); sLSTM (4,d); all in the I/O dtype. */
+ * a_z,a_r,a_n; NLRU (1,d); Titans (2,d) = u,r; sLSTM (4,d); all in the I/O dtype. */
 int prb_residual(int cell, const void* wx, const void* params, const void* h0, const void* states,
                  int B, int T, int d, int dtype, float eps, void* workspace, size_t workspace_bytes,
                  prb_stats* stats, prb_stream_t stream);
@@ -284,7 +300,7 @@ int prb_residual_pass(int cell, const void* wx, const float* params, const float
  * decode_step, kernels/decode.py:119-216 and its three step kernels (:294-475); W_x(x) stays a
  * library GEMM on the caller's side.  state (B, S, d) or, with block_table (B,) int32 slot ids,
  * a pool (C, S, d); wx (B, G*d); params_raw: the UNCLAMPED recurrent vectors (GRU (3,d), NLRU
- * (1,d), sLSTM (4,d)) in the I/O dtype, clamped to [-cap, cap] in the kernel (cap < 0: no
+ * (1,d), Titans (2,d), sLSTM (4,d)) in the I/O dtype, clamped to [-cap, cap] in the kernel (cap < 0: no
  * clamp), so a captured CUDA graph needs no extra kernel; out has the shape of state and may BE
  * state (in-place update of the pool rows named by block_table).  Allocates nothing, takes no
  * workspace, never synchronises: it can be captured in a CUDA graph. */

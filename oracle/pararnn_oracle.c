@@ -32,7 +32,7 @@
 #endif
 typedef REAL real;
 
-enum { CELL_GRU_DIAG = 0, CELL_NLRU = 1, CELL_SLSTM_DIAG = 2, CELL_GRU_HEAD = 3 };
+enum { CELL_GRU_DIAG = 0, CELL_NLRU = 1, CELL_SLSTM_DIAG = 2, CELL_GRU_HEAD = 3, CELL_TITANS = 4 };
 
 static inline real r_exp(real x) { return sizeof(real) == 4 ? (real)expf((float)x) : (real)exp((double)x); }
 static inline real r_tanh(real x) { return sizeof(real) == 4 ? (real)tanhf((float)x) : (real)tanh((double)x); }
@@ -44,7 +44,9 @@ static inline real nanmax(real acc, real v) { return (v != v || v > acc) ? v : a
 
 int oracle_real_bytes(void) { return (int)sizeof(real); }
 
-static int gates_of(int kind) { return kind == CELL_NLRU ? 2 : (kind == CELL_SLSTM_DIAG ? 4 : 3); }
+static int gates_of(int kind) {
+    return kind == CELL_NLRU ? 2 : (kind == CELL_SLSTM_DIAG ? 4 : (kind == CELL_TITANS ? 5 : 3));
+}
 static int slots_of(int kind) { return kind == CELL_SLSTM_DIAG ? 4 : 1; }
 
 /* ------------------------------------------------------------------ */
@@ -71,6 +73,33 @@ static inline void nlru(real h, real ax, real cx, real u, real *f, real *j) {
     real n = r_tanh(cx + u * h);
     *f = a * h + (1 - a) * n;
     if (j) *j = a + (1 - a) * (1 - n * n) * u;
+}
+
+/* ParaTitans step + diagonal Jacobian.  cells/para_titans.py:170-216:
+ * gates (alpha_pre, theta_pre, k, v, n_pre) = chunk5(wx), parameters (u, r) clamped outside. */
+static inline real r_softplus(real x) {
+    if (x > 20) return x; /* torch.nn.functional.softplus threshold */
+    return sizeof(real) == 4 ? (real)log1pf(expf((float)x)) : (real)log1p(exp((double)x));
+}
+static inline void titans(real h, real ap, real tp, real k, real v, real np_, real u, real r, real *f,
+                          real *j) {
+    real alpha = r_sigmoid(ap), theta = r_softplus(tp);
+    real grad = (h * k - v) * k;
+    real n = r_tanh(np_ + r * h);
+    *f = (1 - alpha) * h - theta * grad + u * n;
+    if (j) *j = (1 - alpha) - theta * k * k + u * (1 - n * n) * r;
+}
+
+/* step (+ Jacobian) of a scalar-diagonal cell at channel ch; wt points at the gates of one step */
+static inline void diag_step(int kind, real h, const real *wt, int d, const real *params, int ch, real *f,
+                             real *j) {
+    if (kind == CELL_GRU_DIAG)
+        gru_diag(h, wt[0], wt[d], wt[2 * (size_t)d], params[ch], params[d + ch], params[2 * d + ch], f, j);
+    else if (kind == CELL_TITANS)
+        titans(h, wt[0], wt[d], wt[2 * (size_t)d], wt[3 * (size_t)d], wt[4 * (size_t)d], params[ch],
+               params[d + ch], f, j);
+    else
+        nlru(h, wt[0], wt[d], params[ch], f, j);
 }
 
 /* ------------------------------------------------------------------ */
@@ -307,11 +336,7 @@ void oracle_sequential(int kind, const real *wx, const real *params, const real 
                 for (int t = 0; t < T; ++t) {
                     const real *wt = w + (size_t)t * G * d;
                     real f;
-                    if (kind == CELL_GRU_DIAG)
-                        gru_diag(h, wt[0], wt[d], wt[2 * (size_t)d], params[ch], params[d + ch],
-                                 params[2 * d + ch], &f, NULL);
-                    else
-                        nlru(h, wt[0], wt[d], params[ch], &f, NULL);
+                    diag_step(kind, h, wt, d, params, ch, &f, NULL);
                     h = f;
                     o[(size_t)t * d] = h;
                 }
@@ -417,11 +442,7 @@ static real newton_pass(int kind, const real *wx, const real *params, const real
                     for (int t = 0; t < T; ++t) {
                         const real *wt = w + (size_t)t * G * d;
                         real f, j;
-                        if (kind == CELL_GRU_DIAG)
-                            gru_diag(prev, wt[0], wt[d], wt[2 * (size_t)d], params[ch], params[d + ch],
-                                     params[2 * d + ch], &f, &j);
-                        else
-                            nlru(prev, wt[0], wt[d], params[ch], &f, &j);
+                        diag_step(kind, prev, wt, d, params, ch, &f, &j);
                         real cur = s[(size_t)t * d];
                         real F = f - cur;
                         lmax = nanmax(lmax, r_abs(F));
@@ -491,11 +512,7 @@ static void newton_guess(int kind, const real *wx, const real *params, const rea
                 for (int t = 0; t < T; ++t) {
                     const real *wt = w + (size_t)t * G * d;
                     real hp = (t == 0 && h0) ? h0[(size_t)b * d + ch] : 0, f;
-                    if (kind == CELL_GRU_DIAG)
-                        gru_diag(hp, wt[0], wt[d], wt[2 * (size_t)d], params[ch], params[d + ch],
-                                 params[2 * d + ch], &f, NULL);
-                    else
-                        nlru(hp, wt[0], wt[d], params[ch], &f, NULL);
+                    diag_step(kind, hp, wt, d, params, ch, &f, NULL);
                     s[(size_t)t * d] = f;
                 }
             }
@@ -609,7 +626,7 @@ void oracle_backward(int kind, const real *states, const real *wx, const real *p
         }
         return;
     }
-    const int NP = (kind == CELL_GRU_DIAG) ? 3 : (kind == CELL_NLRU ? 1 : 4);
+    const int NP = (kind == CELL_GRU_DIAG) ? 3 : (kind == CELL_NLRU ? 1 : (kind == CELL_TITANS ? 2 : 4));
 #pragma omp parallel for schedule(static)
     for (int ch = 0; ch < d; ++ch) {
         real gp[4] = {0, 0, 0, 0};
@@ -680,6 +697,22 @@ void oracle_backward(int kind, const real *states, const real *wx, const real *p
                         real d_rpre = (d_npre * an * hp) * r * (1 - r);
                         gwt[0] = d_zpre; gwt[d] = d_rpre; gwt[2 * (size_t)d] = d_npre;
                         gp[0] += d_zpre * hp; gp[1] += d_rpre * hp; gp[2] += d_npre * (hp * r);
+                    } else if (kind == CELL_TITANS) {
+                        /* closed form of the autograd VJP the reference takes through step
+                         * (solvers/vjp.py:77-98) */
+                        real u = params[ch], r = params[d + ch];
+                        real k = wt[2 * (size_t)d], v = wt[3 * (size_t)d];
+                        titans(hp, wt[0], wt[d], k, v, wt[4 * (size_t)d], u, r, &f, &j);
+                        real alpha = r_sigmoid(wt[0]), theta = r_softplus(wt[d]);
+                        real n = r_tanh(wt[4 * (size_t)d] + r * hp);
+                        real err = hp * k - v;
+                        gwt[0] = -mu * hp * alpha * (1 - alpha);
+                        gwt[d] = -mu * err * k * r_sigmoid(wt[d]);
+                        gwt[2 * (size_t)d] = -mu * theta * (err + hp * k);
+                        gwt[3 * (size_t)d] = mu * theta * k;
+                        gwt[4 * (size_t)d] = mu * u * (1 - n * n);
+                        gp[0] += mu * n;
+                        gp[1] += gwt[4 * (size_t)d] * hp;
                     } else {
                         real u = params[ch];
                         nlru(hp, wt[0], wt[d], u, &f, &j);

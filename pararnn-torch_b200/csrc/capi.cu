@@ -154,7 +154,7 @@ struct DiagPlan {
 DiagPlan plan_diag_fwd(void* ws, int cell, int B, int T, int d, int K, bool has_h0) {
     Bump b(ws);
     DiagPlan p;
-    const int np = cell == kCellGruDiag ? 3 : 1;
+    const int np = diag_cell_params(cell);
     p.chain = plan_chain(b, B, T, d, diag_tile_steps(), 2);
     p.par = b.take<float>((size_t)np * d);
     p.h0 = b.take<float>((size_t)B * d);
@@ -171,7 +171,7 @@ int run_diag_fwd(int cell, const void* wx, const void* const* pars, const void* 
                  size_t ws_bytes, prb_stats* stats, cudaStream_t s) {
     if (!wx || !out || !stats || B < 1 || T < 1 || d < 1 || K < 0 || K > kMaxIters || bad_dtype(dtype))
         return PRB_ERR_BAD_ARG;
-    const int np = cell == kCellGruDiag ? 3 : 1;
+    const int np = diag_cell_params(cell);
     for (int i = 0; i < np; ++i)
         if (!pars[i]) return PRB_ERR_BAD_ARG;
     DiagPlan p = plan_diag_fwd(nullptr, cell, B, T, d, K, h0 != nullptr);
@@ -227,7 +227,7 @@ struct DiagBwdPlan {
 DiagBwdPlan plan_diag_bwd(void* ws, int cell, int B, int T, int d) {
     Bump b(ws);
     DiagBwdPlan p;
-    const int np = cell == kCellGruDiag ? 3 : 1;
+    const int np = diag_cell_params(cell);
     p.chain = plan_chain(b, B, T, d, diag_tile_steps(), 2);
     p.par = b.take<float>((size_t)np * d);
     p.h0 = b.take<float>((size_t)B * d);
@@ -243,7 +243,7 @@ int run_diag_bwd(int cell, const void* states, const void* wx, const void* const
     if (!states || !wx || !grad_states || !g_wx || !g_params || !stats || B < 1 || T < 1 || d < 1 ||
         bad_dtype(dtype))
         return PRB_ERR_BAD_ARG;
-    const int np = cell == kCellGruDiag ? 3 : 1;
+    const int np = diag_cell_params(cell);
     for (int i = 0; i < np; ++i)
         if (!pars[i]) return PRB_ERR_BAD_ARG;
     DiagBwdPlan p = plan_diag_bwd(nullptr, cell, B, T, d);
@@ -580,8 +580,7 @@ size_t prb_newton_workspace_bytes(int cell, int dtype, int B, int T, int d, int 
     (void)dtype;
     (void)n_heads;
     if (B < 1 || T < 1 || d < 1) return 0;
-    if (cell == kCellGruDiag || cell == kCellNlru)
-        return plan_diag_fwd(nullptr, cell, B, T, d, max_iters, true).total;
+    if (is_diag_cell(cell)) return plan_diag_fwd(nullptr, cell, B, T, d, max_iters, true).total;
     if (cell == kCellSlstmDiag) return plan_slstm_fwd(nullptr, B, T, d, max_iters, picard_iters, false).total;
     return 0;
 }
@@ -590,7 +589,7 @@ size_t prb_bwd_workspace_bytes(int cell, int dtype, int B, int T, int d, int n_h
     (void)dtype;
     (void)n_heads;
     if (B < 1 || T < 1 || d < 1) return 0;
-    if (cell == kCellGruDiag || cell == kCellNlru) return plan_diag_bwd(nullptr, cell, B, T, d).total;
+    if (is_diag_cell(cell)) return plan_diag_bwd(nullptr, cell, B, T, d).total;
     if (cell == kCellSlstmDiag) return plan_slstm_bwd(nullptr, B, T, d).total;
     return 0;
 }
@@ -611,6 +610,23 @@ int prb_newton_nlru_fused(const void* wx, const void* u, const void* h0, void* o
     const void* pars[3] = {u, nullptr, nullptr};
     return run_diag_fwd(kCellNlru, wx, pars, h0, out, B, T, d, dtype, max_iters, omega, want_residual,
                         workspace, workspace_bytes, stats, (cudaStream_t)stream);
+}
+
+int prb_newton_titans_fused(const void* wx, const void* u, const void* r, const void* h0, void* out, int B,
+                            int T, int d, int dtype, int max_iters, float omega, int want_residual,
+                            void* workspace, size_t workspace_bytes, prb_stats* stats, prb_stream_t stream) {
+    const void* pars[3] = {u, r, nullptr};
+    return run_diag_fwd(kCellTitans, wx, pars, h0, out, B, T, d, dtype, max_iters, omega, want_residual,
+                        workspace, workspace_bytes, stats, (cudaStream_t)stream);
+}
+
+int prb_bwd_titans(const void* states, const void* wx, const void* u, const void* r, const void* h0,
+                   const void* grad_states, void* g_wx, float* g_params, float* g_h0, int B, int T, int d,
+                   int dtype, void* workspace, size_t workspace_bytes, prb_stats* stats,
+                   prb_stream_t stream) {
+    const void* pars[3] = {u, r, nullptr};
+    return run_diag_bwd(kCellTitans, states, wx, pars, h0, grad_states, g_wx, g_params, g_h0, B, T, d,
+                        dtype, workspace, workspace_bytes, stats, (cudaStream_t)stream);
 }
 
 int prb_newton_slstm_fused(const void* wx, const void* r, const void* h0, const void* states_guess,
@@ -835,7 +851,7 @@ int pass_ws(int cell, int B, int T, int d, void* ws, size_t ws_bytes, cudaStream
 int prb_diag_guess(int cell, const void* wx, const float* params, const float* h0, float* out, int B,
                    int T, int d, int dtype, prb_stream_t stream) {
     if (!wx || !params || !out || B < 1 || T < 1 || d < 1 || bad_dtype(dtype)) return PRB_ERR_BAD_ARG;
-    if (cell != kCellGruDiag && cell != kCellNlru) return PRB_ERR_UNSUPPORTED;
+    if (!is_diag_cell(cell)) return PRB_ERR_UNSUPPORTED;
     return launch_diag_guess(cell, dtype, true, wx, params, h0, out, B, T, d, (cudaStream_t)stream) ==
                    cudaSuccess
                ? PRB_OK
@@ -851,7 +867,7 @@ int prb_diag_newton_pass(int cell, const void* wx, const float* params, const fl
     if (!wx || !params || !hin || !stats || B < 1 || T < 1 || d < 1 || bad_dtype(dtype) || mode < 0 ||
         mode > 2 || hist_slot < 0 || hist_slot >= kMaxIters)
         return PRB_ERR_BAD_ARG;
-    if (cell != kCellGruDiag && cell != kCellNlru) return PRB_ERR_UNSUPPORTED;
+    if (!is_diag_cell(cell)) return PRB_ERR_UNSUPPORTED;
     if ((mode == 2 && !agg_out) || (mode != 2 && !hout)) return PRB_ERR_BAD_ARG;
     PassWs w;
     if (int e = pass_ws(cell, B, T, d, workspace, workspace_bytes, s, w)) return e;
@@ -887,12 +903,12 @@ int prb_diag_bwd_pass(int cell, const void* states, const void* wx, const float*
     if (!states || !wx || !params || !grad_states || !stats || B < 1 || T < 1 || d < 1 ||
         bad_dtype(dtype) || (mode != 0 && mode != 2))
         return PRB_ERR_BAD_ARG;
-    if (cell != kCellGruDiag && cell != kCellNlru) return PRB_ERR_UNSUPPORTED;
+    if (!is_diag_cell(cell)) return PRB_ERR_UNSUPPORTED;
     if ((mode == 2 && !agg_out) || (mode == 0 && (!g_wx || !g_params))) return PRB_ERR_BAD_ARG;
     PassWs w;
     if (int e = pass_ws(cell, B, T, d, workspace, workspace_bytes, s, w)) return e;
     DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
-    const int np = cell == kCellGruDiag ? 3 : 1;
+    const int np = diag_cell_params(cell);
     DiagBwdArgs a{};
     a.wx = wx;
     a.states = states;
@@ -1121,7 +1137,7 @@ int prb_residual_pass(int cell, const void* wx, const float* params, const float
     if (cell == kCellSlstmDiag)
         e = launch_slstm_residual(dtype, states_f32 != 0, wx, params, halo, 4 * d, states, B, T, d, eps,
                                   &st->final_bits, s);
-    else if (cell == kCellGruDiag || cell == kCellNlru)
+    else if (is_diag_cell(cell))
         e = launch_diag_residual(cell, dtype, states_f32 != 0, wx, params, halo, states, B, T, d,
                                  &st->final_bits, s);
     else
@@ -1205,9 +1221,9 @@ int prb_residual(int cell, const void* wx, const void* params, const void* h0, c
     cudaStream_t s = (cudaStream_t)stream;
     if (!wx || !params || !states || !stats || B < 1 || T < 1 || d < 1 || bad_dtype(dtype))
         return PRB_ERR_BAD_ARG;
-    const int np = cell == kCellGruDiag ? 3 : (cell == kCellNlru ? 1 : 4);
+    if (!is_diag_cell(cell) && cell != kCellSlstmDiag) return PRB_ERR_UNSUPPORTED;
+    const int np = cell == kCellSlstmDiag ? 4 : diag_cell_params(cell);
     const int S = cell == kCellSlstmDiag ? 4 : 1;
-    if (cell != kCellGruDiag && cell != kCellNlru && cell != kCellSlstmDiag) return PRB_ERR_UNSUPPORTED;
     Bump b(nullptr);
     b.take<float>((size_t)np * d);
     b.take<float>((size_t)B * S * d);
@@ -1237,7 +1253,7 @@ int prb_decode_step(int cell, const void* state, const void* wx, const void* par
                     const int* block_table, void* out, int B, int d, int dtype, float eps,
                     prb_stream_t stream) {
     if (!state || !wx || !params_raw || !out || B < 1 || d < 1 || bad_dtype(dtype)) return PRB_ERR_BAD_ARG;
-    if (cell != kCellGruDiag && cell != kCellNlru && cell != kCellSlstmDiag) return PRB_ERR_UNSUPPORTED;
+    if (!is_diag_cell(cell) && cell != kCellSlstmDiag) return PRB_ERR_UNSUPPORTED;
     return launch_decode_step(cell, dtype, state, wx, params_raw, block_table, out, B, d, cap, eps,
                               (cudaStream_t)stream) == cudaSuccess
                ? PRB_OK

@@ -1,8 +1,10 @@
-// Per-step math of the scalar-diagonal cells (ParaGRU mix='diag', ParaNLRU), shared by the
-// look-back kernels (diag_kernels.cu) and the pipelined persistent kernels (diag_pipe.cu).
+// Per-step math of the scalar-diagonal cells (ParaGRU mix='diag', ParaNLRU, ParaTitans), shared by
+// the look-back kernels (diag_kernels.cu) and the pipelined persistent kernels (diag_pipe.cu).
 //
-// Reference behaviour restated: cells/para_gru.py:418-467, cells/para_nlru.py:149-168 (step and
-// diagonal Jacobian), kernels/vjp_gru.py:107-138, kernels/vjp_nlru.py:88-108 (packed VJP).
+// Reference behaviour restated: cells/para_gru.py:418-467, cells/para_nlru.py:149-168,
+// cells/para_titans.py:170-216 (step and diagonal Jacobian), kernels/vjp_gru.py:107-138,
+// kernels/vjp_nlru.py:88-108 (packed VJP; the Titans VJP is the closed form of what the reference
+// obtains from autograd through ``step``, solvers/vjp.py:77-98).
 #pragma once
 #include "common.cuh"
 #include "kernels.h"
@@ -74,6 +76,52 @@ struct DiagCell<kCellNlru> {
         gw[0] = d_a;
         gw[1] = d_c;
         gp[0] = d_c * h;
+    }
+};
+
+// softplus with the reference's (torch.nn.functional.softplus) overflow guard
+__device__ __forceinline__ float softplus_f(float x) {
+    return x > 20.f ? x : 0.6931471805599453f * __log2f(1.f + exp_f(x));
+}
+
+// ParaTitans: h' = (1 - alpha) h - theta (h k - v) k + u tanh(n_x + r h),
+// gates (alpha_pre, theta_pre, k, v, n_x) = W_x(x), parameters (u, r).
+template <>
+struct DiagCell<kCellTitans> {
+    static constexpr int G = 5, NP = 2;
+    struct Acts {
+        float alpha, theta, sg_theta, k, v, n;
+    };
+    __device__ static __forceinline__ void eval(float h, const float (&g)[5], const float (&p)[2],
+                                                float& f, float& j, Acts& a) {
+        a.alpha = sigmoid_f(g[0]);
+        a.theta = softplus_f(g[1]);
+        a.sg_theta = sigmoid_f(g[1]);  // d softplus / d pre
+        a.k = g[2];
+        a.v = g[3];
+        a.n = tanh_f(fmaf(p[1], h, g[4]));
+        const float grad = (h * a.k - a.v) * a.k;
+        f = fmaf(p[0], a.n, fmaf(-a.theta, grad, (1.f - a.alpha) * h));
+        j = (1.f - a.alpha) - a.theta * a.k * a.k + p[0] * (1.f - a.n * a.n) * p[1];
+    }
+    __device__ static __forceinline__ float step(float h, const float (&g)[5], const float (&p)[2]) {
+        const float alpha = sigmoid_f(g[0]);
+        const float theta = softplus_f(g[1]);
+        const float n = tanh_f(fmaf(p[1], h, g[4]));
+        const float grad = (h * g[2] - g[3]) * g[2];
+        return fmaf(p[0], n, fmaf(-theta, grad, (1.f - alpha) * h));
+    }
+    __device__ static __forceinline__ void vjp(float h, const Acts& a, const float (&p)[2], float mu,
+                                               float (&gw)[5], float (&gp)[2]) {
+        const float np_ = 1.f - a.n * a.n;
+        const float err = h * a.k - a.v;
+        gw[0] = -mu * h * a.alpha * (1.f - a.alpha);
+        gw[1] = -mu * err * a.k * a.sg_theta;
+        gw[2] = -mu * a.theta * (err + h * a.k);
+        gw[3] = mu * a.theta * a.k;
+        gw[4] = mu * p[0] * np_;
+        gp[0] = mu * a.n;
+        gp[1] = gw[4] * h;
     }
 };
 

@@ -439,6 +439,10 @@ cudaError_t launch_diag_newton(int cell, int dtype, const DiagFwdArgs& a, bool f
         return dtype == kF32 ? launch_fwd<kCellGruDiag, float>(a, first, last, s)
                              : launch_fwd<kCellGruDiag, __nv_bfloat16>(a, first, last, s);
     }
+    if (cell == kCellTitans) {
+        return dtype == kF32 ? launch_fwd<kCellTitans, float>(a, first, last, s)
+                             : launch_fwd<kCellTitans, __nv_bfloat16>(a, first, last, s);
+    }
     return dtype == kF32 ? launch_fwd<kCellNlru, float>(a, first, last, s)
                          : launch_fwd<kCellNlru, __nv_bfloat16>(a, first, last, s);
 }
@@ -451,6 +455,11 @@ cudaError_t launch_diag_newton_agg(int cell, int dtype, const DiagFwdArgs& a, cu
             diag_newton_agg_kernel<kCellGruDiag, float, kDiagL, kDiagW><<<grid, blk, 0, s>>>(a);
         else
             diag_newton_agg_kernel<kCellGruDiag, __nv_bfloat16, kDiagL, kDiagW><<<grid, blk, 0, s>>>(a);
+    } else if (cell == kCellTitans) {
+        if (dtype == kF32)
+            diag_newton_agg_kernel<kCellTitans, float, kDiagL, kDiagW><<<grid, blk, 0, s>>>(a);
+        else
+            diag_newton_agg_kernel<kCellTitans, __nv_bfloat16, kDiagL, kDiagW><<<grid, blk, 0, s>>>(a);
     } else {
         if (dtype == kF32)
             diag_newton_agg_kernel<kCellNlru, float, kDiagL, kDiagW><<<grid, blk, 0, s>>>(a);
@@ -480,6 +489,8 @@ cudaError_t launch_diag_guess(int cell, int dtype, bool out_f32, const void* wx,
         launch_guess_t<CELL, __nv_bfloat16, __nv_bfloat16>(wx, par, h0, out, B, T, d, s);
     if (cell == kCellGruDiag) {
         PRB_GUESS(kCellGruDiag)
+    } else if (cell == kCellTitans) {
+        PRB_GUESS(kCellTitans)
     } else {
         PRB_GUESS(kCellNlru)
     }
@@ -506,6 +517,8 @@ cudaError_t launch_diag_residual(int cell, int dtype, bool st_f32, const void* w
             (const __nv_bfloat16*)wx, par, halo, (const __nv_bfloat16*)st, B, T, d, dst);
     if (cell == kCellGruDiag) {
         PRB_RES(kCellGruDiag)
+    } else if (cell == kCellTitans) {
+        PRB_RES(kCellTitans)
     } else {
         PRB_RES(kCellNlru)
     }
@@ -526,6 +539,12 @@ cudaError_t launch_diag_bwd(int cell, int dtype, const DiagBwdArgs& a, bool agg_
             PRB_BWD(kCellGruDiag, float)
         } else {
             PRB_BWD(kCellGruDiag, __nv_bfloat16)
+        }
+    } else if (cell == kCellTitans) {
+        if (dtype == kF32) {
+            PRB_BWD(kCellTitans, float)
+        } else {
+            PRB_BWD(kCellTitans, __nv_bfloat16)
         }
     } else {
         if (dtype == kF32) {

@@ -20,7 +20,10 @@ struct Options {
 };
 Options& options();
 
-enum Cell : int { kCellGruDiag = 0, kCellNlru = 1, kCellSlstmDiag = 2, kCellGruHead = 3 };
+enum Cell : int { kCellGruDiag = 0, kCellNlru = 1, kCellSlstmDiag = 2, kCellGruHead = 3, kCellTitans = 4 };
+// gates and recurrent parameter vectors per channel of the scalar-diagonal cells
+inline bool is_diag_cell(int cell) { return cell == kCellGruDiag || cell == kCellNlru || cell == kCellTitans; }
+inline int diag_cell_params(int cell) { return cell == kCellGruDiag ? 3 : (cell == kCellTitans ? 2 : 1); }
 enum DType : int { kF32 = 0, kBF16 = 1 };
 
 // ---- scalar-diagonal cells ------------------------------------------------

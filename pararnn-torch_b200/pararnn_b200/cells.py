@@ -2,7 +2,7 @@
 
 Constructor arguments, parameter names, shapes, initialisation and clamp rules
 follow the reference cells (reference ``cells/para_gru.py``, ``cells/para_nlru.py``,
-``cells/para_slstm.py``), so a ``state_dict`` moves between the two libraries.
+``cells/para_slstm.py``, ``cells/para_titans.py``), so a ``state_dict`` moves between the two libraries.
 ``step`` is plain PyTorch and is what ``sequential_apply`` unrolls (evaluation and
 agreement checks); the training path never calls it.
 """
@@ -164,6 +164,58 @@ class ParaNLRU(nn.Module):
         return a * h_prev + (1.0 - a) * n
 
 
+class ParaTitans(nn.Module):
+    """Titans-style memory cell with a channelwise-diagonal Jacobian (reference
+    ``cells/para_titans.py``): ``(alpha_pre, theta_pre, k, v, n_pre) = W_x(x)``,
+
+        h_t = (1 - sigmoid(alpha_pre)) h_{t-1} - softplus(theta_pre) (h_{t-1} k - v) k
+              + u tanh(n_pre + r h_{t-1}),
+
+    with diagonal gains ``u``, ``r`` clamped to ``max_recurrent_norm``."""
+
+    def __init__(self, input_size=None, hidden_size=None, *, d_in=None, d_h=None,
+                 max_recurrent_norm=_UNSET, device=None, dtype=None):
+        super().__init__()
+        input_size, hidden_size = _sizes(input_size, hidden_size, d_in, d_h)
+        kw = {"device": device, "dtype": dtype}
+        self.input_size = self.d_in = input_size
+        self.hidden_size = self.d_h = hidden_size
+        self.state_slots = 1
+        self.mix = "diag"
+        self.jac_structure = "diag"
+        self.max_recurrent_norm = 0.5 if max_recurrent_norm is _UNSET else max_recurrent_norm
+        self.u = nn.Parameter(torch.empty(hidden_size, **kw))
+        self.r = nn.Parameter(torch.empty(hidden_size, **kw))
+        self.W_x = nn.Linear(input_size, 5 * hidden_size, bias=True, **kw)
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        nn.init.kaiming_uniform_(self.W_x.weight, a=math.sqrt(5))
+        nn.init.zeros_(self.W_x.bias)
+        with torch.no_grad():  # softplus(-1) ~ 0.31 keeps |theta k^2| modest
+            self.W_x.bias[self.d_h: 2 * self.d_h].fill_(-1.0)
+        _xavier_gaussian_vec_(self.u)
+        _xavier_gaussian_vec_(self.r)
+
+    def clipped_u(self) -> Tensor:
+        return _clamp(self.u, self.max_recurrent_norm)
+
+    def clipped_r(self) -> Tensor:
+        return _clamp(self.r, self.max_recurrent_norm)
+
+    def step(self, h_prev: Tensor, x: Tensor | None = None, *, wx: Tensor | None = None) -> Tensor:
+        if wx is None:
+            if x is None:
+                raise ValueError("ParaTitans.step needs x or wx")
+            wx = self.W_x(x)
+        alpha_pre, theta_pre, k, v, n_pre = wx.chunk(5, dim=-1)
+        alpha = torch.sigmoid(alpha_pre)
+        theta = torch.nn.functional.softplus(theta_pre)
+        grad = (h_prev * k - v) * k
+        n = torch.tanh(n_pre + self.clipped_r() * h_prev)
+        return (1.0 - alpha) * h_prev - theta * grad + self.clipped_u() * n
+
+
 class ParaSLSTM(nn.Module):
     """Stabilised sLSTM with channelwise recurrence ``R (4, d)``; state slots ``(c, n, m, h)``."""
 
@@ -222,10 +274,12 @@ def cell_kind(cell: nn.Module) -> str:
         return "gru_diag" if mix == "diag" else "gru_head"
     if name == "ParaNLRU":
         return "nlru"
+    if name == "ParaTitans":
+        return "titans"
     if name == "ParaSLSTM" and mix == "diag":
         return "slstm_diag"
     raise TypeError(
-        f"the CUDA backend covers ParaGRU (diag, head), ParaNLRU and ParaSLSTM(mix='diag'); "
+        f"the CUDA backend covers ParaGRU (diag, head), ParaNLRU, ParaTitans and ParaSLSTM(mix='diag'); "
         f"got {name}(mix={mix!r})")
 
 

@@ -19,7 +19,8 @@ from torch import Tensor, nn
 from . import _lib as L
 from .cells import cell_kind
 
-_CELL = {"gru_diag": L.CELL_GRU_DIAG, "nlru": L.CELL_NLRU, "slstm_diag": L.CELL_SLSTM_DIAG}
+_CELL = {"gru_diag": L.CELL_GRU_DIAG, "nlru": L.CELL_NLRU, "slstm_diag": L.CELL_SLSTM_DIAG,
+         "titans": L.CELL_TITANS}
 
 
 def can_decode_step(cell: nn.Module, ref: Tensor) -> bool:
@@ -61,6 +62,8 @@ def _raw_params(cell: nn.Module, kind: str, dtype) -> Tensor:
         p = torch.stack([cell.a_z, cell.a_r, cell.a_n])
     elif kind == "nlru":
         p = cell.u[None]
+    elif kind == "titans":
+        p = torch.stack([cell.u, cell.r])
     else:
         p = cell.R
     return p.detach().to(dtype).contiguous()

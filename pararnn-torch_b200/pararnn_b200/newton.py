@@ -86,6 +86,8 @@ def _recurrent_params(cell: nn.Module, kind: str):
         return tuple(cell.clipped_a_head())
     if kind == "nlru":
         return (cell.clipped_u(),)
+    if kind == "titans":
+        return (cell.clipped_u(), cell.clipped_r())
     return (cell.clipped_r(),)
 
 
@@ -100,6 +102,9 @@ def _solve_window(cell, kind, wx, h0, cfg, dstats, want_residual, cu_seqlens=Non
     if kind == "nlru":
         return ops.newton_nlru_fused(wx, rec[0], h0, cu_seqlens, block_table, max_iters=K, omega=cfg.omega,
                                      stats=dstats, want_residual=want_residual)
+    if kind == "titans":
+        return ops.newton_titans_fused(wx, rec[0], rec[1], h0, cu_seqlens, block_table, max_iters=K,
+                                       omega=cfg.omega, stats=dstats, want_residual=want_residual)
     if kind == "slstm_diag":
         return ops.newton_slstm_fused(wx, rec[0], h0, None, block_table, max_iters=K, omega=cfg.omega,
                                       eps=float(cell.eps), picard_iters=int(cfg.picard_iters or 0),
@@ -230,6 +235,9 @@ def _reverse_window(cell, kind, states, wx, grad_states, h0):
     if kind == "nlru":
         g_wx, gu, g_h0 = ops.nlru_reverse_vjp(states, wx, rec[0], grad_states, h0)
         return g_wx, {"u": gu}, g_h0
+    if kind == "titans":
+        g_wx, gu, gr, g_h0 = ops.titans_reverse_vjp(states, wx, rec[0], rec[1], grad_states, h0)
+        return g_wx, {"u": gu, "r": gr}, g_h0
     if kind == "slstm_diag":
         g_wx, gr, g_h0 = ops.slstm_reverse_vjp(states, wx, rec[0], grad_states, h0, float(cell.eps))
         return g_wx, {"R": gr}, g_h0

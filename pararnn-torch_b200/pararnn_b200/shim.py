@@ -30,6 +30,8 @@ def _kind(cell) -> str | None:
         return "gru_diag" if mix == "diag" else ("gru_head" if mix == "head" else None)
     if name == "ParaNLRU":
         return "nlru"
+    if name == "ParaTitans":
+        return "titans"
     if name == "ParaSLSTM" and mix == "diag":
         return "slstm_diag"
     return None
@@ -68,6 +70,9 @@ def install():
         if kind == "nlru":
             return ops.newton_nlru_fused(wx, cell.clipped_u(), h0, cu_seqlens, block_table, max_iters=max_iters,
                                          omega=omega, want_residual=False)
+        if kind == "titans":
+            return ops.newton_titans_fused(wx, cell.clipped_u(), cell.clipped_r(), h0, cu_seqlens, block_table,
+                                           max_iters=max_iters, omega=omega, want_residual=False)
         if kind == "slstm_diag":
             return ops.newton_slstm_fused(wx, cell.clipped_r(), h0, None, block_table, max_iters=max_iters,
                                           omega=omega, eps=float(cell.eps), picard_iters=int(picard_iters or 0),

@@ -86,6 +86,11 @@ def run_case(name, cell, x, *, K, P=None, h0=None, omega=1.0, cu_seqlens=None):
         out["raw_params"] = _np(cell.u)[None]
         out["g_params"] = _np(cell.u.grad)[None]
         out["cell"] = "nlru"
+    elif kind == "ParaTitans":
+        out["params"] = np.stack([_np(cell.clipped_u()), _np(cell.clipped_r())])
+        out["raw_params"] = np.stack([_np(cell.u), _np(cell.r)])
+        out["g_params"] = np.stack([_np(cell.u.grad), _np(cell.r.grad)])
+        out["cell"] = "titans"
     elif kind == "ParaSLSTM":
         out["params"] = _np(cell.clipped_r())
         out["raw_params"] = _np(cell.R)
@@ -111,7 +116,7 @@ def main():
     import logging
 
     logging.disable(logging.CRITICAL)
-    from pararnn import ParaGRU, ParaNLRU, ParaSLSTM
+    from pararnn import ParaGRU, ParaNLRU, ParaSLSTM, ParaTitans
 
     torch.set_num_threads(4)
 
@@ -187,6 +192,17 @@ def main():
              h0=torch.stack([0.3 * torch.randn(3, 8), torch.rand(3, 8) + 0.5,
                              0.2 * torch.randn(3, 8), 0.3 * torch.randn(3, 8)], dim=1),
              cu_seqlens=[0, 16, 17, 45])
+
+    # --- ParaTitans (scalar-diagonal memory cell) ---
+    torch.manual_seed(30)
+    cell_t = ParaTitans(10, 12)
+    with torch.no_grad():
+        cell_t.u.mul_(5.0)  # some entries reach the +-0.5 clamp
+        cell_t.r.mul_(5.0)
+    run_case("titans_k3", cell_t, torch.randn(2, 70, 10), K=3)
+    run_case("titans_k2_h0_omega", cell_t, torch.randn(2, 41, 10), K=2, h0=0.5 * torch.randn(2, 12), omega=0.9)
+    run_case("titans_packed_k3_h0", cell_t, torch.randn(1, 37, 10), K=3, h0=0.5 * torch.randn(3, 12),
+             cu_seqlens=[0, 1, 15, 37])
 
 
 if __name__ == "__main__":

@@ -5,7 +5,7 @@ import torch
 
 from oracle import oracle
 
-GATES = {"gru_diag": 3, "nlru": 2, "slstm_diag": 4, "gru_head": 3}
+GATES = {"gru_diag": 3, "nlru": 2, "slstm_diag": 4, "gru_head": 3, "titans": 5}
 
 
 def bf16_round(a):
@@ -23,6 +23,10 @@ def make_problem(kind, B, T, d, seed, *, h0=False, x_scale=1.0, bias_f=0.0, rec_
         a0 = rng.uniform(0.9, 0.999, size=d)
         wx[..., :d] += np.log(a0 / (1 - a0)).astype(np.float32)
         params = np.clip(rec_scale * 0.3 * rng.standard_normal((1, d)), -0.5, 0.5).astype(np.float32)
+    elif kind == "titans":
+        wx[..., d:2 * d] -= 1.0  # softplus(theta_pre) ~ 0.3, as the cell's bias initialisation
+        wx[..., 2 * d:4 * d] *= 0.5
+        params = np.clip(rec_scale * 0.3 * rng.standard_normal((2, d)), -0.5, 0.5).astype(np.float32)
     elif kind == "slstm_diag":
         wx[..., d:2 * d] += bias_f
         params = np.clip(rec_scale * 0.3 * rng.standard_normal((4, d)), -0.5, 0.5).astype(np.float32)

@@ -19,7 +19,7 @@ BF16_RTOL = 2e-2
 
 
 # the packed (cu_seqlens) fixtures have their own test file
-RECT = [n for n in golden_names("gru_diag") + golden_names("nlru") if "packed" not in n]
+RECT = [n for n in golden_names("gru_diag") + golden_names("nlru") + golden_names("titans") if "packed" not in n]
 
 
 def _fwd(kind, wx, params, h0, K, omega=1.0, dtype=torch.float32):
@@ -29,6 +29,9 @@ def _fwd(kind, wx, params, h0, K, omega=1.0, dtype=torch.float32):
     if kind == "gru_diag":
         H = ops.newton_gru_fused(dev(wx, dtype), dev(params[0], dtype), dev(params[1], dtype),
                                  dev(params[2], dtype), dev(h0, dtype), max_iters=K, omega=omega, stats=st)
+    elif kind == "titans":
+        H = ops.newton_titans_fused(dev(wx, dtype), dev(params[0], dtype), dev(params[1], dtype), dev(h0, dtype),
+                                    max_iters=K, omega=omega, stats=st)
     else:
         H = ops.newton_nlru_fused(dev(wx, dtype), dev(params[0], dtype), dev(h0, dtype), max_iters=K,
                                   omega=omega, stats=st)
@@ -45,6 +48,10 @@ def _bwd(kind, H, wx, params, G, h0, dtype=torch.float32):
                                                      dev(params[1], dtype), dev(params[2], dtype),
                                                      dev(G, dtype), dev(h0, dtype))
         gp = torch.stack([gz, gr, gn])
+    elif kind == "titans":
+        g_wx, gu, gr, g_h0 = ops.titans_reverse_vjp(dev(H, dtype), dev(wx, dtype), dev(params[0], dtype),
+                                                    dev(params[1], dtype), dev(G, dtype), dev(h0, dtype))
+        gp = torch.stack([gu, gr])
     else:
         g_wx, gu, g_h0 = ops.nlru_reverse_vjp(dev(H, dtype), dev(wx, dtype), dev(params[0], dtype),
                                               dev(G, dtype), dev(h0, dtype))
@@ -80,7 +87,7 @@ SHAPES = [(1, 1, 1), (2, 2, 5), (1, 63, 33), (2, 64, 32), (3, 65, 31), (2, 127, 
           (1, 1000, 96), (2, 4096, 40)]
 
 
-@pytest.mark.parametrize("kind", ["gru_diag", "nlru"])
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans"])
 @pytest.mark.parametrize("B,T,d", SHAPES)
 @pytest.mark.parametrize("K", [1, 3])
 def test_forward_seeded_vs_oracle_fp32(kind, B, T, d, K):
@@ -93,7 +100,7 @@ def test_forward_seeded_vs_oracle_fp32(kind, B, T, d, K):
     assert abs(res - want.max_residual) <= 5e-3 * want.max_residual + 2e-6
 
 
-@pytest.mark.parametrize("kind", ["gru_diag", "nlru"])
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans"])
 def test_k0_returns_guess_and_k2_matches(kind):
     wx, params, h0 = make_problem(kind, 2, 200, 48, seed=5, h0=True)
     g0 = oracle.guess(oracle.KIND[kind], wx, params, h0)
@@ -105,7 +112,7 @@ def test_k0_returns_guess_and_k2_matches(kind):
     assert np.abs(H2 - want.states).max() <= FP32_ATOL * max(1.0, max(want.history))
 
 
-@pytest.mark.parametrize("kind", ["gru_diag", "nlru"])
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans"])
 @pytest.mark.parametrize("B,T,d", [(1, 1, 3), (2, 65, 31), (2, 513, 70), (1, 3000, 64)])
 def test_backward_seeded_vs_oracle_fp32(kind, B, T, d):
     wx, params, h0 = make_problem(kind, B, T, d, seed=T + d, h0=(T % 2 == 1))
@@ -118,7 +125,7 @@ def test_backward_seeded_vs_oracle_fp32(kind, B, T, d):
     assert rel_err(g_h0, want_h0) <= 2e-5
 
 
-@pytest.mark.parametrize("kind", ["gru_diag", "nlru"])
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans"])
 def test_bf16_io_within_relative_tolerance(kind):
     wx, params, h0 = make_problem(kind, 2, 2048, 96, seed=9, h0=True)
     wx, params, h0 = bf16_round(wx), bf16_round(params), bf16_round(h0)

@@ -22,6 +22,9 @@ def _cell_from_golden(g):
     elif g["cell"] == "nlru":
         cell = prb.ParaNLRU(d_in, d)
         names = ("u",)
+    elif g["cell"] == "titans":
+        cell = prb.ParaTitans(d_in, d)
+        names = ("u", "r")
     else:
         cell = prb.ParaSLSTM(d_in, d, eps=g["eps"])
         names = ("R",)
