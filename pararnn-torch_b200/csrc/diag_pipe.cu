@@ -445,8 +445,13 @@ inline bool wide_cta(int B, int d) { return 2 * B * ((d + kLanes - 1) / kLanes) 
 
 template <int CELL, typename TIO, int NSTAGE>
 cudaError_t launch_fwd_t(const DiagFwdArgs& a, bool first, bool last, cudaStream_t s) {
-    if (!wide_cta(a.B, a.d)) return launch_fwd_w<CELL, TIO, NSTAGE, 8, 8>(a, first, last, s);
-    return launch_fwd_w<CELL, TIO, NSTAGE, 8, 16>(a, first, last, s);
+    using Wide = DiagPipeFwdSmem<DiagCell<CELL>::G, TIO, 8, 16, NSTAGE>;
+    if constexpr (Wide::TOTAL > 227 * 1024) {
+        return launch_fwd_w<CELL, TIO, NSTAGE, 8, 8>(a, first, last, s);
+    } else {
+        if (!wide_cta(a.B, a.d)) return launch_fwd_w<CELL, TIO, NSTAGE, 8, 8>(a, first, last, s);
+        return launch_fwd_w<CELL, TIO, NSTAGE, 8, 16>(a, first, last, s);
+    }
 }
 
 template <int CELL, typename TIO, int NSTAGE, int L, int W>
@@ -467,10 +472,18 @@ cudaError_t launch_bwd_w(const DiagBwdArgs& a, cudaStream_t s) {
     return cudaGetLastError();
 }
 
+constexpr int kMaxDynSmem = 227 * 1024;
+
 template <int CELL, typename TIO, int NSTAGE>
 cudaError_t launch_bwd_t(const DiagBwdArgs& a, cudaStream_t s) {
-    if (!wide_cta(a.B, a.d)) return launch_bwd_w<CELL, TIO, NSTAGE, 8, 8>(a, s);
-    return launch_bwd_w<CELL, TIO, NSTAGE, 8, 16>(a, s);
+    // the 16-warp ring of a cell with many gates may not fit shared memory (Titans, fp32)
+    using Wide = DiagPipeBwdSmem<DiagCell<CELL>::G, TIO, 8, 16, NSTAGE>;
+    if constexpr (Wide::TOTAL > kMaxDynSmem) {
+        return launch_bwd_w<CELL, TIO, NSTAGE, 8, 8>(a, s);
+    } else {
+        if (!wide_cta(a.B, a.d)) return launch_bwd_w<CELL, TIO, NSTAGE, 8, 8>(a, s);
+        return launch_bwd_w<CELL, TIO, NSTAGE, 8, 16>(a, s);
+    }
 }
 
 }  // namespace

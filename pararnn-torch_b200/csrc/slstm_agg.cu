@@ -155,19 +155,20 @@ slstm_newton_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __g
                     const float fc = lin.pc - cur[0], fn = lin.pn - cur[1];
                     const float fm = lin.pm - cur[2], fh = lin.ph - cur[3];
                     const float fh2 = fh - lin.ia * fc - lin.ib * fn;
+                    // the four matrix columns two at a time on packed FMAs, then the offset column
     #pragma unroll
-                    for (int c5 = 0; c5 < 5; ++c5) {
-                        const bool off = (c5 == 4);
-                        float xc = off ? mp[16] : mp[0 * 4 + c5], xn = off ? mp[17] : mp[1 * 4 + c5];
-                        float xm = off ? mp[18] : mp[2 * 4 + c5], xh = off ? mp[19] : mp[3 * 4 + c5];
-                        slstm_apply(lin, off ? fc : 0.f, off ? fn : 0.f, off ? fm : 0.f, off ? fh2 : 0.f, xc, xn,
-                                    xm, xh);
-                        if (off) {
-                            mp[16] = xc; mp[17] = xn; mp[18] = xm; mp[19] = xh;
-                        } else {
-                            mp[0 * 4 + c5] = xc; mp[1 * 4 + c5] = xn; mp[2 * 4 + c5] = xm; mp[3 * 4 + c5] = xh;
-                        }
+                    for (int c2 = 0; c2 < 4; c2 += 2) {
+                        float2 xc = make_float2(mp[0 * 4 + c2], mp[0 * 4 + c2 + 1]);
+                        float2 xn = make_float2(mp[1 * 4 + c2], mp[1 * 4 + c2 + 1]);
+                        float2 xm = make_float2(mp[2 * 4 + c2], mp[2 * 4 + c2 + 1]);
+                        float2 xh = make_float2(mp[3 * 4 + c2], mp[3 * 4 + c2 + 1]);
+                        slstm_apply_cols2(lin, xc, xn, xm, xh);
+                        mp[0 * 4 + c2] = xc.x; mp[0 * 4 + c2 + 1] = xc.y;
+                        mp[1 * 4 + c2] = xn.x; mp[1 * 4 + c2 + 1] = xn.y;
+                        mp[2 * 4 + c2] = xm.x; mp[2 * 4 + c2 + 1] = xm.y;
+                        mp[3 * 4 + c2] = xh.x; mp[3 * 4 + c2 + 1] = xh.y;
                     }
+                    slstm_apply(lin, fc, fn, fm, fh2, mp[16], mp[17], mp[18], mp[19]);
     #pragma unroll
                     for (int q = 0; q < 4; ++q) prev[q] = cur[q];
                 }
@@ -354,16 +355,21 @@ slstm_bwd_agg_seg_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid
                 SlstmLin lin;
                 slstm_linearize(prev, w, r4, a.eps, lin);
 #pragma unroll
-                for (int c5 = 0; c5 < 5; ++c5) {
-                    const bool off = (c5 == 4);
-                    float xc = off ? mp[16] + g[0] : mp[0 * 4 + c5], xn = off ? mp[17] + g[1] : mp[1 * 4 + c5];
-                    float xm = off ? mp[18] + g[2] : mp[2 * 4 + c5], xh = off ? mp[19] + g[3] : mp[3 * 4 + c5];
+                for (int c2 = 0; c2 < 4; c2 += 2) {
+                    float2 xc = make_float2(mp[0 * 4 + c2], mp[0 * 4 + c2 + 1]);
+                    float2 xn = make_float2(mp[1 * 4 + c2], mp[1 * 4 + c2 + 1]);
+                    float2 xm = make_float2(mp[2 * 4 + c2], mp[2 * 4 + c2 + 1]);
+                    float2 xh = make_float2(mp[3 * 4 + c2], mp[3 * 4 + c2 + 1]);
+                    slstm_apply_t_cols2(lin, xc, xn, xm, xh);
+                    mp[0 * 4 + c2] = xc.x; mp[0 * 4 + c2 + 1] = xc.y;
+                    mp[1 * 4 + c2] = xn.x; mp[1 * 4 + c2 + 1] = xn.y;
+                    mp[2 * 4 + c2] = xm.x; mp[2 * 4 + c2 + 1] = xm.y;
+                    mp[3 * 4 + c2] = xh.x; mp[3 * 4 + c2 + 1] = xh.y;
+                }
+                {
+                    float xc = mp[16] + g[0], xn = mp[17] + g[1], xm = mp[18] + g[2], xh = mp[19] + g[3];
                     slstm_apply_t(lin, xc, xn, xm, xh);
-                    if (off) {
-                        mp[16] = xc; mp[17] = xn; mp[18] = xm; mp[19] = xh;
-                    } else {
-                        mp[0 * 4 + c5] = xc; mp[1 * 4 + c5] = xn; mp[2 * 4 + c5] = xm; mp[3 * 4 + c5] = xh;
-                    }
+                    mp[16] = xc; mp[17] = xn; mp[18] = xm; mp[19] = xh;
                 }
             }
         }

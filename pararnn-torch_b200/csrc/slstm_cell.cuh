@@ -89,6 +89,35 @@ __device__ __forceinline__ void slstm_apply(const SlstmLin& l, float fc, float f
     xh = nh;
 }
 
+// Two columns of a map at once on packed fp32 FMAs (fma.rn.f32x2): x <- J x for both columns, same
+// operations and rounding per column as slstm_apply with a zero offset.
+__device__ __forceinline__ void slstm_apply_cols2(const SlstmLin& l, float2& xc, float2& xn, float2& xm,
+                                                  float2& xh) {
+    const float2 nc = __ffma2_rn(splat2(l.f), xc, __ffma2_rn(splat2(l.jcm), xm, __fmul2_rn(splat2(l.jch), xh)));
+    const float2 nn = __ffma2_rn(splat2(l.f), xn, __ffma2_rn(splat2(l.jnm), xm, __fmul2_rn(splat2(l.jnh), xh)));
+    const float2 nm = __ffma2_rn(splat2(l.alpha), xm, __fmul2_rn(splat2(l.dm), xh));
+    const float2 nh = __ffma2_rn(splat2(l.ia), nc, __ffma2_rn(splat2(l.ib), nn, __fmul2_rn(splat2(l.ie), xh)));
+    xc = nc;
+    xn = nn;
+    xm = nm;
+    xh = nh;
+}
+
+// y = J^T x for two columns at once (packed counterpart of slstm_apply_t)
+__device__ __forceinline__ void slstm_apply_t_cols2(const SlstmLin& l, float2& xc, float2& xn, float2& xm,
+                                                    float2& xh) {
+    const float2 pc = __ffma2_rn(splat2(l.ia), xh, xc), pn = __ffma2_rn(splat2(l.ib), xh, xn);
+    const float2 yc = __fmul2_rn(splat2(l.f), pc), yn = __fmul2_rn(splat2(l.f), pn);
+    const float2 ym = __ffma2_rn(splat2(l.jcm), pc, __ffma2_rn(splat2(l.jnm), pn, __fmul2_rn(splat2(l.alpha), xm)));
+    const float2 yh = __ffma2_rn(
+        splat2(l.jch), pc,
+        __ffma2_rn(splat2(l.jnh), pn, __ffma2_rn(splat2(l.dm), xm, __fmul2_rn(splat2(l.ie), xh))));
+    xc = yc;
+    xn = yn;
+    xm = ym;
+    xh = yh;
+}
+
 // Activations kept between the two phases of the reverse kernel.
 struct SlstmAct {
     float i, f, z, o, c, n, invD, alpha, hp;
