@@ -638,6 +638,7 @@ def run_gpu_sharded(args):
         res = drive(forward_program(ops, rank, world, K_NEWTON, P_PICARD, None), comm)
         keep["bwd"] = drive(backward_program(ops, rank, world, res.states, G_io, res.halo), comm)
         keep["res"] = res
+        keep["launches"] = ops.launches
 
     def barrier():
         dist.barrier(device_ids=[local])
@@ -770,7 +771,9 @@ def run_gpu_sharded(args):
                     "includes": "per rank: H2D of its x shard, 3 W_x GEMMs, sharded Newton+scan fwd and "
                                 "reverse scan + VJP with NCCL carry exchange and gradient all-reduce, "
                                 "D2H of loss"},
-            "gpu_launches": (2 * (P_PICARD + 1 + K_NEWTON + 1) + 12) * args.steps,
+            # kernels of this library per step on rank 0 (sweeps, folds, reductions; counted by the
+            # driver object), the same whether issued from Python or replayed from the graph
+            "gpu_launches": keep.get("launches", 0) * args.steps,
             "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "peak": peak * world,
                          "unit": "GB/s", "achieved": step_bytes / (ms / 1e3) / 1e9,
                          "frac": step_bytes / (ms / 1e3) / 1e9 / (peak * world), "peak_kind": peak_kind,
@@ -1005,6 +1008,81 @@ def c5_sharded_record(args, rank, world, dev, dist, barrier):
     return record
 
 
+def run_reference_gpu(args):
+    """`--workload ref_fused`: the REFERENCE's own GPU path (its Triton kernels behind
+    scan_backend="fused", and its eager PyTorch path on CUDA) timed on this GPU next to this backend
+    on the same tensors -- a secondary comparison, not the `--impl reference` arm (which stays the
+    CPU path).  Needs the importable copy of the reference that `oracle/make_ref.py` creates; prints
+    one JSON line per case, with the error text where the reference's path does not run."""
+    import torch
+
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "pararnn")):
+        print(json.dumps({"workload": "ref_fused", "unavailable": "no copy of the reference under oracle/_ref"}))
+        return
+    sys.path.insert(0, ref_dir)
+    import logging
+
+    logging.disable(logging.WARNING)
+    import pararnn as ref
+
+    import pararnn_b200 as prb
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+
+    def timed(fn, n=5):
+        for _ in range(2):
+            fn()
+        return time_region(fn, n, None) / n
+
+    cases = [("slstm_diag d=1024 bf16 B=1 T=16384 K=2 P=5 (one row of C2)", "slstm", 1024, 1, 16384, torch.bfloat16, 2, 5),
+             ("slstm_diag d=1024 fp32 B=1 T=4096 K=2 P=3", "slstm", 1024, 1, 4096, torch.float32, 2, 3),
+             ("nlru d=768 bf16 B=4 T=8192 K=2 (one layer of C5)", "nlru", 768, 4, 8192, torch.bfloat16, 2, None),
+             ("gru_diag d=64 fp32 B=2 T=1024 K=3 (C1)", "gru", 64, 2, 1024, torch.float32, 3, None)]
+    for label, kind, d, Bc, Tc, dtype, K, P in cases:
+        torch.manual_seed(1)
+        mk = {"slstm": lambda m: m.ParaSLSTM(d, d), "nlru": lambda m: m.ParaNLRU(d, d), "gru": lambda m: m.ParaGRU(d, d)}[kind]
+        cell_ref = mk(ref).to(dev)
+        if kind == "slstm":
+            with torch.no_grad():
+                cell_ref.W_x.bias[d:2 * d] = 3.0
+        cell_ref = cell_ref.to(dtype)
+        cell_ours = mk(prb).to(dev, dtype)
+        cell_ours.load_state_dict(cell_ref.state_dict())
+        x = ((0.5 if kind == "slstm" else 1.0) * torch.randn(Bc, Tc, d, device=dev)).to(dtype)
+        line = {"workload": "ref_fused", "case": label, "tokens": Bc * Tc}
+
+        def run(module, cell, backend):
+            cfg = module.NewtonConfig(max_iters=K, scan_backend=backend, picard_iters=P, picard_adapt=False,
+                                      residual_atol=None, residual_fail=None)
+            xin = x.detach().requires_grad_(True)
+            H = module.newton_apply(cell, xin, cfg)
+            (H.float().sum() if kind != "slstm" else H[:, :, 3].float().sum()).backward()
+            cell.zero_grad(set_to_none=True)
+            return H.detach()
+
+        for name, module, cell, backend in (("ours", prb, cell_ours, "fused"),
+                                            ("reference_fused_triton", ref, cell_ref, "fused"),
+                                            ("reference_eager_cuda", ref, cell_ref, "eager")):
+            if name == "reference_eager_cuda" and Bc * Tc * d > 2 ** 24:
+                line[name] = "skipped: the eager path materialises the (B,T,S,S,d) Jacobian"
+                continue
+            try:
+                H = run(module, cell, backend)
+                sec = timed(lambda: run(module, cell, backend))
+                line[name + "_ms"] = sec * 1e3
+                if name == "ours":
+                    H_ours = H
+                else:
+                    a = H if kind != "slstm" else H[:, :, 3]
+                    b = H_ours if kind != "slstm" else H_ours[:, :, 3]
+                    line[name + "_max_rel_vs_ours"] = float((a.float() - b.float()).abs().max() / b.float().abs().max())
+            except Exception as exc:
+                line[name] = "error: " + repr(exc)[:400]
+        print(json.dumps(line), flush=True)
+
+
 def run_secondary(args):
     """Other BASELINE configurations (one JSON line each): `--workload c1|c3|c5`.
     c1: ParaGRU diag fp32 B=2 T=1024 d=64 K=3; c3: ParaGRU head 8x64 B=16 T=4096 K=3 (fp32 and
@@ -1125,7 +1203,7 @@ def main():
                     help="time steps per GPU (profiling captures use a smaller case)")
     ap.add_argument("--first-shard-weight", type=float, default=1.0,
                     help="N > 1: length of the first time shard relative to the others")
-    ap.add_argument("--workload", default="c2", choices=("c2", "c1", "c3", "c5"),
+    ap.add_argument("--workload", default="c2", choices=("c2", "c1", "c3", "c5", "ref_fused"),
                     help="c2 (default) is the headline line; the others print secondary lines")
     ap.add_argument("--c4-seq-len", type=int, default=0,
                     help="N > 1: sequence length of the c4_strong sub-record (default 131072)")
@@ -1140,6 +1218,9 @@ def main():
     T_PER_GPU = args.seq_len
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.workload == "ref_fused":
+        run_reference_gpu(args)
         return
     if args.workload != "c2":
         run_secondary(args)

@@ -37,7 +37,7 @@ typedef struct CUstream_st* prb_stream_t; /* cudaStream_t */
 
 enum { PRB_F32 = 0, PRB_BF16 = 1 };
 enum { PRB_CELL_GRU_DIAG = 0, PRB_CELL_NLRU = 1, PRB_CELL_SLSTM_DIAG = 2, PRB_CELL_GRU_HEAD = 3,
-       PRB_CELL_TITANS = 4 };
+       PRB_CELL_TITANS = 4, PRB_CELL_LSTM = 5 };
 enum {
     PRB_OK = 0,
     PRB_ERR_BAD_ARG = -1,     /* null pointer, non-positive size, unknown enum */
@@ -103,6 +103,23 @@ int prb_newton_nlru_fused(const void* wx, const void* u, const void* h0, void* o
 int prb_newton_titans_fused(const void* wx, const void* u, const void* r, const void* h0, void* out, int B,
                             int T, int d, int dtype, int max_iters, float omega, int want_residual,
                             void* workspace, size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
+
+/* ParaLSTM (CIFG peephole LSTM, diagonal recurrence, 2x2 block Jacobian per channel).  Replaces
+ * pararnn::newton_lstm_fused, kernels/custom_ops.py:437-483 -> kernels/newton_lstm.py and
+ * kernels/scan_lstm_block.py.  wx (B,T,3d) gates (f,z,o); a_f,a_z,a_o,c_f,c_o (d) clamped;
+ * h0 (B,2,d) slots (c,h) or NULL; out (B,T,2,d).  prb_bwd_lstm replaces reverse_scan_block2
+ * (solvers/scan.py:150-164) + lstm_recurrence_vjp (kernels/vjp_lstm.py): g_wx (B,T,3d), g_params
+ * fp32 (5,d) in the order (a_f,a_z,a_o,c_f,c_o), g_h0 fp32 (B,2,d) or NULL.  `backward` selects
+ * which of the two workspace layouts prb_lstm_workspace_bytes sizes. */
+size_t prb_lstm_workspace_bytes(int B, int T, int d, int max_iters, int backward);
+int prb_newton_lstm_fused(const void* wx, const void* a_f, const void* a_z, const void* a_o, const void* c_f,
+                          const void* c_o, const void* h0, void* out, int B, int T, int d, int dtype,
+                          int max_iters, float omega, int want_residual, void* workspace,
+                          size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
+int prb_bwd_lstm(const void* states, const void* wx, const void* a_f, const void* a_z, const void* a_o,
+                 const void* c_f, const void* c_o, const void* h0, const void* grad_states, void* g_wx,
+                 float* g_params, float* g_h0, int B, int T, int d, int dtype, void* workspace,
+                 size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
 
 /* ParaSLSTM mix='diag', including the frozen-gate Picard warm start.  Replaces
  * pararnn::newton_slstm_fused, kernels/custom_ops.py:486-540 ->

@@ -32,7 +32,7 @@
 #endif
 typedef REAL real;
 
-enum { CELL_GRU_DIAG = 0, CELL_NLRU = 1, CELL_SLSTM_DIAG = 2, CELL_GRU_HEAD = 3, CELL_TITANS = 4 };
+enum { CELL_GRU_DIAG = 0, CELL_NLRU = 1, CELL_SLSTM_DIAG = 2, CELL_GRU_HEAD = 3, CELL_TITANS = 4, CELL_LSTM = 5 };
 
 static inline real r_exp(real x) { return sizeof(real) == 4 ? (real)expf((float)x) : (real)exp((double)x); }
 static inline real r_tanh(real x) { return sizeof(real) == 4 ? (real)tanhf((float)x) : (real)tanh((double)x); }
@@ -47,7 +47,7 @@ int oracle_real_bytes(void) { return (int)sizeof(real); }
 static int gates_of(int kind) {
     return kind == CELL_NLRU ? 2 : (kind == CELL_SLSTM_DIAG ? 4 : (kind == CELL_TITANS ? 5 : 3));
 }
-static int slots_of(int kind) { return kind == CELL_SLSTM_DIAG ? 4 : 1; }
+static int slots_of(int kind) { return kind == CELL_SLSTM_DIAG ? 4 : (kind == CELL_LSTM ? 2 : 1); }
 
 /* ------------------------------------------------------------------ */
 /* Scalar-diagonal cells                                               */
@@ -100,6 +100,36 @@ static inline void diag_step(int kind, real h, const real *wt, int d, const real
                params[d + ch], f, j);
     else
         nlru(h, wt[0], wt[d], params[ch], f, j);
+}
+
+/* ------------------------------------------------------------------ */
+/* ParaLSTM (CIFG peephole LSTM, state (c, h), 2x2 block Jacobian)     */
+/* ------------------------------------------------------------------ */
+
+typedef struct {
+    real c_new, h_new, f, z, o, hact;
+} lstm_acts;
+
+/* cells/para_lstm.py:202-232 (_recurrence): gates (f, z, o) = chunk3(wx), parameters
+ * (a_f, a_z, a_o, c_f, c_o) clamped outside. */
+static inline void lstm_step(real c, real h, real fx, real zx, real ox, const real p[5], lstm_acts *a) {
+    a->f = r_sigmoid(p[0] * h + p[3] * c + fx);
+    a->z = r_tanh(p[1] * h + zx);
+    a->c_new = a->f * c + (1 - a->f) * a->z;
+    a->o = r_sigmoid(p[2] * h + p[4] * a->c_new + ox);
+    a->hact = r_tanh(a->c_new);
+    a->h_new = a->o * a->hact;
+}
+
+/* cells/para_lstm.py:186-200 (step_with_jacobian, eq. 3.2b): J[out*2+in], slots (c, h). */
+static inline void lstm_jac(const lstm_acts *a, real c, const real p[5], real J[4]) {
+    real fp = a->f * (1 - a->f), zp = 1 - a->z * a->z, op = a->o * (1 - a->o), hp = 1 - a->hact * a->hact;
+    real jcc = a->f + (c - a->z) * fp * p[3];
+    real jch = (c - a->z) * fp * p[0] + (1 - a->f) * zp * p[1];
+    J[0] = jcc;
+    J[1] = jch;
+    J[2] = (a->hact * op * p[4] + a->o * hp) * jcc;
+    J[3] = a->hact * op * (p[2] + p[4] * jch) + a->o * hp * jch;
 }
 
 /* ------------------------------------------------------------------ */
@@ -331,6 +361,19 @@ void oracle_sequential(int kind, const real *wx, const real *params, const real 
                     st[0] = a.c_new; st[1] = a.n_new; st[2] = a.m_new; st[3] = a.h_new;
                     for (int s = 0; s < 4; ++s) o[((size_t)t * 4 + s) * d] = st[s];
                 }
+            } else if (kind == CELL_LSTM) {
+                real p5[5];
+                for (int k = 0; k < 5; ++k) p5[k] = params[(size_t)k * d + ch];
+                real c = h0 ? h0[((size_t)b * 2 + 0) * d + ch] : 0, h = h0 ? h0[((size_t)b * 2 + 1) * d + ch] : 0;
+                for (int t = 0; t < T; ++t) {
+                    const real *wt = w + (size_t)t * 3 * d;
+                    lstm_acts a;
+                    lstm_step(c, h, wt[0], wt[d], wt[2 * (size_t)d], p5, &a);
+                    c = a.c_new;
+                    h = a.h_new;
+                    o[((size_t)t * 2 + 0) * d] = c;
+                    o[((size_t)t * 2 + 1) * d] = h;
+                }
             } else {
                 real h = h0 ? h0[(size_t)b * d + ch] : 0;
                 for (int t = 0; t < T; ++t) {
@@ -436,6 +479,32 @@ static real newton_pass(int kind, const real *wx, const real *params, const real
                         }
                         for (int k = 0; k < 4; ++k) prev[k] = cur[k];
                     }
+                } else if (kind == CELL_LSTM) {
+                    real *s = states + (size_t)b * T * 2 * d + ch;
+                    real p5[5];
+                    for (int k = 0; k < 5; ++k) p5[k] = params[(size_t)k * d + ch];
+                    real pc = h0 ? h0[((size_t)b * 2 + 0) * d + ch] : 0, ph = h0 ? h0[((size_t)b * 2 + 1) * d + ch] : 0;
+                    real dc = 0, dh = 0;
+                    for (int t = 0; t < T; ++t) {
+                        const real *wt = w + (size_t)t * 3 * d;
+                        lstm_acts a;
+                        lstm_step(pc, ph, wt[0], wt[d], wt[2 * (size_t)d], p5, &a);
+                        real cc = s[((size_t)t * 2 + 0) * d], ch_ = s[((size_t)t * 2 + 1) * d];
+                        real Fc = a.c_new - cc, Fh = a.h_new - ch_;
+                        lmax = nanmax(lmax, r_abs(Fc));
+                        lmax = nanmax(lmax, r_abs(Fh));
+                        if (apply) {
+                            real J[4];
+                            lstm_jac(&a, pc, p5, J);
+                            real nc = J[0] * dc + J[1] * dh + Fc, nh = J[2] * dc + J[3] * dh + Fh;
+                            dc = nc;
+                            dh = nh;
+                            s[((size_t)t * 2 + 0) * d] = cc + omega * dc;
+                            s[((size_t)t * 2 + 1) * d] = ch_ + omega * dh;
+                        }
+                        pc = cc;
+                        ph = ch_;
+                    }
                 } else {
                     real *s = states + (size_t)b * T * d + ch;
                     real prev = h0 ? h0[(size_t)b * d + ch] : 0, dl = 0;
@@ -507,6 +576,19 @@ static void newton_guess(int kind, const real *wx, const real *params, const rea
                                          (size_t)4 * d, tmp);
                 }
                 free(tmp);
+            } else if (kind == CELL_LSTM) {
+                real *s = states + (size_t)b * T * 2 * d + ch;
+                real p5[5];
+                for (int k = 0; k < 5; ++k) p5[k] = params[(size_t)k * d + ch];
+                for (int t = 0; t < T; ++t) {
+                    const real *wt = w + (size_t)t * 3 * d;
+                    real c = (t == 0 && h0) ? h0[((size_t)b * 2 + 0) * d + ch] : 0;
+                    real h = (t == 0 && h0) ? h0[((size_t)b * 2 + 1) * d + ch] : 0;
+                    lstm_acts a;
+                    lstm_step(c, h, wt[0], wt[d], wt[2 * (size_t)d], p5, &a);
+                    s[((size_t)t * 2 + 0) * d] = a.c_new;
+                    s[((size_t)t * 2 + 1) * d] = a.h_new;
+                }
             } else {
                 real *s = states + (size_t)b * T * d + ch;
                 for (int t = 0; t < T; ++t) {
@@ -626,10 +708,10 @@ void oracle_backward(int kind, const real *states, const real *wx, const real *p
         }
         return;
     }
-    const int NP = (kind == CELL_GRU_DIAG) ? 3 : (kind == CELL_NLRU ? 1 : (kind == CELL_TITANS ? 2 : 4));
+    const int NP = (kind == CELL_GRU_DIAG) ? 3 : (kind == CELL_NLRU ? 1 : (kind == CELL_TITANS ? 2 : (kind == CELL_LSTM ? 5 : 4)));
 #pragma omp parallel for schedule(static)
     for (int ch = 0; ch < d; ++ch) {
-        real gp[4] = {0, 0, 0, 0};
+        real gp[5] = {0, 0, 0, 0, 0};
         for (int b = 0; b < B; ++b) {
             const real *w = wx + (size_t)b * T * G * d + ch;
             real *gw = g_wx + (size_t)b * T * G * d + ch;
@@ -674,6 +756,43 @@ void oracle_backward(int kind, const real *states, const real *wx, const real *p
                     }
                 }
                 if (g_h0) for (int k = 0; k < 4; ++k) g_h0[((size_t)b * 4 + k) * d + ch] = jt[k];
+            } else if (kind == CELL_LSTM) {
+                /* eq. 2.6 with 2x2 blocks (solvers/scan.py:150-164) + the packed VJP of
+                 * kernels/vjp_lstm.py (lstm_recurrence_vjp_eager) */
+                const real *s = states + (size_t)b * T * 2 * d + ch;
+                const real *g = grad_states + (size_t)b * T * 2 * d + ch;
+                real p5[5];
+                for (int k = 0; k < 5; ++k) p5[k] = params[(size_t)k * d + ch];
+                real jc = 0, jh = 0;
+                for (int t = T - 1; t >= 0; --t) {
+                    real mc = (t == T - 1 ? 0 : jc) + g[((size_t)t * 2 + 0) * d];
+                    real mh = (t == T - 1 ? 0 : jh) + g[((size_t)t * 2 + 1) * d];
+                    if (mu_out) {
+                        mu_out[((size_t)b * T + t) * 2 * d + ch] = mc;
+                        mu_out[((size_t)b * T + t) * 2 * d + d + ch] = mh;
+                    }
+                    real pc = t > 0 ? s[((size_t)(t - 1) * 2 + 0) * d] : (h0 ? h0[((size_t)b * 2 + 0) * d + ch] : 0);
+                    real ph = t > 0 ? s[((size_t)(t - 1) * 2 + 1) * d] : (h0 ? h0[((size_t)b * 2 + 1) * d + ch] : 0);
+                    const real *wt = w + (size_t)t * 3 * d;
+                    lstm_acts a;
+                    lstm_step(pc, ph, wt[0], wt[d], wt[2 * (size_t)d], p5, &a);
+                    real J[4];
+                    lstm_jac(&a, pc, p5, J);
+                    real d_opre = mh * a.hact * a.o * (1 - a.o);
+                    real d_cn = mc + mh * a.o * (1 - a.hact * a.hact) + d_opre * p5[4];
+                    real d_fpre = d_cn * (pc - a.z) * a.f * (1 - a.f);
+                    real d_zpre = d_cn * (1 - a.f) * (1 - a.z * a.z);
+                    real *gwt = gw + (size_t)t * 3 * d;
+                    gwt[0] = d_fpre; gwt[d] = d_zpre; gwt[2 * (size_t)d] = d_opre;
+                    gp[0] += d_fpre * ph; gp[1] += d_zpre * ph; gp[2] += d_opre * ph;
+                    gp[3] += d_fpre * pc; gp[4] += d_opre * a.c_new;
+                    jc = J[0] * mc + J[2] * mh;
+                    jh = J[1] * mc + J[3] * mh;
+                }
+                if (g_h0) {
+                    g_h0[((size_t)b * 2 + 0) * d + ch] = jc;
+                    g_h0[((size_t)b * 2 + 1) * d + ch] = jh;
+                }
             } else {
                 const real *s = states + (size_t)b * T * d + ch;
                 const real *g = grad_states + (size_t)b * T * d + ch;

@@ -629,6 +629,124 @@ int prb_bwd_titans(const void* states, const void* wx, const void* u, const void
                         dtype, workspace, workspace_bytes, stats, (cudaStream_t)stream);
 }
 
+/* ---- ParaLSTM --------------------------------------------------------------------------- */
+
+namespace {
+struct LstmPlan {
+    ChainScratch chain;
+    float* par;
+    float* h0;
+    float* buf[2];
+    float* partial;
+    size_t total;
+};
+LstmPlan plan_lstm(void* ws, int B, int T, int d, int K, bool bwd) {
+    Bump b(ws);
+    LstmPlan p;
+    p.chain = plan_chain(b, B, T, d, lstm_tile_steps(), 6);
+    p.par = b.take<float>((size_t)5 * d);
+    p.h0 = b.take<float>((size_t)B * 2 * d);
+    const size_t n = (size_t)B * T * 2 * d;
+    p.buf[0] = (!bwd && K >= 2) ? b.take<float>(n) : nullptr;
+    p.buf[1] = (!bwd && K >= 3) ? b.take<float>(n) : nullptr;
+    p.partial = bwd ? b.take<float>((size_t)B * p.chain.max_tt * 5 * d) : nullptr;
+    p.total = b.off + 256;
+    return p;
+}
+}  // namespace
+
+size_t prb_lstm_workspace_bytes(int B, int T, int d, int max_iters, int backward) {
+    if (B < 1 || T < 1 || d < 1) return 0;
+    return plan_lstm(nullptr, B, T, d, max_iters, backward != 0).total;
+}
+
+int prb_newton_lstm_fused(const void* wx, const void* a_f, const void* a_z, const void* a_o, const void* c_f,
+                          const void* c_o, const void* h0, void* out, int B, int T, int d, int dtype,
+                          int max_iters, float omega, int want_residual, void* workspace,
+                          size_t workspace_bytes, prb_stats* stats, prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    const int K = max_iters;
+    if (!wx || !a_f || !a_z || !a_o || !c_f || !c_o || !out || !stats || B < 1 || T < 1 || d < 1 || K < 0 ||
+        K > kMaxIters || bad_dtype(dtype))
+        return PRB_ERR_BAD_ARG;
+    LstmPlan p = plan_lstm(nullptr, B, T, d, K, false);
+    if (int e = check_ws(workspace, workspace_bytes, p.total)) return e;
+    p = plan_lstm(workspace, B, T, d, K, false);
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    cudaMemsetAsync(st, 0, sizeof(DeviceStats), s);
+    cudaMemsetAsync(p.chain.flags, 0, ((size_t)p.chain.n_chains * p.chain.max_tt + kTickets) * 4, s);
+    const void* pars[5] = {a_f, a_z, a_o, c_f, c_o};
+    for (int i = 0; i < 5; ++i) to_f32(pars[i], p.par + (size_t)i * d, d, dtype, s);
+    const float* h0f = nullptr;
+    if (h0) {
+        to_f32(h0, p.h0, (size_t)B * 2 * d, dtype, s);
+        h0f = p.h0;
+    }
+    if (K == 0) {
+        if (launch_lstm_guess(dtype, wx, p.par, h0f, out, B, T, d, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+        if (want_residual &&
+            launch_lstm_residual(dtype, wx, p.par, h0f, out, B, T, d, &st->final_bits, s) != cudaSuccess)
+            return PRB_ERR_LAUNCH;
+        return PRB_OK;
+    }
+    for (int k = 0; k < K; ++k) {
+        LstmFwdArgs a{};
+        a.wx = wx;
+        a.par = p.par;
+        a.halo = h0f;
+        a.sin = k > 0 ? p.buf[(k - 1) & 1] : nullptr;
+        a.sout = (k == K - 1) ? out : (void*)p.buf[k & 1];
+        a.resid_bits = &st->hist_bits[k];
+        a.final_bits = (want_residual && k == K - 1) ? &st->final_bits : nullptr;
+        a.B = B;
+        a.T = T;
+        a.d = d;
+        a.omega = omega;
+        a.chain = next_chain(p.chain, T, lstm_tile_steps(), &st->status);
+        if (launch_lstm_newton(dtype, a, k == 0, k == K - 1, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+    }
+    return PRB_OK;
+}
+
+int prb_bwd_lstm(const void* states, const void* wx, const void* a_f, const void* a_z, const void* a_o,
+                 const void* c_f, const void* c_o, const void* h0, const void* grad_states, void* g_wx,
+                 float* g_params, float* g_h0, int B, int T, int d, int dtype, void* workspace,
+                 size_t workspace_bytes, prb_stats* stats, prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!states || !wx || !a_f || !a_z || !a_o || !c_f || !c_o || !grad_states || !g_wx || !g_params || !stats ||
+        B < 1 || T < 1 || d < 1 || bad_dtype(dtype))
+        return PRB_ERR_BAD_ARG;
+    LstmPlan p = plan_lstm(nullptr, B, T, d, 0, true);
+    if (int e = check_ws(workspace, workspace_bytes, p.total)) return e;
+    p = plan_lstm(workspace, B, T, d, 0, true);
+    DeviceStats* st = reinterpret_cast<DeviceStats*>(stats);
+    cudaMemsetAsync(st, 0, sizeof(DeviceStats), s);
+    cudaMemsetAsync(p.chain.flags, 0, ((size_t)p.chain.n_chains * p.chain.max_tt + kTickets) * 4, s);
+    const void* pars[5] = {a_f, a_z, a_o, c_f, c_o};
+    for (int i = 0; i < 5; ++i) to_f32(pars[i], p.par + (size_t)i * d, d, dtype, s);
+    const float* h0f = nullptr;
+    if (h0) {
+        to_f32(h0, p.h0, (size_t)B * 2 * d, dtype, s);
+        h0f = p.h0;
+    }
+    LstmBwdArgs a{};
+    a.wx = wx;
+    a.states = states;
+    a.grad_states = grad_states;
+    a.par = p.par;
+    a.halo = h0f;
+    a.g_wx = g_wx;
+    a.gp_partial = p.partial;
+    a.g_h0 = g_h0;
+    a.B = B;
+    a.T = T;
+    a.d = d;
+    a.chain = next_chain(p.chain, T, lstm_tile_steps(), &st->status);
+    if (launch_lstm_bwd(dtype, a, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+    return launch_reduce_partials(p.partial, B * a.chain.n_tt, 5 * d, g_params, s) == cudaSuccess ? PRB_OK
+                                                                                                  : PRB_ERR_LAUNCH;
+}
+
 int prb_newton_slstm_fused(const void* wx, const void* r, const void* h0, const void* states_guess,
                            void* out, int B, int T, int d, int dtype, int max_iters,
                            int picard_iters, float omega, float eps, int want_residual,

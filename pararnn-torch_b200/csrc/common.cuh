@@ -319,6 +319,24 @@ struct Affine1 {
     }
 };
 
+// 2x2 affine monoid x -> M x + v, M row-major in [0,4), v in [4,6) (ParaLSTM, state (c, h)).
+struct Affine2 {
+    static constexpr int NV = 6, NS = 2;
+    __device__ static __forceinline__ void compose(float (&acc)[6], const float (&nx)[6]) {
+        const float m00 = fmaf(nx[0], acc[0], nx[1] * acc[2]), m01 = fmaf(nx[0], acc[1], nx[1] * acc[3]);
+        const float m10 = fmaf(nx[2], acc[0], nx[3] * acc[2]), m11 = fmaf(nx[2], acc[1], nx[3] * acc[3]);
+        const float v0 = fmaf(nx[0], acc[4], fmaf(nx[1], acc[5], nx[4]));
+        const float v1 = fmaf(nx[2], acc[4], fmaf(nx[3], acc[5], nx[5]));
+        acc[0] = m00; acc[1] = m01; acc[2] = m10; acc[3] = m11; acc[4] = v0; acc[5] = v1;
+    }
+    __device__ static __forceinline__ void apply(const float (&m)[6], float (&v)[2]) {
+        const float a = fmaf(m[0], v[0], fmaf(m[1], v[1], m[4]));
+        const float b = fmaf(m[2], v[0], fmaf(m[3], v[1], m[5]));
+        v[0] = a;
+        v[1] = b;
+    }
+};
+
 // 4x4 affine monoid x -> M x + v, M row-major in [0,16), v in [16,20).
 struct Affine4 {
     static constexpr int NV = 20, NS = 4;

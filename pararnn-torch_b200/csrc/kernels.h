@@ -20,7 +20,8 @@ struct Options {
 };
 Options& options();
 
-enum Cell : int { kCellGruDiag = 0, kCellNlru = 1, kCellSlstmDiag = 2, kCellGruHead = 3, kCellTitans = 4 };
+enum Cell : int { kCellGruDiag = 0, kCellNlru = 1, kCellSlstmDiag = 2, kCellGruHead = 3, kCellTitans = 4,
+                  kCellLstm = 5 };
 // gates and recurrent parameter vectors per channel of the scalar-diagonal cells
 inline bool is_diag_cell(int cell) { return cell == kCellGruDiag || cell == kCellNlru || cell == kCellTitans; }
 inline int diag_cell_params(int cell) { return cell == kCellGruDiag ? 3 : (cell == kCellTitans ? 2 : 1); }
@@ -174,6 +175,39 @@ cudaError_t launch_gru_head_fwd(int dtype, const void* wx, const float* A, const
 cudaError_t launch_gru_head_bwd(int dtype, const void* wx, const void* states, const void* grad_states,
                                 const float* A, const float* h0, void* g_wx, float* gA_part, float* g_h0,
                                 float* mu_out, int B, int T, int d, int H, cudaStream_t s);
+
+// ---- ParaLSTM (lstm_kernels.cu): state (B,T,2,d) slots (c,h), gates (f,z,o), 5 parameter vectors
+struct LstmFwdArgs {
+    const void* wx;       // (B,T,3d) I/O dtype
+    const float* par;     // (5,d) fp32 clamped: a_f, a_z, a_o, c_f, c_o
+    const float* halo;    // (B,2,d) fp32 initial state or null
+    const float* sin;     // (B,T,2,d) fp32 input trajectory (unused by the first pass)
+    void* sout;           // (B,T,2,d) fp32 work trajectory, or I/O dtype on the last pass
+    unsigned* resid_bits;
+    unsigned* final_bits;
+    int B, T, d;
+    float omega;
+    Chain chain;
+};
+struct LstmBwdArgs {
+    const void* wx;
+    const void* states;       // (B,T,2,d) I/O dtype
+    const void* grad_states;  // (B,T,2,d) I/O dtype
+    const float* par;
+    const float* halo;
+    void* g_wx;               // (B,T,3d)
+    float* gp_partial;        // (B*n_tt,5,d)
+    float* g_h0;              // (B,2,d) or null
+    int B, T, d;
+    Chain chain;
+};
+int lstm_tile_steps();
+cudaError_t launch_lstm_newton(int dtype, const LstmFwdArgs& a, bool first, bool last, cudaStream_t s);
+cudaError_t launch_lstm_guess(int dtype, const void* wx, const float* par, const float* h0, void* out, int B,
+                              int T, int d, cudaStream_t s);
+cudaError_t launch_lstm_residual(int dtype, const void* wx, const float* par, const float* h0, const void* st,
+                                 int B, int T, int d, unsigned* dst, cudaStream_t s);
+cudaError_t launch_lstm_bwd(int dtype, const LstmBwdArgs& a, cudaStream_t s);
 
 // ---- T = 1 decode (decode.cu) ------------------------------------------------------------------
 cudaError_t launch_decode_step(int cell, int dtype, const void* state, const void* wx, const void* par,

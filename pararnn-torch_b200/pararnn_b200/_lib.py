@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libpararnn_b200.so")
 
 PRB_F32, PRB_BF16 = 0, 1
-CELL_GRU_DIAG, CELL_NLRU, CELL_SLSTM_DIAG, CELL_GRU_HEAD, CELL_TITANS = 0, 1, 2, 3, 4
+CELL_GRU_DIAG, CELL_NLRU, CELL_SLSTM_DIAG, CELL_GRU_HEAD, CELL_TITANS, CELL_LSTM = 0, 1, 2, 3, 4, 5
 MAX_ITERS = 16
 STATS_BYTES = 80
 
@@ -36,6 +36,9 @@ _SIGNATURES = {
     "prb_newton_nlru_fused": (_INT, [_VOIDP] * 4 + [_INT] * 5 + [_FLOAT, _INT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_newton_titans_fused": (_INT, [_VOIDP] * 5 + [_INT] * 5 + [_FLOAT, _INT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_bwd_titans": (_INT, [_VOIDP] * 9 + [_INT] * 4 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
+    "prb_lstm_workspace_bytes": (_SIZE, [_INT] * 5),
+    "prb_newton_lstm_fused": (_INT, [_VOIDP] * 8 + [_INT] * 5 + [_FLOAT, _INT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
+    "prb_bwd_lstm": (_INT, [_VOIDP] * 12 + [_INT] * 4 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_newton_slstm_fused": (_INT, [_VOIDP] * 5 + [_INT] * 6 + [_FLOAT, _FLOAT, _INT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_gru_head_workspace_bytes": (_SIZE, [_INT] * 5),
     "prb_newton_gru_head_fused": (_INT, [_VOIDP] * 6 + [_INT] * 6 + [_FLOAT, _INT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),

@@ -164,6 +164,60 @@ class ParaNLRU(nn.Module):
         return a * h_prev + (1.0 - a) * n
 
 
+LSTM_CELL, LSTM_HIDDEN = 0, 1
+
+
+class ParaLSTM(nn.Module):
+    """Coupled input-forget LSTM with peepholes and diagonal recurrence (reference
+    ``cells/para_lstm.py``): state ``(..., 2, d_h)`` with slots ``(c, h)``, ``(f_x, z_x, o_x) = W_x(x)``,
+
+        f = sigmoid(a_f h + c_f c + f_x);  z = tanh(a_z h + z_x);  c' = f c + (1 - f) z
+        o = sigmoid(a_o h + c_o c' + o_x); h' = o tanh(c')
+
+    All five recurrent vectors are clamped to ``max_recurrent_norm``."""
+
+    def __init__(self, input_size=None, hidden_size=None, *, d_in=None, d_h=None,
+                 max_recurrent_norm=_UNSET, device=None, dtype=None):
+        super().__init__()
+        input_size, hidden_size = _sizes(input_size, hidden_size, d_in, d_h)
+        kw = {"device": device, "dtype": dtype}
+        self.input_size = self.d_in = input_size
+        self.hidden_size = self.d_h = hidden_size
+        self.state_slots = 2
+        self.hidden_slot = LSTM_HIDDEN
+        self.mix = "diag"
+        self.jac_structure = "block2"
+        self.max_recurrent_norm = 0.5 if max_recurrent_norm is _UNSET else max_recurrent_norm
+        for name in ("a_f", "a_z", "a_o", "c_f", "c_o"):
+            setattr(self, name, nn.Parameter(torch.empty(hidden_size, **kw)))
+        self.W_x = nn.Linear(input_size, 3 * hidden_size, bias=True, **kw)
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        for p in (self.a_f, self.a_z, self.a_o, self.c_f, self.c_o):
+            _xavier_gaussian_vec_(p)
+        nn.init.kaiming_uniform_(self.W_x.weight, a=math.sqrt(5))
+        nn.init.zeros_(self.W_x.bias)
+
+    def clipped_recurrent(self):
+        cap = self.max_recurrent_norm
+        return tuple(_clamp(p, cap) for p in (self.a_f, self.a_z, self.a_o, self.c_f, self.c_o))
+
+    def step(self, state_prev: Tensor, x: Tensor | None = None, *, wx: Tensor | None = None) -> Tensor:
+        c_prev, h_prev = state_prev[..., LSTM_CELL, :], state_prev[..., LSTM_HIDDEN, :]
+        a_f, a_z, a_o, c_f, c_o = self.clipped_recurrent()
+        if wx is None:
+            if x is None:
+                raise ValueError("ParaLSTM.step needs x or wx")
+            wx = self.W_x(x)
+        fx, zx, ox = wx.chunk(3, dim=-1)
+        f = torch.sigmoid(a_f * h_prev + c_f * c_prev + fx)
+        z = torch.tanh(a_z * h_prev + zx)
+        c = f * c_prev + (1.0 - f) * z
+        o = torch.sigmoid(a_o * h_prev + c_o * c + ox)
+        return torch.stack((c, o * torch.tanh(c)), dim=-2)
+
+
 class ParaTitans(nn.Module):
     """Titans-style memory cell with a channelwise-diagonal Jacobian (reference
     ``cells/para_titans.py``): ``(alpha_pre, theta_pre, k, v, n_pre) = W_x(x)``,
@@ -276,10 +330,12 @@ def cell_kind(cell: nn.Module) -> str:
         return "nlru"
     if name == "ParaTitans":
         return "titans"
+    if name == "ParaLSTM":
+        return "lstm"
     if name == "ParaSLSTM" and mix == "diag":
         return "slstm_diag"
     raise TypeError(
-        f"the CUDA backend covers ParaGRU (diag, head), ParaNLRU, ParaTitans and ParaSLSTM(mix='diag'); "
+        f"the CUDA backend covers ParaGRU (diag, head), ParaNLRU, ParaTitans, ParaLSTM and ParaSLSTM(mix='diag'); "
         f"got {name}(mix={mix!r})")
 
 

@@ -88,6 +88,8 @@ def _recurrent_params(cell: nn.Module, kind: str):
         return (cell.clipped_u(),)
     if kind == "titans":
         return (cell.clipped_u(), cell.clipped_r())
+    if kind == "lstm":
+        return tuple(cell.clipped_recurrent())
     return (cell.clipped_r(),)
 
 
@@ -101,6 +103,9 @@ def _solve_window(cell, kind, wx, h0, cfg, dstats, want_residual, cu_seqlens=Non
                                     stats=dstats, want_residual=want_residual)
     if kind == "nlru":
         return ops.newton_nlru_fused(wx, rec[0], h0, cu_seqlens, block_table, max_iters=K, omega=cfg.omega,
+                                     stats=dstats, want_residual=want_residual)
+    if kind == "lstm":
+        return ops.newton_lstm_fused(wx, *rec, h0, cu_seqlens, block_table, max_iters=K, omega=cfg.omega,
                                      stats=dstats, want_residual=want_residual)
     if kind == "titans":
         return ops.newton_titans_fused(wx, rec[0], rec[1], h0, cu_seqlens, block_table, max_iters=K,
@@ -235,6 +240,9 @@ def _reverse_window(cell, kind, states, wx, grad_states, h0):
     if kind == "nlru":
         g_wx, gu, g_h0 = ops.nlru_reverse_vjp(states, wx, rec[0], grad_states, h0)
         return g_wx, {"u": gu}, g_h0
+    if kind == "lstm":
+        g_wx, gp, g_h0 = ops.lstm_reverse_vjp(states, wx, *rec, grad_states, h0)
+        return g_wx, {n: gp[i] for i, n in enumerate(("a_f", "a_z", "a_o", "c_f", "c_o"))}, g_h0
     if kind == "titans":
         g_wx, gu, gr, g_h0 = ops.titans_reverse_vjp(states, wx, rec[0], rec[1], grad_states, h0)
         return g_wx, {"u": gu, "r": gr}, g_h0

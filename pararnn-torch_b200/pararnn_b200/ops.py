@@ -341,6 +341,49 @@ def newton_titans_fused(wx: Tensor, u: Tensor, r: Tensor, h0: Tensor | None = No
     return out
 
 
+def newton_lstm_fused(wx: Tensor, a_f: Tensor, a_z: Tensor, a_o: Tensor, c_f: Tensor, c_o: Tensor,
+                      h0: Tensor | None = None, cu_seqlens: Tensor | None = None,
+                      block_table: Tensor | None = None, *, max_iters: int, omega: float = 1.0,
+                      stats: DeviceStats | None = None, want_residual: bool = True) -> Tensor:
+    """Fused Newton for ``ParaLSTM``: ``wx (B,T,3d)`` -> ``H (B,T,2,d)`` with slots ``(c, h)``
+    (reference ``pararnn::newton_lstm_fused``, ``kernels/custom_ops.py:437-483``)."""
+    d = a_f.numel()
+    if cu_seqlens is not None:
+        if stats is not None:
+            stats.parts.clear()
+        return _packed(lambda w, h, st, _g: newton_lstm_fused(w, a_f, a_z, a_o, c_f, c_o, h, max_iters=max_iters,
+                                                               omega=omega, stats=st,
+                                                               want_residual=want_residual),
+                       wx, h0, cu_seqlens, block_table, (2, d), stats)
+    h0 = gather_h0(h0, block_table, wx.shape[0], (2, d))
+    dev = _check_cuda(wx, a_f, a_z, a_o, c_f, c_o, h0)
+    _check_iters(max_iters)
+    if wx.dim() != 3 or wx.shape[-1] != 3 * d:
+        raise ValueError(f"wx must be (B, T, 3*d) with d={d}, got {tuple(wx.shape)}")
+    B, T, _ = wx.shape
+    for name, p in (("a_z", a_z), ("a_o", a_o), ("c_f", c_f), ("c_o", c_o)):
+        if p.numel() != d:
+            raise ValueError(f"{name} must have {d} elements, got {tuple(p.shape)}")
+    if h0 is not None and tuple(h0.shape) != (B, 2, d):
+        raise ValueError(f"h0 must be ({B}, 2, {d}), got {tuple(h0.shape)}")
+    if T < 1:
+        raise ValueError("time must be >= 1")
+    code = _dtype_code(wx)
+    wx_c = wx.detach().contiguous()
+    pars = [_same(p, wx) for p in (a_f, a_z, a_o, c_f, c_o)]
+    h0c = _same(h0, wx)
+    out = torch.empty(B, T, 2, d, dtype=wx.dtype, device=dev)
+    st = stats or DeviceStats(dev, max_iters)
+    lib = L.lib()
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.prb_lstm_workspace_bytes(B, T, d, int(max_iters), 0), dev)
+        rc = lib.prb_newton_lstm_fused(_ptr(wx_c), *[_ptr(p) for p in pars], _ptr(h0c), _ptr(out), B, T, d, code,
+                                       int(max_iters), float(omega), int(want_residual), _ptr(ws), ws.numel(),
+                                       _ptr(st.buf), _stream(dev))
+    _raise(rc, "newton_lstm_fused")
+    return out
+
+
 def newton_slstm_fused(wx: Tensor, r: Tensor, h0: Tensor | None = None,
                        states: Tensor | None = None, block_table: Tensor | None = None, *,
                        max_iters: int, omega: float = 1.0, eps: float = 1e-6,
@@ -460,6 +503,31 @@ def nlru_reverse_vjp(states: Tensor, wx: Tensor, u: Tensor, grad_states: Tensor,
     _raise(rc, "nlru_reverse_vjp")
     _track_backward(sb)
     return g_wx, g_par[0], g_h0
+
+
+def lstm_reverse_vjp(states: Tensor, wx: Tensor, a_f: Tensor, a_z: Tensor, a_o: Tensor, c_f: Tensor,
+                     c_o: Tensor, grad_states: Tensor, h0: Tensor | None = None):
+    """Eq. 2.6 reverse scan (2x2 blocks, J^T) fused with the packed LSTM VJP:
+    ``(g_wx (B,T,3d), g_params (5,d) fp32 in the order a_f,a_z,a_o,c_f,c_o, g_h0 (B,2,d) fp32)``."""
+    dev, code, st, wxc, gs, h0c = _bwd_common(states, wx, grad_states, h0)
+    B, T, d3 = wx.shape
+    d = d3 // 3
+    if tuple(states.shape) != (B, T, 2, d) or tuple(grad_states.shape) != (B, T, 2, d):
+        raise ValueError("states / grad_states must be (B, T, 2, d)")
+    g_wx = torch.empty_like(wxc)
+    g_par = torch.empty(5, d, dtype=torch.float32, device=dev)
+    g_h0 = torch.empty(B, 2, d, dtype=torch.float32, device=dev)
+    sb = DeviceStats(dev, 0)
+    pars = [_same(p, wx) for p in (a_f, a_z, a_o, c_f, c_o)]
+    lib = L.lib()
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.prb_lstm_workspace_bytes(B, T, d, 0, 1), dev)
+        rc = lib.prb_bwd_lstm(_ptr(st), _ptr(wxc), *[_ptr(p) for p in pars], _ptr(h0c), _ptr(gs), _ptr(g_wx),
+                              _ptr(g_par), _ptr(g_h0), B, T, d, code, _ptr(ws), ws.numel(), _ptr(sb.buf),
+                              _stream(dev))
+    _raise(rc, "lstm_reverse_vjp")
+    _track_backward(sb)
+    return g_wx, g_par, g_h0
 
 
 def titans_reverse_vjp(states: Tensor, wx: Tensor, u: Tensor, r: Tensor, grad_states: Tensor,

@@ -175,6 +175,7 @@ class CudaShardOps:
         self.ws = torch.empty(max(n, 256), dtype=torch.uint8, device=self.dev)
         self.stats = ops.DeviceStats(self.dev, L.MAX_ITERS)
         self.monoid = "affine4" if kind == "slstm_diag" else "affine1"
+        self.launches = 0  # kernels of this library launched through this object
         # time segments inside this rank's shard: the library's plan, or `segments` pieces (tests)
         self.n_seg, self.seg_len = 1, int(self.T)
         if kind == "slstm_diag":
@@ -215,6 +216,7 @@ class CudaShardOps:
             rc = self.lib.prb_fold_segments(MONOID[monoid], self._p(agg), agg.shape[0], int(reverse),
                                             self._p(out), self.B, self.d, self._stream())
         self._check(rc, "fold_segments")
+        self.launches += 1
         return out
 
     def segment_carries(self, monoid: str, agg: Tensor, reverse: bool, carry0: Tensor | None) -> Tensor:
@@ -225,6 +227,7 @@ class CudaShardOps:
             rc = self.lib.prb_segment_carries(MONOID[monoid], self._p(agg), n, int(reverse), self._p(carry0),
                                               self._p(out), self.B, self.d, self._stream())
         self._check(rc, "segment_carries")
+        self.launches += 1
         return out
 
     def fold(self, monoid: str, gathered: Tensor, rank: int, world: int, reverse: bool) -> Tensor:
@@ -233,6 +236,7 @@ class CudaShardOps:
             rc = self.lib.prb_fold_carries(MONOID[monoid], self._p(gathered), rank, world, int(reverse),
                                            self._p(out), self.B, self.d, self._stream())
         self._check(rc, "fold_carries")
+        self.launches += 1
         return out
 
     def diag_guess(self, h0):
@@ -241,6 +245,7 @@ class CudaShardOps:
             rc = self.lib.prb_diag_guess(self.cell, self._p(self.wx), self._p(self.par), self._p(h0),
                                          self._p(out), self.B, self.T, self.d, self.code, self._stream())
         self._check(rc, "diag_guess")
+        self.launches += 1
         return out
 
     def newton_pass(self, traj, halo, carry, mode, out, hist_slot):
@@ -268,6 +273,7 @@ class CudaShardOps:
                     self.code, self.omega, self._p(self.ws), self.ws.numel(), self._p(self.stats.buf),
                     hist_slot, self._stream())
         self._check(rc, "newton_pass")
+        self.launches += 1
         return res
 
     def picard_pass(self, h_prev, h_halo, carry, mode, h_out, state_out):
@@ -283,6 +289,7 @@ class CudaShardOps:
                 self.code, self.eps,
                 self._p(self.ws), self.ws.numel(), self._p(self.stats.buf), self._stream())
         self._check(rc, "picard_pass")
+        self.launches += 1
         return res
 
     def bwd_pass(self, states, grad_states, halo, carry, mode):
@@ -313,6 +320,7 @@ class CudaShardOps:
                     mode, self.B, self.T, self.d, self.code, self._p(self.ws), self.ws.numel(),
                     self._p(self.stats.buf), self._stream())
         self._check(rc, "bwd_pass")
+        self.launches += 1 if mode == 2 else 2  # the sweep, and the reduction of the parameter partials
         return agg if mode == 2 else (g_wx, g_par, head)
 
     def stats_bits(self) -> Tensor:

@@ -32,6 +32,8 @@ def _kind(cell) -> str | None:
         return "nlru"
     if name == "ParaTitans":
         return "titans"
+    if name == "ParaLSTM":
+        return "lstm"
     if name == "ParaSLSTM" and mix == "diag":
         return "slstm_diag"
     return None
@@ -70,6 +72,9 @@ def install():
         if kind == "nlru":
             return ops.newton_nlru_fused(wx, cell.clipped_u(), h0, cu_seqlens, block_table, max_iters=max_iters,
                                          omega=omega, want_residual=False)
+        if kind == "lstm":
+            return ops.newton_lstm_fused(wx, *cell.clipped_recurrent(), h0, cu_seqlens, block_table,
+                                         max_iters=max_iters, omega=omega, want_residual=False)
         if kind == "titans":
             return ops.newton_titans_fused(wx, cell.clipped_u(), cell.clipped_r(), h0, cu_seqlens, block_table,
                                            max_iters=max_iters, omega=omega, want_residual=False)

@@ -86,6 +86,12 @@ def run_case(name, cell, x, *, K, P=None, h0=None, omega=1.0, cu_seqlens=None):
         out["raw_params"] = _np(cell.u)[None]
         out["g_params"] = _np(cell.u.grad)[None]
         out["cell"] = "nlru"
+    elif kind == "ParaLSTM":
+        names = ("a_f", "a_z", "a_o", "c_f", "c_o")
+        out["params"] = np.stack([_np(p) for p in cell.clipped_recurrent()])
+        out["raw_params"] = np.stack([_np(getattr(cell, n)) for n in names])
+        out["g_params"] = np.stack([_np(getattr(cell, n).grad) for n in names])
+        out["cell"] = "lstm"
     elif kind == "ParaTitans":
         out["params"] = np.stack([_np(cell.clipped_u()), _np(cell.clipped_r())])
         out["raw_params"] = np.stack([_np(cell.u), _np(cell.r)])
@@ -116,7 +122,7 @@ def main():
     import logging
 
     logging.disable(logging.CRITICAL)
-    from pararnn import ParaGRU, ParaNLRU, ParaSLSTM, ParaTitans
+    from pararnn import ParaGRU, ParaLSTM, ParaNLRU, ParaSLSTM, ParaTitans
 
     torch.set_num_threads(4)
 
@@ -203,6 +209,17 @@ def main():
     run_case("titans_k2_h0_omega", cell_t, torch.randn(2, 41, 10), K=2, h0=0.5 * torch.randn(2, 12), omega=0.9)
     run_case("titans_packed_k3_h0", cell_t, torch.randn(1, 37, 10), K=3, h0=0.5 * torch.randn(3, 12),
              cu_seqlens=[0, 1, 15, 37])
+
+    # --- ParaLSTM (CIFG peephole LSTM, state (c, h), 2x2 block Jacobian) ---
+    torch.manual_seed(40)
+    cell_l = ParaLSTM(10, 12)
+    with torch.no_grad():
+        for p in (cell_l.a_f, cell_l.a_z, cell_l.a_o, cell_l.c_f, cell_l.c_o):
+            p.mul_(4.0)  # some entries reach the +-0.5 clamp
+    run_case("lstm_k3", cell_l, torch.randn(2, 72, 10), K=3)
+    run_case("lstm_k2_h0_omega", cell_l, torch.randn(2, 35, 10), K=2, h0=0.5 * torch.randn(2, 2, 12), omega=0.9)
+    run_case("lstm_packed_k3_h0", cell_l, torch.randn(1, 40, 10), K=3, h0=0.5 * torch.randn(3, 2, 12),
+             cu_seqlens=[0, 9, 10, 40])
 
 
 if __name__ == "__main__":

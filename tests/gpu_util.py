@@ -5,7 +5,7 @@ import torch
 
 from oracle import oracle
 
-GATES = {"gru_diag": 3, "nlru": 2, "slstm_diag": 4, "gru_head": 3, "titans": 5}
+GATES = {"gru_diag": 3, "nlru": 2, "slstm_diag": 4, "gru_head": 3, "titans": 5, "lstm": 3}
 
 
 def bf16_round(a):
@@ -23,6 +23,8 @@ def make_problem(kind, B, T, d, seed, *, h0=False, x_scale=1.0, bias_f=0.0, rec_
         a0 = rng.uniform(0.9, 0.999, size=d)
         wx[..., :d] += np.log(a0 / (1 - a0)).astype(np.float32)
         params = np.clip(rec_scale * 0.3 * rng.standard_normal((1, d)), -0.5, 0.5).astype(np.float32)
+    elif kind == "lstm":
+        params = np.clip(rec_scale * 0.3 * rng.standard_normal((5, d)), -0.5, 0.5).astype(np.float32)
     elif kind == "titans":
         wx[..., d:2 * d] -= 1.0  # softplus(theta_pre) ~ 0.3, as the cell's bias initialisation
         wx[..., 2 * d:4 * d] *= 0.5
@@ -39,7 +41,9 @@ def make_problem(kind, B, T, d, seed, *, h0=False, x_scale=1.0, bias_f=0.0, rec_
         params = np.stack(mats).reshape(3, n_heads, dh, dh).astype(np.float32)
     h0_arr = None
     if h0:
-        if kind == "slstm_diag":
+        if kind == "lstm":
+            h0_arr = (0.5 * rng.standard_normal((B, 2, d))).astype(np.float32)
+        elif kind == "slstm_diag":
             h0_arr = np.stack([0.3 * rng.standard_normal((B, d)), rng.uniform(0.5, 1.5, (B, d)),
                                0.2 * rng.standard_normal((B, d)), 0.3 * rng.standard_normal((B, d))],
                               axis=1).astype(np.float32)

@@ -32,7 +32,8 @@ def test_newton_apply_and_grads_match_reference(name):
         return  # far from converged: gradients of two different iterates are not comparable
     tol = 5e-4 * amp
     names = {"gru_diag": ("a_z", "a_r", "a_n"), "nlru": ("u",), "slstm_diag": ("R",),
-             "gru_head": ("A_z", "A_r", "A_n"), "titans": ("u", "r")}[g["cell"]]
+             "gru_head": ("A_z", "A_r", "A_n"), "titans": ("u", "r"),
+             "lstm": ("a_f", "a_z", "a_o", "c_f", "c_o")}[g["cell"]]
     got = (cell.R.grad.cpu().numpy() if names == ("R",)
            else np.stack([getattr(cell, n).grad.cpu().numpy() for n in names]))
     for a, b in ((x.grad.cpu().numpy(), g["g_x"]), (cell.W_x.weight.grad.cpu().numpy(), g["g_W"]),

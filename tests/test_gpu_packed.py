@@ -28,6 +28,8 @@ def _fwd(kind, wx, params, h0, cs, K, P=0, eps=1e-6):
         H = ops.newton_nlru_fused(dev(wx), dev(params[0]), dev(h0), csd, max_iters=K, stats=st)
     elif kind == "titans":
         H = ops.newton_titans_fused(dev(wx), dev(params[0]), dev(params[1]), dev(h0), csd, max_iters=K, stats=st)
+    elif kind == "lstm":
+        H = ops.newton_lstm_fused(dev(wx), *[dev(p) for p in params], dev(h0), csd, max_iters=K, stats=st)
     else:
         H = ops.newton_slstm_fused(dev(wx), dev(params), dev(h0), max_iters=K, picard_iters=P, eps=eps,
                                    stats=st, cu_seqlens=csd)
@@ -37,7 +39,7 @@ def _fwd(kind, wx, params, h0, cs, K, P=0, eps=1e-6):
 
 
 def test_fixtures_present():
-    assert len(PACKED) == 4
+    assert len(PACKED) == 5
 
 
 @pytest.mark.parametrize("name", PACKED)
@@ -51,7 +53,7 @@ def test_packed_forward_matches_reference_golden(name):
     assert abs(res - float(g["max_residual"])) <= 1e-2 * float(g["max_residual"]) + 4e-6 * scale * amp
 
 
-@pytest.mark.parametrize("kind,P", [("gru_diag", 0), ("nlru", 0), ("titans", 0), ("slstm_diag", 2)])
+@pytest.mark.parametrize("kind,P", [("gru_diag", 0), ("nlru", 0), ("titans", 0), ("lstm", 0), ("slstm_diag", 2)])
 @pytest.mark.parametrize("cs", [[0, 1, 2, 3], [0, 300, 301, 1000], [0, 64, 128, 129, 700]])
 def test_packed_matches_oracle_forward_and_backward(kind, P, cs):
     d, K = 40, 2
@@ -66,13 +68,13 @@ def test_packed_matches_oracle_forward_and_backward(kind, P, cs):
     np.testing.assert_allclose(hist, np.asarray(want.history), rtol=2e-2, atol=4e-6 * scale)
     # backward through newton_apply: grads of a packed call = grads of the per-sequence calls
     torch.manual_seed(3)
-    cls = {"gru_diag": prb.ParaGRU, "nlru": prb.ParaNLRU, "titans": prb.ParaTitans,
+    cls = {"gru_diag": prb.ParaGRU, "nlru": prb.ParaNLRU, "titans": prb.ParaTitans, "lstm": prb.ParaLSTM,
            "slstm_diag": prb.ParaSLSTM}[kind]
     cell = cls(24, d).cuda()
     x = torch.randn(1, N, 24, device="cuda", requires_grad=True)
     h0t = dev(h0).requires_grad_(True)
     cfg = prb.NewtonConfig(max_iters=3, picard_iters=P if kind == "slstm_diag" else None, picard_adapt=False)
-    G = torch.randn(1, N, *((4, d) if kind == "slstm_diag" else (d,)), device="cuda")
+    G = torch.randn(1, N, *({"slstm_diag": (4, d), "lstm": (2, d)}.get(kind, (d,))), device="cuda")
     Hp = prb.newton_apply(cell, x, cfg, h0=h0t, cu_seqlens=torch.tensor(cs, device="cuda"))
     (Hp * G).sum().backward()
     got = [x.grad.clone(), h0t.grad.clone()] + [p.grad.clone() for p in cell.parameters()]

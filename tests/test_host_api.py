@@ -25,6 +25,9 @@ def _cell_from_golden(g):
     elif g["cell"] == "titans":
         cell = prb.ParaTitans(d_in, d)
         names = ("u", "r")
+    elif g["cell"] == "lstm":
+        cell = prb.ParaLSTM(d_in, d)
+        names = ("a_f", "a_z", "a_o", "c_f", "c_o")
     else:
         cell = prb.ParaSLSTM(d_in, d, eps=g["eps"])
         names = ("R",)

@@ -10,7 +10,7 @@ NAMES = golden_names()
 
 
 def test_fixtures_present():
-    assert len(NAMES) >= 17
+    assert len(NAMES) >= 20
 
 
 @pytest.mark.parametrize("name", NAMES)
