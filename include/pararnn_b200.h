@@ -37,7 +37,7 @@ typedef struct CUstream_st* prb_stream_t; /* cudaStream_t */
 
 enum { PRB_F32 = 0, PRB_BF16 = 1 };
 enum { PRB_CELL_GRU_DIAG = 0, PRB_CELL_NLRU = 1, PRB_CELL_SLSTM_DIAG = 2, PRB_CELL_GRU_HEAD = 3,
-       PRB_CELL_TITANS = 4, PRB_CELL_LSTM = 5 };
+       PRB_CELL_TITANS = 4, PRB_CELL_LSTM = 5, PRB_CELL_CFC = 6 };
 enum {
     PRB_OK = 0,
     PRB_ERR_BAD_ARG = -1,     /* null pointer, non-positive size, unknown enum */
@@ -103,6 +103,14 @@ int prb_newton_nlru_fused(const void* wx, const void* u, const void* h0, void* o
 int prb_newton_titans_fused(const void* wx, const void* u, const void* r, const void* h0, void* out, int B,
                             int T, int d, int dtype, int max_iters, float omega, int want_residual,
                             void* workspace, size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
+
+/* ParaCfC (closed-form continuous-time cell with irregular time steps, gate_mix='input').  Replaces
+ * pararnn::newton_cfc_fused, kernels/custom_ops.py:230-266 -> kernels/newton_cfc.py.  wx (B,T,4d) is
+ * the cell's project_wx(x): gates (f_pre, c_x, dt, b) with dt the clamped time step broadcast over the
+ * channels (cells/para_cfc.py:150-157); u (d) clamped; h0 (B,d) or NULL; out (B,T,d). */
+int prb_newton_cfc_fused(const void* wx, const void* u, const void* h0, void* out, int B, int T, int d,
+                         int dtype, int max_iters, float omega, int want_residual, void* workspace,
+                         size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
 
 /* ParaLSTM (CIFG peephole LSTM, diagonal recurrence, 2x2 block Jacobian per channel).  Replaces
  * pararnn::newton_lstm_fused, kernels/custom_ops.py:437-483 -> kernels/newton_lstm.py and
@@ -181,6 +189,13 @@ int prb_bwd_titans(const void* states, const void* wx, const void* u, const void
                    int dtype, void* workspace, size_t workspace_bytes, prb_stats* stats,
                    prb_stream_t stream);
 
+/* ParaCfC: reverse_scan_diag (solvers/scan.py:126-148) + cfc_recurrence_vjp
+ * (kernels/vjp_cfc.py:102-167).  g_wx (B,T,4d) = grads of (f_pre, c_x, dt, b); g_params fp32 (1,d) =
+ * grad of u; g_h0 fp32 (B,d) or NULL. */
+int prb_bwd_cfc(const void* states, const void* wx, const void* u, const void* h0, const void* grad_states,
+                void* g_wx, float* g_params, float* g_h0, int B, int T, int d, int dtype, void* workspace,
+                size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
+
 /* Replaces reverse_scan_block4 + slstm_recurrence_vjp, solvers/scan.py:166-178,
  * kernels/vjp_slstm.py:234-293.  states, grad_states (B,T,4,d); g_wx (B,T,4d);
  * g_params fp32 (4,d); g_h0 fp32 (B,4,d) or NULL. */
@@ -193,7 +208,7 @@ int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void*
 
 /* max|f(H_{t-1},x_t) - H_t| into stats->final_bits.  Replaces the eager
  * evaluation in solvers/newton/__init__.py:602-606.  params: GRU (3,d) packed
- * a_z,a_r,a_n; NLRU (1,d); Titans (2,d) = u,r; sLSTM (4,d); all in the I/O dtype. */
+ * a_z,a_r,a_n; NLRU and CfC (1,d); Titans (2,d) = u,r; sLSTM (4,d); all in the I/O dtype. */
 int prb_residual(int cell, const void* wx, const void* params, const void* h0, const void* states,
                  int B, int T, int d, int dtype, float eps, void* workspace, size_t workspace_bytes,
                  prb_stats* stats, prb_stream_t stream);
@@ -317,7 +332,7 @@ int prb_residual_pass(int cell, const void* wx, const float* params, const float
  * decode_step, kernels/decode.py:119-216 and its three step kernels (:294-475); W_x(x) stays a
  * library GEMM on the caller's side.  state (B, S, d) or, with block_table (B,) int32 slot ids,
  * a pool (C, S, d); wx (B, G*d); params_raw: the UNCLAMPED recurrent vectors (GRU (3,d), NLRU
- * (1,d), Titans (2,d), sLSTM (4,d)) in the I/O dtype, clamped to [-cap, cap] in the kernel (cap < 0: no
+ * (1,d), CfC (1,d), Titans (2,d), sLSTM (4,d)) in the I/O dtype, clamped to [-cap, cap] in the kernel (cap < 0: no
  * clamp), so a captured CUDA graph needs no extra kernel; out has the shape of state and may BE
  * state (in-place update of the pool rows named by block_table).  Allocates nothing, takes no
  * workspace, never synchronises: it can be captured in a CUDA graph. */

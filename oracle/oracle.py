@@ -21,11 +21,11 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "pararnn_oracle.c")
 
-GRU_DIAG, NLRU, SLSTM_DIAG, GRU_HEAD, TITANS, LSTM = 0, 1, 2, 3, 4, 5
+GRU_DIAG, NLRU, SLSTM_DIAG, GRU_HEAD, TITANS, LSTM, CFC = 0, 1, 2, 3, 4, 5, 6
 KIND = {"gru_diag": GRU_DIAG, "nlru": NLRU, "slstm_diag": SLSTM_DIAG, "gru_head": GRU_HEAD, "titans": TITANS,
-        "lstm": LSTM}
-GATES = {GRU_DIAG: 3, NLRU: 2, SLSTM_DIAG: 4, GRU_HEAD: 3, TITANS: 5, LSTM: 3}
-SLOTS = {GRU_DIAG: 1, NLRU: 1, SLSTM_DIAG: 4, GRU_HEAD: 1, TITANS: 1, LSTM: 2}
+        "lstm": LSTM, "cfc": CFC}
+GATES = {GRU_DIAG: 3, NLRU: 2, SLSTM_DIAG: 4, GRU_HEAD: 3, TITANS: 5, LSTM: 3, CFC: 4}
+SLOTS = {GRU_DIAG: 1, NLRU: 1, SLSTM_DIAG: 4, GRU_HEAD: 1, TITANS: 1, LSTM: 2, CFC: 1}
 
 
 def _lib_path(prec: str) -> str:

@@ -32,7 +32,7 @@
 #endif
 typedef REAL real;
 
-enum { CELL_GRU_DIAG = 0, CELL_NLRU = 1, CELL_SLSTM_DIAG = 2, CELL_GRU_HEAD = 3, CELL_TITANS = 4, CELL_LSTM = 5 };
+enum { CELL_GRU_DIAG = 0, CELL_NLRU = 1, CELL_SLSTM_DIAG = 2, CELL_GRU_HEAD = 3, CELL_TITANS = 4, CELL_LSTM = 5, CELL_CFC = 6 };
 
 static inline real r_exp(real x) { return sizeof(real) == 4 ? (real)expf((float)x) : (real)exp((double)x); }
 static inline real r_tanh(real x) { return sizeof(real) == 4 ? (real)tanhf((float)x) : (real)tanh((double)x); }
@@ -45,7 +45,7 @@ static inline real nanmax(real acc, real v) { return (v != v || v > acc) ? v : a
 int oracle_real_bytes(void) { return (int)sizeof(real); }
 
 static int gates_of(int kind) {
-    return kind == CELL_NLRU ? 2 : (kind == CELL_SLSTM_DIAG ? 4 : (kind == CELL_TITANS ? 5 : 3));
+    return kind == CELL_NLRU ? 2 : ((kind == CELL_SLSTM_DIAG || kind == CELL_CFC) ? 4 : (kind == CELL_TITANS ? 5 : 3));
 }
 static int slots_of(int kind) { return kind == CELL_SLSTM_DIAG ? 4 : (kind == CELL_LSTM ? 2 : 1); }
 
@@ -90,6 +90,16 @@ static inline void titans(real h, real ap, real tp, real k, real v, real np_, re
     if (j) *j = (1 - alpha) - theta * k * k + u * (1 - n * n) * r;
 }
 
+/* ParaCfC (gate_mix='input') step + diagonal Jacobian.  cells/para_cfc.py:162-171, 215-231:
+ * gates (f_pre, c_x, dt, b) = chunk4(project_wx(x)), a = sigmoid(-(softplus(f_pre) dt + b)),
+ * h' = a h + (1 - a) tanh(c_x + u h), J = a + (1 - a)(1 - n^2) u. */
+static inline void cfc(real h, real fp, real cx, real dt, real b, real u, real *f, real *j) {
+    real a = r_sigmoid(-(r_softplus(fp) * dt + b));
+    real n = r_tanh(cx + u * h);
+    *f = a * h + (1 - a) * n;
+    if (j) *j = a + (1 - a) * (1 - n * n) * u;
+}
+
 /* step (+ Jacobian) of a scalar-diagonal cell at channel ch; wt points at the gates of one step */
 static inline void diag_step(int kind, real h, const real *wt, int d, const real *params, int ch, real *f,
                              real *j) {
@@ -98,6 +108,8 @@ static inline void diag_step(int kind, real h, const real *wt, int d, const real
     else if (kind == CELL_TITANS)
         titans(h, wt[0], wt[d], wt[2 * (size_t)d], wt[3 * (size_t)d], wt[4 * (size_t)d], params[ch],
                params[d + ch], f, j);
+    else if (kind == CELL_CFC)
+        cfc(h, wt[0], wt[d], wt[2 * (size_t)d], wt[3 * (size_t)d], params[ch], f, j);
     else
         nlru(h, wt[0], wt[d], params[ch], f, j);
 }
@@ -708,7 +720,7 @@ void oracle_backward(int kind, const real *states, const real *wx, const real *p
         }
         return;
     }
-    const int NP = (kind == CELL_GRU_DIAG) ? 3 : (kind == CELL_NLRU ? 1 : (kind == CELL_TITANS ? 2 : (kind == CELL_LSTM ? 5 : 4)));
+    const int NP = (kind == CELL_GRU_DIAG) ? 3 : ((kind == CELL_NLRU || kind == CELL_CFC) ? 1 : (kind == CELL_TITANS ? 2 : (kind == CELL_LSTM ? 5 : 4)));
 #pragma omp parallel for schedule(static)
     for (int ch = 0; ch < d; ++ch) {
         real gp[5] = {0, 0, 0, 0, 0};
@@ -832,6 +844,21 @@ void oracle_backward(int kind, const real *states, const real *wx, const real *p
                         gwt[4 * (size_t)d] = mu * u * (1 - n * n);
                         gp[0] += mu * n;
                         gp[1] += gwt[4 * (size_t)d] * hp;
+                    } else if (kind == CELL_CFC) {
+                        /* kernels/vjp_cfc.py:102-128 (cfc_recurrence_vjp_eager) */
+                        real u = params[ch];
+                        real fp = wt[0], dt = wt[2 * (size_t)d], bb = wt[3 * (size_t)d];
+                        cfc(hp, fp, wt[d], dt, bb, u, &f, &j);
+                        real soft = r_softplus(fp);
+                        real a = r_sigmoid(-(soft * dt + bb));
+                        real n = r_tanh(wt[d] + u * hp);
+                        real d_h_da = mu * (hp - n), a1a = a * (1 - a);
+                        real d_npre = mu * (1 - a) * (1 - n * n);
+                        gwt[0] = d_h_da * a1a * (-dt) * r_sigmoid(fp);
+                        gwt[d] = d_npre;
+                        gwt[2 * (size_t)d] = d_h_da * a1a * (-soft);
+                        gwt[3 * (size_t)d] = d_h_da * a1a * (-1);
+                        gp[0] += d_npre * hp;
                     } else {
                         real u = params[ch];
                         nlru(hp, wt[0], wt[d], u, &f, &j);

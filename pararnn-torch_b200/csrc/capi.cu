@@ -629,6 +629,22 @@ int prb_bwd_titans(const void* states, const void* wx, const void* u, const void
                         dtype, workspace, workspace_bytes, stats, (cudaStream_t)stream);
 }
 
+int prb_newton_cfc_fused(const void* wx, const void* u, const void* h0, void* out, int B, int T, int d,
+                         int dtype, int max_iters, float omega, int want_residual, void* workspace,
+                         size_t workspace_bytes, prb_stats* stats, prb_stream_t stream) {
+    const void* pars[3] = {u, nullptr, nullptr};
+    return run_diag_fwd(kCellCfc, wx, pars, h0, out, B, T, d, dtype, max_iters, omega, want_residual,
+                        workspace, workspace_bytes, stats, (cudaStream_t)stream);
+}
+
+int prb_bwd_cfc(const void* states, const void* wx, const void* u, const void* h0, const void* grad_states,
+                void* g_wx, float* g_params, float* g_h0, int B, int T, int d, int dtype, void* workspace,
+                size_t workspace_bytes, prb_stats* stats, prb_stream_t stream) {
+    const void* pars[3] = {u, nullptr, nullptr};
+    return run_diag_bwd(kCellCfc, states, wx, pars, h0, grad_states, g_wx, g_params, g_h0, B, T, d, dtype,
+                        workspace, workspace_bytes, stats, (cudaStream_t)stream);
+}
+
 /* ---- ParaLSTM --------------------------------------------------------------------------- */
 
 namespace {

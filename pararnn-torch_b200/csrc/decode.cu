@@ -71,6 +71,8 @@ cudaError_t launch_t(int cell, const void* state, const void* wx, const void* pa
         decode_diag_kernel<kCellNlru, TIO><<<grid, threads, 0, s>>>(st, w, p, bt, o, B, d, cap);
     else if (cell == kCellTitans)
         decode_diag_kernel<kCellTitans, TIO><<<grid, threads, 0, s>>>(st, w, p, bt, o, B, d, cap);
+    else if (cell == kCellCfc)
+        decode_diag_kernel<kCellCfc, TIO><<<grid, threads, 0, s>>>(st, w, p, bt, o, B, d, cap);
     else if (cell == kCellSlstmDiag)
         decode_slstm_kernel<TIO><<<grid, threads, 0, s>>>(st, w, p, bt, o, B, d, cap, eps);
     else

@@ -1,9 +1,9 @@
-// Per-step math of the scalar-diagonal cells (ParaGRU mix='diag', ParaNLRU, ParaTitans), shared by
+// Per-step math of the scalar-diagonal cells (ParaGRU mix='diag', ParaNLRU, ParaTitans, ParaCfC), shared by
 // the look-back kernels (diag_kernels.cu) and the pipelined persistent kernels (diag_pipe.cu).
 //
 // Reference behaviour restated: cells/para_gru.py:418-467, cells/para_nlru.py:149-168,
-// cells/para_titans.py:170-216 (step and diagonal Jacobian), kernels/vjp_gru.py:107-138,
-// kernels/vjp_nlru.py:88-108 (packed VJP; the Titans VJP is the closed form of what the reference
+// cells/para_titans.py:170-216, cells/para_cfc.py:162-231 (step and diagonal Jacobian),
+// kernels/vjp_gru.py:107-138, kernels/vjp_nlru.py:88-108, kernels/vjp_cfc.py:26-100 (packed VJP; the Titans VJP is the closed form of what the reference
 // obtains from autograd through ``step``, solvers/vjp.py:77-98).
 #pragma once
 #include "common.cuh"
@@ -122,6 +122,41 @@ struct DiagCell<kCellTitans> {
         gw[4] = mu * p[0] * np_;
         gp[0] = mu * a.n;
         gp[1] = gw[4] * h;
+    }
+};
+
+// ParaCfC (gate_mix='input'): a = sigmoid(-(softplus(f) dt + b)), h' = a h + (1 - a) tanh(c + u h),
+// gates (f, c, dt, b) = project_wx(x) (dt >= 1e-4 is the clamped time step broadcast over the
+// channels, b the input-conditioned time bias), parameter u.
+template <>
+struct DiagCell<kCellCfc> {
+    static constexpr int G = 4, NP = 1;
+    struct Acts {
+        float a, n, soft, sg_f, dt;
+    };
+    __device__ static __forceinline__ void eval(float h, const float (&g)[4], const float (&p)[1],
+                                                float& f, float& j, Acts& a) {
+        a.soft = softplus_f(g[0]);
+        a.sg_f = sigmoid_f(g[0]);  // d softplus / d pre
+        a.dt = g[2];
+        a.a = sigmoid_f(-fmaf(a.soft, g[2], g[3]));
+        a.n = tanh_f(fmaf(p[0], h, g[1]));
+        f = fmaf(a.a, h, (1.f - a.a) * a.n);
+        j = fmaf((1.f - a.a) * (1.f - a.n * a.n), p[0], a.a);
+    }
+    __device__ static __forceinline__ float step(float h, const float (&g)[4], const float (&p)[1]) {
+        const float a = sigmoid_f(-fmaf(softplus_f(g[0]), g[2], g[3]));
+        const float n = tanh_f(fmaf(p[0], h, g[1]));
+        return fmaf(a, h, (1.f - a) * n);
+    }
+    __device__ static __forceinline__ void vjp(float h, const Acts& a, const float (&p)[1], float mu,
+                                               float (&gw)[4], float (&gp)[1]) {
+        const float d_pre = -mu * (h - a.n) * a.a * (1.f - a.a);  // grad of (soft dt + b)
+        gw[0] = d_pre * a.dt * a.sg_f;
+        gw[1] = mu * (1.f - a.a) * (1.f - a.n * a.n);
+        gw[2] = d_pre * a.soft;
+        gw[3] = d_pre;
+        gp[0] = gw[1] * h;
     }
 };
 

@@ -443,6 +443,10 @@ cudaError_t launch_diag_newton(int cell, int dtype, const DiagFwdArgs& a, bool f
         return dtype == kF32 ? launch_fwd<kCellTitans, float>(a, first, last, s)
                              : launch_fwd<kCellTitans, __nv_bfloat16>(a, first, last, s);
     }
+    if (cell == kCellCfc) {
+        return dtype == kF32 ? launch_fwd<kCellCfc, float>(a, first, last, s)
+                             : launch_fwd<kCellCfc, __nv_bfloat16>(a, first, last, s);
+    }
     return dtype == kF32 ? launch_fwd<kCellNlru, float>(a, first, last, s)
                          : launch_fwd<kCellNlru, __nv_bfloat16>(a, first, last, s);
 }
@@ -460,6 +464,11 @@ cudaError_t launch_diag_newton_agg(int cell, int dtype, const DiagFwdArgs& a, cu
             diag_newton_agg_kernel<kCellTitans, float, kDiagL, kDiagW><<<grid, blk, 0, s>>>(a);
         else
             diag_newton_agg_kernel<kCellTitans, __nv_bfloat16, kDiagL, kDiagW><<<grid, blk, 0, s>>>(a);
+    } else if (cell == kCellCfc) {
+        if (dtype == kF32)
+            diag_newton_agg_kernel<kCellCfc, float, kDiagL, kDiagW><<<grid, blk, 0, s>>>(a);
+        else
+            diag_newton_agg_kernel<kCellCfc, __nv_bfloat16, kDiagL, kDiagW><<<grid, blk, 0, s>>>(a);
     } else {
         if (dtype == kF32)
             diag_newton_agg_kernel<kCellNlru, float, kDiagL, kDiagW><<<grid, blk, 0, s>>>(a);
@@ -491,6 +500,8 @@ cudaError_t launch_diag_guess(int cell, int dtype, bool out_f32, const void* wx,
         PRB_GUESS(kCellGruDiag)
     } else if (cell == kCellTitans) {
         PRB_GUESS(kCellTitans)
+    } else if (cell == kCellCfc) {
+        PRB_GUESS(kCellCfc)
     } else {
         PRB_GUESS(kCellNlru)
     }
@@ -519,6 +530,8 @@ cudaError_t launch_diag_residual(int cell, int dtype, bool st_f32, const void* w
         PRB_RES(kCellGruDiag)
     } else if (cell == kCellTitans) {
         PRB_RES(kCellTitans)
+    } else if (cell == kCellCfc) {
+        PRB_RES(kCellCfc)
     } else {
         PRB_RES(kCellNlru)
     }
@@ -545,6 +558,12 @@ cudaError_t launch_diag_bwd(int cell, int dtype, const DiagBwdArgs& a, bool agg_
             PRB_BWD(kCellTitans, float)
         } else {
             PRB_BWD(kCellTitans, __nv_bfloat16)
+        }
+    } else if (cell == kCellCfc) {
+        if (dtype == kF32) {
+            PRB_BWD(kCellCfc, float)
+        } else {
+            PRB_BWD(kCellCfc, __nv_bfloat16)
         }
     } else {
         if (dtype == kF32) {

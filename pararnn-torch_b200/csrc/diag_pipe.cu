@@ -496,6 +496,9 @@ cudaError_t launch_diag_newton_pipe(int cell, int dtype, const DiagFwdArgs& a, b
     if (cell == kCellTitans)
         return dtype == kF32 ? launch_fwd_t<kCellTitans, float, 2>(a, first, last, s)
                              : launch_fwd_t<kCellTitans, __nv_bfloat16, 3>(a, first, last, s);
+    if (cell == kCellCfc)
+        return dtype == kF32 ? launch_fwd_t<kCellCfc, float, 2>(a, first, last, s)
+                             : launch_fwd_t<kCellCfc, __nv_bfloat16, 3>(a, first, last, s);
     return dtype == kF32 ? launch_fwd_t<kCellNlru, float, 2>(a, first, last, s)
                          : launch_fwd_t<kCellNlru, __nv_bfloat16, 3>(a, first, last, s);
 }
@@ -507,6 +510,9 @@ cudaError_t launch_diag_bwd_pipe(int cell, int dtype, const DiagBwdArgs& a, cuda
     if (cell == kCellTitans)
         return dtype == kF32 ? launch_bwd_t<kCellTitans, float, 2>(a, s)
                              : launch_bwd_t<kCellTitans, __nv_bfloat16, 3>(a, s);
+    if (cell == kCellCfc)
+        return dtype == kF32 ? launch_bwd_t<kCellCfc, float, 2>(a, s)
+                             : launch_bwd_t<kCellCfc, __nv_bfloat16, 3>(a, s);
     return dtype == kF32 ? launch_bwd_t<kCellNlru, float, 2>(a, s)
                          : launch_bwd_t<kCellNlru, __nv_bfloat16, 3>(a, s);
 }

@@ -21,9 +21,11 @@ struct Options {
 Options& options();
 
 enum Cell : int { kCellGruDiag = 0, kCellNlru = 1, kCellSlstmDiag = 2, kCellGruHead = 3, kCellTitans = 4,
-                  kCellLstm = 5 };
+                  kCellLstm = 5, kCellCfc = 6 };
 // gates and recurrent parameter vectors per channel of the scalar-diagonal cells
-inline bool is_diag_cell(int cell) { return cell == kCellGruDiag || cell == kCellNlru || cell == kCellTitans; }
+inline bool is_diag_cell(int cell) {
+    return cell == kCellGruDiag || cell == kCellNlru || cell == kCellTitans || cell == kCellCfc;
+}
 inline int diag_cell_params(int cell) { return cell == kCellGruDiag ? 3 : (cell == kCellTitans ? 2 : 1); }
 enum DType : int { kF32 = 0, kBF16 = 1 };
 

@@ -96,7 +96,7 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
         if (lane == 0) {
             for (int r = 0; r < n_rounds; ++r) {
                 const int s = r % NSTAGE;
-                if (r >= NSTAGE && !mbar_wait_bounded(&empty[s], ((r / NSTAGE) - 1) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit))
+                if (r >= NSTAGE && !mbar_wait_bounded_sleepy(&empty[s], ((r / NSTAGE) - 1) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit))
                     timed_out = true;
                 unsigned char* base = smem + s * S::STAGE;
                 mbar_expect_tx(&full[s], S::STAGE);
@@ -119,7 +119,7 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
             const int s = r % NSTAGE;
             // after a time-out the warp keeps walking (the named-barrier hand-over needs every
             // warp) but its waits give up after a few polls: the result is void, status says so
-            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit)) timed_out = true;
+            if (!mbar_wait_bounded_sleepy(&full[s], (r / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const float* t_st = reinterpret_cast<const float*>(smem + s * S::STAGE + S::WX_BYTES);
             const int t0 = sg.lo + r * LT + warp * L;
@@ -520,7 +520,7 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
         if (lane == 0) {
             for (int r = 0; r < n_rounds; ++r) {
                 const int s = r % NSTAGE;
-                if (r >= NSTAGE && !mbar_wait_bounded(&empty[s], ((r / NSTAGE) - 1) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit))
+                if (r >= NSTAGE && !mbar_wait_bounded_sleepy(&empty[s], ((r / NSTAGE) - 1) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit))
                     timed_out = true;
                 unsigned char* base = smem + s * S::STAGE;
                 mbar_expect_tx(&full[s], S::WX_BYTES + (HAS_H ? (LT + 1) * kLanes * 4 : 0));
@@ -541,7 +541,7 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
 
         for (int r = 0; r < n_rounds; ++r) {
             const int s = r % NSTAGE;
-            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit)) timed_out = true;
+            if (!mbar_wait_bounded_sleepy(&full[s], (r / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit)) timed_out = true;
             const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
             const float* t_h = reinterpret_cast<const float*>(smem + s * S::STAGE + S::WX_BYTES);
             const int t0 = sg.lo + r * LT + warp * L;
@@ -594,7 +594,7 @@ slstm_picard_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
                 // (r-1)-th for warp 0
                 if (!(r == 0 && warp == 0)) {
                     const uint32_t par = (warp == 0 ? r - 1 : r) & 1;
-                    if (!mbar_wait_bounded(&cnbar[warp], par, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit)) timed_out = true;
+                    if (!mbar_wait_bounded_sleepy(&cnbar[warp], par, timed_out ? kWaitLimitAfterTimeout : kPipeWaitLimit)) timed_out = true;
                 }
                 float c = slot_in[0], n = slot_in[kLanes];
                 float cs[L], ns[L];

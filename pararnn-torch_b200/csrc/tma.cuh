@@ -41,6 +41,28 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
     return false;
 }
+// Same wait with a suspend-time hint on the polls after the first: the waiting thread sleeps in
+// hardware (and wakes when the phase completes) instead of spinning, which leaves the issue slots
+// to the warps that have work.  Measured: the per-pass sLSTM Newton sweep 1.05 -> 0.92 ms, the
+// Picard sweep 0.43 -> 0.40 ms; the reverse sweep gets slower with it and keeps the plain wait.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_sleepy(uint64_t* bar, uint32_t parity, uint32_t limit) {
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+    }
+    return false;
+}
 // Once a thread has seen one of its bounded waits run out it passes this limit to its later waits
 // (`timed_out ? kWaitLimitAfterTimeout : limit`): a CTA whose input stalled then leaves after about
 // one full limit per warp, not one per remaining wait, and the normal path pays nothing for it.

@@ -5,7 +5,7 @@ Public surface mirrors the part of the reference package that the hot path touch
 ``sequential_apply``, ``verify_agreement`` / ``AgreementReport``, ``ParaRNN`` and the cells.
 """
 
-from .cells import ParaGRU, ParaLSTM, ParaNLRU, ParaSLSTM, ParaTitans
+from .cells import ParaCfC, ParaGRU, ParaLSTM, ParaNLRU, ParaSLSTM, ParaTitans
 from .config import (
     NewtonConfig,
     NewtonDivergenceError,
@@ -24,7 +24,7 @@ from . import custom_ops  # noqa: E402,F401  registers torch.ops.pararnn_b200.*
 __version__ = "0.2.0"
 __all__ = [
     "AgreementError", "AgreementReport", "NewtonConfig", "NewtonDivergenceError", "NewtonStats",
-    "ParaGRU", "ParaLSTM", "ParaNLRU", "ParaRNN", "ParaSLSTM", "ParaTitans", "can_decode_step", "compile_safe_config", "decode_step",
+    "ParaCfC", "ParaGRU", "ParaLSTM", "ParaNLRU", "ParaRNN", "ParaSLSTM", "ParaTitans", "can_decode_step", "compile_safe_config", "decode_step",
     "decode_wx",
     "default_agreement_atol", "newton_apply", "sequential_apply", "slstm_auto_picard",
     "slstm_picard_next", "verify_agreement",

@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libpararnn_b200.so")
 
 PRB_F32, PRB_BF16 = 0, 1
-CELL_GRU_DIAG, CELL_NLRU, CELL_SLSTM_DIAG, CELL_GRU_HEAD, CELL_TITANS, CELL_LSTM = 0, 1, 2, 3, 4, 5
+CELL_GRU_DIAG, CELL_NLRU, CELL_SLSTM_DIAG, CELL_GRU_HEAD, CELL_TITANS, CELL_LSTM, CELL_CFC = 0, 1, 2, 3, 4, 5, 6
 MAX_ITERS = 16
 STATS_BYTES = 80
 
@@ -34,6 +34,8 @@ _SIGNATURES = {
     "prb_bwd_workspace_bytes": (_SIZE, [_INT] * 6),
     "prb_newton_gru_fused": (_INT, [_VOIDP] * 6 + [_INT] * 5 + [_FLOAT, _INT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_newton_nlru_fused": (_INT, [_VOIDP] * 4 + [_INT] * 5 + [_FLOAT, _INT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
+    "prb_newton_cfc_fused": (_INT, [_VOIDP] * 4 + [_INT] * 5 + [_FLOAT, _INT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
+    "prb_bwd_cfc": (_INT, [_VOIDP] * 8 + [_INT] * 4 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_newton_titans_fused": (_INT, [_VOIDP] * 5 + [_INT] * 5 + [_FLOAT, _INT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_bwd_titans": (_INT, [_VOIDP] * 9 + [_INT] * 4 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_lstm_workspace_bytes": (_SIZE, [_INT] * 5),

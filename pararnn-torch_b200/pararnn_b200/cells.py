@@ -270,6 +270,79 @@ class ParaTitans(nn.Module):
         return (1.0 - alpha) * h_prev - theta * grad + self.clipped_u() * n
 
 
+CFC_DT_EPS = 1e-4
+
+
+def split_cfc_input(x: Tensor) -> tuple[Tensor, Tensor]:
+    """``x[..., :-1]`` are the features, ``x[..., -1:]`` the time step, clamped from below
+    (reference ``cells/para_cfc.py:57-60``)."""
+    if x.shape[-1] < 2:
+        raise ValueError(f"ParaCfC needs d_in >= 2 (features + time step), got {x.shape[-1]}")
+    return x[..., :-1], x[..., -1:].clamp_min(CFC_DT_EPS)
+
+
+class ParaCfC(nn.Module):
+    """Closed-form continuous-time cell with irregular time steps (reference
+    ``cells/para_cfc.py``).  The last channel of ``x`` is the time step ``dt``:
+
+        a_t = sigmoid(-(softplus(f_t) dt_t + b_t)),   (f_t, c_t) = W_x(feat_t),  b_t = W_b(feat_t)
+        h_t = a_t h_{t-1} + (1 - a_t) tanh(c_t + u h_{t-1})
+
+    ``project_wx`` packs ``(f, c, dt, b)`` as the ``(…, 4 d_h)`` input of the fused solve.  Only
+    ``gate_mix='input'`` (the reference's fused and packed-VJP case) is covered."""
+
+    def __init__(self, input_size=None, hidden_size=None, *, d_in=None, d_h=None, gate_mix="input",
+                 time_bias_init=-3.0, max_recurrent_norm=_UNSET, device=None, dtype=None):
+        super().__init__()
+        input_size, hidden_size = _sizes(input_size, hidden_size, d_in, d_h)
+        if input_size < 2:
+            raise ValueError(f"ParaCfC d_in must be >= 2, got {input_size}")
+        if gate_mix != "input":
+            raise ValueError("this backend covers ParaCfC(gate_mix='input') only")
+        kw = {"device": device, "dtype": dtype}
+        self.input_size = self.d_in = input_size
+        self.hidden_size = self.d_h = hidden_size
+        self.feature_size = input_size - 1
+        self.state_slots = 1
+        self.mix = "diag"
+        self.gate_mix = gate_mix
+        self.jac_structure = "diag"
+        self.max_recurrent_norm = 0.5 if max_recurrent_norm is _UNSET else max_recurrent_norm
+        self.time_bias_init = float(time_bias_init)
+        self.u = nn.Parameter(torch.empty(hidden_size, **kw))
+        self.register_parameter("v", None)
+        self.W_x = nn.Linear(self.feature_size, 2 * hidden_size, bias=True, **kw)
+        self.W_b = nn.Linear(self.feature_size, hidden_size, bias=True, **kw)
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        nn.init.kaiming_uniform_(self.W_x.weight, a=math.sqrt(5))
+        nn.init.zeros_(self.W_x.bias)
+        _xavier_gaussian_vec_(self.u)
+        # zero weight and bias -3: the gate starts near sigmoid(3) ~ 0.95 for dt -> 0
+        nn.init.zeros_(self.W_b.weight)
+        nn.init.constant_(self.W_b.bias, self.time_bias_init)
+
+    def clipped_u(self) -> Tensor:
+        return _clamp(self.u, self.max_recurrent_norm)
+
+    def project_wx(self, x: Tensor) -> Tensor:
+        feat, dt = split_cfc_input(x)
+        return torch.cat((self.W_x(feat), dt.expand(*feat.shape[:-1], self.d_h), self.W_b(feat)), dim=-1)
+
+    def step(self, h_prev: Tensor, x: Tensor | None = None, *, wx: Tensor | None = None) -> Tensor:
+        if wx is None:
+            if x is None:
+                raise ValueError("ParaCfC.step needs x or wx")
+            wx = self.project_wx(x)
+        if wx.shape[-1] != 4 * self.d_h:
+            raise ValueError(f"ParaCfC wx last dim must be 4*d_h={4 * self.d_h}, got {wx.shape[-1]}")
+        f_pre, cx, dt, b = wx.chunk(4, dim=-1)
+        a = torch.sigmoid(-(torch.nn.functional.softplus(f_pre) * dt + b))
+        n = torch.tanh(cx + self.clipped_u() * h_prev)
+        return a * h_prev + (1.0 - a) * n
+
+
 class ParaSLSTM(nn.Module):
     """Stabilised sLSTM with channelwise recurrence ``R (4, d)``; state slots ``(c, n, m, h)``."""
 
@@ -330,12 +403,16 @@ def cell_kind(cell: nn.Module) -> str:
         return "nlru"
     if name == "ParaTitans":
         return "titans"
+    if name == "ParaCfC":
+        if getattr(cell, "gate_mix", "input") != "input":
+            raise TypeError("the CUDA backend covers ParaCfC(gate_mix='input') only")
+        return "cfc"
     if name == "ParaLSTM":
         return "lstm"
     if name == "ParaSLSTM" and mix == "diag":
         return "slstm_diag"
     raise TypeError(
-        f"the CUDA backend covers ParaGRU (diag, head), ParaNLRU, ParaTitans, ParaLSTM and ParaSLSTM(mix='diag'); "
+        f"the CUDA backend covers ParaGRU (diag, head), ParaNLRU, ParaTitans, ParaCfC, ParaLSTM and ParaSLSTM(mix='diag'); "
         f"got {name}(mix={mix!r})")
 
 

@@ -9,9 +9,10 @@ through ``newton_apply`` (eq. 2.6), never through these ops.
 
 Registered:
 
-* ``pararnn_b200::newton_gru_fused``, ``::newton_nlru_fused``, ``::newton_titans_fused``,
-  ``::newton_lstm_fused``, ``::newton_slstm_fused``, ``::newton_gru_head_fused``  (reference
-  ``custom_ops.py:146-188, 191-227, 269-308, 437-483, 486-540, 311-386``);
+* ``pararnn_b200::newton_gru_fused``, ``::newton_nlru_fused``, ``::newton_cfc_fused``,
+  ``::newton_titans_fused``, ``::newton_lstm_fused``, ``::newton_slstm_fused``,
+  ``::newton_gru_head_fused``  (reference
+  ``custom_ops.py:146-188, 191-227, 230-266, 269-308, 437-483, 486-540, 311-386``);
 * ``pararnn_b200::reverse_gru_head_factor``  (reference ``custom_ops.py:389-434``);
 * ``pararnn_b200::reverse_gru_vjp``, ``::reverse_nlru_vjp``, ``::reverse_slstm_vjp``,
   ``::reverse_gru_head_vjp``: the reverse scan fused with the packed VJP.  The reference has these
@@ -66,6 +67,19 @@ def newton_nlru_fused(wx: Tensor, u: Tensor, h0: Tensor | None = None, cu_seqlen
 
 
 @newton_nlru_fused.register_fake
+def _(wx, u, h0=None, cu_seqlens=None, block_table=None, *, max_iters, omega):
+    batch, time, _ = wx.shape
+    return wx.new_empty(batch, time, int(u.numel()))
+
+
+@torch.library.custom_op("pararnn_b200::newton_cfc_fused", mutates_args=())
+def newton_cfc_fused(wx: Tensor, u: Tensor, h0: Tensor | None = None, cu_seqlens: Tensor | None = None,
+                     block_table: Tensor | None = None, *, max_iters: int, omega: float) -> Tensor:
+    return ops.newton_cfc_fused(wx, u, h0, cu_seqlens, block_table, max_iters=max_iters, omega=omega,
+                                want_residual=False)
+
+
+@newton_cfc_fused.register_fake
 def _(wx, u, h0=None, cu_seqlens=None, block_table=None, *, max_iters, omega):
     batch, time, _ = wx.shape
     return wx.new_empty(batch, time, int(u.numel()))
@@ -207,7 +221,7 @@ def _(states, wx, a_z, a_r, a_n, grad_states, h0=None):
             torch.empty(a_z.shape, **f32), torch.empty(wx.shape[0], d, **f32))
 
 
-OP_NAMES = ("newton_gru_fused", "newton_nlru_fused", "newton_titans_fused", "newton_lstm_fused", "newton_slstm_fused",
+OP_NAMES = ("newton_gru_fused", "newton_nlru_fused", "newton_cfc_fused", "newton_titans_fused", "newton_lstm_fused", "newton_slstm_fused",
             "newton_gru_head_fused",
             "reverse_gru_head_factor", "reverse_gru_vjp", "reverse_nlru_vjp", "reverse_slstm_vjp",
             "reverse_gru_head_vjp")

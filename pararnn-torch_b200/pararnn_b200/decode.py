@@ -20,7 +20,7 @@ from . import _lib as L
 from .cells import cell_kind
 
 _CELL = {"gru_diag": L.CELL_GRU_DIAG, "nlru": L.CELL_NLRU, "slstm_diag": L.CELL_SLSTM_DIAG,
-         "titans": L.CELL_TITANS}
+         "titans": L.CELL_TITANS, "cfc": L.CELL_CFC}
 
 
 def can_decode_step(cell: nn.Module, ref: Tensor) -> bool:
@@ -49,6 +49,13 @@ def decode_wx(cell: nn.Module, x: Tensor, *, out: Tensor | None = None) -> Tenso
     if lin is None:
         raise TypeError(f"decode_wx needs cell.W_x; got {type(cell).__name__}")
     x2 = _squeeze_time(x) if x.dim() == 3 else x
+    project = getattr(cell, "project_wx", None)
+    if callable(project):  # ParaCfC: (f, c, dt, b), not a single linear map
+        y = project(x2)
+        if out is None:
+            return y
+        out.copy_(y)
+        return out
     if out is None:
         return lin(x2)
     torch.mm(x2, lin.weight.t(), out=out)
@@ -60,7 +67,7 @@ def decode_wx(cell: nn.Module, x: Tensor, *, out: Tensor | None = None) -> Tenso
 def _raw_params(cell: nn.Module, kind: str, dtype) -> Tensor:
     if kind == "gru_diag":
         p = torch.stack([cell.a_z, cell.a_r, cell.a_n])
-    elif kind == "nlru":
+    elif kind in ("nlru", "cfc"):
         p = cell.u[None]
     elif kind == "titans":
         p = torch.stack([cell.u, cell.r])

@@ -88,12 +88,22 @@ def _recurrent_params(cell: nn.Module, kind: str):
         return (cell.clipped_u(),)
     if kind == "titans":
         return (cell.clipped_u(), cell.clipped_r())
+    if kind == "cfc":
+        return (cell.clipped_u(),)
     if kind == "lstm":
         return tuple(cell.clipped_recurrent())
     return (cell.clipped_r(),)
 
 
 # --------------------------------------------------------------------------- forward
+
+def input_affine(cell: nn.Module, x: Tensor) -> Tensor:
+    """Input projection of the solve: ``cell.project_wx(x)`` where the cell packs more than
+    ``W_x(x)`` (ParaCfC adds the time step and the time bias), else ``cell.W_x(x)`` (reference
+    ``solvers/newton/__init__.py:959-967``)."""
+    project = getattr(cell, "project_wx", None)
+    return project(x) if callable(project) else cell.W_x(x)
+
 
 def _solve_window(cell, kind, wx, h0, cfg, dstats, want_residual, cu_seqlens=None, block_table=None):
     rec = _recurrent_params(cell, kind)
@@ -104,6 +114,9 @@ def _solve_window(cell, kind, wx, h0, cfg, dstats, want_residual, cu_seqlens=Non
     if kind == "nlru":
         return ops.newton_nlru_fused(wx, rec[0], h0, cu_seqlens, block_table, max_iters=K, omega=cfg.omega,
                                      stats=dstats, want_residual=want_residual)
+    if kind == "cfc":
+        return ops.newton_cfc_fused(wx, rec[0], h0, cu_seqlens, block_table, max_iters=K, omega=cfg.omega,
+                                    stats=dstats, want_residual=want_residual)
     if kind == "lstm":
         return ops.newton_lstm_fused(wx, *rec, h0, cu_seqlens, block_table, max_iters=K, omega=cfg.omega,
                                      stats=dstats, want_residual=want_residual)
@@ -166,7 +179,7 @@ def _forward_once(cell, kind, x, cfg, h0, stats, wx=None, cu_seqlens=None, block
     """One full solve (all windows); returns ``(states, wx)``.  Reads the device statistics
     only when somebody consumes them."""
     if wx is None:
-        wx = cell.W_x(x)
+        wx = input_affine(cell, x)
     need_stats = stats is not None or cfg.residual_fail is not None
     K = int(cfg.max_iters)
     if cfg.chunk_len is None:
@@ -240,6 +253,9 @@ def _reverse_window(cell, kind, states, wx, grad_states, h0):
     if kind == "nlru":
         g_wx, gu, g_h0 = ops.nlru_reverse_vjp(states, wx, rec[0], grad_states, h0)
         return g_wx, {"u": gu}, g_h0
+    if kind == "cfc":
+        g_wx, gu, g_h0 = ops.cfc_reverse_vjp(states, wx, rec[0], grad_states, h0)
+        return g_wx, {"u": gu}, g_h0
     if kind == "lstm":
         g_wx, gp, g_h0 = ops.lstm_reverse_vjp(states, wx, *rec, grad_states, h0)
         return g_wx, {n: gp[i] for i, n in enumerate(("a_f", "a_z", "a_o", "c_f", "c_o"))}, g_h0
@@ -301,6 +317,10 @@ def _backward(cell, kind, states, x, wx, grad_states, h0, chunk_len, cu_seqlens=
         if mask is not None:
             g = g * mask
         grads[name] = g.to(raw.dtype)
+    if kind == "cfc":
+        grad_x, lin_grads = _cfc_input_grads(cell, x, g_wx)
+        grads.update(lin_grads)
+        return grad_x, g_h0, grads
     lin = cell.W_x
     gy = g_wx.reshape(-1, g_wx.shape[-1])
     xx = x.reshape(-1, x.shape[-1])
@@ -309,6 +329,31 @@ def _backward(cell, kind, states, x, wx, grad_states, h0, chunk_len, cu_seqlens=
     if lin.bias is not None:
         grads["W_x.bias"] = gy.sum(0).to(lin.bias.dtype)
     return grad_x, g_h0, grads
+
+
+def _cfc_input_grads(cell, x, g_wx):
+    """Gradients of ``project_wx``: ``g_wx (B,T,4d)`` holds the grads of ``(f, c, dt, b)``.
+    ``(f, c)`` go through ``W_x``, ``b`` through ``W_b``, both on the features; the time step
+    gets the channel sum of its block where the clamp was inactive (reference
+    ``solvers/vjp.py:180-211``)."""
+    from .cells import CFC_DT_EPS
+
+    d = cell.d_h
+    feat = x[..., :-1].reshape(-1, x.shape[-1] - 1)
+    g = g_wx.reshape(-1, 4 * d)
+    g_fc, g_dt, g_b = g[:, :2 * d], g[:, 2 * d:3 * d], g[:, 3 * d:]
+    wx_w, wb_w = cell.W_x.weight.detach().to(g.dtype), cell.W_b.weight.detach().to(g.dtype)
+    grad_feat = g_fc @ wx_w + g_b @ wb_w
+    grad_dt = g_dt.sum(-1, keepdim=True) * (x[..., -1:].reshape(-1, 1) >= CFC_DT_EPS).to(g.dtype)
+    grad_x = torch.cat((grad_feat, grad_dt), dim=-1).reshape(x.shape)
+    featc = feat.to(g.dtype)
+    grads = {"W_x.weight": (g_fc.t() @ featc).to(cell.W_x.weight.dtype),
+             "W_b.weight": (g_b.t() @ featc).to(cell.W_b.weight.dtype)}
+    if cell.W_x.bias is not None:
+        grads["W_x.bias"] = g_fc.sum(0).to(cell.W_x.bias.dtype)
+    if cell.W_b.bias is not None:
+        grads["W_b.bias"] = g_b.sum(0).to(cell.W_b.bias.dtype)
+    return grad_x, grads
 
 
 class _NewtonFixedPoint(torch.autograd.Function):

@@ -300,6 +300,48 @@ def newton_nlru_fused(wx: Tensor, u: Tensor, h0: Tensor | None = None,
     return out
 
 
+def newton_cfc_fused(wx: Tensor, u: Tensor, h0: Tensor | None = None,
+                      cu_seqlens: Tensor | None = None, block_table: Tensor | None = None, *,
+                      max_iters: int, omega: float = 1.0, stats: DeviceStats | None = None,
+                      want_residual: bool = True) -> Tensor:
+    """Fused Newton for ``ParaCfC`` (``gate_mix="input"``): ``wx = cell.project_wx(x) (B,T,4d)`` -> ``H (B,T,d)``.  ``cu_seqlens`` /
+    ``block_table`` as in ``newton_gru_fused`` (reference ``pararnn::newton_cfc_fused``,
+    ``kernels/custom_ops.py:230-266``)."""
+    if cu_seqlens is not None:
+        if stats is not None:
+            stats.parts.clear()
+        return _packed(lambda w, h, st, _g: newton_cfc_fused(w, u, h, max_iters=max_iters, omega=omega,
+                                                               stats=st, want_residual=want_residual),
+                       wx, h0, cu_seqlens, block_table, (u.numel(),), stats)
+    h0 = gather_h0(h0, block_table, wx.shape[0], (u.numel(),))
+    dev = _check_cuda(wx, u, h0)
+    _check_iters(max_iters)
+    if wx.dim() != 3 or wx.shape[-1] % 4:
+        raise ValueError(f"wx must be (B, T, 4*d), got {tuple(wx.shape)}")
+    B, T, d4 = wx.shape
+    d = d4 // 4
+    if u.numel() != d:
+        raise ValueError(f"u must have {d} elements, got {tuple(u.shape)}")
+    if h0 is not None and tuple(h0.shape) != (B, d):
+        raise ValueError(f"h0 must be ({B}, {d}), got {tuple(h0.shape)}")
+    if T < 1:
+        raise ValueError("time must be >= 1")
+    code = _dtype_code(wx)
+    wx_c = wx.detach().contiguous()
+    uc, h0c = _same(u, wx), _same(h0, wx)
+    out = torch.empty(B, T, d, dtype=wx.dtype, device=dev)
+    st = stats or DeviceStats(dev, max_iters)
+    lib = L.lib()
+    with torch.cuda.device(dev):
+        nbytes = lib.prb_newton_workspace_bytes(L.CELL_CFC, code, B, T, d, 1, max_iters, 0)
+        ws = _workspace(nbytes, dev)
+        rc = lib.prb_newton_cfc_fused(_ptr(wx_c), _ptr(uc), _ptr(h0c), _ptr(out), B, T, d, code,
+                                       int(max_iters), float(omega), int(want_residual), _ptr(ws),
+                                       ws.numel(), _ptr(st.buf), _stream(dev))
+    _raise(rc, "newton_cfc_fused")
+    return out
+
+
 def newton_titans_fused(wx: Tensor, u: Tensor, r: Tensor, h0: Tensor | None = None,
                         cu_seqlens: Tensor | None = None, block_table: Tensor | None = None, *,
                         max_iters: int, omega: float = 1.0, stats: DeviceStats | None = None,
@@ -501,6 +543,31 @@ def nlru_reverse_vjp(states: Tensor, wx: Tensor, u: Tensor, grad_states: Tensor,
                               _ptr(g_wx), _ptr(g_par), _ptr(g_h0), B, T, d, code, _ptr(ws),
                               ws.numel(), _ptr(sb.buf), _stream(dev))
     _raise(rc, "nlru_reverse_vjp")
+    _track_backward(sb)
+    return g_wx, g_par[0], g_h0
+
+
+def cfc_reverse_vjp(states: Tensor, wx: Tensor, u: Tensor, grad_states: Tensor,
+                     h0: Tensor | None = None):
+    """Eq. 2.6 reverse scan fused with the packed CfC VJP (reference ``kernels/vjp_cfc.py:102-167``):
+    ``(g_wx (B,T,4d) = grads of (f_pre, c_x, dt, b), g_u, g_h0)``."""
+    dev, code, st, wxc, gs, h0c = _bwd_common(states, wx, grad_states, h0)
+    B, T, d4 = wx.shape
+    d = d4 // 4
+    if tuple(states.shape) != (B, T, d) or tuple(grad_states.shape) != (B, T, d):
+        raise ValueError("states / grad_states must be (B, T, d)")
+    g_wx = torch.empty_like(wxc)
+    g_par = torch.empty(1, d, dtype=torch.float32, device=dev)
+    g_h0 = torch.empty(B, d, dtype=torch.float32, device=dev)
+    sb = DeviceStats(dev, 0)
+    uc = _same(u, wx)
+    lib = L.lib()
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.prb_bwd_workspace_bytes(L.CELL_CFC, code, B, T, d, 1), dev)
+        rc = lib.prb_bwd_cfc(_ptr(st), _ptr(wxc), _ptr(uc), _ptr(h0c), _ptr(gs),
+                              _ptr(g_wx), _ptr(g_par), _ptr(g_h0), B, T, d, code, _ptr(ws),
+                              ws.numel(), _ptr(sb.buf), _stream(dev))
+    _raise(rc, "cfc_reverse_vjp")
     _track_backward(sb)
     return g_wx, g_par[0], g_h0
 

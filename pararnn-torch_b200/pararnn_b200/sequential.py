@@ -27,7 +27,10 @@ def sequential_apply(cell: nn.Module, x: Tensor, h0: Tensor | None = None, *, st
     if time < 1:
         raise ValueError(f"sequential_apply needs time >= 1, got {time}")
     h = h0 if h0 is not None else zero_state(cell, batch, x)
-    wx_all = cell.W_x(x) if step is None and hasattr(cell, "W_x") else None
+    wx_all = None
+    if step is None and hasattr(cell, "W_x"):
+        project = getattr(cell, "project_wx", None)  # reference solvers/sequential.py:70
+        wx_all = project(x) if callable(project) else cell.W_x(x)
     if step is None and time == 1 and wx_all is not None and not torch.is_grad_enabled():
         # T = 1 without a graph: the one-launch decode kernel (reference solvers/sequential.py:77-81)
         from .decode import can_decode_step, decode_step

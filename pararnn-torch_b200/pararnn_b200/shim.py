@@ -32,6 +32,8 @@ def _kind(cell) -> str | None:
         return "nlru"
     if name == "ParaTitans":
         return "titans"
+    if name == "ParaCfC" and getattr(cell, "gate_mix", "input") == "input":
+        return "cfc"
     if name == "ParaLSTM":
         return "lstm"
     if name == "ParaSLSTM" and mix == "diag":
@@ -52,7 +54,7 @@ def install():
     newton_mod = importlib.import_module("pararnn.solvers.newton")
     ref_fused, ref_eq26 = fn_mod.fused_newton, newton_mod._eq26_vjp
     from . import head_ops, ops
-    from .newton import _backward
+    from .newton import _backward, input_affine
 
     def fused_newton(cell, wx, *, max_iters, omega, h0, log_coords=False, picard_iters=0, scan_tile="assoc",
                      fused_time_loop=False, fused_window_len=None, cu_seqlens=None, block_table=None,
@@ -72,6 +74,9 @@ def install():
         if kind == "nlru":
             return ops.newton_nlru_fused(wx, cell.clipped_u(), h0, cu_seqlens, block_table, max_iters=max_iters,
                                          omega=omega, want_residual=False)
+        if kind == "cfc":
+            return ops.newton_cfc_fused(wx, cell.clipped_u(), h0, cu_seqlens, block_table, max_iters=max_iters,
+                                        omega=omega, want_residual=False)
         if kind == "lstm":
             return ops.newton_lstm_fused(wx, *cell.clipped_recurrent(), h0, cu_seqlens, block_table,
                                          max_iters=max_iters, omega=omega, want_residual=False)
@@ -96,7 +101,7 @@ def install():
             return ref_eq26(cell, states, x, partial, backend=backend, jacobian=jacobian,
                             jac_structure=jac_structure, h0=h0, cu_seqlens=cu_seqlens)
         with torch.no_grad():
-            wx = cell.W_x(x)
+            wx = input_affine(cell, x)
             grad_x, g_h0, grads = _backward(cell, kind, states, x.detach(), wx, partial, h0, None, cu_seqlens)
         aligned = []
         for name, p in cell.named_parameters():

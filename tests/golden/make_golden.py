@@ -52,7 +52,8 @@ def run_case(name, cell, x, *, K, P=None, h0=None, omega=1.0, cu_seqlens=None):
             H_seq = torch.cat([sequential_apply(cell, x.detach()[:, a:b],
                                                 None if h0 is None else h0.detach()[i:i + 1])
                                for i, (a, b) in enumerate(zip(cu_seqlens[:-1], cu_seqlens[1:]))], dim=1)
-        wx = cell.W_x(x.detach())
+        project = getattr(cell, "project_wx", None)  # ParaCfC packs (f, c, dt, b)
+        wx = project(x.detach()) if callable(project) else cell.W_x(x.detach())
     out = {
         "x": _np(x), "wx": _np(wx), "W": _np(cell.W_x.weight), "b": _np(cell.W_x.bias),
         "H": _np(H), "H_seq": _np(H_seq), "G": _np(G),
@@ -97,6 +98,13 @@ def run_case(name, cell, x, *, K, P=None, h0=None, omega=1.0, cu_seqlens=None):
         out["raw_params"] = np.stack([_np(cell.u), _np(cell.r)])
         out["g_params"] = np.stack([_np(cell.u.grad), _np(cell.r.grad)])
         out["cell"] = "titans"
+    elif kind == "ParaCfC":
+        out["params"] = _np(cell.clipped_u())[None]
+        out["raw_params"] = _np(cell.u)[None]
+        out["g_params"] = _np(cell.u.grad)[None]
+        out["W_b"], out["b_b"] = _np(cell.W_b.weight), _np(cell.W_b.bias)
+        out["g_W_b"], out["g_b_b"] = _np(cell.W_b.weight.grad), _np(cell.W_b.bias.grad)
+        out["cell"] = "cfc"
     elif kind == "ParaSLSTM":
         out["params"] = _np(cell.clipped_r())
         out["raw_params"] = _np(cell.R)
@@ -122,7 +130,7 @@ def main():
     import logging
 
     logging.disable(logging.CRITICAL)
-    from pararnn import ParaGRU, ParaLSTM, ParaNLRU, ParaSLSTM, ParaTitans
+    from pararnn import ParaCfC, ParaGRU, ParaLSTM, ParaNLRU, ParaSLSTM, ParaTitans
 
     torch.set_num_threads(4)
 
@@ -220,6 +228,24 @@ def main():
     run_case("lstm_k2_h0_omega", cell_l, torch.randn(2, 35, 10), K=2, h0=0.5 * torch.randn(2, 2, 12), omega=0.9)
     run_case("lstm_packed_k3_h0", cell_l, torch.randn(1, 40, 10), K=3, h0=0.5 * torch.randn(3, 2, 12),
              cu_seqlens=[0, 9, 10, 40])
+
+    # --- ParaCfC (irregular time steps in the last input channel, gate_mix='input') ---
+    torch.manual_seed(50)
+    cell_c = ParaCfC(11, 12)
+    with torch.no_grad():
+        cell_c.u.mul_(5.0)  # some entries reach the +-0.5 clamp
+        cell_c.W_b.weight.normal_(0.0, 0.3)  # the default zero weight would leave b constant
+        cell_c.W_b.bias.fill_(-1.0)
+
+    def cfc_x(b, t):
+        x = torch.randn(b, t, 11)
+        x[..., -1] = 2.0 * torch.rand(b, t)  # time steps
+        x[:, ::7, -1] = 0.0  # below the clamp: dt = 1e-4 and no gradient to dt
+        return x
+
+    run_case("cfc_k3", cell_c, cfc_x(2, 66), K=3)
+    run_case("cfc_k2_h0_omega", cell_c, cfc_x(2, 39), K=2, h0=0.5 * torch.randn(2, 12), omega=0.9)
+    run_case("cfc_packed_k3_h0", cell_c, cfc_x(1, 38), K=3, h0=0.5 * torch.randn(3, 12), cu_seqlens=[0, 1, 14, 38])
 
 
 if __name__ == "__main__":

@@ -52,6 +52,19 @@ def linear_grads(g_wx, x, W):
     return (gy @ W.astype(np.float64)).reshape(x.shape), gy.T @ xx, gy.sum(0)
 
 
+def cfc_input_grads(g_wx, x, W, W_b):
+    """Gradients of ParaCfC's ``project_wx`` given the grads of ``(f, c, dt, b)`` (reference
+    ``solvers/vjp.py:180-211``): ``(grad_x, grad_W, grad_b, grad_W_b, grad_b_b)``."""
+    d = W_b.shape[0]
+    g = g_wx.reshape(-1, 4 * d).astype(np.float64)
+    feat = x[..., :-1].reshape(-1, x.shape[-1] - 1).astype(np.float64)
+    g_fc, g_dt, g_b = g[:, :2 * d], g[:, 2 * d:3 * d], g[:, 3 * d:]
+    grad_feat = g_fc @ W.astype(np.float64) + g_b @ W_b.astype(np.float64)
+    grad_dt = g_dt.sum(-1, keepdims=True) * (x[..., -1:].reshape(-1, 1) >= 1e-4)
+    grad_x = np.concatenate([grad_feat, grad_dt], axis=-1).reshape(x.shape)
+    return grad_x, g_fc.T @ feat, g_fc.sum(0), g_b.T @ feat, g_b.sum(0)
+
+
 def clip_mask(raw, cap):
     if cap < 0:
         return np.ones_like(raw)

@@ -5,7 +5,7 @@ import torch
 
 from oracle import oracle
 
-GATES = {"gru_diag": 3, "nlru": 2, "slstm_diag": 4, "gru_head": 3, "titans": 5, "lstm": 3}
+GATES = {"gru_diag": 3, "nlru": 2, "slstm_diag": 4, "gru_head": 3, "titans": 5, "lstm": 3, "cfc": 4}
 
 
 def bf16_round(a):
@@ -25,6 +25,13 @@ def make_problem(kind, B, T, d, seed, *, h0=False, x_scale=1.0, bias_f=0.0, rec_
         params = np.clip(rec_scale * 0.3 * rng.standard_normal((1, d)), -0.5, 0.5).astype(np.float32)
     elif kind == "lstm":
         params = np.clip(rec_scale * 0.3 * rng.standard_normal((5, d)), -0.5, 0.5).astype(np.float32)
+    elif kind == "cfc":
+        # gates (f, c, dt, b): one positive time step per (row, step) broadcast over the channels,
+        # time bias around the cell's initialisation
+        dt = rng.uniform(1e-4, 2.0, size=(B, T, 1)).astype(np.float32)
+        wx[..., 2 * d:3 * d] = dt
+        wx[..., 3 * d:] = 0.5 * wx[..., 3 * d:] - 1.0
+        params = np.clip(rec_scale * 0.3 * rng.standard_normal((1, d)), -0.5, 0.5).astype(np.float32)
     elif kind == "titans":
         wx[..., d:2 * d] -= 1.0  # softplus(theta_pre) ~ 0.3, as the cell's bias initialisation
         wx[..., 2 * d:4 * d] *= 0.5

@@ -32,13 +32,16 @@ def test_newton_apply_and_grads_match_reference(name):
         return  # far from converged: gradients of two different iterates are not comparable
     tol = 5e-4 * amp
     names = {"gru_diag": ("a_z", "a_r", "a_n"), "nlru": ("u",), "slstm_diag": ("R",),
-             "gru_head": ("A_z", "A_r", "A_n"), "titans": ("u", "r"),
+             "gru_head": ("A_z", "A_r", "A_n"), "titans": ("u", "r"), "cfc": ("u",),
              "lstm": ("a_f", "a_z", "a_o", "c_f", "c_o")}[g["cell"]]
     got = (cell.R.grad.cpu().numpy() if names == ("R",)
            else np.stack([getattr(cell, n).grad.cpu().numpy() for n in names]))
     for a, b in ((x.grad.cpu().numpy(), g["g_x"]), (cell.W_x.weight.grad.cpu().numpy(), g["g_W"]),
                  (cell.W_x.bias.grad.cpu().numpy(), g["g_b"]), (got, g["g_params"])):
         assert np.abs(a - b).max() <= tol * max(1.0, np.abs(b).max())
+    if g["cell"] == "cfc":
+        for a, b in ((cell.W_b.weight.grad.cpu().numpy(), g["g_W_b"]), (cell.W_b.bias.grad.cpu().numpy(), g["g_b_b"])):
+            assert np.abs(a - b).max() <= tol * max(1.0, np.abs(b).max())
     if h0 is not None:
         assert np.abs(h0.grad.cpu().numpy() - g["g_h0"]).max() <= tol * max(1.0, np.abs(g["g_h0"]).max())
 

@@ -1,4 +1,4 @@
-"""GPU parity of the scalar-diagonal cells (ParaGRU diag, ParaNLRU), through the C ABI.
+"""GPU parity of the scalar-diagonal cells (ParaGRU diag, ParaNLRU, ParaTitans, ParaCfC), through the C ABI.
 
 fp32 tolerance: 1e-5 max-abs on the hidden trajectory against the reference's eager path
 (golden fixtures) and against the CPU oracle on seeded inputs.  bf16 tolerance: 2e-2 relative
@@ -19,7 +19,8 @@ BF16_RTOL = 2e-2
 
 
 # the packed (cu_seqlens) fixtures have their own test file
-RECT = [n for n in golden_names("gru_diag") + golden_names("nlru") + golden_names("titans") if "packed" not in n]
+RECT = [n for n in golden_names("gru_diag") + golden_names("nlru") + golden_names("titans") + golden_names("cfc")
+        if "packed" not in n]
 
 
 def _fwd(kind, wx, params, h0, K, omega=1.0, dtype=torch.float32):
@@ -32,6 +33,9 @@ def _fwd(kind, wx, params, h0, K, omega=1.0, dtype=torch.float32):
     elif kind == "titans":
         H = ops.newton_titans_fused(dev(wx, dtype), dev(params[0], dtype), dev(params[1], dtype), dev(h0, dtype),
                                     max_iters=K, omega=omega, stats=st)
+    elif kind == "cfc":
+        H = ops.newton_cfc_fused(dev(wx, dtype), dev(params[0], dtype), dev(h0, dtype), max_iters=K,
+                                 omega=omega, stats=st)
     else:
         H = ops.newton_nlru_fused(dev(wx, dtype), dev(params[0], dtype), dev(h0, dtype), max_iters=K,
                                   omega=omega, stats=st)
@@ -53,8 +57,8 @@ def _bwd(kind, H, wx, params, G, h0, dtype=torch.float32):
                                                     dev(params[1], dtype), dev(G, dtype), dev(h0, dtype))
         gp = torch.stack([gu, gr])
     else:
-        g_wx, gu, g_h0 = ops.nlru_reverse_vjp(dev(H, dtype), dev(wx, dtype), dev(params[0], dtype),
-                                              dev(G, dtype), dev(h0, dtype))
+        fn = ops.cfc_reverse_vjp if kind == "cfc" else ops.nlru_reverse_vjp
+        g_wx, gu, g_h0 = fn(dev(H, dtype), dev(wx, dtype), dev(params[0], dtype), dev(G, dtype), dev(h0, dtype))
         gp = gu[None]
     return g_wx.float().cpu().numpy(), gp.cpu().numpy(), g_h0.cpu().numpy()
 
@@ -87,7 +91,7 @@ SHAPES = [(1, 1, 1), (2, 2, 5), (1, 63, 33), (2, 64, 32), (3, 65, 31), (2, 127, 
           (1, 1000, 96), (2, 4096, 40)]
 
 
-@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans"])
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans", "cfc"])
 @pytest.mark.parametrize("B,T,d", SHAPES)
 @pytest.mark.parametrize("K", [1, 3])
 def test_forward_seeded_vs_oracle_fp32(kind, B, T, d, K):
@@ -100,7 +104,7 @@ def test_forward_seeded_vs_oracle_fp32(kind, B, T, d, K):
     assert abs(res - want.max_residual) <= 5e-3 * want.max_residual + 2e-6
 
 
-@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans"])
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans", "cfc"])
 def test_k0_returns_guess_and_k2_matches(kind):
     wx, params, h0 = make_problem(kind, 2, 200, 48, seed=5, h0=True)
     g0 = oracle.guess(oracle.KIND[kind], wx, params, h0)
@@ -112,7 +116,7 @@ def test_k0_returns_guess_and_k2_matches(kind):
     assert np.abs(H2 - want.states).max() <= FP32_ATOL * max(1.0, max(want.history))
 
 
-@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans"])
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans", "cfc"])
 @pytest.mark.parametrize("B,T,d", [(1, 1, 3), (2, 65, 31), (2, 513, 70), (1, 3000, 64)])
 def test_backward_seeded_vs_oracle_fp32(kind, B, T, d):
     wx, params, h0 = make_problem(kind, B, T, d, seed=T + d, h0=(T % 2 == 1))
@@ -125,7 +129,7 @@ def test_backward_seeded_vs_oracle_fp32(kind, B, T, d):
     assert rel_err(g_h0, want_h0) <= 2e-5
 
 
-@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans"])
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans", "cfc"])
 def test_bf16_io_within_relative_tolerance(kind):
     wx, params, h0 = make_problem(kind, 2, 2048, 96, seed=9, h0=True)
     wx, params, h0 = bf16_round(wx), bf16_round(params), bf16_round(h0)

@@ -21,7 +21,7 @@ def _force_pipelined_kernels(prb_options):
 PIPE_SHAPES = [(1, 1, 32), (2, 63, 64), (1, 64, 40), (3, 65, 96), (2, 128, 36), (1, 1000, 64), (4, 4097, 72)]
 
 
-@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans"])
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans", "cfc"])
 @pytest.mark.parametrize("B,T,d", PIPE_SHAPES)
 @pytest.mark.parametrize("K", [1, 2, 4])
 def test_pipe_forward_vs_oracle_fp32(kind, B, T, d, K):
@@ -34,7 +34,7 @@ def test_pipe_forward_vs_oracle_fp32(kind, B, T, d, K):
     assert abs(res - want.max_residual) <= 5e-3 * want.max_residual + 2e-6
 
 
-@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans"])
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans", "cfc"])
 @pytest.mark.parametrize("B,T,d", PIPE_SHAPES)
 def test_pipe_backward_vs_oracle_fp32(kind, B, T, d):
     wx, params, h0 = make_problem(kind, B, T, d, seed=B + T + d, h0=(T % 2 == 0))
@@ -48,7 +48,7 @@ def test_pipe_backward_vs_oracle_fp32(kind, B, T, d):
         assert rel_err(got[2], want[2]) <= 2e-5
 
 
-@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans"])
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans", "cfc"])
 def test_pipe_bf16_matches_lookback_family(kind, prb_options):
     """Two independent implementations on the same bf16 problem."""
     wx, params, h0 = make_problem(kind, 2, 777, 64, seed=9, h0=True)

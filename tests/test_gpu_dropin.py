@@ -56,12 +56,18 @@ def _cells(p):
                 torch.nn.init.orthogonal_(A[hd], gain=0.9)
     c1 = p.ParaGRU(64, 64)
     torch.nn.init.xavier_uniform_(c1.W_x.weight)
-    return {"gru_diag": (gru, (2, 200, 24), 3, None), "nlru": (nlru, (2, 300, 24), 3, None),
+    titans, lstm, cfc = p.ParaTitans(24, 32), p.ParaLSTM(24, 32), p.ParaCfC(24, 32)
+    with torch.no_grad():
+        cfc.W_b.weight.normal_(0.0, 0.3)
+    return {"titans": (titans, (2, 180, 24), 3, None), "lstm": (lstm, (2, 160, 24), 3, None),
+            "cfc": (cfc, (2, 170, 24), 3, None),
+            "gru_diag": (gru, (2, 200, 24), 3, None), "nlru": (nlru, (2, 300, 24), 3, None),
             "slstm_diag": (slstm, (2, 150, 24), 3, 3), "gru_head": (head, (2, 100, 32), 3, None),
             "c1_gru_diag_B2_T1024_d64": (c1, (2, 1024, 64), 3, None)}
 
 
-@pytest.mark.parametrize("name", ["gru_diag", "nlru", "slstm_diag", "gru_head", "c1_gru_diag_B2_T1024_d64"])
+@pytest.mark.parametrize("name", ["gru_diag", "nlru", "slstm_diag", "gru_head", "titans", "lstm", "cfc",
+                                  "c1_gru_diag_B2_T1024_d64"])
 @pytest.mark.parametrize("with_h0", [False, True])
 def test_reference_newton_apply_through_this_backend(ref, name, with_h0):
     p = ref
@@ -69,7 +75,10 @@ def test_reference_newton_apply_through_this_backend(ref, name, with_h0):
     cell = cell.cuda()
     torch.manual_seed(1)
     x0 = torch.randn(*shape, device="cuda") * (0.6 if name == "slstm_diag" else 1.0)
-    state_shape = (shape[0], 4, cell.d_h) if name == "slstm_diag" else (shape[0], cell.d_h)
+    if name == "cfc":
+        x0[..., -1] = 2.0 * torch.rand(shape[:2], device="cuda")  # the last channel is the time step
+    slots = {"slstm_diag": 4, "lstm": 2}.get(name)
+    state_shape = (shape[0], cell.d_h) if slots is None else (shape[0], slots, cell.d_h)
     h00 = None
     if with_h0:
         h00 = 0.3 * torch.randn(*state_shape, device="cuda")

@@ -28,6 +28,8 @@ def _fwd(kind, wx, params, h0, cs, K, P=0, eps=1e-6):
         H = ops.newton_nlru_fused(dev(wx), dev(params[0]), dev(h0), csd, max_iters=K, stats=st)
     elif kind == "titans":
         H = ops.newton_titans_fused(dev(wx), dev(params[0]), dev(params[1]), dev(h0), csd, max_iters=K, stats=st)
+    elif kind == "cfc":
+        H = ops.newton_cfc_fused(dev(wx), dev(params[0]), dev(h0), csd, max_iters=K, stats=st)
     elif kind == "lstm":
         H = ops.newton_lstm_fused(dev(wx), *[dev(p) for p in params], dev(h0), csd, max_iters=K, stats=st)
     else:
@@ -39,7 +41,7 @@ def _fwd(kind, wx, params, h0, cs, K, P=0, eps=1e-6):
 
 
 def test_fixtures_present():
-    assert len(PACKED) == 5
+    assert len(PACKED) == 6
 
 
 @pytest.mark.parametrize("name", PACKED)
@@ -53,7 +55,8 @@ def test_packed_forward_matches_reference_golden(name):
     assert abs(res - float(g["max_residual"])) <= 1e-2 * float(g["max_residual"]) + 4e-6 * scale * amp
 
 
-@pytest.mark.parametrize("kind,P", [("gru_diag", 0), ("nlru", 0), ("titans", 0), ("lstm", 0), ("slstm_diag", 2)])
+@pytest.mark.parametrize("kind,P", [("gru_diag", 0), ("nlru", 0), ("titans", 0), ("cfc", 0), ("lstm", 0),
+                                    ("slstm_diag", 2)])
 @pytest.mark.parametrize("cs", [[0, 1, 2, 3], [0, 300, 301, 1000], [0, 64, 128, 129, 700]])
 def test_packed_matches_oracle_forward_and_backward(kind, P, cs):
     d, K = 40, 2
@@ -68,10 +71,15 @@ def test_packed_matches_oracle_forward_and_backward(kind, P, cs):
     np.testing.assert_allclose(hist, np.asarray(want.history), rtol=2e-2, atol=4e-6 * scale)
     # backward through newton_apply: grads of a packed call = grads of the per-sequence calls
     torch.manual_seed(3)
-    cls = {"gru_diag": prb.ParaGRU, "nlru": prb.ParaNLRU, "titans": prb.ParaTitans, "lstm": prb.ParaLSTM,
+    cls = {"gru_diag": prb.ParaGRU, "nlru": prb.ParaNLRU, "titans": prb.ParaTitans, "cfc": prb.ParaCfC,
+           "lstm": prb.ParaLSTM,
            "slstm_diag": prb.ParaSLSTM}[kind]
     cell = cls(24, d).cuda()
-    x = torch.randn(1, N, 24, device="cuda", requires_grad=True)
+    x = torch.randn(1, N, 24, device="cuda")
+    if kind == "cfc":
+        x[..., -1] = 2.0 * torch.rand(1, N, device="cuda")  # time steps; a few below the clamp
+        x[:, ::5, -1] = 0.0
+    x.requires_grad_(True)
     h0t = dev(h0).requires_grad_(True)
     cfg = prb.NewtonConfig(max_iters=3, picard_iters=P if kind == "slstm_diag" else None, picard_adapt=False)
     G = torch.randn(1, N, *({"slstm_diag": (4, d), "lstm": (2, d)}.get(kind, (d,))), device="cuda")

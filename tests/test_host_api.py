@@ -28,6 +28,13 @@ def _cell_from_golden(g):
     elif g["cell"] == "lstm":
         cell = prb.ParaLSTM(d_in, d)
         names = ("a_f", "a_z", "a_o", "c_f", "c_o")
+    elif g["cell"] == "cfc":
+        d_in += 1  # the last input channel is the time step, not a feature of W_x
+        cell = prb.ParaCfC(d_in, d)
+        names = ("u",)
+        with torch.no_grad():
+            cell.W_b.weight.copy_(torch.from_numpy(g["W_b"]))
+            cell.W_b.bias.copy_(torch.from_numpy(g["b_b"]))
     else:
         cell = prb.ParaSLSTM(d_in, d, eps=g["eps"])
         names = ("R",)
@@ -60,6 +67,8 @@ def test_parameter_order_is_the_autograd_contract():
         "A_z", "A_r", "A_n", "W_x.weight", "W_x.bias"]
     assert [n for n, _ in prb.ParaNLRU(4, 8).named_parameters()] == ["u", "W_x.weight", "W_x.bias"]
     assert [n for n, _ in prb.ParaSLSTM(4, 8).named_parameters()] == ["R", "W_x.weight", "W_x.bias"]
+    assert [n for n, _ in prb.ParaCfC(4, 8).named_parameters()] == ["u", "W_x.weight", "W_x.bias", "W_b.weight",
+                                                                    "W_b.bias"]
 
 
 def test_config_validation_errors():

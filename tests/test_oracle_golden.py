@@ -3,14 +3,14 @@
 import numpy as np
 import pytest
 
-from golden_util import clip_mask, golden_names, linear_grads, load_golden, oracle_calls
+from golden_util import cfc_input_grads, clip_mask, golden_names, linear_grads, load_golden, oracle_calls
 from oracle import oracle
 
 NAMES = golden_names()
 
 
 def test_fixtures_present():
-    assert len(NAMES) >= 20
+    assert len(NAMES) >= 23
 
 
 @pytest.mark.parametrize("name", NAMES)
@@ -45,8 +45,13 @@ def test_backward_matches_reference_autograd(name):
     kind = oracle.KIND[g["cell"]]
     g_wx, g_params, g_h0 = oracle_calls(g)[2](kind, g["H"], g["wx"], g["params"], g["G"], g["h0"],
                                               n_heads=g["n_heads"], eps=g["eps"])
-    gx, gW, gb = linear_grads(g_wx, g["x"], g["W"])
-    for got, want in ((gx, g["g_x"]), (gW, g["g_W"]), (gb, g["g_b"])):
+    if g["cell"] == "cfc":
+        gx, gW, gb, gWb, gbb = cfc_input_grads(g_wx, g["x"], g["W"], g["W_b"])
+        pairs = ((gx, g["g_x"]), (gW, g["g_W"]), (gb, g["g_b"]), (gWb, g["g_W_b"]), (gbb, g["g_b_b"]))
+    else:
+        gx, gW, gb = linear_grads(g_wx, g["x"], g["W"])
+        pairs = ((gx, g["g_x"]), (gW, g["g_W"]), (gb, g["g_b"]))
+    for got, want in pairs:
         tol = 2e-5 * max(1.0, float(np.abs(want).max()))
         assert np.abs(got - want).max() <= tol
     gp = g_params.reshape(g["raw_params"].shape) * clip_mask(g["raw_params"], float(g["cap"]))
