@@ -204,6 +204,18 @@ int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void*
                   int d, int dtype, float eps, void* workspace, size_t workspace_bytes,
                   prb_stats* stats, prb_stream_t stream);
 
+/* prb_bwd_slstm for a layer: the same reverse scan and VJP with two things a layer around the op
+ * otherwise does in separate passes over (B,T,4d) arrays.  grad_slot in 0..3: `grad` is (B,T,d), the
+ * cotangent of that state slot alone (a layer that outputs the hidden slot h = 3 receives exactly
+ * this; the reference materialises the zero-filled (B,T,4,d) array, layers/para_rnn.py:279-283 through
+ * select_backward); grad_slot = -1: `grad` is (B,T,4,d) as in prb_bwd_slstm.  g_bias fp32 (4,d) or
+ * NULL: the per-gate sums of g_wx over batch and time, i.e. the gradient of the bias of W_x
+ * (solvers/vjp.py:109-120 computes it as g_wx.sum over (B,T)). */
+int prb_bwd_slstm_ex(const void* states, const void* wx, const void* r, const void* h0,
+                     const void* grad, int grad_slot, void* g_wx, float* g_params, float* g_bias,
+                     float* g_h0, int B, int T, int d, int dtype, float eps, void* workspace,
+                     size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
+
 /* ---- residual gate ------------------------------------------------------------------- */
 
 /* max|f(H_{t-1},x_t) - H_t| into stats->final_bits.  Replaces the eager

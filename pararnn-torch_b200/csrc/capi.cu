@@ -446,7 +446,7 @@ SlstmBwdPlan plan_slstm_bwd(void* ws, int B, int T, int d) {
     p.chain = plan_chain(b, B, T, d, slstm_tile_steps(), 20);
     p.r = b.take<float>((size_t)4 * d);
     p.h0 = b.take<float>((size_t)B * 4 * d);
-    p.partial = b.take<float>((size_t)B * p.chain.max_tt * 4 * d);
+    p.partial = b.take<float>((size_t)B * p.chain.max_tt * 8 * d);  // grad R rows, then bias rows
     p.total = b.off + 256;
     return p;
 }
@@ -790,13 +790,13 @@ int prb_bwd_nlru(const void* states, const void* wx, const void* u, const void* 
                         dtype, workspace, workspace_bytes, stats, (cudaStream_t)stream);
 }
 
-int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void* h0,
-                  const void* grad_states, void* g_wx, float* g_params, float* g_h0, int B, int T,
-                  int d, int dtype, float eps, void* workspace, size_t workspace_bytes,
-                  prb_stats* stats, prb_stream_t stream) {
+int prb_bwd_slstm_ex(const void* states, const void* wx, const void* r, const void* h0,
+                     const void* grad, int grad_slot, void* g_wx, float* g_params, float* g_bias,
+                     float* g_h0, int B, int T, int d, int dtype, float eps, void* workspace,
+                     size_t workspace_bytes, prb_stats* stats, prb_stream_t stream) {
     cudaStream_t s = (cudaStream_t)stream;
-    if (!states || !wx || !r || !grad_states || !g_wx || !g_params || !stats || B < 1 || T < 1 ||
-        d < 1 || bad_dtype(dtype))
+    if (!states || !wx || !r || !grad || !g_wx || !g_params || !stats || B < 1 || T < 1 || d < 1 ||
+        bad_dtype(dtype) || grad_slot < -1 || grad_slot > 3)
         return PRB_ERR_BAD_ARG;
     SlstmBwdPlan p = plan_slstm_bwd(nullptr, B, T, d);
     if (int e = check_ws(workspace, workspace_bytes, p.total)) return e;
@@ -813,12 +813,14 @@ int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void*
     SlstmBwdArgs a{};
     a.wx = wx;
     a.states = states;
-    a.grad_states = grad_states;
+    a.grad_states = grad;
+    a.g_slot = grad_slot;
     a.r = p.r;
     a.halo = h0f;
     a.halo_stride = 4 * d;
     a.g_wx = g_wx;
     a.gp_partial = p.partial;
+    a.gb_partial = g_bias ? p.partial + (size_t)B * p.chain.max_tt * 4 * d : nullptr;
     a.g_h0 = g_h0;
     a.B = B;
     a.T = T;
@@ -834,7 +836,17 @@ int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void*
     if (e != cudaSuccess) return PRB_ERR_LAUNCH;
     if (launch_reduce_partials(p.partial, rows, 4 * d, g_params, s) != cudaSuccess)
         return PRB_ERR_LAUNCH;
+    if (g_bias && launch_reduce_partials(a.gb_partial, rows, 4 * d, g_bias, s) != cudaSuccess)
+        return PRB_ERR_LAUNCH;
     return PRB_OK;
+}
+
+int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void* h0,
+                  const void* grad_states, void* g_wx, float* g_params, float* g_h0, int B, int T,
+                  int d, int dtype, float eps, void* workspace, size_t workspace_bytes,
+                  prb_stats* stats, prb_stream_t stream) {
+    return prb_bwd_slstm_ex(states, wx, r, h0, grad_states, -1, g_wx, g_params, nullptr, g_h0, B, T, d, dtype,
+                            eps, workspace, workspace_bytes, stats, stream);
 }
 
 /* ---- ParaGRU mix='head' -------------------------------------------------------------- */

@@ -128,8 +128,12 @@ struct SlstmBwdArgs {
     const float* carry_in;  // (B,4,d) nu entering the last step
     void* g_wx;             // (B,T,4d)
     float* gp_partial;      // (B*n_tt,4,d)
+    float* gb_partial;      // same rows as gp_partial: per-gate sums of g_wx (bias gradient), or null
     float* g_h0;            // (B,4,d)
     float* agg_out;         // (B,20,d)
+    // -1: grad_states is (B,T,4,d).  0..3: grad_states is (B,T,d), the cotangent of that state slot
+    // alone (the other slots have none) -- what a layer that outputs the hidden slot receives.
+    int g_slot = -1;
     int halo_stride;
     int B, T, d;
     float eps;

@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(W * 32) slstm_bwd_kernel(SlstmBwdArgs a) {
     for (int q = 0; q < 4; ++q) r4[q] = __ldg(a.r + (size_t)q * d + chl);
     const TIO* wx = reinterpret_cast<const TIO*>(a.wx) + (size_t)b * a.T * 4 * d + chl;
     const TIO* sp = reinterpret_cast<const TIO*>(a.states) + (size_t)b * a.T * 4 * d + chl;
-    const TIO* gs = reinterpret_cast<const TIO*>(a.grad_states) + (size_t)b * a.T * 4 * d + chl;
+    const TIO* gs = reinterpret_cast<const TIO*>(a.grad_states) + (size_t)b * a.T * (a.g_slot < 0 ? 4 : 1) * d + chl;
 
     SlstmAct act[L];
     float g[L][4];
@@ -370,7 +370,12 @@ __global__ void __launch_bounds__(W * 32) slstm_bwd_kernel(SlstmBwdArgs a) {
                           ? (a.halo ? __ldg(a.halo + (size_t)b * a.halo_stride + (size_t)q * d + chl) : 0.f)
                           : ld_f(sp + ((size_t)(tc - 1) * 4 + q) * d);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) g[i][q] = ok ? ld_f(gs + ((size_t)tc * 4 + q) * d) : 0.f;
+        for (int q = 0; q < 4; ++q) g[i][q] = (ok && a.g_slot < 0) ? ld_f(gs + ((size_t)tc * 4 + q) * d) : 0.f;
+        if (ok && a.g_slot >= 0) {
+            const float v = ld_f(gs + (size_t)tc * d);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) g[i][q] = (q == a.g_slot) ? v : 0.f;
+        }
         SlstmLin lin;
         slstm_linearize(prev, w, r4, a.eps, lin);
         // activations needed by the VJP in the apply phase
@@ -430,7 +435,7 @@ __global__ void __launch_bounds__(W * 32) slstm_bwd_kernel(SlstmBwdArgs a) {
     tile_exchange<Affine4, W>(a.chain, chain, tt, mp, boundary, carry, smem, tile_end);
 
     float nc = carry[0], nn = carry[1], nm = carry[2], nh = carry[3];
-    float gr[4] = {0.f, 0.f, 0.f, 0.f};
+    float gr[4] = {0.f, 0.f, 0.f, 0.f}, gb[4] = {0.f, 0.f, 0.f, 0.f};
     TIO* gwx = reinterpret_cast<TIO*>(a.g_wx) + (size_t)b * a.T * 4 * d + ch;
 #pragma unroll
     for (int i = 0; i < L; ++i) {
@@ -462,6 +467,10 @@ __global__ void __launch_bounds__(W * 32) slstm_bwd_kernel(SlstmBwdArgs a) {
             gr[1] = fmaf(d_zf, s.hp, gr[1]);
             gr[2] = fmaf(d_zz, s.hp, gr[2]);
             gr[3] = fmaf(d_zo, s.hp, gr[3]);
+            gb[0] += d_zi;
+            gb[1] += d_zf;
+            gb[2] += d_zz;
+            gb[3] += d_zo;
             nc = d_cn * s.f;
             nn = d_nn * s.f;
             nm = d_zf;
@@ -484,6 +493,21 @@ __global__ void __launch_bounds__(W * 32) slstm_bwd_kernel(SlstmBwdArgs a) {
 #pragma unroll
             for (int w2 = 0; w2 < W; ++w2) s += s_gp[(w2 * 4 + p) * kLanes + lane];
             a.gp_partial[(((size_t)b * a.chain.n_tt + tile_t) * 4 + p) * d + ch] = s;
+        }
+    }
+    if (a.gb_partial) {  // same fixed-order reduction for the bias terms
+        __syncthreads();
+#pragma unroll
+        for (int p = 0; p < 4; ++p) s_gp[(warp * 4 + p) * kLanes + lane] = gb[p];
+        __syncthreads();
+        if (warp == 0 && ch_ok) {
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                float s = 0.f;
+#pragma unroll
+                for (int w2 = 0; w2 < W; ++w2) s += s_gp[(w2 * 4 + p) * kLanes + lane];
+                a.gb_partial[(((size_t)b * a.chain.n_tt + tile_t) * 4 + p) * d + ch] = s;
+            }
         }
     }
 }

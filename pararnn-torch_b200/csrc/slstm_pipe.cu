@@ -243,12 +243,14 @@ slstm_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx,
 }
 
 // ------------------------------------------------------------------ backward
-template <typename TIO, int L, int W, int NSTAGE>
+// HID: the cotangent arrives for one state slot only, as a (B,T,d) array
+template <typename TIO, int L, int W, int NSTAGE, bool HID = false>
 struct PipeBwdSmem {
     static constexpr int LT = W * L;
     static constexpr int WX_BYTES = LT * 4 * kLanes * (int)sizeof(TIO);
     static constexpr int ST_BYTES = ((LT + 1) * 4 * kLanes * (int)sizeof(TIO) + 127) / 128 * 128;
-    static constexpr int G_BYTES = WX_BYTES;
+    static constexpr int G_BYTES = HID ? (LT * kLanes * (int)sizeof(TIO) + 127) / 128 * 128 : WX_BYTES;
+    static constexpr int G_TX = HID ? LT * kLanes * (int)sizeof(TIO) : WX_BYTES;
     static constexpr int STAGE = WX_BYTES + ST_BYTES + G_BYTES;
     static constexpr int SLOT_OFF = NSTAGE * STAGE;
     static constexpr int SLOT_BYTES = (W + 1) * 4 * kLanes * 4;  // W carry slots + reduction scratch
@@ -260,11 +262,11 @@ struct PipeBwdSmem {
 // baton (nu, the adjoint propagated from later steps) moves towards lower steps.
 // nu_{t-1} = J_t^T (nu_t + g_t) is evaluated through the packed-VJP quantities:
 // (d_cn f, d_nn f, d_zf, sum_g r_g d_zg).
-template <typename TIO, int L, int W, int NSTAGE>
+template <typename TIO, int L, int W, int NSTAGE, bool HID, bool BIAS>
 __global__ void __launch_bounds__(W * 32, 2)
 slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_st,
                       const __grid_constant__ CUtensorMap tm_g, SlstmBwdArgs a) {
-    using S = PipeBwdSmem<TIO, L, W, NSTAGE>;
+    using S = PipeBwdSmem<TIO, L, W, NSTAGE, HID>;
     constexpr int LT = S::LT;
     extern __shared__ __align__(128) unsigned char smem[];
     float* s_slot = reinterpret_cast<float*>(smem + S::SLOT_OFF);
@@ -302,7 +304,7 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
     }
     __syncthreads();
     bool timed_out = false;
-    float gr[4] = {0.f, 0.f, 0.f, 0.f};
+    float gr[4] = {0.f, 0.f, 0.f, 0.f}, gb[4] = {0.f, 0.f, 0.f, 0.f};
 
     // No dedicated producer warp: lane 0 of warp 0 keeps the TMA ring full.  At the start of round r
     // it refills the stage of round r-1, which every warp has copied to registers by then.
@@ -310,7 +312,7 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
         const int s = r % NSTAGE;
         const int tile_t = n_rounds - 1 - r;
         unsigned char* base = smem + s * S::STAGE;
-        mbar_expect_tx(&full[s], S::WX_BYTES + (LT + 1) * 4 * kLanes * (int)sizeof(TIO) + S::G_BYTES);
+        mbar_expect_tx(&full[s], S::WX_BYTES + (LT + 1) * 4 * kLanes * (int)sizeof(TIO) + S::G_TX);
         tma_load_3d(base, &tm_wx, &full[s], cb * kLanes, 0, row0 + tile_t * LT);
         tma_load_3d(base + S::WX_BYTES, &tm_st, &full[s], cb * kLanes, 0, row0 + tile_t * LT - 1);
         tma_load_3d(base + S::WX_BYTES + S::ST_BYTES, &tm_g, &full[s], cb * kLanes, 0, row0 + tile_t * LT);
@@ -364,8 +366,14 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
     #pragma unroll
                         for (int q = 0; q < 4; ++q) prev[q] = (float)t_st[(row * 4 + q) * kLanes + lane];
                     }
+                    if (HID) {
+                        const float v = (float)t_g[row * kLanes + lane];
     #pragma unroll
-                    for (int q = 0; q < 4; ++q) g[i][q] = (float)t_g[(row * 4 + q) * kLanes + lane];
+                        for (int q = 0; q < 4; ++q) g[i][q] = (q == a.g_slot) ? v : 0.f;
+                    } else {
+    #pragma unroll
+                        for (int q = 0; q < 4; ++q) g[i][q] = (float)t_g[(row * 4 + q) * kLanes + lane];
+                    }
                     slstm_acts(prev, w, r4, a.eps, act[i]);
                 }
                 __syncwarp();
@@ -421,7 +429,10 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
                             st_f(o + 3 * (size_t)d, dz[i][3]);
                         }
     #pragma unroll
-                        for (int q = 0; q < 4; ++q) gr[q] = fmaf(dz[i][q], act[i].hp, gr[q]);
+                        for (int q = 0; q < 4; ++q) {
+                            gr[q] = fmaf(dz[i][q], act[i].hp, gr[q]);
+                            if (BIAS) gb[q] += dz[i][q];
+                        }
                     }
                 }
                 if (r == n_rounds - 1 && warp == W - 1 && a.g_h0 && ch_ok && sg.lo == 0) {
@@ -449,6 +460,21 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
 #pragma unroll
             for (int w2 = 0; w2 < W; ++w2) sum += s_gp[(w2 * 4 + p) * kLanes + lane];
             a.gp_partial[(((size_t)sg.seg * a.B + b) * 4 + p) * d + ch] = sum;
+        }
+    }
+    if (BIAS) {  // per-gate sums of g_wx (bias gradient), same fixed-order reduction
+        __syncthreads();
+#pragma unroll
+        for (int p = 0; p < 4; ++p) s_gp[(warp * 4 + p) * kLanes + lane] = gb[p];
+        __syncthreads();
+        if (warp == 0 && ch_ok) {
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                float sum = 0.f;
+#pragma unroll
+                for (int w2 = 0; w2 < W; ++w2) sum += s_gp[(w2 * 4 + p) * kLanes + lane];
+                a.gb_partial[(((size_t)sg.seg * a.B + b) * 4 + p) * d + ch] = sum;
+            }
         }
     }
 }
@@ -673,17 +699,29 @@ static cudaError_t launch_newton_pipe_t(const SlstmNewtonArgs& a, bool last, cud
 
 template <typename TIO, int NSTAGE>
 static cudaError_t launch_bwd_pipe_t(const SlstmBwdArgs& a, cudaStream_t s) {
-    using S = PipeBwdSmem<TIO, kQL, kQW, NSTAGE>;
+    using S = PipeBwdSmem<TIO, kQL, kQW, NSTAGE, false>;
+    using SH = PipeBwdSmem<TIO, kQL, kQW, NSTAGE, true>;
     CUtensorMap tm_wx, tm_st, tm_g;
     const uint64_t rows = (uint64_t)a.B * a.T;
+    const bool hid = a.g_slot >= 0;
     if (!make_tile_map(&tm_wx, a.wx, sizeof(TIO), rows, 4, a.d, S::LT) ||
         !make_tile_map(&tm_st, a.states, sizeof(TIO), rows, 4, a.d, S::LT + 1) ||
-        !make_tile_map(&tm_g, a.grad_states, sizeof(TIO), rows, 4, a.d, S::LT))
+        !make_tile_map(&tm_g, a.grad_states, sizeof(TIO), rows, hid ? 1 : 4, a.d, S::LT))
         return cudaErrorNotSupported;
     const dim3 grid(a.B * ((a.d + kLanes - 1) / kLanes), a.n_seg > 1 ? a.n_seg : 1);
-    auto k = slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE>;
-    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    k<<<grid, kQW * 32, S::TOTAL, s>>>(tm_wx, tm_st, tm_g, a);
+    auto go = [&](auto k, int smem) {
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        k<<<grid, kQW * 32, smem, s>>>(tm_wx, tm_st, tm_g, a);
+    };
+    const bool bias = a.gb_partial != nullptr;
+    if (hid && bias)
+        go(slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE, true, true>, SH::TOTAL);
+    else if (hid)
+        go(slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE, true, false>, SH::TOTAL);
+    else if (bias)
+        go(slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE, false, true>, S::TOTAL);
+    else
+        go(slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE, false, false>, S::TOTAL);
     return cudaGetLastError();
 }
 

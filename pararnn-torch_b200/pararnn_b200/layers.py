@@ -39,14 +39,17 @@ class ParaRNN(nn.Module):
         out = x
         for i, cell in enumerate(self.cells):
             h0_i = h0 if (h0 is not None and i == 0) else None
+            slot = getattr(cell, "hidden_slot", None)
+            hidden = slot is not None and (self.output_hidden or i + 1 < len(self.cells))
             if self.training:
                 stats = NewtonStats()
-                states = newton_apply(cell, out, self.config, h0=h0_i, stats=stats)
+                # the hidden slot straight from the solve: its backward takes the (B,T,d) cotangent
+                out = newton_apply(cell, out, self.config, h0=h0_i, stats=stats,
+                                   output_slot=slot if hidden else None)
                 self.last_stats = stats
             else:
                 states = sequential_apply(cell, out, h0_i)
-            slot = getattr(cell, "hidden_slot", None)
-            out = states[:, :, slot] if (slot is not None and (self.output_hidden or i + 1 < len(self.cells))) else states
+                out = states[:, :, slot] if hidden else states
         if not self.batch_first:
             out = out.transpose(0, 1)
         return out

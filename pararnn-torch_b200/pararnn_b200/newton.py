@@ -245,7 +245,10 @@ def _clip_mask(raw: Tensor, cap) -> Tensor | None:
     return None if cap is None else (raw.abs() <= cap)
 
 
-def _reverse_window(cell, kind, states, wx, grad_states, h0):
+_BIAS = "__bias__"  # key of the kernel-side sum of g_wx in the dict `_reverse_window` returns
+
+
+def _reverse_window(cell, kind, states, wx, grad_states, h0, grad_slot=None):
     rec = _recurrent_params(cell, kind)
     if kind == "gru_diag":
         g_wx, gz, gr, gn, g_h0 = ops.gru_reverse_vjp(states, wx, *rec, grad_states, h0)
@@ -263,16 +266,23 @@ def _reverse_window(cell, kind, states, wx, grad_states, h0):
         g_wx, gu, gr, g_h0 = ops.titans_reverse_vjp(states, wx, rec[0], rec[1], grad_states, h0)
         return g_wx, {"u": gu, "r": gr}, g_h0
     if kind == "slstm_diag":
-        g_wx, gr, g_h0 = ops.slstm_reverse_vjp(states, wx, rec[0], grad_states, h0, float(cell.eps))
-        return g_wx, {"R": gr}, g_h0
+        g_wx, gr, g_h0, g_bias = ops.slstm_reverse_vjp(states, wx, rec[0], grad_states, h0, float(cell.eps),
+                                                       grad_slot=grad_slot, want_bias=True)
+        return g_wx, {"R": gr, _BIAS: g_bias}, g_h0
     from . import head_ops
 
     g_wx, gz, gr, gn, g_h0 = head_ops.gru_head_reverse_vjp(states, wx, *rec, grad_states, h0)
     return g_wx, {"A_z": gz, "A_r": gr, "A_n": gn}, g_h0
 
 
-def _backward(cell, kind, states, x, wx, grad_states, h0, chunk_len, cu_seqlens=None):
-    """``(grad_x, grad_h0, {name: grad})`` — eq. 2.6 + packed VJP + the W_x GEMMs."""
+def _backward(cell, kind, states, x, wx, grad_states, h0, chunk_len, cu_seqlens=None, grad_slot=None):
+    """``(grad_x, grad_h0, {name: grad})`` — eq. 2.6 + packed VJP + the W_x GEMMs.
+    ``grad_slot``: ``grad_states`` is the ``(B,T,d)`` cotangent of that state slot alone."""
+    if grad_slot is not None and (cu_seqlens is not None or chunk_len is not None or kind != "slstm_diag"):
+        # only the one-window sLSTM kernel takes the compact cotangent
+        full = torch.zeros_like(states)
+        full[:, :, grad_slot] = grad_states
+        grad_states, grad_slot = full, None
     if cu_seqlens is not None:
         # packed sequences: independent reverse scans, grad_h0 (S, ...) row by row
         cs = ops.validate_cu_seqlens(cu_seqlens, x.shape[1])
@@ -288,7 +298,7 @@ def _backward(cell, kind, states, x, wx, grad_states, h0, chunk_len, cu_seqlens=
                 rec_grads[k] = v if k not in rec_grads else rec_grads[k] + v
         g_h0 = torch.cat(heads, dim=0)
     elif chunk_len is None:
-        g_wx, rec_grads, g_h0 = _reverse_window(cell, kind, states, wx, grad_states, h0)
+        g_wx, rec_grads, g_h0 = _reverse_window(cell, kind, states, wx, grad_states, h0, grad_slot)
     else:
         # same windows as the forward, walked backwards; grad_h0 of window i+1 is added to
         # the cotangent of the last step of window i (reference _eq26_vjp_chunked)
@@ -310,6 +320,7 @@ def _backward(cell, kind, states, x, wx, grad_states, h0, chunk_len, cu_seqlens=
     cap = getattr(cell, "max_recurrent_norm", None)
     named = dict(cell.named_parameters())
     grads = {}
+    bias_sum = rec_grads.pop(_BIAS, None)
     for name, g in rec_grads.items():
         raw = named[name]
         g = g.reshape(raw.shape)
@@ -327,7 +338,8 @@ def _backward(cell, kind, states, x, wx, grad_states, h0, chunk_len, cu_seqlens=
     grad_x = (gy @ lin.weight.detach().to(gy.dtype)).reshape(x.shape)
     grads["W_x.weight"] = (gy.t() @ xx.to(gy.dtype)).to(lin.weight.dtype)
     if lin.bias is not None:
-        grads["W_x.bias"] = gy.sum(0).to(lin.bias.dtype)
+        # the sLSTM reverse kernel accumulates the sum of g_wx itself; the other cells sum here
+        grads["W_x.bias"] = (gy.sum(0) if bias_sum is None else bias_sum).to(lin.bias.dtype)
     return grad_x, g_h0, grads
 
 
@@ -362,17 +374,19 @@ class _NewtonFixedPoint(torch.autograd.Function):
     ``(grad_x, grad_h0, *param_grads)`` in ``cell.named_parameters()`` order."""
 
     @staticmethod
-    def forward(ctx, cell, kind, cfg, stats, has_h0, cu_seqlens, x_in, h0_in, *params):
+    def forward(ctx, cell, kind, cfg, stats, has_h0, cu_seqlens, out_slot, x_in, h0_in, *params):
         del params
         h0 = h0_in if has_h0 else None
         with torch.no_grad():
             states, wx = _forward(cell, kind, x_in, cfg, h0, stats, cu_seqlens=cu_seqlens)
         ctx.cell, ctx.kind, ctx.cfg, ctx.has_h0, ctx.cu_seqlens = cell, kind, cfg, has_h0, cu_seqlens
+        ctx.out_slot = out_slot
         if cfg.recompute:
             ctx.save_for_backward(x_in, h0_in)
         else:
             ctx.save_for_backward(x_in, h0_in, states, wx)
-        return states
+        # one slot only: a view of the trajectory; the backward then receives its (B,T,d) cotangent
+        return states if out_slot is None else states.select(2, out_slot)
 
     @staticmethod
     def backward(ctx, grad_states):
@@ -389,7 +403,7 @@ class _NewtonFixedPoint(torch.autograd.Function):
             h0 = h0_in if ctx.has_h0 else None
         with torch.no_grad():
             grad_x, g_h0, grads = _backward(cell, kind, states, x_in.detach(), wx,
-                                            grad_states, h0, cfg.chunk_len, ctx.cu_seqlens)
+                                            grad_states, h0, cfg.chunk_len, ctx.cu_seqlens, ctx.out_slot)
         out_params = []
         for name, p in cell.named_parameters():
             g = grads.get(name)
@@ -399,12 +413,13 @@ class _NewtonFixedPoint(torch.autograd.Function):
         grad_h0 = None
         if ctx.has_h0 and h0_in.requires_grad and g_h0 is not None:
             grad_h0 = g_h0.to(h0_in.dtype)
-        return (None, None, None, None, None, None, grad_x, grad_h0, *out_params)
+        return (None, None, None, None, None, None, None, grad_x, grad_h0, *out_params)
 
 
 def newton_apply(cell: nn.Module, x: Tensor, config: NewtonConfig | None = None, *,
                  h0: Tensor | None = None, stats: NewtonStats | None = None,
-                 cu_seqlens: Tensor | None = None, block_table: Tensor | None = None) -> Tensor:
+                 cu_seqlens: Tensor | None = None, block_table: Tensor | None = None,
+                 output_slot: int | None = None) -> Tensor:
     """Solve ``F(H) = 0`` for the whole trajectory with Newton + chained scans on the GPU.
 
     Same call signature and return layout as the reference's ``newton_apply``:
@@ -416,8 +431,18 @@ def newton_apply(cell: nn.Module, x: Tensor, config: NewtonConfig | None = None,
     own scan starting from ``h0[s]`` (``h0`` is ``(S, *state)``), differentiable.  ``block_table``
     ``(B,)`` or ``(S,)``: ``h0`` is a pool ``(C, *state)`` and sequence ``i`` starts from
     ``h0[block_table[i]]``; inference only, as in the reference
-    (``solvers/newton/__init__.py:286-304``)."""
+    (``solvers/newton/__init__.py:286-304``).
+
+    ``output_slot`` (not in the reference; multi-slot cells only): return ``H[:, :, output_slot]``
+    ``(B,T,d)`` instead of all slots.  Same values as slicing the full result, but the backward
+    takes the ``(B,T,d)`` cotangent as it is instead of a zero-filled ``(B,T,S,d)`` array;
+    ``ParaRNN`` uses it for the hidden slot."""
     cfg, kind = _resolve(cell, x, config or NewtonConfig())
+    if output_slot is not None:
+        slots = int(getattr(cell, "state_slots", 1))
+        if slots == 1 or not 0 <= int(output_slot) < slots:
+            raise ValueError(f"output_slot={output_slot} needs a cell with state slots, 0 <= slot < {slots}")
+        output_slot = int(output_slot)
     if cu_seqlens is not None or block_table is not None:
         if kind == "gru_head":
             raise TypeError("ParaGRU(mix='head') takes rectangular batches with a dense h0 only")
@@ -430,7 +455,8 @@ def newton_apply(cell: nn.Module, x: Tensor, config: NewtonConfig | None = None,
     if cfg.scan_backend == "context_parallel":
         from .seq_shard import newton_apply_sharded
 
-        return newton_apply_sharded(cell, kind, x, cfg, h0=h0, stats=stats)
+        H = newton_apply_sharded(cell, kind, x, cfg, h0=h0, stats=stats)
+        return H if output_slot is None else H[:, :, output_slot]
     if torch.is_autocast_enabled("cuda"):
         ctx_mgr = torch.autocast(device_type="cuda", enabled=False)
     else:
@@ -446,7 +472,8 @@ def newton_apply(cell: nn.Module, x: Tensor, config: NewtonConfig | None = None,
     with ctx_mgr:
         if not needs_grad:
             with torch.no_grad():
-                return _forward(cell, kind, x, cfg, h0, stats, cu_seqlens=cu_seqlens,
-                                block_table=block_table)[0]
+                H = _forward(cell, kind, x, cfg, h0, stats, cu_seqlens=cu_seqlens, block_table=block_table)[0]
+                return H if output_slot is None else H[:, :, output_slot]
         h0_leaf = h0 if has_h0 else x.new_zeros(())
-        return _NewtonFixedPoint.apply(cell, kind, cfg, stats, has_h0, cu_seqlens, x, h0_leaf, *params)
+        return _NewtonFixedPoint.apply(cell, kind, cfg, stats, has_h0, cu_seqlens, output_slot, x, h0_leaf,
+                                       *params)

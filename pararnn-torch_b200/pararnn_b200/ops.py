@@ -622,27 +622,41 @@ def titans_reverse_vjp(states: Tensor, wx: Tensor, u: Tensor, r: Tensor, grad_st
 
 
 def slstm_reverse_vjp(states: Tensor, wx: Tensor, r: Tensor, grad_states: Tensor,
-                      h0: Tensor | None = None, eps: float = 1e-6):
+                      h0: Tensor | None = None, eps: float = 1e-6, *, grad_slot: int | None = None,
+                      want_bias: bool = False):
     """Eq. 2.6 reverse scan (4x4 blocks, J^T) fused with the packed sLSTM VJP:
-    ``(g_wx (B,T,4d), g_r (4,d) fp32, g_h0 (B,4,d) fp32)``."""
+    ``(g_wx (B,T,4d), g_r (4,d) fp32, g_h0 (B,4,d) fp32)``.
+
+    ``grad_slot`` in 0..3: ``grad_states`` is ``(B,T,d)``, the cotangent of that state slot alone
+    (what a layer that outputs the hidden slot receives) -- the zero-filled ``(B,T,4,d)`` array is
+    never built.  ``want_bias``: a fourth result ``g_bias (4d,) fp32``, the sum of ``g_wx`` over
+    batch and time (the gradient of the bias of ``W_x``) accumulated by the same kernel."""
     dev, code, st, wxc, gs, h0c = _bwd_common(states, wx, grad_states, h0)
     B, T, d4 = wx.shape
     d = d4 // 4
-    if tuple(states.shape) != (B, T, 4, d) or tuple(grad_states.shape) != (B, T, 4, d):
-        raise ValueError("states / grad_states must be (B, T, 4, d)")
+    want_g = (B, T, 4, d) if grad_slot is None else (B, T, d)
+    if grad_slot is not None and not 0 <= int(grad_slot) <= 3:
+        raise ValueError(f"grad_slot must be in 0..3, got {grad_slot}")
+    if tuple(states.shape) != (B, T, 4, d) or tuple(grad_states.shape) != want_g:
+        raise ValueError(f"states must be (B, T, 4, d) and grad_states {want_g}, got "
+                         f"{tuple(states.shape)} / {tuple(grad_states.shape)}")
     g_wx = torch.empty_like(wxc)
     g_par = torch.empty(4, d, dtype=torch.float32, device=dev)
+    g_bias = torch.empty(4 * d, dtype=torch.float32, device=dev) if want_bias else None
     g_h0 = torch.empty(B, 4, d, dtype=torch.float32, device=dev)
     sb = DeviceStats(dev, 0)
     rc_ = _same(r, wx)
     lib = L.lib()
     with torch.cuda.device(dev):
         ws = _workspace(lib.prb_bwd_workspace_bytes(L.CELL_SLSTM_DIAG, code, B, T, d, 1), dev)
-        rc = lib.prb_bwd_slstm(_ptr(st), _ptr(wxc), _ptr(rc_), _ptr(h0c), _ptr(gs),
-                               _ptr(g_wx), _ptr(g_par), _ptr(g_h0), B, T, d, code, float(eps),
-                               _ptr(ws), ws.numel(), _ptr(sb.buf), _stream(dev))
+        rc = lib.prb_bwd_slstm_ex(_ptr(st), _ptr(wxc), _ptr(rc_), _ptr(h0c), _ptr(gs),
+                                  -1 if grad_slot is None else int(grad_slot), _ptr(g_wx), _ptr(g_par),
+                                  _ptr(g_bias), _ptr(g_h0), B, T, d, code, float(eps), _ptr(ws), ws.numel(),
+                                  _ptr(sb.buf), _stream(dev))
     _raise(rc, "slstm_reverse_vjp")
     _track_backward(sb)
+    if want_bias:
+        return g_wx, g_par, g_h0, g_bias
     return g_wx, g_par, g_h0
 
 

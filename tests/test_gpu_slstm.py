@@ -169,3 +169,81 @@ def test_divergence_is_reported_not_hidden():
     wx[0, 10, 2] = np.inf
     _, hist, res = _fwd(wx, r, None, 2, 1)
     assert not np.isfinite(res)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,T,d,h0,slot", [(1, 1, 32, False, 3), (2, 65, 40, True, 3), (2, 1000, 96, True, 0),
+                                            (1, 4099, 64, False, 3), (3, 513, 32, True, 2)])
+def test_one_slot_cotangent_and_bias_sum(B, T, d, h0, slot, dtype):
+    """grad_slot: the (B,T,d) cotangent of one state slot gives what the zero-filled (B,T,4,d)
+    array gives; want_bias: the kernel's own sum of g_wx over batch and time."""
+    from pararnn_b200 import ops
+
+    wx, r, h0a = make_problem("slstm_diag", B, T, d, seed=T + d, h0=h0, x_scale=0.7, bias_f=2.0)
+    if dtype == torch.bfloat16:
+        wx, r, h0a = bf16_round(wx), bf16_round(r), (None if h0a is None else bf16_round(h0a))
+    H = oracle.sequential(oracle.SLSTM_DIAG, wx, r, h0a)
+    g1 = np.random.default_rng(T).standard_normal((B, T, d)).astype(np.float32)
+    full = np.zeros((B, T, 4, d), np.float32)
+    full[:, :, slot] = g1
+    a = ops.slstm_reverse_vjp(dev(H, dtype), dev(wx, dtype), dev(r, dtype), dev(full, dtype), dev(h0a, dtype))
+    b = ops.slstm_reverse_vjp(dev(H, dtype), dev(wx, dtype), dev(r, dtype), dev(g1, dtype), dev(h0a, dtype),
+                              grad_slot=slot, want_bias=True)
+    for u, v in zip(a, b[:3]):
+        assert torch.equal(u, v)
+    want_bias = a[0].double().sum((0, 1))
+    tol = 2e-5 if dtype == torch.float32 else 1e-2  # bf16: g_wx is rounded on store, the kernel's sum is not
+    assert float((b[3].double() - want_bias).abs().max()) <= tol * max(1.0, float(want_bias.abs().max()))
+    with pytest.raises(ValueError):
+        ops.slstm_reverse_vjp(dev(H, dtype), dev(wx, dtype), dev(r, dtype), dev(full, dtype), dev(h0a, dtype),
+                              grad_slot=3)
+
+
+@pytest.mark.parametrize("chunk_len", [None, 128])
+def test_output_slot_equals_slicing_the_states(chunk_len):
+    import pararnn_b200 as prb
+
+    torch.manual_seed(0)
+    cell = prb.ParaSLSTM(24, 32).cuda()
+    with torch.no_grad():
+        cell.W_x.bias[32:64] = 1.0
+    x = (0.6 * torch.randn(2, 300, 24, device="cuda")).requires_grad_(True)
+    h0 = torch.zeros(2, 4, 32, device="cuda")
+    h0[:, 1] = 1.0
+    h0.requires_grad_(True)
+    cfg = prb.NewtonConfig(max_iters=3, picard_iters=3, picard_adapt=False, chunk_len=chunk_len)
+    G = torch.randn(2, 300, 32, device="cuda")
+
+    def grads(sliced):
+        for t in (x, h0):
+            t.grad = None
+        cell.zero_grad(set_to_none=True)
+        out = (prb.newton_apply(cell, x, cfg, h0=h0)[:, :, 3] if sliced
+               else prb.newton_apply(cell, x, cfg, h0=h0, output_slot=3))
+        (out * G).sum().backward()
+        return [out.detach().clone(), x.grad.clone(), h0.grad.clone()] + [p.grad.clone() for p in cell.parameters()]
+
+    a, b = grads(True), grads(False)
+    assert torch.equal(a[0], b[0])
+    names = ["out", "x", "h0"] + [n for n, _ in cell.named_parameters()]
+    for n, u, v in zip(names, a, b):
+        # W_x.bias: summed by the kernel in fp32 instead of by a reduction over the stored g_wx
+        assert float((u - v).abs().max()) <= 2e-5 * max(1.0, float(u.abs().max())), n
+    with pytest.raises(ValueError):
+        prb.newton_apply(prb.ParaGRU(8, 8).cuda(), torch.randn(1, 4, 8, device="cuda"), output_slot=0)
+    with pytest.raises(ValueError):
+        prb.newton_apply(cell, x, cfg, output_slot=4)
+
+
+def test_para_rnn_layer_outputs_the_hidden_slot_with_gradients():
+    import pararnn_b200 as prb
+
+    torch.manual_seed(1)
+    rnn = prb.ParaRNN(prb.ParaSLSTM(32, 32).cuda(), config=prb.NewtonConfig(max_iters=3), num_layers=2).train()
+    x = (0.5 * torch.randn(2, 200, 32, device="cuda")).requires_grad_(True)
+    y = rnn(x)
+    assert y.shape == (2, 200, 32)
+    y.square().sum().backward()
+    want = prb.sequential_apply(rnn.cells[1], prb.sequential_apply(rnn.cells[0], x.detach())[:, :, 3])[:, :, 3]
+    assert float((y.detach() - want).abs().max()) <= 1e-4
+    assert x.grad is not None and all(p.grad is not None for p in rnn.parameters())
