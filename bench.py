@@ -767,6 +767,9 @@ def run_gpu_sharded(args):
         parity = slice_parity(sl_wx, rec[0][:, :PARITY_CH], sl_H, sl_g, D, K_NEWTON, P_PICARD)
         parity["path"] = f"time-sharded over {world} ranks, NCCL carry exchange"
     extra = {}
+    # kernels of this library per step, summed over the ranks (rank 0 sweeps once per pass, the others twice)
+    n_launch = torch.tensor([keep.get("launches", 0)], dtype=torch.int64, device=dev)
+    dist.all_reduce(n_launch)
     if not args.no_extra:
         extra["c4_strong"] = c4_strong_record(args, rank, world, dev, dist, comm, barrier)
         extra["c5_sharded"] = c5_sharded_record(args, rank, world, dev, dist, barrier)
@@ -794,7 +797,7 @@ def run_gpu_sharded(args):
                                 "D2H of loss"},
             # kernels of this library per step on rank 0 (sweeps, folds, reductions; counted by the
             # driver object), the same whether issued from Python or replayed from the graph
-            "gpu_launches": keep.get("launches", 0) * args.steps,
+            "gpu_launches": int(n_launch.item()) * args.steps,
             "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "peak": peak * world,
                          "unit": "GB/s", "achieved": step_bytes / (ms / 1e3) / 1e9,
                          "frac": step_bytes / (ms / 1e3) / 1e9 / (peak * world), "peak_kind": peak_kind,
