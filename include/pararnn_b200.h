@@ -204,6 +204,16 @@ int prb_bwd_slstm(const void* states, const void* wx, const void* r, const void*
                   int d, int dtype, float eps, void* workspace, size_t workspace_bytes,
                   prb_stats* stats, prb_stream_t stream);
 
+/* The reverse scan + VJP of any scalar-diagonal cell (cell = PRB_CELL_GRU_DIAG, _NLRU, _TITANS, _CFC;
+ * p0..p2 = its recurrent vectors in the order of the per-cell entry points, unused ones NULL) with one
+ * more output: g_bias fp32 (G*d) or NULL = the per-gate sums of g_wx over batch and time, i.e. the
+ * gradient of the bias of the input projection (solvers/vjp.py:109-120 computes it as a separate
+ * reduction over g_wx).  Everything else as prb_bwd_gru / _nlru / _titans / _cfc. */
+int prb_bwd_diag_ex(int cell, const void* states, const void* wx, const void* p0, const void* p1,
+                    const void* p2, const void* h0, const void* grad_states, void* g_wx, float* g_params,
+                    float* g_bias, float* g_h0, int B, int T, int d, int dtype, void* workspace,
+                    size_t workspace_bytes, prb_stats* stats, prb_stream_t stream);
+
 /* prb_bwd_slstm for a layer: the same reverse scan and VJP with two things a layer around the op
  * otherwise does in separate passes over (B,T,4d) arrays.  grad_slot in 0..3: `grad` is (B,T,d), the
  * cotangent of that state slot alone (a layer that outputs the hidden slot h = 3 receives exactly

@@ -231,7 +231,8 @@ DiagBwdPlan plan_diag_bwd(void* ws, int cell, int B, int T, int d) {
     p.chain = plan_chain(b, B, T, d, diag_tile_steps(), 2);
     p.par = b.take<float>((size_t)np * d);
     p.h0 = b.take<float>((size_t)B * d);
-    p.partial = b.take<float>((size_t)B * p.chain.max_tt * np * d);
+    // parameter rows, then the per-gate bias rows
+    p.partial = b.take<float>((size_t)B * p.chain.max_tt * (np + diag_cell_gates(cell)) * d);
     p.total = b.off + 256;
     return p;
 }
@@ -239,7 +240,7 @@ DiagBwdPlan plan_diag_bwd(void* ws, int cell, int B, int T, int d) {
 int run_diag_bwd(int cell, const void* states, const void* wx, const void* const* pars,
                  const void* h0, const void* grad_states, void* g_wx, float* g_params, float* g_h0,
                  int B, int T, int d, int dtype, void* ws, size_t ws_bytes, prb_stats* stats,
-                 cudaStream_t s) {
+                 cudaStream_t s, float* g_bias = nullptr) {
     if (!states || !wx || !grad_states || !g_wx || !g_params || !stats || B < 1 || T < 1 || d < 1 ||
         bad_dtype(dtype))
         return PRB_ERR_BAD_ARG;
@@ -266,6 +267,7 @@ int run_diag_bwd(int cell, const void* states, const void* wx, const void* const
     a.halo = h0f;
     a.g_wx = g_wx;
     a.gp_partial = p.partial;
+    a.gb_partial = g_bias ? p.partial + (size_t)B * p.chain.max_tt * np * d : nullptr;
     a.g_h0 = g_h0;
     a.B = B;
     a.T = T;
@@ -280,7 +282,9 @@ int run_diag_bwd(int cell, const void* states, const void* wx, const void* const
     }
     if (e != cudaSuccess) return PRB_ERR_LAUNCH;
     // one partial row per tile (look-back) or per batch row (one CTA per chain)
-    if (launch_reduce_partials(p.partial, pipe ? B : B * a.chain.n_tt, np * d, g_params, s) != cudaSuccess)
+    const int rows = pipe ? B : B * a.chain.n_tt;
+    if (launch_reduce_partials(p.partial, rows, np * d, g_params, s) != cudaSuccess) return PRB_ERR_LAUNCH;
+    if (g_bias && launch_reduce_partials(a.gb_partial, rows, diag_cell_gates(cell) * d, g_bias, s) != cudaSuccess)
         return PRB_ERR_LAUNCH;
     return PRB_OK;
 }
@@ -643,6 +647,16 @@ int prb_bwd_cfc(const void* states, const void* wx, const void* u, const void* h
     const void* pars[3] = {u, nullptr, nullptr};
     return run_diag_bwd(kCellCfc, states, wx, pars, h0, grad_states, g_wx, g_params, g_h0, B, T, d, dtype,
                         workspace, workspace_bytes, stats, (cudaStream_t)stream);
+}
+
+int prb_bwd_diag_ex(int cell, const void* states, const void* wx, const void* p0, const void* p1,
+                    const void* p2, const void* h0, const void* grad_states, void* g_wx, float* g_params,
+                    float* g_bias, float* g_h0, int B, int T, int d, int dtype, void* workspace,
+                    size_t workspace_bytes, prb_stats* stats, prb_stream_t stream) {
+    if (!is_diag_cell(cell)) return PRB_ERR_BAD_ARG;
+    const void* pars[3] = {p0, p1, p2};
+    return run_diag_bwd(cell, states, wx, pars, h0, grad_states, g_wx, g_params, g_h0, B, T, d, dtype,
+                        workspace, workspace_bytes, stats, (cudaStream_t)stream, g_bias);
 }
 
 /* ---- ParaLSTM --------------------------------------------------------------------------- */

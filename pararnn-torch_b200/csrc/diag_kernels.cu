@@ -310,9 +310,12 @@ __global__ void __launch_bounds__(W * 32) diag_bwd_kernel(DiagBwdArgs a) {
         float boundary[1] = {a.carry_in ? __ldg(a.carry_in + (size_t)b * a.d + chl) : 0.f};
         float carry[1], tile_end[1];
         tile_exchange<Affine1, W>(a.chain, chain, tt, my_map, boundary, carry, smem, tile_end);
-        float gp_acc[NP];
+        float gp_acc[NP], gb_acc[G];
 #pragma unroll
         for (int p = 0; p < NP; ++p) gp_acc[p] = 0.f;
+#pragma unroll
+        for (int q = 0; q < G; ++q) gb_acc[q] = 0.f;
+        const bool want_bias = a.gb_partial != nullptr;
         TIO* gwx = reinterpret_cast<TIO*>(a.g_wx) + (size_t)b * a.T * G * a.d + ch;
 #pragma unroll
         for (int i = 0; i < L; ++i) {
@@ -328,6 +331,10 @@ __global__ void __launch_bounds__(W * 32) diag_bwd_kernel(DiagBwdArgs a) {
                 }
 #pragma unroll
                 for (int p = 0; p < NP; ++p) gp_acc[p] += gp[p];
+                if (want_bias) {
+#pragma unroll
+                    for (int q = 0; q < G; ++q) gb_acc[q] += gw[q];
+                }
             }
         }
         if (ch_ok && warp == 0 && tt == a.chain.n_tt - 1 && a.g_h0)
@@ -345,6 +352,20 @@ __global__ void __launch_bounds__(W * 32) diag_bwd_kernel(DiagBwdArgs a) {
 #pragma unroll
                 for (int w = 0; w < W; ++w) s += s_gp[(w * NP + p) * kLanes + lane];
                 a.gp_partial[(((size_t)b * a.chain.n_tt + tile_t) * NP + p) * a.d + ch] = s;
+            }
+        }
+        if (want_bias) {  // the same fixed-order reduction for the bias terms, one gate at a time
+#pragma unroll
+            for (int q = 0; q < G; ++q) {
+                __syncthreads();
+                s_gp[warp * kLanes + lane] = gb_acc[q];
+                __syncthreads();
+                if (warp == 0 && ch_ok) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int w = 0; w < W; ++w) s += s_gp[w * kLanes + lane];
+                    a.gb_partial[(((size_t)b * a.chain.n_tt + tile_t) * G + q) * a.d + ch] = s;
+                }
             }
         }
     }

@@ -293,9 +293,12 @@ diag_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
     }
     __syncthreads();
     bool timed_out = false;
-    float gp_acc[NP];
+    float gp_acc[NP], gb_acc[G];
 #pragma unroll
     for (int p = 0; p < NP; ++p) gp_acc[p] = 0.f;
+#pragma unroll
+    for (int q = 0; q < G; ++q) gb_acc[q] = 0.f;
+    const bool want_bias = a.gb_partial != nullptr;
 
     if (warp == W) {
         if (lane == 0) {
@@ -385,6 +388,10 @@ diag_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
                         }
     #pragma unroll
                         for (int p = 0; p < NP; ++p) gp_acc[p] += gp[p];
+                        if (want_bias) {
+    #pragma unroll
+                            for (int q = 0; q < G; ++q) gb_acc[q] += gw[q];
+                        }
                     }
                 }
                 if (r == n_rounds - 1 && warp == 0 && ch_ok && a.g_h0) a.g_h0[(size_t)b * d + ch] = carry;
@@ -406,6 +413,20 @@ diag_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
 #pragma unroll
             for (int w = 0; w < W; ++w) sum += s_gp[(w * NP + p) * kLanes + lane];
             a.gp_partial[((size_t)b * NP + p) * d + ch] = sum;
+        }
+    }
+    if (want_bias) {  // per-gate sums of g_wx (bias gradient): same fixed-order reduction, one gate at a time
+#pragma unroll
+        for (int q = 0; q < G; ++q) {
+            __syncthreads();
+            if (warp < W) s_gp[warp * kLanes + lane] = gb_acc[q];
+            __syncthreads();
+            if (warp == 0 && ch_ok) {
+                float sum = 0.f;
+#pragma unroll
+                for (int w = 0; w < W; ++w) sum += s_gp[w * kLanes + lane];
+                a.gb_partial[((size_t)b * G + q) * d + ch] = sum;
+            }
         }
     }
 }

@@ -27,6 +27,9 @@ inline bool is_diag_cell(int cell) {
     return cell == kCellGruDiag || cell == kCellNlru || cell == kCellTitans || cell == kCellCfc;
 }
 inline int diag_cell_params(int cell) { return cell == kCellGruDiag ? 3 : (cell == kCellTitans ? 2 : 1); }
+inline int diag_cell_gates(int cell) {
+    return cell == kCellGruDiag ? 3 : (cell == kCellNlru ? 2 : (cell == kCellTitans ? 5 : 4));
+}
 enum DType : int { kF32 = 0, kBF16 = 1 };
 
 // ---- scalar-diagonal cells ------------------------------------------------
@@ -55,6 +58,7 @@ struct DiagBwdArgs {
     const float* carry_in;  // (B,d) nu entering the last step (from the next shard), may be null
     void* g_wx;             // (B,T,G*d) I/O dtype
     float* gp_partial;      // (B*n_tt, NP, d) per-tile parameter partial sums
+    float* gb_partial;      // (same rows, G, d) per-gate sums of g_wx (bias gradient), or null
     float* g_h0;            // (B,d) nu leaving step 0 (= grad_h0 on the first shard), may be null
     float* agg_out;         // (B,2,d)
     float* mu_out;          // optional (B,T,d) fp32

@@ -48,6 +48,7 @@ _SIGNATURES = {
     "prb_bwd_gru": (_INT, [_VOIDP] * 10 + [_INT] * 4 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_bwd_nlru": (_INT, [_VOIDP] * 8 + [_INT] * 4 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_bwd_slstm": (_INT, [_VOIDP] * 8 + [_INT] * 4 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
+    "prb_bwd_diag_ex": (_INT, [_INT] + [_VOIDP] * 11 + [_INT] * 4 + [_VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_bwd_slstm_ex": (_INT, [_VOIDP] * 5 + [_INT] + [_VOIDP] * 4 + [_INT] * 4 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_residual": (_INT, [_INT] + [_VOIDP] * 4 + [_INT] * 4 + [_FLOAT, _VOIDP, _SIZE, _VOIDP, _VOIDP]),
     "prb_pass_workspace_bytes": (_SIZE, [_INT] * 4),

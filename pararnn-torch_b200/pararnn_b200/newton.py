@@ -251,20 +251,21 @@ _BIAS = "__bias__"  # key of the kernel-side sum of g_wx in the dict `_reverse_w
 def _reverse_window(cell, kind, states, wx, grad_states, h0, grad_slot=None):
     rec = _recurrent_params(cell, kind)
     if kind == "gru_diag":
-        g_wx, gz, gr, gn, g_h0 = ops.gru_reverse_vjp(states, wx, *rec, grad_states, h0)
-        return g_wx, {"a_z": gz, "a_r": gr, "a_n": gn}, g_h0
+        g_wx, gz, gr, gn, g_h0, gb = ops.gru_reverse_vjp(states, wx, *rec, grad_states, h0, want_bias=True)
+        return g_wx, {"a_z": gz, "a_r": gr, "a_n": gn, _BIAS: gb}, g_h0
     if kind == "nlru":
-        g_wx, gu, g_h0 = ops.nlru_reverse_vjp(states, wx, rec[0], grad_states, h0)
-        return g_wx, {"u": gu}, g_h0
+        g_wx, gu, g_h0, gb = ops.nlru_reverse_vjp(states, wx, rec[0], grad_states, h0, want_bias=True)
+        return g_wx, {"u": gu, _BIAS: gb}, g_h0
     if kind == "cfc":
-        g_wx, gu, g_h0 = ops.cfc_reverse_vjp(states, wx, rec[0], grad_states, h0)
-        return g_wx, {"u": gu}, g_h0
+        g_wx, gu, g_h0, gb = ops.cfc_reverse_vjp(states, wx, rec[0], grad_states, h0, want_bias=True)
+        return g_wx, {"u": gu, _BIAS: gb}, g_h0
     if kind == "lstm":
         g_wx, gp, g_h0 = ops.lstm_reverse_vjp(states, wx, *rec, grad_states, h0)
         return g_wx, {n: gp[i] for i, n in enumerate(("a_f", "a_z", "a_o", "c_f", "c_o"))}, g_h0
     if kind == "titans":
-        g_wx, gu, gr, g_h0 = ops.titans_reverse_vjp(states, wx, rec[0], rec[1], grad_states, h0)
-        return g_wx, {"u": gu, "r": gr}, g_h0
+        g_wx, gu, gr, g_h0, gb = ops.titans_reverse_vjp(states, wx, rec[0], rec[1], grad_states, h0,
+                                                        want_bias=True)
+        return g_wx, {"u": gu, "r": gr, _BIAS: gb}, g_h0
     if kind == "slstm_diag":
         g_wx, gr, g_h0, g_bias = ops.slstm_reverse_vjp(states, wx, rec[0], grad_states, h0, float(cell.eps),
                                                        grad_slot=grad_slot, want_bias=True)
@@ -329,7 +330,7 @@ def _backward(cell, kind, states, x, wx, grad_states, h0, chunk_len, cu_seqlens=
             g = g * mask
         grads[name] = g.to(raw.dtype)
     if kind == "cfc":
-        grad_x, lin_grads = _cfc_input_grads(cell, x, g_wx)
+        grad_x, lin_grads = _cfc_input_grads(cell, x, g_wx, bias_sum)
         grads.update(lin_grads)
         return grad_x, g_h0, grads
     lin = cell.W_x
@@ -343,7 +344,7 @@ def _backward(cell, kind, states, x, wx, grad_states, h0, chunk_len, cu_seqlens=
     return grad_x, g_h0, grads
 
 
-def _cfc_input_grads(cell, x, g_wx):
+def _cfc_input_grads(cell, x, g_wx, bias_sum=None):
     """Gradients of ``project_wx``: ``g_wx (B,T,4d)`` holds the grads of ``(f, c, dt, b)``.
     ``(f, c)`` go through ``W_x``, ``b`` through ``W_b``, both on the features; the time step
     gets the channel sum of its block where the clamp was inactive (reference
@@ -361,10 +362,11 @@ def _cfc_input_grads(cell, x, g_wx):
     featc = feat.to(g.dtype)
     grads = {"W_x.weight": (g_fc.t() @ featc).to(cell.W_x.weight.dtype),
              "W_b.weight": (g_b.t() @ featc).to(cell.W_b.weight.dtype)}
+    # bias_sum: the reverse kernel's own per-gate sums of g_wx, (4d,) in the order (f, c, dt, b)
     if cell.W_x.bias is not None:
-        grads["W_x.bias"] = g_fc.sum(0).to(cell.W_x.bias.dtype)
+        grads["W_x.bias"] = (g_fc.sum(0) if bias_sum is None else bias_sum[:2 * d]).to(cell.W_x.bias.dtype)
     if cell.W_b.bias is not None:
-        grads["W_b.bias"] = g_b.sum(0).to(cell.W_b.bias.dtype)
+        grads["W_b.bias"] = (g_b.sum(0) if bias_sum is None else bias_sum[3 * d:]).to(cell.W_b.bias.dtype)
     return grad_x, grads
 
 

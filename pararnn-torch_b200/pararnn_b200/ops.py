@@ -495,81 +495,62 @@ def _bwd_common(states, wx, grad_states, h0):
     return dev, code, st, wx.detach().contiguous(), gs, _same(h0, wx)
 
 
+def _diag_reverse_vjp(what: str, cell_code: int, gates: int, states: Tensor, wx: Tensor, params: tuple,
+                      grad_states: Tensor, h0: Tensor | None, want_bias: bool):
+    """Shared body of the scalar-diagonal reverse scan + VJP operators: returns
+    ``(g_wx, g_params (NP,d) fp32, g_h0 (B,d) fp32, g_bias (G*d,) fp32 or None)``."""
+    dev, code, st, wxc, gs, h0c = _bwd_common(states, wx, grad_states, h0)
+    B, T, dg = wx.shape
+    if dg % gates:
+        raise ValueError(f"wx must be (B, T, {gates}*d), got {tuple(wx.shape)}")
+    d = dg // gates
+    if tuple(states.shape) != (B, T, d) or tuple(grad_states.shape) != (B, T, d):
+        raise ValueError("states / grad_states must be (B, T, d)")
+    g_wx = torch.empty_like(wxc)
+    g_par = torch.empty(len(params), d, dtype=torch.float32, device=dev)
+    g_bias = torch.empty(gates * d, dtype=torch.float32, device=dev) if want_bias else None
+    g_h0 = torch.empty(B, d, dtype=torch.float32, device=dev)
+    sb = DeviceStats(dev, 0)
+    pc = [_same(p, wx) for p in params] + [None] * (3 - len(params))  # keep alive across the call
+    lib = L.lib()
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.prb_bwd_workspace_bytes(cell_code, code, B, T, d, 1), dev)
+        rc = lib.prb_bwd_diag_ex(cell_code, _ptr(st), _ptr(wxc), _ptr(pc[0]), _ptr(pc[1]), _ptr(pc[2]), _ptr(h0c),
+                                 _ptr(gs), _ptr(g_wx), _ptr(g_par), _ptr(g_bias), _ptr(g_h0), B, T, d, code,
+                                 _ptr(ws), ws.numel(), _ptr(sb.buf), _stream(dev))
+    _raise(rc, what)
+    _track_backward(sb)
+    return g_wx, g_par, g_h0, g_bias
+
+
 def gru_reverse_vjp(states: Tensor, wx: Tensor, a_z: Tensor, a_r: Tensor, a_n: Tensor,
-                    grad_states: Tensor, h0: Tensor | None = None):
+                    grad_states: Tensor, h0: Tensor | None = None, *, want_bias: bool = False):
     """Eq. 2.6 reverse scan fused with the packed GRU VJP.
 
     Returns ``(g_wx, g_az, g_ar, g_an, g_h0)``; parameter grads are fp32 sums over batch and
-    time with no clip mask (the caller applies it, reference ``solvers/vjp.py:141-144``)."""
-    dev, code, st, wxc, gs, h0c = _bwd_common(states, wx, grad_states, h0)
-    B, T, d3 = wx.shape
-    d = d3 // 3
-    if tuple(states.shape) != (B, T, d) or tuple(grad_states.shape) != (B, T, d):
-        raise ValueError("states / grad_states must be (B, T, d)")
-    g_wx = torch.empty_like(wxc)
-    g_par = torch.empty(3, d, dtype=torch.float32, device=dev)
-    g_h0 = torch.empty(B, d, dtype=torch.float32, device=dev)
-    sb = DeviceStats(dev, 0)
-    az, ar, an = _same(a_z, wx), _same(a_r, wx), _same(a_n, wx)  # keep alive across the call
-    lib = L.lib()
-    with torch.cuda.device(dev):
-        ws = _workspace(lib.prb_bwd_workspace_bytes(L.CELL_GRU_DIAG, code, B, T, d, 1), dev)
-        rc = lib.prb_bwd_gru(_ptr(st), _ptr(wxc), _ptr(az), _ptr(ar),
-                             _ptr(an), _ptr(h0c), _ptr(gs), _ptr(g_wx), _ptr(g_par),
-                             _ptr(g_h0), B, T, d, code, _ptr(ws), ws.numel(), _ptr(sb.buf),
-                             _stream(dev))
-    _raise(rc, "gru_reverse_vjp")
-    _track_backward(sb)
-    return g_wx, g_par[0], g_par[1], g_par[2], g_h0
+    time with no clip mask (the caller applies it, reference ``solvers/vjp.py:141-144``).
+    ``want_bias`` (all scalar-diagonal cells): one more result, ``g_bias (G*d,) fp32`` = the sum of
+    ``g_wx`` over batch and time, accumulated by the same kernel."""
+    g_wx, gp, g_h0, gb = _diag_reverse_vjp("gru_reverse_vjp", L.CELL_GRU_DIAG, 3, states, wx, (a_z, a_r, a_n),
+                                           grad_states, h0, want_bias)
+    return (g_wx, gp[0], gp[1], gp[2], g_h0) + ((gb,) if want_bias else ())
 
 
 def nlru_reverse_vjp(states: Tensor, wx: Tensor, u: Tensor, grad_states: Tensor,
-                     h0: Tensor | None = None):
+                     h0: Tensor | None = None, *, want_bias: bool = False):
     """Eq. 2.6 reverse scan fused with the packed NLRU VJP: ``(g_wx, g_u, g_h0)``."""
-    dev, code, st, wxc, gs, h0c = _bwd_common(states, wx, grad_states, h0)
-    B, T, d2 = wx.shape
-    d = d2 // 2
-    if tuple(states.shape) != (B, T, d) or tuple(grad_states.shape) != (B, T, d):
-        raise ValueError("states / grad_states must be (B, T, d)")
-    g_wx = torch.empty_like(wxc)
-    g_par = torch.empty(1, d, dtype=torch.float32, device=dev)
-    g_h0 = torch.empty(B, d, dtype=torch.float32, device=dev)
-    sb = DeviceStats(dev, 0)
-    uc = _same(u, wx)
-    lib = L.lib()
-    with torch.cuda.device(dev):
-        ws = _workspace(lib.prb_bwd_workspace_bytes(L.CELL_NLRU, code, B, T, d, 1), dev)
-        rc = lib.prb_bwd_nlru(_ptr(st), _ptr(wxc), _ptr(uc), _ptr(h0c), _ptr(gs),
-                              _ptr(g_wx), _ptr(g_par), _ptr(g_h0), B, T, d, code, _ptr(ws),
-                              ws.numel(), _ptr(sb.buf), _stream(dev))
-    _raise(rc, "nlru_reverse_vjp")
-    _track_backward(sb)
-    return g_wx, g_par[0], g_h0
+    g_wx, gp, g_h0, gb = _diag_reverse_vjp("nlru_reverse_vjp", L.CELL_NLRU, 2, states, wx, (u,), grad_states, h0,
+                                           want_bias)
+    return (g_wx, gp[0], g_h0) + ((gb,) if want_bias else ())
 
 
 def cfc_reverse_vjp(states: Tensor, wx: Tensor, u: Tensor, grad_states: Tensor,
-                     h0: Tensor | None = None):
+                    h0: Tensor | None = None, *, want_bias: bool = False):
     """Eq. 2.6 reverse scan fused with the packed CfC VJP (reference ``kernels/vjp_cfc.py:102-167``):
     ``(g_wx (B,T,4d) = grads of (f_pre, c_x, dt, b), g_u, g_h0)``."""
-    dev, code, st, wxc, gs, h0c = _bwd_common(states, wx, grad_states, h0)
-    B, T, d4 = wx.shape
-    d = d4 // 4
-    if tuple(states.shape) != (B, T, d) or tuple(grad_states.shape) != (B, T, d):
-        raise ValueError("states / grad_states must be (B, T, d)")
-    g_wx = torch.empty_like(wxc)
-    g_par = torch.empty(1, d, dtype=torch.float32, device=dev)
-    g_h0 = torch.empty(B, d, dtype=torch.float32, device=dev)
-    sb = DeviceStats(dev, 0)
-    uc = _same(u, wx)
-    lib = L.lib()
-    with torch.cuda.device(dev):
-        ws = _workspace(lib.prb_bwd_workspace_bytes(L.CELL_CFC, code, B, T, d, 1), dev)
-        rc = lib.prb_bwd_cfc(_ptr(st), _ptr(wxc), _ptr(uc), _ptr(h0c), _ptr(gs),
-                              _ptr(g_wx), _ptr(g_par), _ptr(g_h0), B, T, d, code, _ptr(ws),
-                              ws.numel(), _ptr(sb.buf), _stream(dev))
-    _raise(rc, "cfc_reverse_vjp")
-    _track_backward(sb)
-    return g_wx, g_par[0], g_h0
+    g_wx, gp, g_h0, gb = _diag_reverse_vjp("cfc_reverse_vjp", L.CELL_CFC, 4, states, wx, (u,), grad_states, h0,
+                                           want_bias)
+    return (g_wx, gp[0], g_h0) + ((gb,) if want_bias else ())
 
 
 def lstm_reverse_vjp(states: Tensor, wx: Tensor, a_f: Tensor, a_z: Tensor, a_o: Tensor, c_f: Tensor,
@@ -598,27 +579,11 @@ def lstm_reverse_vjp(states: Tensor, wx: Tensor, a_f: Tensor, a_z: Tensor, a_o: 
 
 
 def titans_reverse_vjp(states: Tensor, wx: Tensor, u: Tensor, r: Tensor, grad_states: Tensor,
-                       h0: Tensor | None = None):
+                       h0: Tensor | None = None, *, want_bias: bool = False):
     """Eq. 2.6 reverse scan fused with the Titans VJP: ``(g_wx (B,T,5d), g_u, g_r, g_h0)``."""
-    dev, code, st, wxc, gs, h0c = _bwd_common(states, wx, grad_states, h0)
-    B, T, d5 = wx.shape
-    d = d5 // 5
-    if tuple(states.shape) != (B, T, d) or tuple(grad_states.shape) != (B, T, d):
-        raise ValueError("states / grad_states must be (B, T, d)")
-    g_wx = torch.empty_like(wxc)
-    g_par = torch.empty(2, d, dtype=torch.float32, device=dev)
-    g_h0 = torch.empty(B, d, dtype=torch.float32, device=dev)
-    sb = DeviceStats(dev, 0)
-    uc, rc_ = _same(u, wx), _same(r, wx)
-    lib = L.lib()
-    with torch.cuda.device(dev):
-        ws = _workspace(lib.prb_bwd_workspace_bytes(L.CELL_TITANS, code, B, T, d, 1), dev)
-        rc = lib.prb_bwd_titans(_ptr(st), _ptr(wxc), _ptr(uc), _ptr(rc_), _ptr(h0c), _ptr(gs), _ptr(g_wx),
-                                _ptr(g_par), _ptr(g_h0), B, T, d, code, _ptr(ws), ws.numel(), _ptr(sb.buf),
-                                _stream(dev))
-    _raise(rc, "titans_reverse_vjp")
-    _track_backward(sb)
-    return g_wx, g_par[0], g_par[1], g_h0
+    g_wx, gp, g_h0, gb = _diag_reverse_vjp("titans_reverse_vjp", L.CELL_TITANS, 5, states, wx, (u, r), grad_states,
+                                           h0, want_bias)
+    return (g_wx, gp[0], gp[1], g_h0) + ((gb,) if want_bias else ())
 
 
 def slstm_reverse_vjp(states: Tensor, wx: Tensor, r: Tensor, grad_states: Tensor,

@@ -161,3 +161,27 @@ def test_nan_input_propagates_to_residual():
     wx[0, 50, 3] = np.nan
     _, hist, res = _fwd("nlru", wx, params, h0, 2)
     assert np.isnan(res) and np.isnan(hist[0])
+
+
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans", "cfc"])
+@pytest.mark.parametrize("B,T,d", [(1, 1, 3), (2, 65, 31), (3, 1000, 64), (2, 4097, 96)])
+def test_bias_sum_from_the_reverse_kernel(kind, B, T, d, prb_options):
+    """want_bias: the kernel's own per-gate sum of g_wx over batch and time, on both kernel families;
+    the other results are unchanged by asking for it."""
+    from pararnn_b200 import ops
+
+    wx, params, h0 = make_problem(kind, B, T, d, seed=T + d, h0=True)
+    H = oracle.sequential(oracle.KIND[kind], wx, params, h0)
+    G = np.random.default_rng(T).standard_normal(H.shape).astype(np.float32)
+    fn = {"gru_diag": ops.gru_reverse_vjp, "nlru": ops.nlru_reverse_vjp, "titans": ops.titans_reverse_vjp,
+          "cfc": ops.cfc_reverse_vjp}[kind]
+    for family in ("auto", "lookback"):
+        if family == "lookback":
+            prb_options("kernel_family", "lookback")
+        plain = fn(dev(H), dev(wx), *[dev(p) for p in params], dev(G), dev(h0))
+        withb = fn(dev(H), dev(wx), *[dev(p) for p in params], dev(G), dev(h0), want_bias=True)
+        assert len(withb) == len(plain) + 1
+        for u, v in zip(plain, withb):
+            assert torch.equal(u, v)
+        want = plain[0].double().sum((0, 1))
+        assert float((withb[-1].double() - want).abs().max()) <= 2e-5 * max(1.0, float(want.abs().max()))

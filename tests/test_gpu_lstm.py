@@ -84,3 +84,26 @@ def test_bf16_io_within_relative_tolerance():
     want = oracle.newton(oracle.LSTM, wx, params, h0, max_iters=3)
     H, _, _ = _fwd(wx, params, h0, 3, dtype=torch.bfloat16)
     assert rel_err(H, want.states) <= 2e-2
+
+
+def test_output_slot_on_the_two_slot_cell_equals_slicing():
+    """ParaLSTM has no compact-cotangent kernel: output_slot goes through the zero-filled array."""
+    import pararnn_b200 as prb
+
+    torch.manual_seed(0)
+    cell = prb.ParaLSTM(16, 24).cuda()
+    x = torch.randn(2, 150, 16, device="cuda", requires_grad=True)
+    cfg = prb.NewtonConfig(max_iters=3)
+    G = torch.randn(2, 150, 24, device="cuda")
+
+    def grads(sliced):
+        x.grad = None
+        cell.zero_grad(set_to_none=True)
+        out = prb.newton_apply(cell, x, cfg)[:, :, 1] if sliced else prb.newton_apply(cell, x, cfg, output_slot=1)
+        (out * G).sum().backward()
+        return [out.detach().clone(), x.grad.clone()] + [p.grad.clone() for p in cell.parameters()]
+
+    for u, v in zip(grads(True), grads(False)):
+        assert torch.equal(u, v)
+    rnn = prb.ParaRNN(cell, config=cfg).train()
+    assert rnn(x.detach()).shape == (2, 150, 24)
