@@ -344,6 +344,18 @@ int prb_fold_segments(int monoid, const float* agg, int n_seg, int reverse, floa
 int prb_segment_carries(int monoid, const float* agg, int n_seg, int reverse, const float* carry0,
                         float* carries, int B, int d, prb_stream_t stream);
 
+/* prb_fold_carries and prb_segment_carries in ONE launch, for a rank that is not the first in scan
+ * order.  gathered (world, B, slot_rows, d) fp32: every rank's slot holds its map (or, for the first
+ * rank, its outgoing state) in the first rows and whatever rides along after them (slot_rows >= NV).
+ * carry_out (B,NS,d): the carry entering the rank.  carries (n_seg+1, B, NS, d) or NULL: the carries
+ * entering the rank's segments and the one leaving it, through the segment maps agg (n_seg,B,NV,d).
+ * h_end (B,d) or NULL, frozen-gate monoid only: sigmoid(zo) c / (n + eps) with zo = row NV of the
+ * previous rank's slot, i.e. the hidden value at the previous rank's last step
+ * (cells/para_slstm.py:347-446, the h output of the state the carry holds). */
+int prb_shard_carries(int monoid, const float* gathered, int slot_rows, int rank, int world, int reverse,
+                      const float* agg, int n_seg, float* carry_out, float* carries, float eps, float* h_end,
+                      int B, int d, prb_stream_t stream);
+
 /* residual of a shard with an fp32 halo; states fp32 (states_f32 != 0) or I/O dtype */
 int prb_residual_pass(int cell, const void* wx, const float* params, const float* halo,
                       const void* states, int states_f32, int B, int T, int d, int dtype, float eps,

@@ -510,6 +510,54 @@ __global__ void segment_carries_kernel(const float* agg, int n_seg, int reverse,
     for (int i = 0; i < M::NS; ++i) out[(((size_t)n_seg * B + b) * M::NS + i) * d + ch] = vec[i];
 }
 
+// fold_carries_kernel and segment_carries_kernel in one launch, for a rank that is not the first in
+// scan order: the carry entering the rank is folded from the gathered slots (slot stride slot_rows
+// floats per channel: the map or tail in the first rows, anything riding along after them), written
+// to carry_out and pushed through the rank's own segment maps.  For the frozen-gate passes the
+// hidden value at the previous rank's last step follows from the carry and that step's output-gate
+// pre-activation, which the previous rank ships in row NV of its slot: h_end = sigmoid(zo) c / (n + eps).
+template <class M>
+__global__ void shard_carries_kernel(const float* gathered, int slot_rows, int rank, int world, int reverse,
+                                     const float* agg, int n_seg, float* carry_out, float* carries, float eps,
+                                     float* h_end, int B, int d) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= B * d) return;
+    const int b = idx / d, ch = idx % d;
+    const size_t slot = (size_t)slot_rows * B * d;
+    const int first = reverse ? world - 1 : 0;
+    const int step = reverse ? -1 : 1;
+    float vec[M::NS];
+    const float* p0 = gathered + (size_t)first * slot + (size_t)b * slot_rows * d + ch;
+#pragma unroll
+    for (int i = 0; i < M::NS; ++i) vec[i] = p0[(size_t)i * d];
+    for (int q = first + step; q != rank; q += step) {
+        float m[M::NV];
+        const float* p = gathered + (size_t)q * slot + (size_t)b * slot_rows * d + ch;
+#pragma unroll
+        for (int i = 0; i < M::NV; ++i) m[i] = p[(size_t)i * d];
+        M::apply(m, vec);
+    }
+#pragma unroll
+    for (int i = 0; i < M::NS; ++i) carry_out[((size_t)b * M::NS + i) * d + ch] = vec[i];
+    if (h_end) {
+        const float zo = gathered[(size_t)(rank - step) * slot + ((size_t)b * slot_rows + M::NV) * d + ch];
+        h_end[(size_t)b * d + ch] = sigmoid_f(zo) * vec[0] / (vec[1] + eps);
+    }
+    if (!carries) return;
+    for (int k = 0; k < n_seg; ++k) {
+        const int j = reverse ? n_seg - 1 - k : k;
+#pragma unroll
+        for (int i = 0; i < M::NS; ++i) carries[(((size_t)j * B + b) * M::NS + i) * d + ch] = vec[i];
+        float m[M::NV];
+        const float* p = agg + ((size_t)j * B + b) * M::NV * d + ch;
+#pragma unroll
+        for (int i = 0; i < M::NV; ++i) m[i] = p[(size_t)i * d];
+        M::apply(m, vec);
+    }
+#pragma unroll
+    for (int i = 0; i < M::NS; ++i) carries[(((size_t)n_seg * B + b) * M::NS + i) * d + ch] = vec[i];
+}
+
 // Map of a whole rank = composition of its segment maps in scan order.
 template <class M>
 __global__ void fold_segments_kernel(const float* agg, int n_seg, int reverse, float* out, int B, int d) {
@@ -1370,6 +1418,31 @@ int prb_segment_carries(int monoid, const float* agg, int n_seg, int reverse, co
         segment_carries_kernel<Affine4><<<grid, blk, 0, s>>>(agg, n_seg, reverse, carry0, carries, B, d);
     else if (monoid == 2)
         segment_carries_kernel<PicardMonoid><<<grid, blk, 0, s>>>(agg, n_seg, reverse, carry0, carries, B, d);
+    else
+        return PRB_ERR_BAD_ARG;
+    return cudaGetLastError() == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
+}
+
+int prb_shard_carries(int monoid, const float* gathered, int slot_rows, int rank, int world, int reverse,
+                      const float* agg, int n_seg, float* carry_out, float* carries, float eps, float* h_end,
+                      int B, int d, prb_stream_t stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!gathered || !carry_out || B < 1 || d < 1 || world < 2 || rank < 0 || rank >= world || n_seg < 1)
+        return PRB_ERR_BAD_ARG;
+    if ((!reverse && rank == 0) || (reverse && rank == world - 1)) return PRB_ERR_BAD_ARG;
+    if (carries && !agg) return PRB_ERR_BAD_ARG;
+    const int nv = monoid == 0 ? 2 : (monoid == 1 ? 20 : 4);
+    if (slot_rows < nv || (h_end && (monoid != 2 || slot_rows < nv + 1))) return PRB_ERR_BAD_ARG;
+    const int n = B * d, blk = 128, grid = (n + blk - 1) / blk;
+    if (monoid == 0)
+        shard_carries_kernel<Affine1><<<grid, blk, 0, s>>>(gathered, slot_rows, rank, world, reverse, agg, n_seg,
+                                                           carry_out, carries, eps, nullptr, B, d);
+    else if (monoid == 1)
+        shard_carries_kernel<Affine4><<<grid, blk, 0, s>>>(gathered, slot_rows, rank, world, reverse, agg, n_seg,
+                                                           carry_out, carries, eps, nullptr, B, d);
+    else if (monoid == 2)
+        shard_carries_kernel<PicardMonoid><<<grid, blk, 0, s>>>(gathered, slot_rows, rank, world, reverse, agg,
+                                                                n_seg, carry_out, carries, eps, h_end, B, d);
     else
         return PRB_ERR_BAD_ARG;
     return cudaGetLastError() == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;

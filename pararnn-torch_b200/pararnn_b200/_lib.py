@@ -63,6 +63,7 @@ _SIGNATURES = {
     "prb_plan_segments": (_INT, [_INT] * 5 + [_VOIDP, _VOIDP]),
     "prb_fold_segments": (_INT, [_INT, _VOIDP, _INT, _INT, _VOIDP, _INT, _INT, _VOIDP]),
     "prb_segment_carries": (_INT, [_INT, _VOIDP, _INT, _INT, _VOIDP, _VOIDP, _INT, _INT, _VOIDP]),
+    "prb_shard_carries": (_INT, [_INT, _VOIDP, _INT, _INT, _INT, _INT, _VOIDP, _INT, _VOIDP, _VOIDP, _FLOAT, _VOIDP, _INT, _INT, _VOIDP]),
     "prb_fold_carries": (_INT, [_INT, _VOIDP, _INT, _INT, _INT, _VOIDP, _INT, _INT, _VOIDP]),
     "prb_decode_step": (_INT, [_INT, _VOIDP, _VOIDP, _VOIDP, _FLOAT, _VOIDP, _VOIDP, _INT, _INT, _INT, _FLOAT, _VOIDP]),
     "prb_static_scratch_bytes": (_SIZE, []),

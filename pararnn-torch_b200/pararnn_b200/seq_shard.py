@@ -239,6 +239,26 @@ class CudaShardOps:
         self.launches += 1
         return out
 
+    def shard_carries(self, monoid: str, gathered: Tensor, rank: int, world: int, reverse: bool,
+                      agg: Tensor | None, want_h_end: bool = False):
+        """``fold`` and ``segment_carries`` in one launch on the gathered slots as they are (the
+        map rows first, anything riding along after them).  Returns ``(carry entering the rank,
+        carries entering its segments + the one leaving it or None, h_end or None)``; ``h_end`` is
+        the hidden value at the previous rank's last step (frozen-gate passes)."""
+        n_seg = 1 if agg is None else agg.shape[0]
+        carry = torch.empty(self.B, NS[monoid], self.d, dtype=torch.float32, device=self.dev)
+        carries = None
+        if agg is not None and n_seg > 1:
+            carries = torch.empty(n_seg + 1, self.B, NS[monoid], self.d, dtype=torch.float32, device=self.dev)
+        h_end = torch.empty(self.B, self.d, dtype=torch.float32, device=self.dev) if want_h_end else None
+        with torch.cuda.device(self.dev):
+            rc = self.lib.prb_shard_carries(MONOID[monoid], self._p(gathered), gathered.shape[2], rank, world,
+                                            int(reverse), self._p(agg), n_seg, self._p(carry), self._p(carries),
+                                            float(self.eps), self._p(h_end), self.B, self.d, self._stream())
+        self._check(rc, "shard_carries")
+        self.launches += 1
+        return carry, carries, h_end
+
     def diag_guess(self, h0):
         out = self.new_traj()
         with torch.cuda.device(self.dev):
@@ -338,12 +358,14 @@ def _pad(t: Tensor, nv: int) -> Tensor:
     return out
 
 
-def _sharded_scan(ops, rank, world, reverse, monoid, boundary, sweep, extra=None):
+def _sharded_scan(ops, rank, world, reverse, monoid, boundary, sweep, extra=None, want_h_end=False):
     """One sharded scan pass.  ``sweep(True, None)`` returns the aggregates of the rank's time
     segments ``(n_seg, B, NV, d)``; ``sweep(False, carries)`` applies the carries entering the
     segments ``(n_seg, B, NS, d)`` (None = zeros) and returns the carry leaving the shard.
     ``extra`` (B, E, d) rides along in the rank's gather slot.  Yields at most one gather; returns
-    ``(carry entering this rank, carry leaving it, gathered slots or None)``."""
+    ``(carry entering this rank, carry leaving it, gathered slots or None, h_end or None)``;
+    ``h_end`` (``want_h_end``, frozen-gate passes, ranks after the first) is the hidden value at
+    the previous rank's last step, from the carry and the gate value in the extra row."""
     first = world - 1 if reverse else 0
     n_seg = getattr(ops, "n_seg", 1)
     nv = NV[monoid]
@@ -359,15 +381,26 @@ def _sharded_scan(ops, rank, world, reverse, monoid, boundary, sweep, extra=None
         if world > 1:
             slot = _pad(leaving, nv)
             gathered = yield ("gather", slot if extra is None else torch.cat([slot, extra], dim=1))
-        return boundary, leaving, gathered
+        return boundary, leaving, gathered, None
     agg = sweep(True, None)
     slot = agg[0] if n_seg == 1 else ops.fold_segments(monoid, agg, reverse)
     gathered = yield ("gather", slot if extra is None else torch.cat([slot, extra], dim=1))
-    maps = gathered if extra is None else gathered[:, :, :nv].contiguous()
-    carry = ops.fold(monoid, maps, rank, world, reverse)
-    carries = carry if n_seg == 1 else ops.segment_carries(monoid, agg, reverse, carry)
+    h_end = None
+    if hasattr(ops, "shard_carries"):
+        # one launch: fold of the gathered maps, the segment carries and (frozen-gate passes) h_end
+        carry, carries, h_end = ops.shard_carries(monoid, gathered, rank, world, reverse,
+                                                  agg if n_seg > 1 else None, want_h_end)
+        if carries is None:
+            carries = carry
+    else:
+        maps = gathered if extra is None else gathered[:, :, :nv].contiguous()
+        carry = ops.fold(monoid, maps, rank, world, reverse)
+        carries = carry if n_seg == 1 else ops.segment_carries(monoid, agg, reverse, carry)
+        if want_h_end:
+            zo_prev = gathered[rank - 1][:, nv]
+            h_end = torch.sigmoid(zo_prev) * carry[:, 0] / (carry[:, 1] + ops.eps)
     leaving = sweep(False, carries)
-    return carry, leaving, gathered
+    return carry, leaving, gathered, h_end
 
 
 def forward_program(ops, rank: int, world: int, K: int, P: int, h0: Tensor | None):
@@ -402,7 +435,7 @@ def forward_program(ops, rank: int, world: int, K: int, P: int, h0: Tensor | Non
             if h_prev is None:
                 zo_last = wx_o_last
             elif ops.T >= 2:
-                zo_last = wx_o_last + r_o * h_prev[:, -2]
+                zo_last = torch.addcmul(wx_o_last, r_o, h_prev[:, -2])
             else:
                 zo_last = wx_o_last + r_o * (h_halo if h_halo is not None else 0.0)
             def sweep(agg_only, carry, h_prev=h_prev, h_halo=h_halo, h_out=h_out, state_out=state_out):
@@ -410,12 +443,11 @@ def forward_program(ops, rank: int, world: int, K: int, P: int, h0: Tensor | Non
                     return ops.picard_pass(h_prev, h_halo, None, 2, None, None)
                 return ops.picard_pass(h_prev, h_halo, carry, 0, h_out, state_out)
 
-            carry, _, gathered = yield from _sharded_scan(ops, rank, world, False, "picard", carry0, sweep,
-                                                          extra=zo_last[:, None] if world > 1 else None)
+            carry, _, gathered, h_end = yield from _sharded_scan(
+                ops, rank, world, False, "picard", carry0, sweep,
+                extra=zo_last[:, None] if world > 1 else None, want_h_end=world > 1)
             if rank > 0:
                 # hidden state at the previous rank's last step under the new trajectory
-                zo_prev = gathered[rank - 1][:, 4]
-                h_end = torch.sigmoid(zo_prev) * carry[:, 0] / (carry[:, 1] + ops.eps)
                 h_halo = h_end
                 if last:
                     halo = torch.cat([carry, h_end[:, None]], dim=1)
@@ -441,7 +473,7 @@ def forward_program(ops, rank: int, world: int, K: int, P: int, h0: Tensor | Non
         def sweep(agg_only, carry, traj=traj, halo=halo, dst=dst, last=last, k=k):
             return ops.newton_pass(traj, halo, carry, 2 if agg_only else (1 if last else 0), dst, k)
 
-        carry, _, _ = yield from _sharded_scan(ops, rank, world, False, ops.monoid, None, sweep)
+        carry, _, _, _ = yield from _sharded_scan(ops, rank, world, False, ops.monoid, None, sweep)
         if rank > 0 and carry is not None:
             # the carry entering the shard is the update of the previous rank's last step
             c = carry if ops.slots == 4 else carry[:, 0]
