@@ -262,10 +262,13 @@ struct PipeBwdSmem {
 // baton (nu, the adjoint propagated from later steps) moves towards lower steps.
 // nu_{t-1} = J_t^T (nu_t + g_t) is evaluated through the packed-VJP quantities:
 // (d_cn f, d_nn f, d_zf, sum_g r_g d_zg).
-template <typename TIO, int L, int W, int NSTAGE, bool HID, bool BIAS>
+// SLOT = -1: the cotangent is the full (B,T,4,d) array; SLOT = 0..3: it is (B,T,d), of that slot alone
+// (a compile-time slot, so the three absent terms cost nothing).
+template <typename TIO, int L, int W, int NSTAGE, int SLOT, bool BIAS>
 __global__ void __launch_bounds__(W * 32, 2)
 slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_st,
                       const __grid_constant__ CUtensorMap tm_g, SlstmBwdArgs a) {
+    constexpr bool HID = SLOT >= 0;
     using S = PipeBwdSmem<TIO, L, W, NSTAGE, HID>;
     constexpr int LT = S::LT;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -369,7 +372,7 @@ slstm_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
                     if (HID) {
                         const float v = (float)t_g[row * kLanes + lane];
     #pragma unroll
-                        for (int q = 0; q < 4; ++q) g[i][q] = (q == a.g_slot) ? v : 0.f;
+                        for (int q = 0; q < 4; ++q) g[i][q] = (q == SLOT) ? v : 0.f;
                     } else {
     #pragma unroll
                         for (int q = 0; q < 4; ++q) g[i][q] = (float)t_g[(row * 4 + q) * kLanes + lane];
@@ -703,7 +706,9 @@ static cudaError_t launch_bwd_pipe_t(const SlstmBwdArgs& a, cudaStream_t s) {
     using SH = PipeBwdSmem<TIO, kQL, kQW, NSTAGE, true>;
     CUtensorMap tm_wx, tm_st, tm_g;
     const uint64_t rows = (uint64_t)a.B * a.T;
-    const bool hid = a.g_slot >= 0;
+    // the compact cotangent is built for the hidden slot (3) only; other slots: not supported here
+    if (a.g_slot >= 0 && a.g_slot != 3) return cudaErrorNotSupported;
+    const bool hid = a.g_slot == 3;
     if (!make_tile_map(&tm_wx, a.wx, sizeof(TIO), rows, 4, a.d, S::LT) ||
         !make_tile_map(&tm_st, a.states, sizeof(TIO), rows, 4, a.d, S::LT + 1) ||
         !make_tile_map(&tm_g, a.grad_states, sizeof(TIO), rows, hid ? 1 : 4, a.d, S::LT))
@@ -715,13 +720,13 @@ static cudaError_t launch_bwd_pipe_t(const SlstmBwdArgs& a, cudaStream_t s) {
     };
     const bool bias = a.gb_partial != nullptr;
     if (hid && bias)
-        go(slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE, true, true>, SH::TOTAL);
+        go(slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE, 3, true>, SH::TOTAL);
     else if (hid)
-        go(slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE, true, false>, SH::TOTAL);
+        go(slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE, 3, false>, SH::TOTAL);
     else if (bias)
-        go(slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE, false, true>, S::TOTAL);
+        go(slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE, -1, true>, S::TOTAL);
     else
-        go(slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE, false, false>, S::TOTAL);
+        go(slstm_bwd_pipe_kernel<TIO, kQL, kQW, NSTAGE, -1, false>, S::TOTAL);
     return cudaGetLastError();
 }
 

@@ -56,9 +56,12 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
         : "memory");
     return ok != 0;
 }
+// A hinted poll may sleep up to the hint (20 us), so the poll count is capped: 2^16 polls are at most
+// 1.3 s, the same order as the 2^24 plain polls of mbar_wait_bounded.
 __device__ __forceinline__ bool mbar_wait_bounded_sleepy(uint64_t* bar, uint32_t parity, uint32_t limit) {
     if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < limit; ++i) {
+    const uint32_t n = limit > (1u << 16) ? (1u << 16) : limit;
+    for (uint32_t i = 0; i < n; ++i) {
         if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
     }
     return false;
