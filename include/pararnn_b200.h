@@ -218,7 +218,8 @@ int prb_bwd_diag_ex(int cell, const void* states, const void* wx, const void* p0
  * otherwise does in separate passes over (B,T,4d) arrays.  grad_slot in 0..3: `grad` is (B,T,d), the
  * cotangent of that state slot alone (a layer that outputs the hidden slot h = 3 receives exactly
  * this; the reference materialises the zero-filled (B,T,4,d) array, layers/para_rnn.py:279-283 through
- * select_backward); grad_slot = -1: `grad` is (B,T,4,d) as in prb_bwd_slstm.  g_bias fp32 (4,d) or
+ * select_backward); grad_slot = -1: `grad` is (B,T,4,d) as in prb_bwd_slstm.  The
+ * pipelined kernel has the compact form for the hidden slot (3); other slots run on the look-back kernels.  g_bias fp32 (4,d) or
  * NULL: the per-gate sums of g_wx over batch and time, i.e. the gradient of the bias of W_x
  * (solvers/vjp.py:109-120 computes it as g_wx.sum over (B,T)). */
 int prb_bwd_slstm_ex(const void* states, const void* wx, const void* r, const void* h0,

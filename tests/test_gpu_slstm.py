@@ -190,7 +190,13 @@ def test_one_slot_cotangent_and_bias_sum(B, T, d, h0, slot, dtype):
     b = ops.slstm_reverse_vjp(dev(H, dtype), dev(wx, dtype), dev(r, dtype), dev(g1, dtype), dev(h0a, dtype),
                               grad_slot=slot, want_bias=True)
     for u, v in zip(a, b[:3]):
-        assert torch.equal(u, v)
+        if slot == 3:
+            assert torch.equal(u, v)  # same kernel family: the three absent terms are exact zeros
+        else:
+            # slots other than the hidden one are served by the look-back kernels, whatever family
+            # the full cotangent ran on: same values up to the order of the fp32 sums
+            tol = 2e-5 if dtype == torch.float32 else 1e-2
+            assert float((u.float() - v.float()).abs().max()) <= tol * max(1.0, float(u.float().abs().max()))
     want_bias = a[0].double().sum((0, 1))
     tol = 2e-5 if dtype == torch.float32 else 1e-2  # bf16: g_wx is rounded on store, the kernel's sum is not
     assert float((b[3].double() - want_bias).abs().max()) <= tol * max(1.0, float(want_bias.abs().max()))
