@@ -11,14 +11,17 @@ so per-GPU work is fixed (weak scaling) and N = 8 is the T = 131072 case.
 
 `value` is tokens/s at the op boundary (gate pre-activations resident in HBM -> states,
 cotangent -> gradients of the pre-activations and of R), timed with CUDA events.
-`e2e` is the same metric through `newton_apply` + autograd with host-resident inputs,
-including the three W_x GEMMs and the host<->device copies.
+`e2e` is the same metric through the `ParaRNN` layer + autograd with host-resident inputs,
+including the three W_x GEMMs and the host<->device copies (with a GEMM / scan / rest breakdown).
 `roofline` is computed on the bytes the dominant launch really moves; the figure the
 separate passes it replaces would need is reported beside it under its own name.
 `parity` compares a 32-channel slice of this run's own result with the CPU oracle.
 `sustained` repeats the step back to back for at least three seconds.
-With N > 1 the line also carries `c4_strong` (B=1, T=131072, d=2048 sharded over the N
-ranks against the same shape on one GPU) and `c5_sharded` (12 x ParaNLRU stack).
+With N > 1 the timed step is one CUDA graph per rank (kernels, folds, NCCL all-gathers;
+the same programs issued from Python are `eager_ms_per_step`), and the line also carries
+`c4_strong` (B=1, T=131072, d=2048 sharded over the N ranks against the same shape on one
+GPU) and `c5_sharded` (12 x ParaNLRU stack).  `--workload c1|c3|c5` time the secondary
+configurations, `--workload ref_fused` the reference's own GPU paths next to this backend.
 The CPU arm (`--impl reference`, and `cpu_baseline` at N = 1) times the C restatement of
 the reference's eager algorithm (oracle/) on the host cores.
 """
