@@ -189,7 +189,28 @@ int run_diag_fwd(int cell, const void* wx, const void* const* pars, const void* 
     if (K == 0) {
         launch_diag_guess(cell, dtype, false, wx, p.par, h0f, out, B, T, d, s);
     }
-    for (int k = 0; k < K; ++k) {
+    bool fused_done = false;
+    if (K >= 1 && options().newton_fused && diag_pipe(dtype, B, T, d)) {
+        // all iterations in one sweep (no work trajectory); shapes it cannot take fall through
+        DiagFwdArgs a{};
+        a.wx = wx;
+        a.par = p.par;
+        a.halo = h0f;
+        a.hout = out;
+        a.resid_bits = &st->hist_bits[0];
+        a.final_bits = want_residual ? &st->final_bits : nullptr;
+        a.B = B;
+        a.T = T;
+        a.d = d;
+        a.omega = omega;
+        a.chain = next_chain(p.chain, T, diag_tile_steps(), &st->status);
+        const cudaError_t e = launch_diag_newton_fused(cell, dtype, a, K, s);
+        if (e == cudaSuccess)
+            fused_done = true;
+        else if (e != cudaErrorNotSupported)
+            return PRB_ERR_LAUNCH;
+    }
+    for (int k = 0; k < K && !fused_done; ++k) {
         DiagFwdArgs a{};
         a.wx = wx;
         a.par = p.par;

@@ -1,4 +1,4 @@
-// Scalar-diagonal cells (ParaGRU mix='diag', ParaNLRU): warp-pipelined persistent kernels.
+// Scalar-diagonal cells (ParaGRU mix='diag', ParaNLRU, ParaTitans, ParaCfC): warp-pipelined persistent kernels.
 //
 // One CTA owns one chain (batch row x 32 channels, lane = channel) for the whole time axis and
 // walks it in rounds of W*L steps.  A producer warp streams the inputs of the coming rounds into
@@ -233,6 +233,168 @@ diag_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_
     }
 }
 
+// ------------------------------------------------------------------ forward, all iterations in one sweep
+// The K Newton iterations of a solve (and the residual of the result) in ONE walk over the time
+// axis.  Iteration k+1 at step t needs iterate k at steps t-1 and t only; inside a round every warp
+// holds the iterates of its own L steps in registers, and the state just before its sub-tile moves
+// with the same delta carry the fold gives it (H_{t0-1} += omega * delta_{t0-1}).  So the passes
+// follow each other round by round: K times (evaluate, compose, one named barrier, fold, update in
+// registers), then the result is written once.  Reads wx once, writes H once; no work trajectory.
+// Same arithmetic, in the same order, as K launches of diag_newton_pipe_kernel.
+constexpr int kDiagFusedMaxK = 4;
+
+template <int CELL, typename TIO, int L, int W, int NSTAGE>
+__global__ void __launch_bounds__((W + 1) * 32, W * L > 64 ? 1 : 2)
+diag_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, DiagFwdArgs a, int K) {
+    using C = DiagCell<CELL>;
+    constexpr int G = C::G;
+    using S = DiagPipeFwdSmem<G, TIO, L, W, NSTAGE>;
+    constexpr int LT = S::LT;
+    extern __shared__ __align__(128) unsigned char smem[];
+    float* s_map = reinterpret_cast<float*>(smem + S::MAP_OFF);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::BAR_OFF);
+    uint64_t* empty = full + NSTAGE;
+    unsigned* s_red = reinterpret_cast<unsigned*>(smem + S::RED_OFF);
+
+    const int d = a.d;
+    const int ncb = (d + kLanes - 1) / kLanes;
+    const int chain = blockIdx.x;
+    const int b = chain / ncb, cb = chain % ncb;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ch = cb * kLanes + lane;
+    const bool ch_ok = ch < d;
+    const int chl = ch_ok ? ch : d - 1;
+    const int n_rounds = (a.T + LT - 1) / LT;
+    const int row0 = b * a.T;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tm_wx);
+        for (int s = 0; s < NSTAGE; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], W);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    unsigned rmax[kDiagFusedMaxK] = {0u, 0u, 0u, 0u};
+    unsigned fmax = 0u;
+    bool timed_out = false;
+
+    if (warp == W) {
+        if (lane == 0) {
+            for (int r = 0; r < n_rounds; ++r) {
+                const int s = r % NSTAGE;
+                if (r >= NSTAGE && !mbar_wait_bounded(&empty[s], ((r / NSTAGE) - 1) & 1, timed_out ? kWaitLimitAfterTimeout : kDiagPipeWaitLimit))
+                    timed_out = true;
+                mbar_expect_tx(&full[s], S::WX_TX);
+                tma_load_3d(smem + s * S::STAGE, &tm_wx, &full[s], cb * kLanes, 0, row0 + r * LT - 1);
+            }
+            if (timed_out) drain_ring(full, NSTAGE, n_rounds, kDrainLimit);
+        }
+    } else {
+        float par[C::NP];
+#pragma unroll
+        for (int p = 0; p < C::NP; ++p) par[p] = __ldg(a.par + (size_t)p * d + chl);
+        const float h_init = a.halo ? __ldg(a.halo + (size_t)b * d + chl) : 0.f;
+        const bool want_final = a.final_bits != nullptr;
+        float carry[kDiagFusedMaxK] = {0.f, 0.f, 0.f, 0.f};
+        int parity = 0;  // the two map buffers alternate from barrier to barrier
+
+        for (int r = 0; r < n_rounds; ++r) {
+            const int s = r % NSTAGE;
+            if (!mbar_wait_bounded(&full[s], (r / NSTAGE) & 1, timed_out ? kWaitLimitAfterTimeout : kDiagPipeWaitLimit)) timed_out = true;
+            const TIO* t_wx = reinterpret_cast<const TIO*>(smem + s * S::STAGE);
+            const int t0 = r * LT + warp * L;
+
+            auto round_body = [&](auto full_c) {
+                constexpr bool FULL = decltype(full_c)::value;
+                // row k of the box is time step r*LT - 1 + k
+                float g[L][G], hold[L + 1];
+    #pragma unroll
+                for (int i = 0; i < L; ++i)
+    #pragma unroll
+                    for (int q = 0; q < G; ++q) g[i][q] = (float)t_wx[((warp * L + i + 1) * G + q) * kLanes + lane];
+                // App. A guess: H^0_t = f(0, x_t), h0 only at t = 0
+                if (t0 == 0) {
+                    hold[0] = h_init;
+                } else {
+                    float gp[G];
+    #pragma unroll
+                    for (int q = 0; q < G; ++q) gp[q] = (float)t_wx[((warp * L) * G + q) * kLanes + lane];
+                    hold[0] = C::step(t0 - 1 == 0 ? h_init : 0.f, gp, par);
+                }
+                __syncwarp();
+                if (lane == 0) dp_mbar_arrive(&empty[s]);
+    #pragma unroll
+                for (int i = 0; i < L; ++i) hold[i + 1] = C::step(t0 + i == 0 ? h_init : 0.f, g[i], par);
+
+    #pragma unroll
+                for (int k = 0; k < kDiagFusedMaxK; ++k) {
+                    if (k < K) {
+                        // hold[0..L] is iterate k of steps t0-1 .. t0+L-1 (the guess for k = 0)
+                        float P[L], D[L];
+                        float pp = 1.f, dd = 0.f;
+    #pragma unroll
+                        for (int i = 0; i < L; ++i) {
+                            float f, j;
+                            typename C::Acts acts;
+                            C::eval(hold[i], g[i], par, f, j, acts);
+                            float F = f - hold[i + 1];
+                            const bool ok = FULL || t0 + i < a.T;
+                            if (!ok) {
+                                j = 1.f;
+                                F = 0.f;
+                            }
+                            if (ok && ch_ok) rmax[k] = max(rmax[k], absbits(F));
+                            dd = fmaf(j, dd, F);
+                            pp = j * pp;
+                            P[i] = pp;
+                            D[i] = dd;
+                        }
+                        float* maps = s_map + parity * (W * 2 * kLanes);
+                        parity ^= 1;
+                        maps[(warp * 2) * kLanes + lane] = P[L - 1];
+                        maps[(warp * 2 + 1) * kLanes + lane] = D[L - 1];
+                        dp_named_sync(1, W * 32);
+                        const float c = fold_round<W>(maps, warp, lane, carry[k]);
+                        hold[0] = fmaf(a.omega, c, hold[0]);
+    #pragma unroll
+                        for (int i = 0; i < L; ++i) hold[i + 1] = fmaf(a.omega, fmaf(P[i], c, D[i]), hold[i + 1]);
+                    }
+                }
+
+                if (ch_ok) {
+                    const size_t o_base = ((size_t)b * a.T + t0) * d + ch;
+    #pragma unroll
+                    for (int i = 0; i < L; ++i) {
+                        if (FULL || t0 + i < a.T) {
+                            if (want_final) fmax = max(fmax, absbits(C::step(hold[i], g[i], par) - hold[i + 1]));
+                            st_f(reinterpret_cast<TIO*>(a.hout) + o_base + (size_t)i * d, hold[i + 1]);
+                        }
+                    }
+                }
+            };
+            if (t0 + L <= a.T)
+                round_body(std::true_type{});
+            else
+                round_body(std::false_type{});
+        }
+    }
+    if (timed_out) atomicExch(a.chain.status, (int)kErrChainTimeout);
+#pragma unroll
+    for (int k = 0; k < kDiagFusedMaxK; ++k) {
+        if (k < K) {
+            __syncthreads();
+            block_residual_max(rmax[k], a.resid_bits + k, s_red);
+        }
+    }
+    if (a.final_bits != nullptr) {
+        __syncthreads();
+        block_residual_max(fmax, a.final_bits, s_red);
+    }
+}
+
 // ------------------------------------------------------------------ backward
 template <int G, typename TIO, int L, int W, int NSTAGE>
 struct DiagPipeBwdSmem {
@@ -460,6 +622,20 @@ cudaError_t launch_fwd_w(const DiagFwdArgs& a, bool first, bool last, cudaStream
     return cudaGetLastError();
 }
 
+template <int CELL, typename TIO, int NSTAGE, int L, int W>
+cudaError_t launch_fused_w(const DiagFwdArgs& a, int K, cudaStream_t s) {
+    constexpr int G = DiagCell<CELL>::G;
+    using S = DiagPipeFwdSmem<G, TIO, L, W, NSTAGE>;
+    CUtensorMap tm_wx;
+    const uint64_t rows = (uint64_t)a.B * a.T;
+    if (!make_tile_map(&tm_wx, a.wx, sizeof(TIO), rows, G, a.d, S::LT + 1)) return cudaErrorNotSupported;
+    const int grid = a.B * ((a.d + kLanes - 1) / kLanes);
+    auto k = diag_newton_fused_kernel<CELL, TIO, L, W, NSTAGE>;
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    k<<<grid, (W + 1) * 32, S::TOTAL, s>>>(tm_wx, a, K);
+    return cudaGetLastError();
+}
+
 // With few chains (up to 1.5 per SM) every chain gets 16 compute warps per CTA; with many chains
 // two 8-warp CTAs share an SM.
 inline bool wide_cta(int B, int d) { return 2 * B * ((d + kLanes - 1) / kLanes) <= 3 * sm_count(); }
@@ -472,6 +648,17 @@ cudaError_t launch_fwd_t(const DiagFwdArgs& a, bool first, bool last, cudaStream
     } else {
         if (!wide_cta(a.B, a.d)) return launch_fwd_w<CELL, TIO, NSTAGE, 8, 8>(a, first, last, s);
         return launch_fwd_w<CELL, TIO, NSTAGE, 8, 16>(a, first, last, s);
+    }
+}
+
+template <int CELL, typename TIO, int NSTAGE>
+cudaError_t launch_fused_t(const DiagFwdArgs& a, int K, cudaStream_t s) {
+    using Wide = DiagPipeFwdSmem<DiagCell<CELL>::G, TIO, 8, 16, NSTAGE>;
+    if constexpr (Wide::TOTAL > 227 * 1024) {
+        return launch_fused_w<CELL, TIO, NSTAGE, 8, 8>(a, K, s);
+    } else {
+        if (!wide_cta(a.B, a.d)) return launch_fused_w<CELL, TIO, NSTAGE, 8, 8>(a, K, s);
+        return launch_fused_w<CELL, TIO, NSTAGE, 8, 16>(a, K, s);
     }
 }
 
@@ -522,6 +709,23 @@ cudaError_t launch_diag_newton_pipe(int cell, int dtype, const DiagFwdArgs& a, b
                              : launch_fwd_t<kCellCfc, __nv_bfloat16, 3>(a, first, last, s);
     return dtype == kF32 ? launch_fwd_t<kCellNlru, float, 2>(a, first, last, s)
                          : launch_fwd_t<kCellNlru, __nv_bfloat16, 3>(a, first, last, s);
+}
+
+// all K iterations (1 <= K <= 4) from the App. A guess in one sweep; a.resid_bits points at the first
+// of K history slots, a.hout is the result in the I/O dtype, a.hin / a.carry_in are not used
+cudaError_t launch_diag_newton_fused(int cell, int dtype, const DiagFwdArgs& a, int K, cudaStream_t s) {
+    if (K < 1 || K > kDiagFusedMaxK || a.carry_in) return cudaErrorNotSupported;
+    if (cell == kCellGruDiag)
+        return dtype == kF32 ? launch_fused_t<kCellGruDiag, float, 2>(a, K, s)
+                             : launch_fused_t<kCellGruDiag, __nv_bfloat16, 3>(a, K, s);
+    if (cell == kCellTitans)
+        return dtype == kF32 ? launch_fused_t<kCellTitans, float, 2>(a, K, s)
+                             : launch_fused_t<kCellTitans, __nv_bfloat16, 3>(a, K, s);
+    if (cell == kCellCfc)
+        return dtype == kF32 ? launch_fused_t<kCellCfc, float, 2>(a, K, s)
+                             : launch_fused_t<kCellCfc, __nv_bfloat16, 3>(a, K, s);
+    return dtype == kF32 ? launch_fused_t<kCellNlru, float, 2>(a, K, s)
+                         : launch_fused_t<kCellNlru, __nv_bfloat16, 3>(a, K, s);
 }
 
 cudaError_t launch_diag_bwd_pipe(int cell, int dtype, const DiagBwdArgs& a, cudaStream_t s) {

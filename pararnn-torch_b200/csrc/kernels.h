@@ -73,6 +73,8 @@ cudaError_t launch_diag_newton_agg(int cell, int dtype, const DiagFwdArgs& a, cu
 // pipelined persistent family (diag_pipe.cu): one CTA per chain, TMA-fed
 cudaError_t launch_diag_newton_pipe(int cell, int dtype, const DiagFwdArgs& a, bool first, bool last,
                                     cudaStream_t s);
+// all K Newton iterations (1..4) from the App. A guess, and the residual of the result, in one sweep
+cudaError_t launch_diag_newton_fused(int cell, int dtype, const DiagFwdArgs& a, int K, cudaStream_t s);
 cudaError_t launch_diag_bwd_pipe(int cell, int dtype, const DiagBwdArgs& a, cudaStream_t s);
 cudaError_t launch_diag_guess(int cell, int dtype, bool out_f32, const void* wx, const float* par,
                               const float* h0, void* out, int B, int T, int d, cudaStream_t s);

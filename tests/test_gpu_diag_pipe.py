@@ -57,3 +57,26 @@ def test_pipe_bf16_matches_lookback_family(kind, prb_options):
     prb_options("kernel_family", "lookback")
     b, _, _ = _fwd(kind, wx, params, h0, 2, dtype=torch.bfloat16)
     assert rel_err(a, b) <= 1e-2
+
+
+@pytest.mark.parametrize("kind", ["gru_diag", "nlru", "titans", "cfc"])
+@pytest.mark.parametrize("B,T,d,h0", [(1, 1, 32, False), (2, 63, 64, True), (3, 1000, 96, True), (2, 4099, 40, False)])
+@pytest.mark.parametrize("K", [1, 2, 3, 4, 5])
+def test_fused_iterations_equal_separate_passes(kind, B, T, d, h0, K, prb_options):
+    """All K Newton iterations in one sweep against K launches: the same arithmetic in the same
+    order, so states, residual history and final residual agree to the last bit (K = 5 exceeds
+    the fused kernel's limit and takes the separate passes either way)."""
+    prb_options("kernel_family", "pipe")
+    wx, params, h0a = make_problem(kind, B, T, d, seed=K + T, h0=h0)
+    a = _fwd(kind, wx, params, h0a, K)
+    prb_options("newton_fused", 0)
+    b = _fwd(kind, wx, params, h0a, K)
+    assert np.array_equal(a[0], b[0])
+    assert list(a[1]) == list(b[1]) and a[2] == b[2]
+    wxq, pq = bf16_round(wx), bf16_round(params)
+    h0q = None if h0a is None else bf16_round(h0a)
+    prb_options("newton_fused", 1)
+    a = _fwd(kind, wxq, pq, h0q, K, dtype=torch.bfloat16)
+    prb_options("newton_fused", 0)
+    b = _fwd(kind, wxq, pq, h0q, K, dtype=torch.bfloat16)
+    assert np.array_equal(a[0], b[0]) and list(a[1]) == list(b[1]) and a[2] == b[2]
