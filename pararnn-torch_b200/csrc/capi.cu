@@ -788,6 +788,24 @@ int prb_newton_lstm_fused(const void* wx, const void* a_f, const void* a_z, cons
             return PRB_ERR_LAUNCH;
         return PRB_OK;
     }
+    if (options().newton_fused && diag_pipe(dtype, B, T, d)) {
+        // all iterations in one sweep (no work trajectory); shapes it cannot take fall through
+        LstmFwdArgs a{};
+        a.wx = wx;
+        a.par = p.par;
+        a.halo = h0f;
+        a.sout = out;
+        a.resid_bits = &st->hist_bits[0];
+        a.final_bits = want_residual ? &st->final_bits : nullptr;
+        a.B = B;
+        a.T = T;
+        a.d = d;
+        a.omega = omega;
+        a.chain = next_chain(p.chain, T, lstm_tile_steps(), &st->status);
+        const cudaError_t e = launch_lstm_newton_fused(dtype, a, K, s);
+        if (e == cudaSuccess) return PRB_OK;
+        if (e != cudaErrorNotSupported) return PRB_ERR_LAUNCH;
+    }
     for (int k = 0; k < K; ++k) {
         LstmFwdArgs a{};
         a.wx = wx;
@@ -841,9 +859,15 @@ int prb_bwd_lstm(const void* states, const void* wx, const void* a_f, const void
     a.T = T;
     a.d = d;
     a.chain = next_chain(p.chain, T, lstm_tile_steps(), &st->status);
-    if (launch_lstm_bwd(dtype, a, s) != cudaSuccess) return PRB_ERR_LAUNCH;
-    return launch_reduce_partials(p.partial, B * a.chain.n_tt, 5 * d, g_params, s) == cudaSuccess ? PRB_OK
-                                                                                                  : PRB_ERR_LAUNCH;
+    cudaError_t e = cudaErrorNotSupported;
+    int rows = B * a.chain.n_tt;
+    if (diag_pipe(dtype, B, T, d)) e = launch_lstm_bwd_pipe(dtype, a, s);
+    if (e == cudaSuccess)
+        rows = B;  // the pipelined kernel writes one partial row per batch row
+    else if (e == cudaErrorNotSupported)
+        e = launch_lstm_bwd(dtype, a, s);
+    if (e != cudaSuccess) return PRB_ERR_LAUNCH;
+    return launch_reduce_partials(p.partial, rows, 5 * d, g_params, s) == cudaSuccess ? PRB_OK : PRB_ERR_LAUNCH;
 }
 
 int prb_newton_slstm_fused(const void* wx, const void* r, const void* h0, const void* states_guess,

@@ -220,6 +220,10 @@ cudaError_t launch_lstm_guess(int dtype, const void* wx, const float* par, const
 cudaError_t launch_lstm_residual(int dtype, const void* wx, const float* par, const float* h0, const void* st,
                                  int B, int T, int d, unsigned* dst, cudaStream_t s);
 cudaError_t launch_lstm_bwd(int dtype, const LstmBwdArgs& a, cudaStream_t s);
+// pipelined persistent family (lstm_pipe.cu): all K <= 4 iterations from the guess in one sweep, and the
+// reverse sweep with one parameter-partial row per batch row
+cudaError_t launch_lstm_newton_fused(int dtype, const LstmFwdArgs& a, int K, cudaStream_t s);
+cudaError_t launch_lstm_bwd_pipe(int dtype, const LstmBwdArgs& a, cudaStream_t s);
 
 // ---- T = 1 decode (decode.cu) ------------------------------------------------------------------
 cudaError_t launch_decode_step(int cell, int dtype, const void* state, const void* wx, const void* par,
