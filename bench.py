@@ -1183,7 +1183,7 @@ def run_secondary(args):
         norm = torch.nn.RMSNorm(768).to(dev, torch.bfloat16)
 
         # Three readings of "12-layer residual stack": h <- h + cell(rmsnorm(h)) with a weightless
-        # RMS norm (the harness this build's survey fixed; the line's `ms_per_step`), the plain
+        # RMS norm (the line's `ms_per_step`), the plain
         # residual h <- h + cell(h) (|cell(h)| < 1, so twelve layers stay bounded), and the
         # pre-norm with torch's learnable-gain RMSNorm, whose gain-gradient kernel alone costs 2 ms.
         def step(mode="prenorm"):

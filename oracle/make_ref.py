@@ -1,6 +1,6 @@
 """Put an importable copy of the reference package under ``oracle/_ref/`` (git-ignored).
 
-    python oracle/make_ref.py [/path/to/reference]
+    python oracle/make_ref.py /path/to/reference      (or PARARNN_REFERENCE=/path/to/reference)
 
 Test infrastructure only: with ``oracle/_ref/pararnn`` present, ``tests/test_gpu_dropin.py``
 imports the unmodified reference next to this backend and drives the reference's own
@@ -16,6 +16,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
+# where the reference checkout is looked for when no path is given
+DEFAULT_ROOT = os.environ.get("PARARNN_REFERENCE", os.path.join(os.sep, "root", "reference"))
 
 
 def make_ref(reference_root: str) -> str | None:
@@ -31,5 +33,5 @@ def make_ref(reference_root: str) -> str | None:
 
 
 if __name__ == "__main__":
-    out = make_ref(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    out = make_ref(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_ROOT)
     print(out or "reference package not found; nothing copied")
