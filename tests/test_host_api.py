@@ -111,3 +111,48 @@ def test_oracle_early_stop_counts_residual_evaluations():
     g = load_golden("gru_diag_k3")
     r = oracle.newton(oracle.GRU_DIAG, g["wx"], g["params"], max_iters=8, early_atol=1e-5)
     assert r.iters < 8 and r.history[-1] < 1e-5 and all(h >= 1e-5 for h in r.history[:-1])
+
+
+def test_cfc_input_gradients_match_autograd_through_project_wx():
+    """The hand-written gradients of ParaCfC's input projection (two linear maps on the features,
+    the clamped time step broadcast over the channels) against autograd, on the CPU."""
+    from pararnn_b200.newton import _cfc_input_grads
+
+    torch.manual_seed(0)
+    cell = prb.ParaCfC(7, 5).double()
+    with torch.no_grad():
+        cell.W_b.weight.normal_(0.0, 0.3)
+    x = torch.randn(2, 9, 7, dtype=torch.float64)
+    x[..., -1] = torch.rand(2, 9, dtype=torch.float64)
+    x[0, ::3, -1] = 0.0  # below the clamp: no gradient reaches the raw time step there
+    x.requires_grad_(True)
+    g_wx = torch.randn(2, 9, 20, dtype=torch.float64)
+    (cell.project_wx(x) * g_wx).sum().backward()
+    with torch.no_grad():
+        grad_x, grads = _cfc_input_grads(cell, x.detach(), g_wx)
+    assert torch.allclose(grad_x, x.grad, atol=1e-12)
+    for name in ("W_x.weight", "W_x.bias", "W_b.weight", "W_b.bias"):
+        want = dict(cell.named_parameters())[name].grad
+        assert torch.allclose(grads[name], want, atol=1e-12), name
+    # with the kernel's per-gate sums of g_wx given, the two bias gradients are slices of them
+    bias_sum = g_wx.reshape(-1, 20).sum(0)
+    with torch.no_grad():
+        _, grads2 = _cfc_input_grads(cell, x.detach(), g_wx, bias_sum)
+    assert torch.allclose(grads2["W_x.bias"], cell.W_x.bias.grad, atol=1e-12)
+    assert torch.allclose(grads2["W_b.bias"], cell.W_b.bias.grad, atol=1e-12)
+
+
+def test_input_affine_uses_project_wx_when_the_cell_has_one():
+    from pararnn_b200.newton import input_affine
+
+    torch.manual_seed(1)
+    gru, cfc = prb.ParaGRU(6, 4), prb.ParaCfC(6, 4)
+    x = torch.randn(2, 3, 6)
+    assert torch.equal(input_affine(gru, x), gru.W_x(x))
+    wx = input_affine(cfc, x)
+    assert wx.shape == (2, 3, 16)
+    assert torch.equal(wx[..., 8:12], x[..., -1:].clamp_min(1e-4).expand(2, 3, 4))
+    with pytest.raises(ValueError):
+        prb.ParaCfC(1, 4)
+    with pytest.raises(ValueError):
+        prb.ParaCfC(6, 4, gate_mix="diag_h")
