@@ -20,7 +20,7 @@ separate passes it replaces would need is reported beside it under its own name.
 With N > 1 the timed step is one CUDA graph per rank (kernels, folds, NCCL all-gathers;
 the same programs issued from Python are `eager_ms_per_step`), and the line also carries
 `c4_strong` (B=1, T=131072, d=2048 sharded over the N ranks against the same shape on one
-GPU) and `c5_sharded` (12 x ParaNLRU stack).  `--workload c1|c3|c5` time the secondary
+GPU) and `c5_sharded` (12 x ParaNLRU stack).  `--workload c1|c3|c5|lstm` time the secondary
 configurations, `--workload ref_fused` the reference's own GPU paths next to this backend.
 The CPU arm (`--impl reference`, and `cpu_baseline` at N = 1) times the C restatement of
 the reference's eager algorithm (oracle/) on the host cores.
@@ -1150,6 +1150,30 @@ def run_secondary(args):
         lines.append({"workload": "c1 ParaGRU diag fp32 B=2 T=1024 d=64 K=3", "ms_per_step": sec * 1e3,
                       "tokens_per_s": 2 * 1024 / sec, "agreement_max_abs": rep.max_abs,
                       "newton_iters": rep.newton_iters})
+    elif args.workload == "lstm":
+        # not a BASELINE configuration: ParaLSTM at C2's shape (or --seq-len), op and layer boundary
+        from pararnn_b200 import ops
+
+        t_l = args.seq_len if args.seq_len != DEFAULT_T else 16384
+        torch.manual_seed(5)
+        cell = prb.ParaLSTM(1024, 1024).to(dev, torch.bfloat16)
+        x = (0.5 * torch.randn(8, t_l, 1024, device=dev)).bfloat16().requires_grad_(True)
+        cfg = prb.NewtonConfig(max_iters=2)
+        with torch.no_grad():
+            wx = cell.W_x(x).contiguous()
+            rec = [p_.detach() for p_ in cell.clipped_recurrent()]
+            G = torch.randn(8, t_l, 2, 1024, device=dev).bfloat16()
+            Hs = ops.newton_lstm_fused(wx, *rec, None, max_iters=2)
+        fwd = timed(lambda: ops.newton_lstm_fused(wx, *rec, None, max_iters=2))
+        bwd = timed(lambda: ops.lstm_reverse_vjp(Hs, wx, *rec, G))
+
+        def step():
+            prb.newton_apply(cell, x, cfg, output_slot=1).float().sum().backward()
+
+        sec = timed(step)
+        lines.append({"workload": f"ParaLSTM d=1024 bf16 B=8 T={t_l} K=2", "op_fwd_ms": fwd * 1e3,
+                      "op_bwd_ms": bwd * 1e3, "op_tokens_per_s": 8 * t_l / (fwd + bwd),
+                      "layer_ms_per_step": sec * 1e3})
     elif args.workload == "c3":
         for dtype in (torch.float32, torch.bfloat16):
             torch.manual_seed(2)
@@ -1249,7 +1273,7 @@ def main():
                     help="time steps per GPU (profiling captures use a smaller case)")
     ap.add_argument("--first-shard-weight", type=float, default=1.0,
                     help="N > 1: length of the first time shard relative to the others")
-    ap.add_argument("--workload", default="c2", choices=("c2", "c1", "c3", "c5", "ref_fused"),
+    ap.add_argument("--workload", default="c2", choices=("c2", "c1", "c3", "c5", "lstm", "ref_fused"),
                     help="c2 (default) is the headline line; the others print secondary lines")
     ap.add_argument("--c4-seq-len", type=int, default=0,
                     help="N > 1: sequence length of the c4_strong sub-record (default 131072)")

@@ -41,7 +41,8 @@ __device__ __forceinline__ float fold_round(const float* maps, int warp, int lan
 #pragma unroll
     for (int v = 0; v < W; ++v) {
         if (v == warp) mine = carry;
-        carry = fmaf(maps[(v * 2) * kLanes + lane], carry, maps[(v * 2 + 1) * kLanes + lane]);
+        const float2 m = reinterpret_cast<const float2*>(maps)[v * kLanes + lane];  // (P, D) of sub-tile v
+        carry = fmaf(m.x, carry, m.y);
     }
     return mine;
 }
@@ -190,8 +191,7 @@ diag_newton_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_
 
                 // ---- the sub-tile maps of the round meet in shared memory
                 float* maps = s_map + (r & 1) * (W * 2 * kLanes);
-                maps[(warp * 2) * kLanes + lane] = P[L - 1];
-                maps[(warp * 2 + 1) * kLanes + lane] = D[L - 1];
+                reinterpret_cast<float2*>(maps)[warp * kLanes + lane] = make_float2(P[L - 1], D[L - 1]);
                 dp_named_sync(1, W * 32);
                 const float c = fold_round<W>(maps, warp, lane, carry);
 
@@ -354,8 +354,7 @@ diag_newton_fused_kernel(const __grid_constant__ CUtensorMap tm_wx, DiagFwdArgs 
                         }
                         float* maps = s_map + parity * (W * 2 * kLanes);
                         parity ^= 1;
-                        maps[(warp * 2) * kLanes + lane] = P[L - 1];
-                        maps[(warp * 2 + 1) * kLanes + lane] = D[L - 1];
+                        reinterpret_cast<float2*>(maps)[warp * kLanes + lane] = make_float2(P[L - 1], D[L - 1]);
                         dp_named_sync(1, W * 32);
                         const float c = fold_round<W>(maps, warp, lane, carry[k]);
                         hold[0] = fmaf(a.omega, c, hold[0]);
@@ -529,8 +528,7 @@ diag_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
 
                 // ---- the sub-tile maps of the round meet in shared memory
                 float* maps = s_map + (r & 1) * (W * 2 * kLanes);
-                maps[(warp * 2) * kLanes + lane] = pp;
-                maps[(warp * 2 + 1) * kLanes + lane] = dd;
+                reinterpret_cast<float2*>(maps)[warp * kLanes + lane] = make_float2(pp, dd);
                 dp_named_sync(1, W * 32);
                 const float c = fold_round<W>(maps, warp, lane, carry);
 
